@@ -1,0 +1,70 @@
+// Shared device helpers: storage-type conversion, warp and block reductions.
+// Every kernel in this folder computes in float and rounds once on store.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+constexpr int kWarp = 32;
+
+// Storage types are selected at run time by an integer tag so that the C entry
+// points need no templates in their signatures.
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; `scratch` holds 32 floats.  The order
+// of additions depends only on blockDim, never on the data or on other blocks.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int nwarps = (blockDim.x + 31) >> 5;
+  float total = (lane < nwarps) ? scratch[lane] : 0.f;
+  total = warp_sum(total);
+  return total;
+}
+
+// Launch status for the C entry points: 0 on success, else the cudaError value.
+inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
+
+}  // namespace b200
+
+// Error codes of our own, above the CUDA range, for refused sizes.
+#define B200_ERR_BAD_SIZE 10001
+#define B200_ERR_BAD_DTYPE 10002
+#define B200_ERR_TOO_LARGE 10003
+
+#define B200_DISPATCH_DTYPE(tag, T, ...)                                  \
+  switch (tag) {                                                          \
+    case b200::kF32: { using T = float; __VA_ARGS__; break; }             \
+    case b200::kBF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }    \
+    default: return B200_ERR_BAD_DTYPE;                                   \
+  }

@@ -1,0 +1,77 @@
+"""The generic decoder: embedding, the layers in their given order, the final
+norm and the output head on the rows whose logits are wanted
+(mini_llm/model/base.py:55-89 for the traversal)."""
+
+from __future__ import annotations
+
+from typing import Any, Mapping
+
+import torch
+
+from ..cache.manager import CacheLayout, CacheManager, LayerCache
+from ..parts.base import ResidualStream, Runtime
+from ..weights.checkpoint import TensorSpec
+from ..weights.view import TensorView
+from .description import ModelDescription, build_parts
+
+
+class DecoderModel:
+    def __init__(self, description: ModelDescription) -> None:
+        self.description = description
+        parts = build_parts(description)
+        self.embedding_prefix, self.embedding = parts["embedding"]
+        self.blocks = parts["blocks"]  # [(prefix, block)]
+        self.final_norm_prefix, self.final_norm = parts["final_norm"]
+        self.head_prefix, self.head = parts["head"]
+        self.order = description.order
+        self.runtime: Runtime | None = None
+        self._layer_caches: list[LayerCache] | None = None
+
+    # ------------------------------------------------------------ weights
+    def tensor_schema(self) -> dict[str, TensorSpec]:
+        schema: dict[str, TensorSpec] = {}
+        named = [(self.embedding_prefix, self.embedding), *self.blocks,
+                 (self.final_norm_prefix, self.final_norm), (self.head_prefix, self.head)]
+        for prefix, part in named:
+            for name, spec in part.tensor_specs().items():
+                schema[f"{prefix}.{name}"] = spec
+        return schema
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        """Place every weight.  ``tensors`` is keyed by checkpoint name and has
+        been validated against ``tensor_schema()`` already."""
+
+        self.runtime = runtime
+        view = TensorView.of(tensors)
+        self.embedding.load(view.sub(self.embedding_prefix), runtime)
+        for prefix, block in self.blocks:
+            block.load(view.sub(prefix), runtime)
+        self.final_norm.load(view.sub(self.final_norm_prefix), runtime)
+        self.head.load(view.sub(self.head_prefix), runtime, embedding=self.embedding)
+
+    # -------------------------------------------------------------- cache
+    def cache_layout(self) -> CacheLayout:
+        needs = []
+        for layer, (_, block) in zip(self.description.layers, self.blocks):
+            needs.append(None if layer.cache_source is not None else block.mixer.cache_requirement())
+        return CacheLayout.from_requirements(needs)
+
+    def bind_cache(self, manager: CacheManager) -> None:
+        caches = []
+        for index, layer in enumerate(self.description.layers):
+            owner = index if layer.cache_source is None else layer.cache_source
+            caches.append(manager.layer_cache(owner))
+        self._layer_caches = caches
+
+    # ------------------------------------------------------------ forward
+    def forward(self, ctx: Any) -> torch.Tensor | None:
+        """Run the batch in ``ctx``; return float32 logits ``[wanted, vocab]``
+        (``None`` when no row is wanted: the cache is written all the same)."""
+
+        stream = ResidualStream(self.embedding.forward(ctx.token_ids))
+        for index in self.order:
+            self.blocks[index][1].forward(stream, ctx, self._layer_caches[index])
+        if ctx.num_logit_rows == 0:
+            return None
+        x = self.final_norm.norm_rows(stream.resid, stream.delta, ctx.logit_rows)
+        return self.head.forward(x)

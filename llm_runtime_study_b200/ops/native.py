@@ -1,0 +1,133 @@
+"""Loader of the native kernel libraries and thin typed wrappers over them.
+
+Every wrapper checks shapes, dtypes, contiguity and device on the host, then
+calls the C entry point with raw device pointers and the current CUDA stream.
+There is no other implementation behind these functions: if the library cannot
+be built or loaded, or a tensor is not on a CUDA device, a ``KernelError`` is
+raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Sequence
+
+import torch
+
+from ..csrc.build import load_library
+from ..errors import KernelError
+
+c_int, c_float, c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+DTYPE_TAG = {torch.float32: 0, torch.bfloat16: 1}
+
+_OWN_ERRORS = {
+    10001: "a size argument is not supported by this kernel",
+    10002: "unsupported storage type",
+    10003: "a size exceeds what this kernel can hold on chip",
+    10004: "scratch buffer too small",
+}
+
+# library name -> (sources, {function: argument types})
+_LIBRARIES = {
+    "b200_elementwise": (
+        ("elementwise.cu",),
+        {
+            "b200_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
+            "b200_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
+            "b200_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+            "b200_qk_norm_rope_write": [
+                c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p,
+                c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+            ],
+        },
+    ),
+    "b200_gemm_f32": (
+        ("gemm_f32.cu",),
+        {"b200_gemm_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]},
+    ),
+    "b200_attention_simt": (
+        ("attention_simt.cu",),
+        {
+            "b200_paged_attention_simt": [
+                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+            ],
+        },
+    ),
+}
+
+_functions: dict[str, ctypes._CFuncPtr] = {}
+
+
+def library_specs() -> dict:
+    """Sources of every library, for the build-everything entry point."""
+
+    return {name: sources for name, (sources, _) in _LIBRARIES.items()}
+
+
+def _function(name: str):
+    fn = _functions.get(name)
+    if fn is None:
+        for lib_name, (sources, table) in _LIBRARIES.items():
+            if name in table:
+                lib = load_library(lib_name, sources)
+                for fname, argtypes in table.items():
+                    f = getattr(lib, fname)
+                    f.argtypes = argtypes
+                    f.restype = c_int
+                    _functions[fname] = f
+                break
+        else:
+            raise KernelError(f"no native library provides {name}")
+        fn = _functions[name]
+    return fn
+
+
+def register_library(lib_name: str, sources: Sequence[str], table: dict) -> None:
+    """Add a library (used by kernels that are built per head size)."""
+
+    _LIBRARIES[lib_name] = (tuple(sources), dict(table))
+
+
+def check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status in _OWN_ERRORS:
+        raise KernelError(f"{what}: {_OWN_ERRORS[status]}")
+    raise KernelError(f"{what}: CUDA error {status} ({torch.cuda.cudart().cudaGetErrorString(status) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else 'see cudaError_t'})")
+
+
+def call(name: str, *args) -> None:
+    check(_function(name)(*args), name)
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def require(t: torch.Tensor, name: str, *, dtype=None, shape=None, dims=None) -> torch.Tensor:
+    if not isinstance(t, torch.Tensor) or t.device.type != "cuda":
+        raise KernelError(f"{name} must be a CUDA tensor: the kernels have no other path")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None:
+        allowed = dtype if isinstance(dtype, (tuple, list)) else (dtype,)
+        if t.dtype not in allowed:
+            raise KernelError(f"{name} has dtype {t.dtype}, expected {allowed}")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name} has {t.dim()} dimensions, expected {dims}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise KernelError(f"{name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
+    return t
+
+
+def tag(dtype: torch.dtype) -> int:
+    try:
+        return DTYPE_TAG[dtype]
+    except KeyError:
+        raise KernelError(f"unsupported storage type {dtype}; expected float32 or bfloat16") from None

@@ -1,0 +1,48 @@
+"""Dense projections ``y = x W^T (+ b)`` with ``W`` stored ``[out, in]``."""
+
+from __future__ import annotations
+
+import torch
+
+from ..errors import KernelError
+from ..ops import functional as F
+from .base import Runtime
+
+
+class Projection:
+    """One weight matrix (possibly several checkpoint tensors stacked along the
+    output axis, so that q/k/v or gate/up are one product) and an optional bias.
+
+    float32 runtime: our FFMA kernel.  bfloat16 runtime: a library matrix product
+    with float32 accumulation (the reference's projections are ``nn.Linear``,
+    i.e. library products too: mini_llm/nn/attention.py:102-111), writing either
+    bfloat16 or float32.
+    """
+
+    def __init__(self, weights: list[torch.Tensor], biases: list[torch.Tensor] | None, runtime: Runtime) -> None:
+        self.runtime = runtime
+        stacked = weights[0] if len(weights) == 1 else torch.cat(list(weights), dim=0)
+        self.weight = runtime.place_matrix(stacked)
+        self.out_features, self.in_features = self.weight.shape
+        self.bias = None
+        if biases:
+            b = biases[0] if len(biases) == 1 else torch.cat(list(biases), dim=0)
+            self.bias = b.to(device=runtime.device, dtype=torch.float32).contiguous()
+
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        out_dtype = out_dtype or self.runtime.dtype
+        if x.shape[-1] != self.in_features:
+            raise KernelError(f"projection expects width {self.in_features}, got {x.shape[-1]}")
+        if self.runtime.dtype == torch.float32:
+            if out_dtype != torch.float32:
+                raise KernelError("the float32 path keeps every activation in float32")
+            return F.linear_f32(x, self.weight, self.bias)
+        if x.dtype != torch.bfloat16:
+            raise KernelError(f"bfloat16 projection got {x.dtype} input")
+        if out_dtype == torch.bfloat16:
+            y = torch.mm(x, self.weight.t())
+        else:
+            y = torch.mm(x, self.weight.t(), out_dtype=torch.float32)
+        if self.bias is not None:
+            y += self.bias.to(y.dtype)
+        return y

@@ -1,0 +1,250 @@
+"""Each CUDA kernel alone against a plain float64 computation of the same
+operation, at sizes other than the engine's tiny models."""
+
+import math
+
+import pytest
+import torch
+
+from tests.plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def F():
+    from llm_runtime_study_b200.ops import functional
+
+    return functional
+
+
+def tol(dtype):
+    return dict(atol=2e-6, rtol=2e-6) if dtype == torch.float32 else dict(atol=1e-2, rtol=1e-2)
+
+
+def dev(t, dtype=None):
+    return t.to(device="cuda", dtype=dtype or t.dtype).contiguous()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,vocab", [(70, 33), (4104, 5)])
+def test_embedding(dtype, hidden, vocab):
+    torch.manual_seed(0)
+    table = torch.randn(vocab, hidden).to(dtype)
+    ids = torch.randint(0, vocab, (13,), dtype=torch.int32)
+    out = F().embedding(dev(ids), dev(table), 1.0)
+    assert out.dtype == torch.float32
+    torch.testing.assert_close(out.cpu(), table[ids.long()].float(), atol=0, rtol=0)
+    out = F().embedding(dev(ids), dev(table), 12.0)
+    torch.testing.assert_close(out.cpu(), table[ids.long()].float() * 12.0, atol=0, rtol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [1, 100, 4104, 13000])
+def test_add_rmsnorm(dtype, hidden):
+    torch.manual_seed(1)
+    n, eps = 7, 3e-5
+    resid, delta = torch.randn(n, hidden) * 3, torch.randn(n, hidden)
+    weight = 1 + 0.1 * torch.randn(hidden)
+    r = dev(resid)
+    out = F().add_rmsnorm(r, dev(delta), dev(weight), eps, dtype)
+    total = (resid + delta)
+    torch.testing.assert_close(r.cpu(), total, atol=0, rtol=0)          # residual updated in place
+    want = plain.rms_norm(total.double(), weight.double(), eps)
+    torch.testing.assert_close(out.cpu().double(), want, **tol(dtype))
+    # without delta the residual is left alone; with rows it gathers
+    r2 = dev(resid)
+    out2 = F().add_rmsnorm(r2, None, dev(weight), eps, dtype)
+    torch.testing.assert_close(r2.cpu(), resid, atol=0, rtol=0)
+    torch.testing.assert_close(out2.cpu().double(), plain.rms_norm(resid.double(), weight.double(), eps), **tol(dtype))
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32)
+    out3 = F().add_rmsnorm(r2, dev(delta), dev(weight), eps, dtype, rows=dev(rows))
+    torch.testing.assert_close(r2.cpu(), resid, atol=0, rtol=0)
+    torch.testing.assert_close(out3.cpu().double(), want[rows.long()], **tol(dtype))
+
+
+def test_rmsnorm_eps_matters():
+    x = torch.full((1, 64), 1e-3)
+    w = torch.ones(64)
+    a = F().add_rmsnorm(dev(x), None, dev(w), 1e-6, torch.float32).cpu()
+    b = F().add_rmsnorm(dev(x), None, dev(w), 1e-5, torch.float32).cpu()
+    torch.testing.assert_close(a.double(), plain.rms_norm(x.double(), w.double(), 1e-6), atol=1e-6, rtol=1e-6)
+    assert float((a - b).abs().max()) > 1e-2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter", [11, 272, 1000])
+def test_silu_mul(dtype, inter):
+    torch.manual_seed(2)
+    gu = (torch.randn(5, 2 * inter) * 3).to(dtype)
+    out = F().silu_mul(dev(gu))
+    g, u = gu[:, :inter].double(), gu[:, inter:].double()
+    torch.testing.assert_close(out.cpu().double(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 101, 53), (37, 64, 16), (65, 130, 257), (3, 503, 96)])
+def test_gemm_f32_is_exact_and_batch_invariant(m, n, k):
+    torch.manual_seed(3)
+    x, w, b = torch.randn(m, k), torch.randn(n, k), torch.randn(n)
+    out = F().linear_f32(dev(x), dev(w), dev(b)).cpu()
+    want = x.double() @ w.double().T + b.double()
+    torch.testing.assert_close(out.double(), want, atol=1e-5 * math.sqrt(k), rtol=1e-6)
+    # true 32-bit: the error is far below what a 10-bit mantissa (TF32) would leave
+    assert float((out.double() - want).abs().max()) < 2e-6 * k
+    alone = F().linear_f32(dev(x[m // 2 : m // 2 + 1]), dev(w), dev(b)).cpu()
+    assert torch.equal(alone[0], out[m // 2])
+
+
+def _scatter_to_pages(k, v, page_size, nkv, d, dtype, seed=0, extra_pages=3):
+    """Put contiguous k, v [T, nkv, d] into shuffled pages; return pools + table row."""
+
+    T = k.shape[0]
+    pages = -(-T // page_size)
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randperm(pages + extra_pages, generator=g)[:pages]
+    k_pool = torch.full((pages + extra_pages, nkv, page_size, d), 1e4, dtype=dtype)  # poison
+    v_pool = torch.full_like(k_pool, -1e4)
+    for t in range(T):
+        k_pool[ids[t // page_size], :, t % page_size] = k[t].to(dtype)
+        v_pool[ids[t // page_size], :, t % page_size] = v[t].to(dtype)
+    return k_pool, v_pool, ids.to(torch.int32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page,rot", [(4, 2, 16, 4, 16), (6, 1, 32, 8, 32), (5, 5, 48, 16, 48), (8, 2, 128, 16, 64)])
+def test_qk_norm_rope_write(dtype, nq, nkv, d, page, rot):
+    torch.manual_seed(4)
+    eps, theta = 1e-5, 1e6
+    # two requests: a portion at positions 37..45 and a single token far out
+    positions = torch.tensor(list(range(37, 46)) + [3001], dtype=torch.int32)
+    entry = torch.tensor([0] * 9 + [1], dtype=torch.int32)
+    n = positions.shape[0]
+    qkv = torch.randn(n, (nq + 2 * nkv) * d).to(dtype)
+    qw, kw = 1 + 0.1 * torch.randn(d), 1 + 0.1 * torch.randn(d)
+    pages_per_req = -(-3002 // page)
+    table = torch.stack([torch.randperm(2 * pages_per_req)[:pages_per_req],
+                         torch.randperm(2 * pages_per_req)[:pages_per_req] + 2 * pages_per_req]).to(torch.int32)
+    pool_shape = (4 * pages_per_req, nkv, page, d)
+    k_pool, v_pool = torch.zeros(pool_shape, dtype=dtype), torch.zeros(pool_shape, dtype=dtype)
+    inv_freq = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    kp, vp = dev(k_pool), dev(v_pool)
+    q_out = F().qk_norm_rope_write(
+        dev(qkv), num_q_heads=nq, num_kv_heads=nkv, head_dim=d, q_weight=dev(qw), k_weight=dev(kw), eps=eps,
+        inv_freq=dev(inv_freq), rotary_dim=rot, positions=dev(positions), token_entry=dev(entry),
+        block_table=dev(table), page_size=page, k_pool=kp, v_pool=vp)
+    x = qkv.double()
+    q = x[:, : nq * d].view(n, nq, d)
+    k = x[:, nq * d : (nq + nkv) * d].view(n, nkv, d)
+    v = x[:, (nq + nkv) * d :].view(n, nkv, d)
+    q, k = plain.rms_norm(q, qw.double(), eps), plain.rms_norm(k, kw.double(), eps)
+    cos, sin = plain.rotary_tables(positions, rot, theta, torch.float64)
+    q = torch.cat((plain.rotate(q[..., :rot], cos, sin), q[..., rot:]), dim=-1)
+    k = torch.cat((plain.rotate(k[..., :rot], cos, sin), k[..., rot:]), dim=-1)
+    torch.testing.assert_close(q_out.cpu().double(), q, **tol(dtype))
+    kp, vp = kp.cpu().double(), vp.cpu().double()
+    written = torch.zeros(pool_shape[0], page, dtype=torch.bool)
+    for i in range(n):
+        pg, slot = int(table[entry[i], positions[i] // page]), int(positions[i]) % page
+        torch.testing.assert_close(kp[pg, :, slot], k[i], **tol(dtype))
+        torch.testing.assert_close(vp[pg, :, slot], v[i], atol=0, rtol=0)   # values are copied as they are
+        written[pg, slot] = True
+    assert float(kp.permute(0, 2, 1, 3)[~written].abs().max()) == 0.0        # nothing else was touched
+    assert float(vp.permute(0, 2, 1, 3)[~written].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_qk_write_without_norm_or_rotation(dtype):
+    torch.manual_seed(5)
+    nq, nkv, d, page = 2, 1, 16, 4
+    qkv = torch.randn(3, (nq + 2 * nkv) * d).to(dtype)
+    positions, entry = torch.tensor([0, 1, 2], dtype=torch.int32), torch.zeros(3, dtype=torch.int32)
+    table = torch.tensor([[1, 0]], dtype=torch.int32)
+    kp, vp = dev(torch.zeros(2, nkv, page, d, dtype=dtype)), dev(torch.zeros(2, nkv, page, d, dtype=dtype))
+    q = F().qk_norm_rope_write(
+        dev(qkv), num_q_heads=nq, num_kv_heads=nkv, head_dim=d, q_weight=None, k_weight=None, eps=1.0,
+        inv_freq=None, rotary_dim=0, positions=dev(positions), token_entry=dev(entry), block_table=dev(table),
+        page_size=page, k_pool=kp, v_pool=vp)
+    assert torch.equal(q.cpu().view(3, -1), qkv[:, : nq * d])
+    assert torch.equal(kp.cpu()[1, 0, :3].reshape(3, -1), qkv[:, nq * d : (nq + nkv) * d])
+
+
+def _attention_case(dtype, nq, nkv, d, page, lens_and_chunks, window=0, seed=6, boost=None):
+    """Requests with cached length L and the last n tokens as queries."""
+
+    torch.manual_seed(seed)
+    qs, pos, ent, wants, tables, pools_k, pools_v = [], [], [], [], [], [], []
+    base = 0
+    for e, (L, n) in enumerate(lens_and_chunks):
+        q, k, v = torch.randn(L, nq, d), torch.randn(L, nkv, d), torch.randn(L, nkv, d)
+        if boost is not None:   # one far key dominates the last query's scores
+            t = boost if boost >= 0 else L + boost
+            k[t] = 0
+            k[t, :, 0] = 6.0
+            q[L - 1] = 0
+            q[L - 1, :, 0] = 6.0
+            v[t] = 5.0
+        q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+        out = plain.causal_attention(q.double(), k.double(), v.double(), 1 / math.sqrt(d), window=window or None)
+        kp, vp, ids = _scatter_to_pages(k, v, page, nkv, d, dtype, seed=seed + e)
+        pools_k.append(kp), pools_v.append(vp), tables.append(ids + base)
+        base += kp.shape[0]
+        qs.append(q[L - n :]), wants.append(out[L - n :])
+        pos += list(range(L - n, L)), ent.__iadd__([e] * n)
+    width = max(t.shape[0] for t in tables)
+    table = torch.full((len(tables), width), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        table[i, : t.shape[0]] = t
+    return (torch.cat(qs), torch.cat(pools_k), torch.cat(pools_v), torch.tensor(pos, dtype=torch.int32),
+            torch.tensor(ent, dtype=torch.int32), table, torch.cat(wants))
+
+
+ATTENTION_SHAPES = [(4, 2, 16, 4), (6, 1, 32, 8), (5, 5, 48, 16), (8, 2, 128, 16), (2, 2, 256, 32)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page", ATTENTION_SHAPES)
+def test_paged_attention_simt(dtype, nq, nkv, d, page):
+    q, kp, vp, pos, ent, table, want = _attention_case(
+        dtype, nq, nkv, d, page, [(1, 1), (33, 33), (70, 5), (131, 1), (64, 2)])
+    out = F().paged_attention_simt(dev(q), dev(kp), dev(vp), positions=dev(pos), token_entry=dev(ent),
+                                   block_table=dev(table), scale=1 / math.sqrt(d))
+    torch.testing.assert_close(out.cpu().double(), want, **tol(dtype) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 7, 32, 33])
+def test_paged_attention_simt_window(dtype, window):
+    nq, nkv, d, page = 4, 2, 32, 8
+    q, kp, vp, pos, ent, table, want = _attention_case(dtype, nq, nkv, d, page, [(100, 40), (9, 9)], window=window)
+    out = F().paged_attention_simt(dev(q), dev(kp), dev(vp), positions=dev(pos), token_entry=dev(ent),
+                                   block_table=dev(table), scale=1 / math.sqrt(d), window=window)
+    torch.testing.assert_close(out.cpu().double(), want, **tol(dtype) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("boost", [0, 15, 16, -2, 300])
+def test_attention_finds_a_far_key(dtype, boost):
+    """One key among hundreds carries nearly all the weight: a kernel that drops
+    or misplaces it (a page's edge, the first key, the last but one) shows."""
+
+    nq, nkv, d, page = 4, 1, 64, 16
+    q, kp, vp, pos, ent, table, want = _attention_case(dtype, nq, nkv, d, page, [(700, 3)], boost=boost)
+    out = F().paged_attention_simt(dev(q), dev(kp), dev(vp), positions=dev(pos), token_entry=dev(ent),
+                                   block_table=dev(table), scale=1 / math.sqrt(d))
+    assert float(want[-1].abs().mean()) > 3.0      # the boosted value dominates
+    torch.testing.assert_close(out.cpu().double(), want, **tol(dtype) if dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2))
+
+
+def test_kernels_refuse_what_they_cannot_take():
+    from llm_runtime_study_b200.errors import KernelError
+
+    with pytest.raises(KernelError, match="CUDA tensor"):
+        F().silu_mul(torch.zeros(2, 4))
+    with pytest.raises(KernelError, match="multiple of 16"):
+        q = torch.zeros(1, 1, 24, device="cuda")
+        pool = torch.zeros(1, 1, 4, 24, device="cuda")
+        z = torch.zeros(1, dtype=torch.int32, device="cuda")
+        F().paged_attention_simt(q, pool, pool, positions=z, token_entry=z, block_table=z.view(1, 1), scale=1.0)
+    with pytest.raises(KernelError, match="storage type"):
+        F().silu_mul(torch.zeros(2, 4, device="cuda", dtype=torch.float16))
