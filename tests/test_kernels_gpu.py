@@ -187,10 +187,14 @@ def _attention_case(dtype, nq, nkv, d, page, lens_and_chunks, window=0, seed=6, 
         q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
         out = plain.causal_attention(q.double(), k.double(), v.double(), 1 / math.sqrt(d), window=window or None)
         kp, vp, ids = _scatter_to_pages(k, v, page, nkv, d, dtype, seed=seed + e)
-        pools_k.append(kp), pools_v.append(vp), tables.append(ids + base)
+        pools_k.append(kp)
+        pools_v.append(vp)
+        tables.append(ids + base)
         base += kp.shape[0]
-        qs.append(q[L - n :]), wants.append(out[L - n :])
-        pos += list(range(L - n, L)), ent.__iadd__([e] * n)
+        qs.append(q[L - n :])
+        wants.append(out[L - n :])
+        pos += list(range(L - n, L))
+        ent += [e] * n
     width = max(t.shape[0] for t in tables)
     table = torch.full((len(tables), width), -1, dtype=torch.int32)
     for i, t in enumerate(tables):
