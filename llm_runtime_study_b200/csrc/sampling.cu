@@ -27,10 +27,11 @@ __host__ __device__ __forceinline__ uint64_t splitmix64(uint64_t z) {
   return z ^ (z >> 31);
 }
 
-// uniform in (0, 1) with 24 bits, from (stream key, vocabulary index)
-__device__ __forceinline__ float uniform24(uint64_t stream, uint32_t index) {
+// uniform in (0, 1) from (stream key, vocabulary index): 23 random bits plus one half,
+// which float32 holds exactly, so neither 0 nor 1 can come out
+__device__ __forceinline__ float uniform23(uint64_t stream, uint32_t index) {
   const uint64_t z = splitmix64(stream + static_cast<uint64_t>(index) * 0xD1B54A32D192ED03ull);
-  return (static_cast<float>(static_cast<uint32_t>(z >> 40)) + 0.5f) * (1.0f / 16777216.0f);
+  return (static_cast<float>(static_cast<uint32_t>(z >> 41)) + 0.5f) * (1.0f / 8388608.0f);
 }
 
 struct ArgMax {
@@ -136,7 +137,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const int* __
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
     const float v = x[i] / temperature;
     if (ordered_key(v) < low_key) continue;
-    const float u = uniform24(stream, static_cast<uint32_t>(i));
+    const float u = uniform23(stream, static_cast<uint32_t>(i));
     best = better(best, ArgMax{v - logf(-logf(u)), i});
   }
   best = block_argmax(best, arg_scratch);

@@ -57,6 +57,7 @@ class StepContext:
         # host-side copies, for choosing kernels and grids
         self.q_lens: list[int] = []
         self.kv_lens: list[int] = []
+        self.entry_slots: list[int] = []
         self.max_q_len = 0
         self.max_kv_len = 0
         self.all_decode = False
@@ -216,6 +217,7 @@ class StepRunner:
         ctx.q_start, ctx.kv_len, ctx.slots, ctx.logit_rows = view(3), view(4), view(5), view(6)
         ctx.tables = [view(7 + g).view(num_entries, tables[g].shape[1]) for g in range(len(tables))]
         ctx.q_lens, ctx.kv_lens = q_lens, kv_lens
+        ctx.entry_slots = [e.request.slot for e in entries]
         ctx.max_q_len, ctx.max_kv_len = max(q_lens), max(kv_lens)
         ctx.all_decode = ctx.max_q_len == 1
         return ctx

@@ -3,8 +3,9 @@
 An architecture's ``describe(config)`` returns a ``ModelDescription``.  The
 generic ``DecoderModel`` is built from it; the tensor schema, the cache groups
 and the random-weights mode are derived from it.  The order in which layers run
-is a list too: it may name a layer twice (weights shared between depths), and a
-layer may read the cache that another layer writes (``cache_source``).
+is a list too: it may name a layer twice (weights shared between depths; each
+run of a layer has a cache of its own), and a run may instead use the cache that
+an earlier run writes (``cache_of``).
 """
 
 from __future__ import annotations
@@ -22,12 +23,10 @@ from ..weights.checkpoint import TensorSpec
 class LayerDescription:
     """One layer: ``block`` is ``{"kind": ..., "mixer": {...}, "feed_forward": {...},
     ...}`` for the block registry; ``prefix`` is where its tensors live in the
-    checkpoint; ``cache_source`` is the index of the layer whose cache it uses
-    (``None``: its own)."""
+    checkpoint."""
 
     block: Mapping[str, Any]
     prefix: str
-    cache_source: int | None = None
 
 
 @dataclass(frozen=True)
@@ -42,16 +41,20 @@ class ModelDescription:
     order: tuple[int, ...]                # indices into ``layers``, in execution order
     final_norm: Mapping[str, Any]         # norm description + "prefix"
     head: Mapping[str, Any]               # parameters of OutputHead + "prefix"
+    cache_of: tuple[int | None, ...] = () # per run: the earlier run whose cache it uses (None: its own)
     extra: Mapping[str, Any] = field(default_factory=dict)
 
     def __post_init__(self) -> None:
         n = len(self.layers)
         if not self.order or any(not 0 <= i < n for i in self.order):
             raise ValueError(f"layer order {self.order} does not index {n} layers")
-        for i, layer in enumerate(self.layers):
-            src = layer.cache_source
-            if src is not None and (not 0 <= src < n or self.layers[src].cache_source is not None):
-                raise ValueError(f"layer {i} reads the cache of layer {src}, which owns none")
+        if not self.cache_of:
+            object.__setattr__(self, "cache_of", (None,) * len(self.order))
+        if len(self.cache_of) != len(self.order):
+            raise ValueError("cache_of needs one entry for every run in order")
+        for run, src in enumerate(self.cache_of):
+            if src is not None and (not 0 <= src < run or self.cache_of[src] is not None):
+                raise ValueError(f"run {run} uses the cache of run {src}, which is not an earlier run with a cache of its own")
 
 
 def _split(description: Mapping[str, Any]) -> tuple[str, dict[str, Any]]:

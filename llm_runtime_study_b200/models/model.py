@@ -51,17 +51,19 @@ class DecoderModel:
 
     # -------------------------------------------------------------- cache
     def cache_layout(self) -> CacheLayout:
+        """One requirement per *run* of a layer (a layer named twice in the order
+        has two caches); a run that uses an earlier run's cache asks for none."""
+
         needs = []
-        for layer, (_, block) in zip(self.description.layers, self.blocks):
-            needs.append(None if layer.cache_source is not None else block.mixer.cache_requirement())
+        for layer_index, source in zip(self.order, self.description.cache_of):
+            needs.append(None if source is not None else self.blocks[layer_index][1].mixer.cache_requirement())
         return CacheLayout.from_requirements(needs)
 
     def bind_cache(self, manager: CacheManager) -> None:
-        caches = []
-        for index, layer in enumerate(self.description.layers):
-            owner = index if layer.cache_source is None else layer.cache_source
-            caches.append(manager.layer_cache(owner))
-        self._layer_caches = caches
+        self._layer_caches = [
+            manager.layer_cache(run if source is None else source)
+            for run, source in enumerate(self.description.cache_of)
+        ]
 
     # ------------------------------------------------------------ forward
     def forward(self, ctx: Any) -> torch.Tensor | None:
@@ -69,8 +71,8 @@ class DecoderModel:
         (``None`` when no row is wanted: the cache is written all the same)."""
 
         stream = ResidualStream(self.embedding.forward(ctx.token_ids))
-        for index in self.order:
-            self.blocks[index][1].forward(stream, ctx, self._layer_caches[index])
+        for run, index in enumerate(self.order):
+            self.blocks[index][1].forward(stream, ctx, self._layer_caches[run])
         if ctx.num_logit_rows == 0:
             return None
         x = self.final_norm.norm_rows(stream.resid, stream.delta, ctx.logit_rows)

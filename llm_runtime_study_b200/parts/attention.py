@@ -29,7 +29,7 @@ class GroupedQueryAttention(Mixer):
     def __init__(
         self, *, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
         scale: float | None = None, bias: bool = False, qk_norm: Mapping[str, Any] | None = None,
-        position: Mapping[str, Any] | None = None, window: int | None = None,
+        position: Mapping[str, Any] | None = None, window: int | None = None, shares_kv: bool = False,
     ) -> None:
         if min(hidden_size, num_heads, num_kv_heads, head_dim) <= 0:
             raise ValueError("attention sizes must be positive")
@@ -41,6 +41,9 @@ class GroupedQueryAttention(Mixer):
         self.scale = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
         self.bias = bool(bias)
         self.window = window
+        # A layer that reads keys and values written by an earlier layer: it has a
+        # query and an output projection only, and writes nothing into the cache.
+        self.shares_kv = bool(shares_kv)
         self.q_norm = NORMS.build(qk_norm) if qk_norm else None
         self.k_norm = NORMS.build(qk_norm) if qk_norm else None
         self.position = POSITION_ENCODINGS.build(position) if position else None
@@ -63,11 +66,13 @@ class GroupedQueryAttention(Mixer):
         if self.q_norm is not None:
             specs.update({f"q_norm.{n}": s for n, s in self.q_norm.tensor_specs().items()})
             specs.update({f"k_norm.{n}": s for n, s in self.k_norm.tensor_specs().items()})
+        if self.shares_kv:
+            specs = {n: s for n, s in specs.items() if not n.startswith(("k_", "v_"))}
         return specs
 
     def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         self.runtime = runtime
-        names = ("q_proj", "k_proj", "v_proj")
+        names = ("q_proj",) if self.shares_kv else ("q_proj", "k_proj", "v_proj")
         self.qkv_proj = Projection(
             [tensors[f"{n}.weight"] for n in names],
             [tensors[f"{n}.bias"] for n in names] if self.bias else None,
@@ -77,32 +82,35 @@ class GroupedQueryAttention(Mixer):
         if self.q_norm is not None:
             view = TensorView.of(tensors)
             self.q_norm.load(view.sub("q_norm"), runtime)
-            self.k_norm.load(view.sub("k_norm"), runtime)
+            if not self.shares_kv:
+                self.k_norm.load(view.sub("k_norm"), runtime)
         if self.position is not None:
             self.position.load({}, runtime)
 
     # --------------------------------------------------------------- cache
-    def cache_requirement(self) -> PagedKV:
-        return PagedKV(self.num_kv_heads, self.head_dim, self.window)
+    def cache_requirement(self) -> PagedKV | None:
+        return None if self.shares_kv else PagedKV(self.num_kv_heads, self.head_dim, self.window)
 
     # ------------------------------------------------------------- forward
     def forward(self, x: torch.Tensor, ctx: Any, cache: Any) -> torch.Tensor:
         qkv = self.qkv_proj(x)
         rotary = self.position.rotary_parameters() if self.position is not None else None
         table = ctx.block_table(cache.group)
+        written_kv_heads = 0 if self.shares_kv else self.num_kv_heads
         if self.position is not None and rotary is None:
-            nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+            nq, nkv, d = self.num_heads, written_kv_heads, self.head_dim
             q_view = qkv[:, : nq * d].unflatten(1, (nq, d))
-            k_view = qkv[:, nq * d : (nq + nkv) * d].unflatten(1, (nkv, d))
+            k_view = qkv[:, nq * d : (nq + nkv) * d].unflatten(1, (nkv, d)) if nkv else None
             self.position.apply(q_view, k_view, ctx)
         q = F.qk_norm_rope_write(
-            qkv, num_q_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+            qkv, num_q_heads=self.num_heads, num_kv_heads=written_kv_heads, head_dim=self.head_dim,
             q_weight=self.q_norm.weight if self.q_norm is not None else None,
-            k_weight=self.k_norm.weight if self.k_norm is not None else None,
+            k_weight=self.k_norm.weight if self.k_norm is not None and not self.shares_kv else None,
             eps=self.q_norm.eps if self.q_norm is not None else 1.0,
             inv_freq=rotary[0] if rotary else None, rotary_dim=rotary[1] if rotary else 0,
-            positions=ctx.positions, token_entry=ctx.token_entry, block_table=table,
-            page_size=cache.page_size, k_pool=cache.keys, v_pool=cache.values,
+            positions=ctx.positions, token_entry=ctx.token_entry,
+            block_table=None if self.shares_kv else table, page_size=cache.page_size,
+            k_pool=None if self.shares_kv else cache.keys, v_pool=None if self.shares_kv else cache.values,
         )
         out = ctx.attention(q, cache, scale=self.scale, window=self.window or 0)
         return self.o_proj(out.view(out.shape[0], -1), torch.float32)

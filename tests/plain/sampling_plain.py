@@ -19,11 +19,11 @@ def splitmix64(z: int) -> int:
 
 
 def uniforms(seed: int, counter: int, vocab: int) -> torch.Tensor:
-    """u_i = (top 24 bits of splitmix64(stream + i * c) + 0.5) / 2^24,
+    """u_i = (top 23 bits of splitmix64(stream + i * c) + 0.5) / 2^23,
     stream = splitmix64(seed ^ splitmix64(counter))."""
 
     stream = splitmix64(seed ^ splitmix64(counter))
-    values = [((splitmix64((stream + i * 0xD1B54A32D192ED03) & _M) >> 40) + 0.5) / 16777216.0 for i in range(vocab)]
+    values = [((splitmix64((stream + i * 0xD1B54A32D192ED03) & _M) >> 41) + 0.5) / 8388608.0 for i in range(vocab)]
     return torch.tensor(values, dtype=torch.float64)
 
 

@@ -1,0 +1,115 @@
+"""Generation through the Python entry point and the command line, against a
+plain loop that recomputes the whole sequence for every token."""
+
+import io
+import json
+import random
+
+import pytest
+import torch
+
+from tests import helpers
+from tests.plain import sampling_plain
+
+pytestmark = pytest.mark.gpu
+
+
+def plain_generate(weights, raw, prompt, n, *, temperature=0.0, top_k=None, top_p=1.0, seed=0, eos=()):
+    """Greedy or sampled continuation; returns tokens and, per token, the gap
+    between the best and second-best score (a tie is a rounding matter)."""
+
+    tokens, gaps = list(prompt), []
+    for counter in range(n):
+        logits = helpers.plain_logits(weights, raw, tokens)[-1]
+        token, scores = sampling_plain.sample(logits, temperature, top_k, top_p, seed, counter)
+        top2 = torch.topk(scores, 2).values
+        gaps.append(float(top2[0] - top2[1]))
+        tokens.append(token)
+        if token in eos:
+            break
+    return tokens[len(prompt):], gaps
+
+
+def assert_same_until_a_tie(got, want, gaps, tie):
+    for i, (g, w) in enumerate(zip(got, want)):
+        if g != w:
+            assert gaps[i] < tie, f"token {i}: got {g}, plain {w}, gap {gaps[i]:.3e}"
+            return        # after a legitimate tie the sequences differ
+    assert len(got) == len(want)
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("B", "bfloat16")])
+def test_greedy_generation_matches_plain(tmp_path, name, dtype):
+    from llm_runtime_study_b200.engine.engine import Engine
+
+    raw, seed, page = helpers.TINY[name]
+    path, weights = helpers.make_model_dir(tmp_path / "m", raw, seed, torch_dtype=dtype)
+    eos = raw["eos_token_id"] if isinstance(raw["eos_token_id"], list) else [raw["eos_token_id"]]
+    rng = random.Random(3)
+    prompts = [helpers.random_tokens(rng, raw["vocab_size"], n) for n in (1, 7, 19, 40, 3)]
+    engine = Engine.from_model_dir(path, device="cuda:0", dtype=dtype, max_seq_len=128, max_batch_size=3,
+                                   page_size=page, max_tokens_per_step=16)
+    out = {}
+    for index, event in engine.generate(prompts, max_new_tokens=8):
+        out.setdefault(index, []).append(event)
+    tie = 1e-5 if dtype == "float32" else 3e-2
+    for i, prompt in enumerate(prompts):
+        want, gaps = plain_generate(weights, raw, prompt, 8, eos=eos)
+        got = [e.token_id for e in out[i]]
+        assert_same_until_a_tie(got, want, gaps, tie)
+        assert out[i][-1].finish_reason in ("max_new_tokens", "eos")
+        assert out[i][0].prompt_token_count == len(prompt)
+    manager = engine.cache_manager
+    manager.check()
+    assert manager.active_sequences == 0 and manager.free_pages == manager.num_pages
+
+
+def test_seeded_temperature_generation_matches_plain(tmp_path):
+    """Tiny B, portions of 13 beside running decodes, temperature 0.7, seed 1234."""
+
+    from llm_runtime_study_b200.engine.engine import Engine
+    from llm_runtime_study_b200.sampling import SamplingConfig
+
+    raw, seed, page = helpers.TINY["B"]
+    path, weights = helpers.make_model_dir(tmp_path / "m", raw, seed)
+    rng = random.Random(4)
+    prompts = [helpers.random_tokens(rng, raw["vocab_size"], n) for n in (2, 9, 16, 33, 70)]
+    engine = Engine.from_model_dir(path, device="cuda:0", dtype="float32", max_seq_len=128, max_batch_size=4,
+                                   page_size=page, max_tokens_per_step=13 + 4)
+    sampling = SamplingConfig(temperature=0.7, seed=1234)
+    runs = []
+    for _ in range(2):
+        out = {}
+        for index, event in engine.generate(prompts, max_new_tokens=12, sampling=sampling):
+            out.setdefault(index, []).append(event.token_id)
+        runs.append(out)
+    assert runs[0] == runs[1]                                   # same seed, same tokens
+    for i, prompt in enumerate(prompts):
+        want, gaps = plain_generate(weights, raw, prompt, 12, temperature=0.7, seed=1234, eos=raw["eos_token_id"])
+        assert_same_until_a_tie(runs[0][i], want, gaps, 1e-4)
+
+
+def test_command_line(tmp_path):
+    from llm_runtime_study_b200.cli import main
+
+    raw, seed, page = helpers.TINY["A"]
+    config_path = tmp_path / "config.json"
+    config_path.write_text(json.dumps(raw))
+    out, err = io.StringIO(), io.StringIO()
+    code = main(["--model", str(tmp_path / "m"), "--random-weights", str(config_path), "--weights-seed", str(seed),
+                 "--prompt-ids", "5 17 3", "--max-new-tokens", "6", "--max-seq-len", "64", "--dtype", "float32",
+                 "--page-size", str(page), "--no-stream"], output=out, error=err)
+    assert code == 0, err.getvalue()
+    lines = out.getvalue().splitlines()
+    generated = [int(t) for t in lines[0].split()]
+    from llm_runtime_study_b200.weights import Checkpoint
+
+    weights = Checkpoint.from_model_dir(tmp_path / "m").get_tensors()
+    want, gaps = plain_generate(weights, raw, [5, 17, 3], 6, eos=[raw["eos_token_id"]])
+    assert_same_until_a_tie(generated, want, gaps, 1e-5)
+    text = out.getvalue()
+    assert "prompt tokens:       3" in text and "stop reason:" in text and "decode throughput:" in text
+    out, err = io.StringIO(), io.StringIO()
+    assert main(["--model", str(tmp_path / "m"), "--prompt-ids", "999999"], output=out, error=err) == 2
+    assert err.getvalue().startswith("error: ")
+    assert main(["--model", str(tmp_path / "none"), "--prompt-ids", "1"], output=out, error=err) == 2

@@ -1,0 +1,159 @@
+"""A toy architecture defined here, in the test, and run by the unchanged
+framework: a mixer with per-request state of fixed size, a layer that runs twice
+(shared weights, two caches), and a layer that reads the keys and values another
+run wrote.  It is registered, built from a description, given random weights from
+its own schema, and stepped under different cuts of the batch."""
+
+import math
+import random
+
+import pytest
+import torch
+
+from tests import helpers
+from tests.plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+H, NQ, NKV, D, I, V, EPS, THETA = 48, 3, 1, 16, 80, 97, 1e-5, 1e4
+
+
+def register_toy():
+    from llm_runtime_study_b200.config import Architecture, register_architecture
+    from llm_runtime_study_b200.models import LayerDescription, ModelDescription
+    from llm_runtime_study_b200.parts import MIXERS, FixedState, Mixer, Projection
+    from llm_runtime_study_b200.weights import TensorSpec
+
+    class DecaySum(Mixer):
+        """s_t = sigmoid(a) * s_{t-1} + x_t per channel, y_t = W s_t; the state s is
+        kept per request in a slot of fixed size."""
+
+        def __init__(self, *, hidden_size: int) -> None:
+            self.hidden_size = hidden_size
+
+        def tensor_specs(self):
+            return {"a": TensorSpec((self.hidden_size,), init="normal", std=1.0),
+                    "out.weight": TensorSpec((self.hidden_size, self.hidden_size))}
+
+        def load(self, tensors, runtime):
+            self.runtime = runtime
+            self.decay = torch.sigmoid(tensors["a"].to(device=runtime.device, dtype=torch.float32))
+            self.out = Projection([tensors["out.weight"]], None, runtime)
+
+        def cache_requirement(self):
+            return FixedState((self.hidden_size,), torch.float32)
+
+        def forward(self, x, ctx, cache):
+            sums = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            at = 0
+            for slot, n in zip(ctx.entry_slots, ctx.q_lens):
+                s = cache.state[slot]
+                for t in range(at, at + n):
+                    s = self.decay * s + x[t].float()
+                    sums[t] = s
+                cache.state[slot] = s
+                at += n
+            return self.out(sums.to(x.dtype), torch.float32)
+
+    MIXERS.register("toy_decay_sum", DecaySum, replace=True)
+
+    def describe(cfg):
+        norm = {"kind": "rms_norm", "dim": H, "eps": EPS}
+        attention = {"kind": "gqa_attention", "hidden_size": H, "num_heads": NQ, "num_kv_heads": NKV, "head_dim": D,
+                     "qk_norm": {"kind": "rms_norm", "dim": D, "eps": EPS},
+                     "position": {"kind": "rope", "head_dim": D, "theta": THETA}}
+        ffn = {"kind": "swiglu", "hidden_size": H, "intermediate_size": I}
+
+        def block(mixer):
+            return {"kind": "pre_norm", "mixer": mixer, "feed_forward": ffn, "mixer_norm": norm, "ffn_norm": norm,
+                    "names": {"mixer": "mix"}}
+
+        layers = (
+            LayerDescription(block(attention), "toy.layers.0"),
+            LayerDescription(block({"kind": "toy_decay_sum", "hidden_size": H}), "toy.layers.1"),
+            LayerDescription(block({**attention, "shares_kv": True}), "toy.layers.2"),
+        )
+        return ModelDescription(
+            architecture="ToyHybrid", vocab_size=V, hidden_size=H, max_positions=128, eos_token_ids=(0,),
+            embedding={"prefix": "toy.embed", "vocab_size": V, "hidden_size": H}, layers=layers,
+            order=(0, 1, 0, 2), cache_of=(None, None, None, 2),
+            final_norm={"prefix": "toy.norm", **norm},
+            head={"prefix": "toy.head", "vocab_size": V, "hidden_size": H, "tied": True},
+        )
+
+    class ToyConfig:
+        def validate_context_length(self, n):
+            assert n <= 128
+
+    register_architecture(Architecture("ToyHybrid", "toy_hybrid", lambda raw: ToyConfig(), describe), replace=True)
+
+
+def plain_toy(w, tokens):
+    """The same model, whole sequence, float64, from the plain functions."""
+
+    w = {n: t.double() for n, t in w.items()}
+    ids = torch.tensor(tokens)
+    T = len(tokens)
+    h = w["toy.embed.weight"][ids]
+    cos, sin = plain.rotary_tables(torch.arange(T), D, THETA, torch.float64)
+    cfg = {"num_attention_heads": NQ, "num_key_value_heads": NKV, "head_dim": D, "rms_norm_eps": EPS}
+
+    def ffn(h, p):
+        x = plain.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], EPS)
+        return h + plain.swiglu(x, w, f"{p}.mlp")
+
+    def attention_layer(h, p, shared_kv=None):
+        x = plain.rms_norm(h, w[f"{p}.input_layernorm.weight"], EPS)
+        q = plain.rotate(plain.rms_norm((x @ w[f"{p}.mix.q_proj.weight"].T).view(T, NQ, D), w[f"{p}.mix.q_norm.weight"], EPS), cos, sin)
+        if shared_kv is None:
+            k = plain.rotate(plain.rms_norm((x @ w[f"{p}.mix.k_proj.weight"].T).view(T, NKV, D), w[f"{p}.mix.k_norm.weight"], EPS), cos, sin)
+            v = (x @ w[f"{p}.mix.v_proj.weight"].T).view(T, NKV, D)
+        else:
+            k, v = shared_kv
+        o = plain.causal_attention(q, k, v, 1 / math.sqrt(D)).reshape(T, NQ * D) @ w[f"{p}.mix.o_proj.weight"].T
+        return ffn(h + o, p), (k, v)
+
+    h, _ = attention_layer(h, "toy.layers.0")
+    x = plain.rms_norm(h, w["toy.layers.1.input_layernorm.weight"], EPS)
+    decay, s, sums = torch.sigmoid(w["toy.layers.1.mix.a"]), torch.zeros(H, dtype=torch.float64), []
+    for t in range(T):
+        s = decay * s + x[t]
+        sums.append(s)
+    h = ffn(h + torch.stack(sums) @ w["toy.layers.1.mix.out.weight"].T, "toy.layers.1")
+    h, kv = attention_layer(h, "toy.layers.0")                # the same weights again, a cache of its own
+    h, _ = attention_layer(h, "toy.layers.2", shared_kv=kv)   # reads what the run before wrote
+    return plain.rms_norm(h, w["toy.norm.weight"], EPS) @ w["toy.embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_is_built_and_stepped(tmp_path, dtype):
+    from llm_runtime_study_b200.engine.replay import TraceReplayer
+    from llm_runtime_study_b200.engine.runtime import load
+    from llm_runtime_study_b200.weights import Checkpoint, write_random_model
+
+    register_toy()
+    raw = {"model_type": "toy_hybrid", "architectures": ["ToyHybrid"], "torch_dtype": dtype}
+    write_random_model(tmp_path / "toy", raw, seed=5)
+    weights = Checkpoint.from_model_dir(tmp_path / "toy").get_tensors()
+    assert "toy.layers.2.mix.k_proj.weight" not in weights and "toy.layers.1.mix.a" in weights
+    loaded = load(tmp_path / "toy", device="cuda:0", dtype=dtype)
+    layout = loaded.model.cache_layout()
+    assert [g.layers for g in layout.groups] == [(0, 2)] and [s.layer for s in layout.states] == [1]
+
+    rng = random.Random(8)
+    requests = {f"t{i}": helpers.random_tokens(rng, V, n) for i, n in enumerate([5, 23, 64, 41, 17, 9])}
+    want = {rid: plain_toy(weights, toks) for rid, toks in requests.items()}
+    tol = dict(atol=3e-5, rtol=1e-4) if dtype == "float32" else dict(atol=4e-2, rtol=3e-2)
+    for steps in (helpers.trace_whole(requests), helpers.trace_chunked(requests, random.Random(1)),
+                  helpers.trace_mixed(requests, random.Random(2), live_max=3)):
+        replayer = TraceReplayer(loaded, max_tokens=helpers.pool_tokens(steps), page_size=8)
+        outputs = {}
+        for record in steps:
+            rows = replayer.run_step(record)
+            if rows is not None:
+                outputs[record["step"]] = torch.from_numpy(rows.copy())
+        got = helpers.collect_logits(steps, outputs)
+        for rid, toks in requests.items():
+            rows = torch.stack([got[rid][p] for p in range(len(toks))]).double()
+            torch.testing.assert_close(rows, want[rid], **tol)
+        replayer.runner.manager.check()
