@@ -1,0 +1,270 @@
+"""Decode and prefill throughput of the engine at Qwen3-8B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line: ``value`` is decoded tokens per second at batch 8 with 2,048
+cached tokens per request (device time, CUDA events around K steps of the step
+function plus sampling); ``e2e`` is the same through the scheduler the Python
+entry point uses, host token ids in and out, by the wall clock; ``prefill`` is one
+2,048-token prompt; ``points`` holds decode at batch 1 and 64; ``roofline`` is the
+bytes a decode step must read (every weight once plus the live requests' cache)
+over its time.  Weights are random (N(0, 0.02); norms 1 + N(0, 0.05)) and token
+ids uniform random: there is no network for checkpoints or datasets.  Every
+decode step reads far more than the 126 MB L2 holds (16 GB of weights), so no
+separate L2 flush is needed between timed iterations.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 151936, "hidden_size": 4096,
+    "intermediate_size": 12288, "num_hidden_layers": 36, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 128, "max_position_embeddings": 4096, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "hidden_act": "silu", "attention_bias": False, "tie_word_embeddings": False, "torch_dtype": "bfloat16",
+    "bos_token_id": 151643, "eos_token_id": 151645,
+}
+CONTEXT = 2048          # cached tokens per request when decoding
+PREFILL_TOKENS = 2048
+PAGE_SIZE = 16
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            raw = json.load(open(path))
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(raw.get("bf16_tflops_sustained", raw["bf16_tflops"])),
+                    "source": "measured"}
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed
+    region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0) -> None:
+        self.lines: list[str] = []
+        self.process = None
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.process = None
+
+    def _read(self) -> None:
+        for line in self.process.stdout:
+            self.lines.append(line.strip())
+
+    def mark(self) -> int:
+        return len(self.lines)
+
+    def stop(self, start: int = 0) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.process.terminate()
+        rows = [l.split(", ") for l in self.lines[start:] if l.count(",") >= 7] or [l.split(", ") for l in self.lines if l.count(",") >= 7]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in rows for n, v in zip(names, r[4:8]) if v.strip().lower() == "active"})
+        mhz = [float(r[0]) for r in rows]
+        return {"sm_mhz": statistics.median(mhz), "sm_max_mhz": float(rows[0][1]), "reasons": reasons,
+                "power_w": statistics.median(float(r[2]) for r in rows), "samples": len(rows)}
+
+
+def model_bytes(cfg: dict, layers: int) -> int:
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q, kv = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = (q + 2 * kv) * h + h * q + 3 * h * i + 2 * h + 2 * cfg["head_dim"]
+    # a decode step reads every layer, the final norm, the head, and one embedding row per token
+    return 2 * (layers * per_layer + h + v * h)
+
+
+def kv_bytes_per_token(cfg: dict, layers: int) -> int:
+    return layers * 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+
+
+def prefill_flops(cfg: dict, layers: int, tokens: int) -> float:
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q, kv = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    gemm = 2.0 * tokens * layers * ((q + 2 * kv) * h + h * q + 3 * h * i)
+    attention = 4.0 * layers * cfg["num_attention_heads"] * cfg["head_dim"] * tokens * (tokens + 1) / 2
+    return gemm + attention + 2.0 * v * h
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from llm_runtime_study_b200.engine.engine import Engine
+    from llm_runtime_study_b200.engine.step import StepEntry
+    from llm_runtime_study_b200.ops import native
+    from llm_runtime_study_b200.sampling import SamplingConfig
+
+    cfg = dict(QWEN3_8B)
+    full_layers = cfg["num_hidden_layers"]
+    layers = args.layers or full_layers
+    cfg["num_hidden_layers"] = layers
+    torch.cuda.set_device(0)
+    generator = torch.Generator().manual_seed(0)
+
+    def ids(n):
+        return torch.randint(0, cfg["vocab_size"], (n,), generator=generator).tolist()
+
+    max_batch = max(args.batch, 64)
+    engine = Engine.from_random_weights(
+        cfg, seed=0, device="cuda:0", dtype="bfloat16", max_seq_len=cfg["max_position_embeddings"],
+        max_batch_size=max_batch, page_size=PAGE_SIZE, max_cache_tokens=max_batch * (CONTEXT + 64),
+        max_tokens_per_step=PREFILL_TOKENS, use_cuda_graph=True)
+    runner, manager = engine.runner, engine.cache_manager
+    sampler = engine._sampler
+    greedy = SamplingConfig()
+
+    def timed(fn, repeat):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(repeat):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / repeat
+
+    # ------------------------------------------------------------- prefill
+    def one_prefill():
+        request = manager.admit()
+        logits = runner.step([StepEntry(request, prompt, [PREFILL_TOKENS - 1])])
+        sampler.sample(logits, [(greedy, 0, 0)])
+        manager.release(request)
+
+    prompt = ids(PREFILL_TOKENS)
+    for _ in range(max(args.warmup, 3)):
+        one_prefill()
+    prefill_ms = statistics.median(timed(one_prefill, 1) for _ in range(5))
+
+    # -------------------------------------------------------------- decode
+    def decode_point(batch, steps, warmup, sample_clocks=False):
+        requests = [manager.admit() for _ in range(batch)]
+        for request in requests:
+            runner.step([StepEntry(request, ids(CONTEXT), [])])
+        tokens = [ids(1) for _ in range(batch)]
+
+        def one_step():
+            logits = runner.step([StepEntry(r, t, [0]) for r, t in zip(requests, tokens)])
+            out = sampler.sample(logits, [(greedy, 0, 0)] * batch)
+            for t, o in zip(tokens, out):
+                t[0] = o
+
+        for _ in range(max(warmup, 3)):
+            one_step()
+        clocks = ClockSampler() if sample_clocks else None
+        mark = clocks.mark() if clocks else 0
+        before = native.launch_count()
+        ms = timed(one_step, steps)
+        launches = native.launch_count() - before
+        info = clocks.stop(mark) if clocks else None
+        for request in requests:
+            manager.release(request)
+        return ms, launches, info
+
+    ms_b8, launches, clocks = decode_point(args.batch, args.steps, args.warmup, sample_clocks=True)
+    ms_b1, _, _ = decode_point(1, args.steps, args.warmup)
+    ms_b64, _, _ = decode_point(64, args.steps, args.warmup)
+
+    # ------------------------------------- end to end through the scheduler
+    engine.max_batch_size = args.batch
+    scheduler = engine.create_scheduler()
+    scheduler.max_batch_size = args.batch
+    for _ in range(args.batch):
+        scheduler.add_request(ids(CONTEXT), max_new_tokens=args.steps + max(args.warmup, 3) + 2)
+    while scheduler.num_waiting or any(r.prefilling for r in scheduler._running):
+        scheduler.step()
+    for _ in range(max(args.warmup, 3)):
+        scheduler.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    produced = 0
+    for _ in range(args.steps):
+        produced += len(scheduler.step())
+    torch.cuda.synchronize()
+    e2e_seconds = time.perf_counter() - t0
+    scheduler.abort_all()
+    graph = runner._graphs._graphs.get(args.batch) if runner._graphs else None
+    h2d = (graph.dev.numel() * 4 if graph else 0) + args.batch * 6 * 4
+    d2h = args.batch * 4
+
+    pk = peaks()
+    step_bytes = model_bytes(cfg, layers) + args.batch * CONTEXT * kv_bytes_per_token(cfg, layers)
+    achieved = step_bytes / (ms_b8 * 1e-3) / 1e9
+    flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
+    value = args.batch / (ms_b8 * 1e-3)
+    return {
+        "metric": "decode tok/s at batch 8 (2,048 cached tokens each), Qwen3-8B shape",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_b8, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights, uniform random token ids", "impl": "ours",
+        "config": {
+            "model": "Qwen3-8B shape", "layers": layers, "layers_full": full_layers, "hidden": cfg["hidden_size"],
+            "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
+            "seq_len": CONTEXT, "context_limit": cfg["max_position_embeddings"], "page_size": PAGE_SIZE,
+            "parallelism": "none (1 GPU)", "cuda_graph": True, "sampling": "greedy, in the timed step",
+            "l2": "inputs larger than L2 (16 GB of weights per step)", "peaks": pk["source"],
+        },
+        "e2e": {"value": round(produced / e2e_seconds, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "prefill": {"value": round(PREFILL_TOKENS / (prefill_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3), "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": {"decode_b1": round(1 / (ms_b1 * 1e-3), 1), "decode_b64": round(64 / (ms_b64 * 1e-3), 1)},
+        "clocks": clocks,
+    }
+
+
+def run_reference(args) -> dict:
+    return {"impl": "reference", "unavailable": "reference install not attempted yet"}
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
+    args = parser.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU: --gpus {args.gpus} is not supported by this engine (single-GPU tier)")
+        return 2
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

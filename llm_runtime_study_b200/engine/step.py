@@ -61,6 +61,7 @@ class StepContext:
         self.max_q_len = 0
         self.max_kv_len = 0
         self.all_decode = False
+        self.captured = False   # True while a CUDA graph holds this batch's launches
 
     def block_table(self, group: int) -> torch.Tensor:
         return self.tables[group]
@@ -129,12 +130,19 @@ class StepRunner:
         self._buffers = _MetaBuffers(runtime.device, 4096)
         model.bind_cache(manager)
         self.last_context: StepContext | None = None
+        self.use_cuda_graph = False
+        self._graphs = None
 
     # ---------------------------------------------------------------- build
     def build_context(self, entries: Sequence[StepEntry], *, table_width: int | None = None) -> StepContext:
         """Validate the batch on the host, take the pages it needs, and put its
         metadata on the device.  Nothing is launched and no length changes."""
 
+        q_lens, starts = self.validate_and_grow(entries)
+        manager = self.manager
+        return self._pack_context(entries, q_lens, starts, table_width)
+
+    def validate_and_grow(self, entries: Sequence[StepEntry]) -> tuple[list[int], list[int]]:
         if not entries:
             raise GenerationError("a step needs at least one entry")
         manager = self.manager
@@ -174,7 +182,10 @@ class StepRunner:
                 )
         for entry, start, n in zip(entries, starts, q_lens):
             manager.grow(entry.request, start + n)
+        return q_lens, starts
 
+    def _pack_context(self, entries, q_lens, starts, table_width) -> StepContext:
+        manager = self.manager
         num_tokens, num_entries = sum(q_lens), len(entries)
         token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
         positions = np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(starts, q_lens)])
@@ -228,10 +239,27 @@ class StepRunner:
         device, rows in the order of the entries and of each entry's ``want``
         (``None`` if nothing was wanted)."""
 
+        if self.use_cuda_graph and self.runtime.device.type == "cuda":
+            if self._graphs is None:
+                from .graph import DecodeGraphs
+
+                self._graphs = DecodeGraphs(self)
+            if self._graphs.eligible(entries):
+                return self._step_captured(entries)
         ctx = self.build_context(entries)
         with torch.inference_mode():
             logits = self.model.forward(ctx)
         for entry, length in zip(entries, ctx.kv_lens):
             self.manager.commit(entry.request, length)
         self.last_context = ctx
+        return logits
+
+    def _step_captured(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """A batch of single decoded tokens, replayed from a CUDA graph.  The
+        same host-side checks and page-taking as the eager path come first."""
+
+        self.validate_and_grow(entries)
+        logits, kv_lens = self._graphs.run(entries)
+        for entry, length in zip(entries, kv_lens):
+            self.manager.commit(entry.request, length)
         return logits

@@ -12,3 +12,7 @@ def try_paged_attention(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Tens
     this case (the caller then uses the CUDA-core kernel)."""
 
     return None
+
+
+def build(head_dim: int) -> None:
+    """Compile the kernels for one head size (no-op until they exist)."""

@@ -95,10 +95,27 @@ def check(status: int, what: str) -> None:
         return
     if status in _OWN_ERRORS:
         raise KernelError(f"{what}: {_OWN_ERRORS[status]}")
-    raise KernelError(f"{what}: CUDA error {status} ({torch.cuda.cudart().cudaGetErrorString(status) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else 'see cudaError_t'})")
+    raise KernelError(f"{what}: CUDA error {status} (cudaError_t)")
+
+
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many of this package's kernels have been launched (graph replays
+    count every kernel they hold)."""
+
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
 
 
 def call(name: str, *args) -> None:
+    global _launches
+    _launches += 1
     check(_function(name)(*args), name)
 
 

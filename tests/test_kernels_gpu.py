@@ -180,9 +180,9 @@ def _attention_case(dtype, nq, nkv, d, page, lens_and_chunks, window=0, seed=6, 
         if boost is not None:   # one far key dominates the last query's scores
             t = boost if boost >= 0 else L + boost
             k[t] = 0
-            k[t, :, 0] = 6.0
+            k[t, :, 0] = 16.0
             q[L - 1] = 0
-            q[L - 1, :, 0] = 6.0
+            q[L - 1, :, 0] = 16.0
             v[t] = 5.0
         q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
         out = plain.causal_attention(q.double(), k.double(), v.double(), 1 / math.sqrt(d), window=window or None)
