@@ -1,18 +1,141 @@
-"""bfloat16 tensor-core attention kernels (built per head size)."""
+"""bfloat16 tensor-core attention kernels, one build per head size."""
 
 from __future__ import annotations
 
 from typing import Any
 
+import numpy as np
 import torch
+
+from . import native
+from ..errors import KernelError
+from .native import c_float, c_int, c_void_p
+
+c_long = native.ctypes.c_long
+MAX_HEAD_DIM = 256
+_TARGET_CTAS = 592       # four CTAs on each of 148 SMs
+_MIN_KEYS_PER_SPLIT = 128
+
+_TABLE = {
+    "b200_attention_head_dim": [],
+    "b200_attention_prefill_rows": [],
+    "b200_attention_prefill_bf16": [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_float, c_int] + [c_void_p] * 3 + [c_int, c_void_p],
+    "b200_attention_decode_scratch_floats": [c_int, c_int, c_int],
+    "b200_attention_decode_bf16": [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_long, c_void_p],
+}
+
+
+def library_name(head_dim: int) -> str:
+    name = f"b200_attention_mma_d{head_dim}"
+    if name not in native.library_specs():
+        native.register_library(name, ("attention_mma.cu",), _TABLE, defines=(f"HEAD_DIM={head_dim}",))
+    return name
+
+
+def supported(head_dim: int) -> bool:
+    return head_dim % 16 == 0 and 16 <= head_dim <= MAX_HEAD_DIM
+
+
+def build(head_dim: int) -> None:
+    """Compile the kernels for one head size."""
+
+    from ..csrc.build import build_library
+
+    name = library_name(head_dim)
+    build_library(name, ("attention_mma.cu",), native.library_defines(name))
+
+
+def decode_splits(requests: int, kv_heads: int, slices: int, longest: int) -> int:
+    """Into how many parts each sequence is cut so that the GPU is filled."""
+
+    ctas = max(1, requests * kv_heads * slices)
+    by_occupancy = -(-_TARGET_CTAS // ctas)
+    by_length = max(1, -(-longest // _MIN_KEYS_PER_SPLIT))
+    return max(1, min(by_occupancy, by_length))
+
+
+def tile_map(q_lens, tokens_per_tile: int, device) -> tuple[torch.Tensor, int]:
+    """Cut every entry into tiles of consecutive tokens: rows [entry, first token, count]."""
+
+    rows, first = [], 0
+    for entry, n in enumerate(q_lens):
+        for s in range(0, n, tokens_per_tile):
+            rows.append((entry, first + s, min(tokens_per_tile, n - s)))
+        first += n
+    table = np.ascontiguousarray(np.asarray(rows, dtype=np.int32).T)
+    return torch.from_numpy(table).to(device), len(rows)
+
+
+def _geometry(q: torch.Tensor, keys: torch.Tensor):
+    n, nq, d = q.shape
+    nkv, page_size = keys.shape[1], keys.shape[2]
+    if keys.shape[3] != d or nq % nkv:
+        raise KernelError(f"attention shapes do not fit: q {tuple(q.shape)}, cache {tuple(keys.shape)}")
+    group = nq // nkv
+    gs = min(group, 16)
+    return n, nq, d, nkv, page_size, gs, -(-group // gs)
+
+
+def prefill_attention(
+    q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, *, positions: torch.Tensor, block_table: torch.Tensor,
+    q_lens, scale: float, window: int = 0, tiles: tuple[torch.Tensor, int] | None = None,
+) -> torch.Tensor:
+    """Causal attention for a batch whose entries hold ``q_lens[i]`` consecutive
+    tokens each (prompt portions and single tokens alike); ``block_table[i]`` is
+    entry ``i``'s row."""
+
+    for t, name in ((q, "q"), (keys, "keys"), (values, "values")):
+        native.require(t, name, dtype=torch.bfloat16)
+    n, nq, d, nkv, page_size, gs, _ = _geometry(q, keys)
+    lib = library_name(d)
+    if tiles is None:
+        tiles = tile_map(q_lens, 64 // gs, q.device)
+    table, count = tiles
+    out = torch.empty_like(q)
+    native.call(
+        "b200_attention_prefill_bf16", q.data_ptr(), keys.data_ptr(), values.data_ptr(), out.data_ptr(),
+        positions.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, nq, nkv, float(scale), int(window),
+        table[0].data_ptr(), table[1].data_ptr(), table[2].data_ptr(), count, native.stream_ptr(), library=lib)
+    return out
+
+
+def decode_attention(
+    q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, *, kv_len: torch.Tensor, block_table: torch.Tensor,
+    scale: float, window: int = 0, splits: int = 1,
+) -> torch.Tensor:
+    """One query token per request (row ``i`` of ``q`` belongs to row ``i`` of
+    ``block_table``) over its ``kv_len[i]`` cached keys, the sequence cut into
+    ``splits`` parts that are merged afterwards."""
+
+    for t, name in ((q, "q"), (keys, "keys"), (values, "values")):
+        native.require(t, name, dtype=torch.bfloat16)
+    n, nq, d, nkv, page_size, _, _ = _geometry(q, keys)
+    lib = library_name(d)
+    floats = native.query("b200_attention_decode_scratch_floats", n, nq, splits, library=lib)
+    scratch = torch.empty(max(floats, 1), dtype=torch.float32, device=q.device)
+    out = torch.empty_like(q)
+    native.call(
+        "b200_attention_decode_bf16", q.data_ptr(), keys.data_ptr(), values.data_ptr(), out.data_ptr(),
+        kv_len.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, n, nq, nkv, float(scale),
+        int(window), splits, scratch.data_ptr(), floats, native.stream_ptr(), library=lib,
+        launches=2 if splits > 1 else 1)
+    return out
 
 
 def try_paged_attention(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Tensor, *, scale: float, window: int):
     """Return the attention output, or ``None`` when no tensor-core kernel takes
-    this case (the caller then uses the CUDA-core kernel)."""
+    this head size (the caller then uses the CUDA-core kernel)."""
 
-    return None
-
-
-def build(head_dim: int) -> None:
-    """Compile the kernels for one head size (no-op until they exist)."""
+    n, nq, d = q.shape
+    if not supported(d):
+        return None
+    _, _, _, nkv, _, gs, slices = _geometry(q, cache.keys)
+    if ctx.all_decode and n == ctx.num_entries:
+        return decode_attention(q, cache.keys, cache.values, kv_len=ctx.kv_len, block_table=table, scale=scale,
+                                window=window, splits=decode_splits(n, nkv, slices, ctx.max_kv_len))
+    maps = ctx.__dict__.setdefault("_tile_maps", {})
+    per_tile = 64 // gs
+    if per_tile not in maps:
+        maps[per_tile] = tile_map(ctx.q_lens, per_tile, q.device)
+    return prefill_attention(q, cache.keys, cache.values, positions=ctx.positions, block_table=table,
+                             q_lens=ctx.q_lens, scale=scale, window=window, tiles=maps[per_tile])

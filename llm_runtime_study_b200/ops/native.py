@@ -60,34 +60,46 @@ _LIBRARIES = {
 _functions: dict[str, ctypes._CFuncPtr] = {}
 
 
+_DEFINES: dict[str, tuple[str, ...]] = {}
+
+
 def library_specs() -> dict:
     """Sources of every library, for the build-everything entry point."""
 
     return {name: sources for name, (sources, _) in _LIBRARIES.items()}
 
 
-def _function(name: str):
-    fn = _functions.get(name)
+def library_defines(name: str) -> tuple[str, ...]:
+    return _DEFINES.get(name, ())
+
+
+def _function(name: str, library: str | None = None):
+    """The C function ``name``; ``library`` picks among libraries that export
+    the same symbol (one build per head size)."""
+
+    key = name if library is None else f"{library}:{name}"
+    fn = _functions.get(key)
     if fn is None:
         for lib_name, (sources, table) in _LIBRARIES.items():
-            if name in table:
-                lib = load_library(lib_name, sources)
+            if name in table and library in (None, lib_name):
+                lib = load_library(lib_name, sources, _DEFINES.get(lib_name, ()))
                 for fname, argtypes in table.items():
                     f = getattr(lib, fname)
                     f.argtypes = argtypes
-                    f.restype = c_int
-                    _functions[fname] = f
+                    f.restype = ctypes.c_long if fname.endswith("_floats") else c_int
+                    _functions[fname if library is None else f"{lib_name}:{fname}"] = f
                 break
         else:
             raise KernelError(f"no native library provides {name}")
-        fn = _functions[name]
+        fn = _functions[key]
     return fn
 
 
-def register_library(lib_name: str, sources: Sequence[str], table: dict) -> None:
+def register_library(lib_name: str, sources: Sequence[str], table: dict, defines: Sequence[str] = ()) -> None:
     """Add a library (used by kernels that are built per head size)."""
 
     _LIBRARIES[lib_name] = (tuple(sources), dict(table))
+    _DEFINES[lib_name] = tuple(defines)
 
 
 def check(status: int, what: str) -> None:
@@ -113,10 +125,16 @@ def add_launches(n: int) -> None:
     _launches += n
 
 
-def call(name: str, *args) -> None:
+def call(name: str, *args, library: str | None = None, launches: int = 1) -> None:
     global _launches
-    _launches += 1
-    check(_function(name)(*args), name)
+    _launches += launches
+    check(_function(name, library)(*args), name)
+
+
+def query(name: str, *args, library: str | None = None) -> int:
+    """Call a C function that returns a number rather than a status."""
+
+    return _function(name, library)(*args)
 
 
 def stream_ptr() -> int:

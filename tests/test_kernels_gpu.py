@@ -252,3 +252,84 @@ def test_kernels_refuse_what_they_cannot_take():
         F().paged_attention_simt(q, pool, pool, positions=z, token_entry=z, block_table=z.view(1, 1), scale=1.0)
     with pytest.raises(KernelError, match="storage type"):
         F().silu_mul(torch.zeros(2, 4, device="cuda", dtype=torch.float16))
+
+
+# ------------------------------------------------------ bfloat16 tensor-core attention
+def _mma():
+    from llm_runtime_study_b200.ops import attention_bf16
+
+    return attention_bf16
+
+
+BF16_TOL = dict(atol=2e-2, rtol=2e-2)
+
+
+def _q_lens(ent):
+    return torch.bincount(ent.long()).tolist()
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", ATTENTION_SHAPES + [(32, 1, 64, 16), (6, 6, 80, 4), (12, 2, 128, 8)])
+def test_prefill_attention_mma(nq, nkv, d, page):
+    q, kp, vp, pos, ent, table, want = _attention_case(
+        torch.bfloat16, nq, nkv, d, page, [(1, 1), (33, 33), (70, 5), (131, 1), (64, 2), (200, 200), (129, 65)])
+    out = _mma().prefill_attention(dev(q), dev(kp), dev(vp), positions=dev(pos), block_table=dev(table),
+                                   q_lens=_q_lens(ent), scale=1 / math.sqrt(d))
+    torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
+
+
+@pytest.mark.parametrize("window", [1, 7, 64, 65, 100])
+def test_prefill_attention_mma_window(window):
+    nq, nkv, d, page = 4, 2, 32, 8
+    q, kp, vp, pos, ent, table, want = _attention_case(torch.bfloat16, nq, nkv, d, page, [(300, 140), (9, 9), (70, 1)], window=window)
+    out = _mma().prefill_attention(dev(q), dev(kp), dev(vp), positions=dev(pos), block_table=dev(table),
+                                   q_lens=_q_lens(ent), scale=1 / math.sqrt(d), window=window)
+    torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", ATTENTION_SHAPES + [(32, 1, 64, 16), (6, 6, 80, 4), (32, 8, 128, 16)])
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+def test_decode_attention_mma(nq, nkv, d, page, splits):
+    lens = [1, 33, 70, 131, 64, 700, 65]
+    q, kp, vp, pos, ent, table, want = _attention_case(torch.bfloat16, nq, nkv, d, page, [(L, 1) for L in lens])
+    out = _mma().decode_attention(dev(q), dev(kp), dev(vp), kv_len=dev(torch.tensor(lens, dtype=torch.int32)),
+                                  block_table=dev(table), scale=1 / math.sqrt(d), splits=splits)
+    torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
+
+
+@pytest.mark.parametrize("window", [1, 7, 64, 65, 500])
+def test_decode_attention_mma_window(window):
+    nq, nkv, d, page = 8, 2, 64, 16
+    lens = [300, 9, 64, 65]
+    q, kp, vp, pos, ent, table, want = _attention_case(torch.bfloat16, nq, nkv, d, page, [(L, 1) for L in lens], window=window)
+    out = _mma().decode_attention(dev(q), dev(kp), dev(vp), kv_len=dev(torch.tensor(lens, dtype=torch.int32)),
+                                  block_table=dev(table), scale=1 / math.sqrt(d), window=window, splits=3)
+    torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
+
+
+@pytest.mark.parametrize("boost", [0, 15, 16, 63, 64, -2, 300, 511, 512])
+def test_mma_attention_finds_a_far_key(boost):
+    nq, nkv, d, page = 8, 2, 64, 16
+    q, kp, vp, pos, ent, table, want = _attention_case(torch.bfloat16, nq, nkv, d, page, [(700, 3)], boost=boost)
+    assert float(want[-1].abs().mean()) > 3.0
+    out = _mma().prefill_attention(dev(q), dev(kp), dev(vp), positions=dev(pos), block_table=dev(table),
+                                   q_lens=[3], scale=1 / math.sqrt(d))
+    torch.testing.assert_close(out.cpu().double(), want, atol=3e-2, rtol=2e-2)
+    last = _mma().decode_attention(dev(q[-1:]), dev(kp), dev(vp), kv_len=dev(torch.tensor([700], dtype=torch.int32)),
+                                   block_table=dev(table), scale=1 / math.sqrt(d), splits=4)
+    torch.testing.assert_close(last.cpu().double(), want[-1:], atol=3e-2, rtol=2e-2)
+
+
+def test_masked_cache_rows_may_hold_anything():
+    """Unused slots of a page hold poison (1e4 / -1e4 here, see _scatter_to_pages);
+    NaN bit patterns beyond a request's length must not leak either."""
+
+    nq, nkv, d, page = 4, 2, 32, 16
+    q, kp, vp, pos, ent, table, want = _attention_case(torch.bfloat16, nq, nkv, d, page, [(37, 37)])
+    kp[table[0, 2].long(), :, 37 - 32:] = float("nan")
+    vp[table[0, 2].long(), :, 37 - 32:] = float("nan")
+    out = _mma().prefill_attention(dev(q), dev(kp), dev(vp), positions=dev(pos), block_table=dev(table),
+                                   q_lens=[37], scale=1 / math.sqrt(d))
+    torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
+    last = _mma().decode_attention(dev(q[-1:]), dev(kp), dev(vp), kv_len=dev(torch.tensor([37], dtype=torch.int32)),
+                                   block_table=dev(table), scale=1 / math.sqrt(d), splits=2)
+    torch.testing.assert_close(last.cpu().double(), want[-1:], **BF16_TOL)
