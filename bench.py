@@ -198,7 +198,7 @@ def run_ours(args) -> dict:
     scheduler = engine.create_scheduler()
     scheduler.max_batch_size = args.batch
     for _ in range(args.batch):
-        scheduler.add_request(ids(CONTEXT), max_new_tokens=args.steps + max(args.warmup, 3) + 2)
+        scheduler.add_request(ids(CONTEXT), max_new_tokens=1024)
     while scheduler.num_waiting or any(r.prefilling for r in scheduler._running):
         scheduler.step()
     for _ in range(max(args.warmup, 3)):

@@ -1,0 +1,402 @@
+// bfloat16 matrix product on the 5th-generation tensor cores: C[M,N] = A[M,K] * W[N,K]^T (+ bias)
+// with float32 accumulation in tensor memory (TMEM).
+//
+// One CTA computes one 128 x BN tile.  Roles, one per warp:
+//   warp 0   producer: one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of a
+//            128 x 64 tile of the row operand and a BN x 64 tile of the column operand into a
+//            ring of shared-memory stages, signalling a "full" mbarrier per stage;
+//   warp 1   allocates TMEM; one lane issues tcgen05.mma (M = 128, N = BN, K = 16, four per
+//            stage) and commits each stage's completion to its "empty" mbarrier;
+//   warps 2-5  epilogue: tcgen05.ld of the accumulator (each warp its quarter of the 128 TMEM
+//            lanes), bias, conversion, store.
+// Both operands are K-major ("row . row^T"), which is how nn.Linear stores its weight
+// (mini_llm/nn/attention.py:102-111), so no transposition is needed anywhere.
+//
+// "Swapped" mode serves small M (decoding): the weight is the row operand (128 output
+// features per CTA), the tokens are the column operand (BN = tokens rounded up to 16), and the
+// K range may be split over the CTAs of a thread-block cluster whose partial tiles are summed
+// through distributed shared memory in rank order (deterministic, no atomics, no scratch).
+//
+// Every wait on an mbarrier is bounded: after kSpinLimit polls the kernel records an error
+// code, stops issuing work, frees its TMEM and returns.
+#include <cooperative_groups.h>
+#include <cuda.h>
+
+#include "common.cuh"
+#include "mma.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace b200 {
+
+constexpr int BM = 128;   // rows of the row operand per CTA = TMEM lanes
+constexpr int BK = 64;    // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr int kThreads = 192;
+
+__device__ int g_gemm_error = 0;
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_addr(bar);
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(
+          smem_addr(dst)),
+      "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+// shared-memory matrix descriptor: K-major tile, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_byte_addr & 0x3FFFF) >> 4);   // start address
+  d |= static_cast<uint64_t>(1) << 16;                            // leading byte offset (unused with swizzle)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                    // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                            // descriptor version of sm_100
+  d |= static_cast<uint64_t>(2) << 61;                            // SWIZZLE_128B
+  return d;
+}
+// instruction descriptor, kind::f16: D = f32, A = B = bf16, both K-major, M = 128, N = n
+__host__ __device__ constexpr uint32_t umma_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_load_16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <typename OutT> __device__ __forceinline__ void store_out(OutT* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ void store_row_32(float* dst, const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+}
+__device__ __forceinline__ void store_row_32(__nv_bfloat16* dst, const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    uint4 q;
+    q.x = pack_bf16(v[j], v[j + 1]);
+    q.y = pack_bf16(v[j + 2], v[j + 3]);
+    q.z = pack_bf16(v[j + 4], v[j + 5]);
+    q.w = pack_bf16(v[j + 6], v[j + 7]);
+    *reinterpret_cast<uint4*>(dst + j) = q;
+  }
+}
+
+struct GemmParams {
+  void* c;
+  const float* bias;
+  int M, N, K, ldc;
+  int vector_ok;      // rows of C start on 16-byte boundaries
+  int kb_per_split;   // 64-wide K blocks per CTA of a cluster (swapped mode); all of them otherwise
+};
+
+// SWAP = false: rows operand = A (activations), columns operand = W; tile (m0, n0) = (blockIdx.x*128, blockIdx.y*BN).
+// SWAP = true : rows operand = W, columns operand = A (all M <= BN tokens); n0 = blockIdx.x*128; blockIdx.y = K split.
+template <int BN, int STAGES, bool SWAP, typename OutT>
+__global__ void __launch_bounds__(kThreads)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols, GemmParams p) {
+  constexpr uint32_t ROW_BYTES = BM * BK * 2, COL_BYTES = BN * BK * 2, STAGE_BYTES = ROW_BYTES + COL_BYTES;
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : (BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256)));
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  int* failed = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * BM;
+  const int col0 = SWAP ? 0 : blockIdx.y * BN;
+  const int total_kb = (p.K + BK - 1) / BK;
+  const int kb_begin = SWAP ? blockIdx.y * p.kb_per_split : 0;
+  const int kb_end = SWAP ? min(total_kb, kb_begin + p.kb_per_split) : total_kb;
+  const int num_kb = max(0, kb_end - kb_begin);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(acc_full, 1);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------------------------------------------------------- producer
+    for (int i = 0; i < num_kb; ++i) {
+      const int s = i % STAGES;
+      const uint32_t phase = (i / STAGES) & 1;
+      if (!mbar_wait(empty + s, phase ^ 1)) { *failed = 1; atomicExch(&g_gemm_error, 1); break; }
+      mbar_expect_tx(full + s, STAGE_BYTES);
+      unsigned char* stage = smem + s * STAGE_BYTES;
+      const int k = (kb_begin + i) * BK;
+      tma_load_2d(stage, &map_rows, full + s, k, row0);
+      tma_load_2d(stage + ROW_BYTES, &map_cols, full + s, k, col0);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------------------------------------------------------- tensor-core issue
+    constexpr uint32_t idesc = umma_idesc(BN);
+    bool ok = true;
+    for (int i = 0; i < num_kb && ok; ++i) {
+      const int s = i % STAGES;
+      const uint32_t phase = (i / STAGES) & 1;
+      if (!mbar_wait(full + s, phase)) { *failed = 1; atomicExch(&g_gemm_error, 2); ok = false; break; }
+      tcgen05_fence_after();
+      const uint32_t a_addr = smem_addr(smem + s * STAGE_BYTES), b_addr = a_addr + ROW_BYTES;
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; ++k)
+        umma_bf16(tmem_base, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, (i | k) != 0);
+      umma_commit(empty + s);
+    }
+    umma_commit(acc_full);   // arrives when every MMA issued so far has finished (also when none was issued)
+  }
+  __syncwarp();
+
+  // -------------------------------------------------------------------- epilogue
+  float* partial = reinterpret_cast<float*>(smem);   // swapped mode: [BN tokens][128 features] float, over the stage ring
+  if (warp >= 2) {
+    const int quarter = warp & 3;              // TMEM lanes this warp may read
+    const int row = quarter * 32 + lane;       // row of the tile = TMEM lane
+    bool ok = mbar_wait(acc_full, 0);
+    if (!ok) { *failed = 1; atomicExch(&g_gemm_error, 3); }
+    tcgen05_fence_after();
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    if (!SWAP) {
+      const int m = row0 + row;
+      OutT* crow = static_cast<OutT*>(p.c) + static_cast<size_t>(m) * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        float v[32];
+        if (ok && num_kb > 0) {
+          tmem_load_32(taddr + c, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        if (m < p.M) {
+          const int nb = col0 + c;
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += nb + j < p.N ? p.bias[nb + j] : 0.f;
+          }
+          if (p.vector_ok && nb + 32 <= p.N) {
+            store_row_32(crow + nb, v);     // 16-byte stores
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nb + j < p.N) store_out<OutT>(crow + nb + j, v[j]);
+          }
+        }
+      }
+    } else {
+      // lane = output feature, TMEM column = token.  Park the partial tile in shared memory.
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float v[16];
+        if (ok && num_kb > 0) {
+          tmem_load_16(taddr + c, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) partial[(c + j) * BM + row] = v[j];
+      }
+    }
+  }
+  if (SWAP) {
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned splits = cluster.num_blocks(), rank = cluster.block_rank();
+    cluster.sync();                                    // every CTA's partial tile is in its shared memory
+    if (rank == 0 && warp >= 2) {
+      const int quarter = warp & 3, row = quarter * 32 + lane;
+      const int n = row0 + row;
+      if (n < p.N) {
+        const float b = p.bias ? p.bias[n] : 0.f;
+        for (int m = 0; m < p.M; ++m) {
+          float acc = partial[m * BM + row];
+          for (unsigned r = 1; r < splits; ++r) acc += cluster.map_shared_rank(partial, r)[m * BM + row];
+          store_out<OutT>(static_cast<OutT*>(p.c) + static_cast<size_t>(m) * p.ldc + n, acc + b);
+        }
+      }
+    }
+    cluster.sync();                                    // nobody leaves while its memory may still be read
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------ host side
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_fn() {
+  static EncodeTiled fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) == cudaSuccess &&
+        status == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(ptr);
+  }
+  return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] matrix, box = [box_rows, 64 columns], 128-byte swizzle
+static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
+  EncodeTiled fn = encode_fn();
+  if (!fn) return 10005;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 10006;
+}
+
+template <int BN, int STAGES, bool SWAP, typename OutT>
+static int launch(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, dim3 grid, int cluster_y, cudaStream_t stream) {
+  constexpr size_t smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+  static_assert(!SWAP || STAGES * (BM * BK * 2 + BN * BK * 2) >= BN * BM * 4, "partial tile must fit in the stage ring");
+  auto kernel = gemm_tcgen05_kernel<BN, STAGES, SWAP, OutT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = cluster_y;
+  attr[0].val.clusterDim.z = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, rows, cols, p);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Read and clear the error flag set by a bounded wait that ran out (0: none; 1: producer,
+// 2: tensor-core issue, 3: epilogue).  Synchronises the device.
+extern "C" int b200_gemm_tcgen05_error() {
+  int v = 0, zero = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int));
+  cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+  return v;
+}
+
+// C[M,N] (ldc) = A[M,K] * W[N,K]^T + bias; out_f32 selects float or bfloat16 output.
+// K must be a multiple of 8 and both bases 16-byte aligned (TMA); refused otherwise.
+// splits > 0 selects the swapped kernel for M <= 64 with the K range cut into `splits` (1..8) parts.
+extern "C" int b200_gemm_tcgen05(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
+                                 int out_f32, int splits, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || ldc < N) return B200_ERR_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return B200_ERR_BAD_SIZE;
+  GemmParams p{C, bias, M, N, K, ldc, (ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0, 0};
+  CUtensorMap rows, cols;
+  const int total_kb = (K + BK - 1) / BK;
+  if (splits > 0) {
+    if (M > 64 || splits > 8) return B200_ERR_BAD_SIZE;
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    if (int e = make_map(&rows, W, N, K, BM)) return e;
+    if (int e = make_map(&cols, A, M, K, bn)) return e;
+    p.kb_per_split = (total_kb + splits - 1) / splits;
+    dim3 grid((N + BM - 1) / BM, splits);
+#define B200_SWAP(BN_)                                                                               \
+  return out_f32 ? launch<BN_, 8, true, float>(rows, cols, p, grid, splits, stream)                 \
+                 : launch<BN_, 8, true, __nv_bfloat16>(rows, cols, p, grid, splits, stream)
+    if (bn == 16) { B200_SWAP(16); }
+    if (bn == 32) { B200_SWAP(32); }
+    B200_SWAP(64);
+#undef B200_SWAP
+  }
+  constexpr int BN = 256;
+  if (int e = make_map(&rows, A, M, K, BM)) return e;
+  if (int e = make_map(&cols, W, N, K, BN)) return e;
+  dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN);
+  if (grid.y > 65535) return B200_ERR_TOO_LARGE;
+  return out_f32 ? launch<BN, 4, false, float>(rows, cols, p, grid, 1, stream)
+                 : launch<BN, 4, false, __nv_bfloat16>(rows, cols, p, grid, 1, stream);
+}

@@ -1,0 +1,71 @@
+"""bfloat16 projections on the 5th-generation tensor cores (tcgen05, TMEM, TMA)."""
+
+from __future__ import annotations
+
+import torch
+
+from ..errors import KernelError
+from . import native
+from .native import c_int, c_void_p
+
+native.register_library(
+    "b200_gemm_tcgen05", ("gemm_tcgen05.cu",),
+    {
+        "b200_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "b200_gemm_tcgen05_error": [],
+    },
+)
+
+SMALL_M = 64          # up to here the weight is the row operand ("swapped")
+_SM_COUNT = 148
+
+
+def supported(m: int, n: int, k: int) -> bool:
+    """TMA needs rows that start on 16-byte boundaries: K a multiple of 8."""
+
+    return k % 8 == 0 and m > 0 and n > 0
+
+
+def pick_splits(m: int, n: int, k: int) -> int:
+    """Parts the K range is cut into (a cluster of that many CTAs) so that a
+    small-M product still puts a CTA on every SM.  0: the large-M kernel."""
+
+    if m > SMALL_M:
+        return 0
+    tiles = -(-n // 128)
+    k_blocks = -(-k // 64)
+    splits = max(1, min(8, _SM_COUNT // tiles, k_blocks // 8))
+    return splits
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+           out_dtype: torch.dtype = torch.bfloat16, *, splits: int | None = None) -> torch.Tensor:
+    """``x @ weight.T (+ bias)``; float32 accumulation; bfloat16 or float32 output."""
+
+    native.require(x, "x", dtype=torch.bfloat16, dims=2)
+    native.require(weight, "weight", dtype=torch.bfloat16, dims=2)
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k:
+        raise KernelError(f"linear: x has width {k}, weight expects {weight.shape[1]}")
+    if not supported(m, n, k):
+        raise KernelError(f"tcgen05 projection needs K to be a multiple of 8, got {k}")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"unsupported output type {out_dtype}")
+    if bias is not None:
+        native.require(bias, "bias", dtype=torch.float32, shape=(n,))
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    if splits is None:
+        splits = pick_splits(m, n, k)
+    native.call("b200_gemm_tcgen05", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k, n,
+                1 if out_dtype == torch.float32 else 0, splits, native.stream_ptr())
+    return out
+
+
+def check_error() -> None:
+    """Synchronise and raise if a bounded wait inside the kernel ran out."""
+
+    code = native.query("b200_gemm_tcgen05_error")
+    if code:
+        where = {1: "producer", 2: "tensor-core issue", 3: "epilogue", -1: "device error"}.get(code, str(code))
+        raise KernelError(f"tcgen05 projection: a bounded wait ran out ({where})")
