@@ -14,26 +14,6 @@ namespace b200 {
 
 constexpr int kMaxChunks = 8;  // head_dim <= 256
 
-template <typename T> struct Vec;
-template <> struct Vec<float> {
-  static constexpr int n = 4;
-  using type = float4;
-  __device__ static void unpack(const type& v, float* f) { f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w; }
-};
-template <> struct Vec<__nv_bfloat16> {
-  static constexpr int n = 8;
-  using type = uint4;
-  __device__ static void unpack(const type& v, float* f) {
-    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 t = __bfloat1622float2(p[i]);
-      f[2 * i] = t.x;
-      f[2 * i + 1] = t.y;
-    }
-  }
-};
-
 template <typename T>
 __global__ void __launch_bounds__(128)
 paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_pool,

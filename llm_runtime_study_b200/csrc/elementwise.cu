@@ -71,6 +71,22 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
   out[row * inter + i] = from_float<T>(s * u);
 }
 
+// 16-byte loads and stores when the row width allows it
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+  constexpr int VN = Vec<T>::n;
+  using V = typename Vec<T>::type;
+  const size_t row = blockIdx.y;
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VN;
+  if (i >= inter) return;
+  float g[VN], u[VN];
+  Vec<T>::unpack(*reinterpret_cast<const V*>(gate_up + row * 2 * inter + i), g);
+  Vec<T>::unpack(*reinterpret_cast<const V*>(gate_up + row * 2 * inter + inter + i), u);
+#pragma unroll
+  for (int e = 0; e < VN; ++e) g[e] = g[e] / (1.f + expf(-g[e])) * u[e];
+  *reinterpret_cast<V*>(out + row * inter + i) = Vec<T>::pack(g);
+}
+
 // ------------------------------- q/k norm + rotary + paged K/V write (fused)
 // qkv row layout: [q heads | k heads | v heads], each head `d` wide.
 // One block per token; each warp takes heads in turn.
@@ -187,10 +203,18 @@ extern "C" int b200_silu_mul(const void* gate_up, void* out, int n, int inter, i
                              cudaStream_t stream) {
   if (n <= 0) return 0;
   if (inter <= 0) return B200_ERR_BAD_SIZE;
-  dim3 grid((inter + 255) / 256, n);
-  B200_DISPATCH_DTYPE(dtype, T,
-      silu_mul_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(gate_up),
-                                                   static_cast<T*>(out), inter));
+  if (n > 65535) return B200_ERR_TOO_LARGE;
+  B200_DISPATCH_DTYPE(dtype, T, {
+    constexpr int VN = Vec<T>::n;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    if (inter % VN == 0 && aligned) {
+      dim3 grid((inter / VN + 255) / 256, n);
+      silu_mul_vec_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(gate_up), static_cast<T*>(out), inter);
+    } else {
+      dim3 grid((inter + 255) / 256, n);
+      silu_mul_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(gate_up), static_cast<T*>(out), inter);
+    }
+  });
   return launch_status();
 }
 

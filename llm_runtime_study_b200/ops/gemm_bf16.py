@@ -16,6 +16,12 @@ native.register_library(
     },
 )
 
+native.register_library(
+    "b200_gemm_skinny", ("gemm_skinny.cu",),
+    {"b200_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]},
+)
+
+SKINNY_M = 16         # up to here weights are streamed straight into mma.sync fragments
 SMALL_M = 64          # up to here the weight is the row operand ("swapped")
 _SM_COUNT = 148
 
@@ -69,3 +75,23 @@ def check_error() -> None:
     if code:
         where = {1: "producer", 2: "tensor-core issue", 3: "epilogue", -1: "device error"}.get(code, str(code))
         raise KernelError(f"tcgen05 projection: a bounded wait ran out ({where})")
+
+
+def linear_skinny(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+                  out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``x @ weight.T (+ bias)`` for at most 16 rows of ``x``: the weight-streaming kernel."""
+
+    native.require(x, "x", dtype=torch.bfloat16, dims=2)
+    native.require(weight, "weight", dtype=torch.bfloat16, dims=2)
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k:
+        raise KernelError(f"linear: x has width {k}, weight expects {weight.shape[1]}")
+    if m > SKINNY_M or k % 8:
+        raise KernelError(f"the weight-streaming kernel takes at most {SKINNY_M} rows and K a multiple of 8; got {m}, {k}")
+    if bias is not None:
+        native.require(bias, "bias", dtype=torch.float32, shape=(n,))
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    native.call("b200_gemm_skinny", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k, n,
+                1 if out_dtype == torch.float32 else 0, native.stream_ptr())
+    return out

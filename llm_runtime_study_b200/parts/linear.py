@@ -2,10 +2,13 @@
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..errors import KernelError
 from ..ops import functional as F
+from ..ops import gemm_bf16
 from .base import Runtime
 
 
@@ -13,11 +16,17 @@ class Projection:
     """One weight matrix (possibly several checkpoint tensors stacked along the
     output axis, so that q/k/v or gate/up are one product) and an optional bias.
 
-    float32 runtime: our FFMA kernel.  bfloat16 runtime: a library matrix product
-    with float32 accumulation (the reference's projections are ``nn.Linear``,
-    i.e. library products too: mini_llm/nn/attention.py:102-111), writing either
-    bfloat16 or float32.
+    float32 runtime: our FFMA kernel.  bfloat16 runtime, float32 accumulation,
+    bfloat16 or float32 output:
+      * up to 16 rows (decoding): our weight-streaming mma.sync kernel;
+      * more rows: our tcgen05/TMEM/TMA kernel when ``GEMM_BACKEND`` is "tcgen05",
+        else a library product (the reference's projections are ``nn.Linear``,
+        i.e. library products: mini_llm/nn/attention.py:102-111).
+    K must be a multiple of 8 for our bfloat16 kernels (16-byte rows); other
+    widths go to the library product.
     """
+
+    GEMM_BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_GEMM", "library")
 
     def __init__(self, weights: list[torch.Tensor], biases: list[torch.Tensor] | None, runtime: Runtime) -> None:
         self.runtime = runtime
@@ -39,6 +48,12 @@ class Projection:
             return F.linear_f32(x, self.weight, self.bias)
         if x.dtype != torch.bfloat16:
             raise KernelError(f"bfloat16 projection got {x.dtype} input")
+        m = x.shape[0]
+        if self.in_features % 8 == 0 and x.is_contiguous():
+            if m <= gemm_bf16.SKINNY_M:
+                return gemm_bf16.linear_skinny(x, self.weight, self.bias, out_dtype)
+            if self.GEMM_BACKEND == "tcgen05":
+                return gemm_bf16.linear(x, self.weight, self.bias, out_dtype, splits=0)
         if out_dtype == torch.bfloat16:
             y = torch.mm(x, self.weight.t())
         else:

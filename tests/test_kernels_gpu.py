@@ -333,3 +333,55 @@ def test_masked_cache_rows_may_hold_anything():
     last = _mma().decode_attention(dev(q[-1:]), dev(kp), dev(vp), kv_len=dev(torch.tensor([37], dtype=torch.int32)),
                                    block_table=dev(table), scale=1 / math.sqrt(d), splits=2)
     torch.testing.assert_close(last.cpu().double(), want[-1:], **BF16_TOL)
+
+
+# ------------------------------------------------------------ bfloat16 projections
+def _gemm():
+    from llm_runtime_study_b200.ops import gemm_bf16
+
+    return gemm_bf16
+
+
+def _gemm_case(m, n, k, bias, seed=7):
+    torch.manual_seed(seed)
+    x = torch.randn(m, k).bfloat16()
+    w = (torch.randn(n, k) * 0.05).bfloat16()
+    b = torch.randn(n) if bias else None
+    want = x.double() @ w.double().T + (b.double() if bias else 0)
+    return x, w, b, want
+
+
+@pytest.mark.parametrize("m,n,k,bias", [(1, 136, 4096, False), (8, 4096, 4096, True), (3, 1000, 520, True),
+                                        (16, 272, 96, False), (9, 503, 12288, False), (5, 17, 8, True)])
+@pytest.mark.parametrize("out", [torch.float32, torch.bfloat16])
+def test_weight_streaming_projection(m, n, k, bias, out):
+    x, w, b, want = _gemm_case(m, n, k, bias)
+    got = _gemm().linear_skinny(dev(x), dev(w), dev(b) if bias else None, out)
+    again = _gemm().linear_skinny(dev(x), dev(w), dev(b) if bias else None, out)
+    assert torch.equal(got, again)                                   # fixed summation order
+    scale = float(want.abs().max())
+    torch.testing.assert_close(got.cpu().double(), want, atol=(1e-2 if out == torch.bfloat16 else 1e-5) * scale, rtol=0)
+    alone = _gemm().linear_skinny(dev(x[:1]), dev(w), dev(b) if bias else None, out)
+    assert torch.equal(alone[0], got[0])                             # a row does not depend on the batch
+
+
+@pytest.mark.parametrize("m,n,k,bias,splits", [
+    (128, 256, 64, False, 0), (130, 264, 72, True, 0), (300, 1000, 520, True, 0), (2048, 1024, 4096, False, 0),
+    (8, 4096, 4096, False, 4), (1, 136, 4096, True, 3), (64, 1000, 512, False, 1), (33, 640, 1024, True, 2)])
+@pytest.mark.parametrize("out", [torch.float32, torch.bfloat16])
+def test_tcgen05_projection(m, n, k, bias, splits, out):
+    x, w, b, want = _gemm_case(m, n, k, bias)
+    got = _gemm().linear(dev(x), dev(w), dev(b) if bias else None, out, splits=splits)
+    _gemm().check_error()
+    scale = float(want.abs().max())
+    torch.testing.assert_close(got.cpu().double(), want, atol=(1e-2 if out == torch.bfloat16 else 2e-5) * scale, rtol=0)
+
+
+def test_projections_refuse_unaligned_widths():
+    from llm_runtime_study_b200.errors import KernelError
+
+    x, w = torch.zeros(2, 12, device="cuda").bfloat16(), torch.zeros(4, 12, device="cuda").bfloat16()
+    with pytest.raises(KernelError, match="multiple of 8"):
+        _gemm().linear_skinny(x, w)
+    with pytest.raises(KernelError, match="multiple of 8"):
+        _gemm().linear(x, w)
