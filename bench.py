@@ -160,9 +160,15 @@ def run_ours(args) -> dict:
         manager.release(request)
 
     prompt = ids(PREFILL_TOKENS)
-    for _ in range(max(args.warmup, 3)):
-        one_prefill()
-    prefill_ms = statistics.median(timed(one_prefill, 1) for _ in range(5))
+    if args.only == "prefill":  # profiling aid: nothing but prefills of one prompt
+        for _ in range(max(args.warmup, 1)):
+            one_prefill()
+        return {"only": "prefill", "layers": layers, "ms": round(timed(one_prefill, args.steps), 3)}
+    prefill_ms = 0.0
+    if args.only != "decode":
+        for _ in range(max(args.warmup, 3)):
+            one_prefill()
+        prefill_ms = statistics.median(timed(one_prefill, 1) for _ in range(5))
 
     # -------------------------------------------------------------- decode
     def decode_point(batch, steps, warmup, sample_clocks=False):
@@ -189,6 +195,9 @@ def run_ours(args) -> dict:
             manager.release(request)
         return ms, launches, info
 
+    if args.only == "decode":   # profiling aid: nothing but the decode steps of one batch size
+        ms, launches, _ = decode_point(args.batch, args.steps, args.warmup)
+        return {"only": "decode", "layers": layers, "batch": args.batch, "ms_per_step": round(ms, 4), "gpu_launches": launches}
     ms_b8, launches, clocks = decode_point(args.batch, args.steps, args.warmup, sample_clocks=True)
     ms_b1, _, _ = decode_point(1, args.steps, args.warmup)
     ms_b64, _, _ = decode_point(64, args.steps, args.warmup)
@@ -245,8 +254,132 @@ def run_ours(args) -> dict:
     }
 
 
+class _IdsTokenizer:
+    """Stands in for the tokenizer files, which cannot be had offline: a prompt's
+    "text" is its token ids separated by spaces.  It implements the reference's
+    ``RuntimeTokenizer`` protocol (mini_llm/tokenizer.py:27-41) and is the only
+    object on the reference arm that is not the reference's own."""
+
+    def encode(self, text):
+        return [int(t) for t in text.split()]
+
+    def decode(self, token_ids, *, skip_special_tokens=False):
+        return " ".join(str(t) for t in token_ids)
+
+    def format_chat(self, messages, *, enable_thinking=False):
+        return messages[-1].content
+
+
 def run_reference(args) -> dict:
-    return {"impl": "reference", "unavailable": "reference install not attempted yet"}
+    """The unmodified reference from baseline/_ref: its own Qwen3ForCausalLM, paged cache,
+    CUDA-graph decode and BatchScheduler, driven through Engine.create_scheduler()."""
+
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "mini_llm")):
+        return {"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}
+    sys.path.insert(0, ref)
+    try:
+        import torch
+
+        from mini_llm.config import Qwen3Config
+        from mini_llm.engine import Engine
+        from mini_llm.model.qwen import Qwen3ForCausalLM
+        from mini_llm.tokenizer import ChatMessage
+
+        cfg = dict(QWEN3_8B)
+        layers = args.layers or cfg["num_hidden_layers"]
+        full_layers = cfg["num_hidden_layers"]
+        cfg["num_hidden_layers"] = layers
+        config = Qwen3Config.from_dict({**cfg, "attention_dropout": 0.0})
+        device = torch.device("cuda", 0)
+        torch.cuda.set_device(0)
+        with torch.device("meta"):
+            model = Qwen3ForCausalLM(config)
+        model.to_empty(device=device)
+        generator = torch.Generator(device=device).manual_seed(0)
+        with torch.no_grad():
+            for name, parameter in model.named_parameters():
+                values = torch.empty(parameter.shape, dtype=torch.float32, device=device)
+                if name.endswith("norm.weight") or "layernorm" in name:
+                    values.normal_(1.0, 0.05, generator=generator)
+                else:
+                    values.normal_(0.0, 0.02, generator=generator)
+                parameter.data = values.to(torch.bfloat16)
+        model.materialize_derived_buffers(device)
+        model.eval().requires_grad_(False)
+        host = torch.Generator().manual_seed(0)
+
+        def prompt(n):
+            ids = torch.randint(0, cfg["vocab_size"], (n,), generator=host).tolist()
+            return [ChatMessage(role="user", content=" ".join(str(t) for t in ids))]
+
+        def engine_for(batch):
+            return Engine(model=model, tokenizer=_IdsTokenizer(), device=device, dtype=torch.bfloat16,
+                          max_seq_len=cfg["max_position_embeddings"], load_seconds=0.0, max_batch_size=batch)
+
+        def decode_rate(batch, steps, warmup):
+            scheduler = engine_for(batch).create_scheduler()
+            for _ in range(batch):
+                scheduler.add_request(prompt(CONTEXT), max_new_tokens=1024)
+            while scheduler.num_waiting:
+                scheduler.step()
+            for _ in range(max(warmup, 3)):
+                scheduler.step()
+            torch.cuda.synchronize()
+            started = time.perf_counter()
+            produced = 0
+            for _ in range(steps):
+                produced += len(scheduler.step())
+            torch.cuda.synchronize()
+            seconds = time.perf_counter() - started
+            scheduler.abort_all()
+            return produced / seconds, seconds / steps * 1e3
+
+        def prefill_ms():
+            times = []
+            for _ in range(max(args.warmup, 3) + 5):
+                scheduler = engine_for(1).create_scheduler()
+                scheduler.add_request(prompt(PREFILL_TOKENS), max_new_tokens=1)
+                torch.cuda.synchronize()
+                started = time.perf_counter()
+                scheduler.step()
+                torch.cuda.synchronize()
+                times.append((time.perf_counter() - started) * 1e3)
+                scheduler.abort_all()
+            return statistics.median(times[-5:])
+
+        pre = prefill_ms()
+        clocks = ClockSampler()
+        rate8, ms8 = decode_rate(args.batch, args.steps, args.warmup)
+        clock_info = clocks.stop()
+        rate1, _ = decode_rate(1, args.steps, args.warmup)
+        rate64, _ = decode_rate(64, args.steps, args.warmup)
+        pk = peaks()
+        step_bytes = model_bytes(cfg, layers) + args.batch * CONTEXT * kv_bytes_per_token(cfg, layers)
+        achieved = step_bytes / (ms8 * 1e-3) / 1e9
+        flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
+        return {
+            "metric": "decode tok/s at batch 8 (2,048 cached tokens each), Qwen3-8B shape", "impl": "reference",
+            "value": round(rate8, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms8, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic: random weights, uniform random token ids",
+            "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_full": full_layers, "global_batch": args.batch,
+                       "seq_len": CONTEXT, "context_limit": cfg["max_position_embeddings"], "page_size": 16,
+                       "parallelism": "none (1 GPU)", "cuda_graph": True,
+                       "timing": "wall clock around BatchScheduler.step, synchronised", "peaks": pk["source"]},
+            "e2e": {"value": round(rate8, 1), "unit": "tokens/s", "h2d_bytes_per_step": args.batch * 8 * 2,
+                    "d2h_bytes_per_step": args.batch * 8},
+            "gpu_launches": 0,
+            "prefill": {"value": round(PREFILL_TOKENS / (pre * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre, 3),
+                        "frac": round(flops / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / pk["hbm_gbs"], 4)},
+            "points": {"decode_b1": round(rate1, 1), "decode_b64": round(rate64, 1)},
+            "clocks": clock_info,
+        }
+    except Exception as exc:  # the reference or one of its dependencies does not run here
+        reason = f"{type(exc).__name__}: {exc}".splitlines()[0][:300]
+        return {"impl": "reference", "unavailable": reason}
 
 
 def main() -> int:
@@ -257,6 +390,8 @@ def main() -> int:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
+    parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
+                        help="run only the decode steps or only the prefill (for profiler captures of a small case)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: --gpus {args.gpus} is not supported by this engine (single-GPU tier)")

@@ -30,6 +30,27 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]) * scale;
 }
 
+// 16-byte loads of the table row, two 16-byte stores of floats per load
+template <typename T>
+__global__ void embedding_vec_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                     float* __restrict__ out, int hidden, int vocab, float scale) {
+  constexpr int VN = Vec<T>::n;
+  using V = typename Vec<T>::type;
+  const int row = blockIdx.x;
+  const int id = ids[row];
+  const bool ok = id >= 0 && id < vocab;
+  const T* src = table + static_cast<size_t>(ok ? id : 0) * hidden;
+  float* dst = out + static_cast<size_t>(row) * hidden;
+  for (int i = threadIdx.x * VN; i < hidden; i += blockDim.x * VN) {
+    float f[VN];
+    Vec<T>::unpack(*reinterpret_cast<const V*>(src + i), f);
+#pragma unroll
+    for (int e = 0; e < VN; e += 4)
+      *reinterpret_cast<float4*>(dst + i + e) =
+          ok ? make_float4(f[e] * scale, f[e + 1] * scale, f[e + 2] * scale, f[e + 3] * scale) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
 // ------------------------------------------------- residual add + RMS norm
 // x = resid[src] (+ delta[src]);  if write_resid: resid[src] = x
 // out[row] = x * rsqrt(mean(x^2) + eps) * weight
@@ -57,6 +78,54 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const float* __res
   OutT* dst = out + static_cast<size_t>(row) * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x)
     dst[i] = from_float<OutT>(x[i] * r * weight[i]);
+}
+
+// Rows up to 4 * VPT * blockDim wide stay in registers: all loads are issued before any
+// store, 16 bytes at a time.  The order of the sum depends on the width and the block
+// size only.
+template <typename OutT, int VPT>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const float* __restrict__ delta,
+                                       const float* __restrict__ weight, OutT* __restrict__ out,
+                                       const int* __restrict__ rows, int hidden, float eps, int write_resid) {
+  __shared__ float scratch[32];
+  const int row = blockIdx.x;
+  const size_t src = static_cast<size_t>(rows ? rows[row] : row) * hidden;
+  const int nvec = hidden >> 2;
+  float4 x[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = threadIdx.x + v * blockDim.x;
+    x[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < nvec) {
+      x[v] = *reinterpret_cast<const float4*>(resid + src + 4 * i);
+      if (delta) {
+        const float4 d = *reinterpret_cast<const float4*>(delta + src + 4 * i);
+        x[v].x += d.x; x[v].y += d.y; x[v].z += d.z; x[v].w += d.w;
+      }
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) ss += x[v].x * x[v].x + x[v].y * x[v].y + x[v].z * x[v].z + x[v].w * x[v].w;
+  const float r = rsqrtf(block_sum(ss, scratch) / static_cast<float>(hidden) + eps);
+  OutT* dst = out + static_cast<size_t>(row) * hidden;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = threadIdx.x + v * blockDim.x;
+    if (i >= nvec) continue;
+    if (write_resid) *reinterpret_cast<float4*>(resid + src + 4 * i) = x[v];
+    const float4 w = *reinterpret_cast<const float4*>(weight + 4 * i);
+    const float y[4] = {x[v].x * r * w.x, x[v].y * r * w.y, x[v].z * r * w.z, x[v].w * r * w.w};
+    if constexpr (sizeof(OutT) == 4) {
+      *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(y[0], y[1], y[2], y[3]);
+    } else {
+      uint2 packed;
+      __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+      packed.x = *reinterpret_cast<uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(dst + 4 * i) = packed;
+    }
+  }
 }
 
 // ------------------------------------------------------------------ SiLU * up
@@ -88,79 +157,95 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict
 }
 
 // ------------------------------- q/k norm + rotary + paged K/V write (fused)
-// qkv row layout: [q heads | k heads | v heads], each head `d` wide.
-// One block per token; each warp takes heads in turn.
+// qkv row layout: [q heads | k heads | v heads], each head `d` wide.  One warp per
+// (token, head), everything in registers: a lane owns the rotation pairs (j, j + half)
+// for j = lane, lane + 32, ... and the unrotated tail columns lane-strided.
+constexpr int kMaxPairs = 4;   // rotary_dim / 2 <= 128
+constexpr int kMaxTail = 8;    // head_dim <= 256
+
 template <typename T>
-__global__ void qk_norm_rope_write_kernel(
+__global__ void __launch_bounds__(128) qk_norm_rope_write_kernel(
     const T* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ q_weight,
     const float* __restrict__ k_weight, float eps, const float* __restrict__ inv_freq,
     int rotary_dim, const int* __restrict__ positions, const int* __restrict__ token_entry,
     const int* __restrict__ block_table, int table_stride, int page_size,
     T* __restrict__ k_pool, T* __restrict__ v_pool, int nq, int nkv, int d, int qkv_stride) {
-  extern __shared__ float smem[];
-  const int half = rotary_dim / 2;
-  float* cs = smem;                 // [half] cos
-  float* sn = smem + half;          // [half] sin
-  float* work = smem + 2 * half;    // [warps][d]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int token = blockIdx.x;
+  const int h = blockIdx.y * 4 + warp;
+  if (h >= nq + 2 * nkv) return;
+  const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
   const int pos = positions[token];
-  if (inv_freq) {
-    for (int j = threadIdx.x; j < half; j += blockDim.x) {
-      const float angle = static_cast<float>(pos) * inv_freq[j];
-      float s, c;
-      sincosf(angle, &s, &c);
-      cs[j] = c;
-      sn[j] = s;
-    }
-  }
-  __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  float* x = work + warp * d;
-  const T* row = qkv + static_cast<size_t>(token) * qkv_stride;
-
-  int64_t kv_base = -1;  // element offset of this token's slot for kv head 0
-  if (nkv > 0) {
+  const T* src = qkv + static_cast<size_t>(token) * qkv_stride + static_cast<size_t>(h) * d;
+  T* dst;
+  if (is_q) {
+    dst = q_out + (static_cast<size_t>(token) * nq + h) * d;
+  } else {
     const int page = block_table[static_cast<size_t>(token_entry[token]) * table_stride + pos / page_size];
-    if (page >= 0)
-      kv_base = (static_cast<int64_t>(page) * nkv * page_size + pos % page_size) * d;
+    if (page < 0) return;
+    const int kvh = is_k ? h - nq : h - nq - nkv;
+    dst = (is_k ? k_pool : v_pool) +
+          ((static_cast<int64_t>(page) * nkv + kvh) * page_size + pos % page_size) * static_cast<int64_t>(d);
   }
-
-  for (int h = warp; h < nq + 2 * nkv; h += nwarps) {
-    const T* src = row + static_cast<size_t>(h) * d;
-    const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
-    const float* w = is_q ? q_weight : (is_k ? k_weight : nullptr);
-    float ss = 0.f;
-    for (int i = lane; i < d; i += 32) {
-      const float v = to_float(src[i]);
-      x[i] = v;
-      ss += v * v;
+  const bool rotate = inv_freq != nullptr && (is_q || is_k);
+  const int half = rotate ? rotary_dim / 2 : 0;
+  const int tail0 = 2 * half;
+  float lo[kMaxPairs], hi[kMaxPairs], tail[kMaxTail];
+  float ss = 0.f;
+#pragma unroll
+  for (int p = 0; p < kMaxPairs; ++p) {
+    const int j = lane + 32 * p;
+    lo[p] = hi[p] = 0.f;
+    if (j < half) {
+      lo[p] = to_float(src[j]);
+      hi[p] = to_float(src[j + half]);
+      ss += lo[p] * lo[p] + hi[p] * hi[p];
     }
+  }
+#pragma unroll
+  for (int q = 0; q < kMaxTail; ++q) {
+    const int i = tail0 + lane + 32 * q;
+    tail[q] = 0.f;
+    if (i < d) {
+      tail[q] = to_float(src[i]);
+      ss += tail[q] * tail[q];
+    }
+  }
+  const float* w = is_q ? q_weight : (is_k ? k_weight : nullptr);
+  const float r = w ? rsqrtf(warp_sum(ss) / static_cast<float>(d) + eps) : 1.f;
+#pragma unroll
+  for (int p = 0; p < kMaxPairs; ++p) {
+    const int j = lane + 32 * p;
+    if (j >= half) continue;
+    float a = lo[p], b = hi[p];
     if (w) {
-      ss = warp_sum(ss);
-      const float r = rsqrtf(ss / static_cast<float>(d) + eps);
-      __syncwarp();
-      for (int i = lane; i < d; i += 32) x[i] = x[i] * r * w[i];
+      a *= r * w[j];
+      b *= r * w[j + half];
     }
-    __syncwarp();
-    T* dst;
-    if (is_q) {
-      dst = q_out + (static_cast<size_t>(token) * nq + h) * d;
-    } else {
-      if (kv_base < 0) continue;
-      const int kvh = is_k ? h - nq : h - nq - nkv;
-      dst = (is_k ? k_pool : v_pool) + kv_base + static_cast<int64_t>(kvh) * page_size * d;
-    }
-    const bool rotate = inv_freq && (is_q || is_k);
-    for (int i = lane; i < d; i += 32) {
-      float v = x[i];
-      if (rotate && i < rotary_dim) {
-        if (i < half) v = x[i] * cs[i] - x[i + half] * sn[i];
-        else          v = x[i] * cs[i - half] + x[i - half] * sn[i - half];
-      }
-      dst[i] = from_float<T>(v);
-    }
-    __syncwarp();
+    float sn, cs;
+    sincosf(static_cast<float>(pos) * inv_freq[j], &sn, &cs);
+    dst[j] = from_float<T>(a * cs - b * sn);
+    dst[j + half] = from_float<T>(b * cs + a * sn);
   }
+#pragma unroll
+  for (int q = 0; q < kMaxTail; ++q) {
+    const int i = tail0 + lane + 32 * q;
+    if (i >= d) continue;
+    dst[i] = from_float<T>(w ? tail[q] * r * w[i] : tail[q]);
+  }
+}
+
+template <typename T>
+static void launch_norm_vec(float* resid, const float* delta, const float* weight, T* out, const int* rows, int n,
+                            int hidden, float eps, int write_resid, cudaStream_t stream) {
+  const int nvec = hidden / 4;
+  if (nvec <= 128) add_rmsnorm_vec_kernel<T, 1><<<n, 128, 0, stream>>>(resid, delta, weight, out, rows, hidden, eps, write_resid);
+  else if (nvec <= 256) add_rmsnorm_vec_kernel<T, 1><<<n, 256, 0, stream>>>(resid, delta, weight, out, rows, hidden, eps, write_resid);
+  else if (nvec <= 512) add_rmsnorm_vec_kernel<T, 2><<<n, 256, 0, stream>>>(resid, delta, weight, out, rows, hidden, eps, write_resid);
+  else if (nvec <= 1024) add_rmsnorm_vec_kernel<T, 4><<<n, 256, 0, stream>>>(resid, delta, weight, out, rows, hidden, eps, write_resid);
+  else if (nvec <= 2048) add_rmsnorm_vec_kernel<T, 4><<<n, 512, 0, stream>>>(resid, delta, weight, out, rows, hidden, eps, write_resid);
+  else if (nvec <= 4096) add_rmsnorm_vec_kernel<T, 4><<<n, 1024, 0, stream>>>(resid, delta, weight, out, rows, hidden, eps, write_resid);
+  else add_rmsnorm_vec_kernel<T, 8><<<n, 1024, 0, stream>>>(resid, delta, weight, out, rows, hidden, eps, write_resid);
 }
 
 }  // namespace b200
@@ -172,9 +257,13 @@ extern "C" int b200_embedding(const int* ids, const void* table, float* out, int
   if (n <= 0) return 0;
   if (hidden <= 0 || vocab <= 0) return B200_ERR_BAD_SIZE;
   const int threads = hidden >= 1024 ? 256 : 128;
-  B200_DISPATCH_DTYPE(dtype, T,
-      embedding_kernel<T><<<n, threads, 0, stream>>>(ids, static_cast<const T*>(table), out,
-                                                      hidden, vocab, scale));
+  const bool aligned = ((reinterpret_cast<uintptr_t>(table) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  B200_DISPATCH_DTYPE(dtype, T, {
+    if (aligned && hidden % Vec<T>::n == 0)
+      embedding_vec_kernel<T><<<n, threads, 0, stream>>>(ids, static_cast<const T*>(table), out, hidden, vocab, scale);
+    else
+      embedding_kernel<T><<<n, threads, 0, stream>>>(ids, static_cast<const T*>(table), out, hidden, vocab, scale);
+  });
   return launch_status();
 }
 
@@ -183,6 +272,13 @@ extern "C" int b200_add_rmsnorm(float* resid, const float* delta, const float* w
                                 int out_dtype, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (hidden <= 0) return B200_ERR_BAD_SIZE;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(resid) | reinterpret_cast<uintptr_t>(delta) |
+                         reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  if (aligned && hidden % 4 == 0 && hidden <= 4 * 8 * 1024) {
+    B200_DISPATCH_DTYPE(out_dtype, T,
+        launch_norm_vec<T>(resid, delta, weight, static_cast<T*>(out), rows, n, hidden, eps, write_resid, stream));
+    return launch_status();
+  }
   const size_t smem = (static_cast<size_t>(hidden) + 32) * sizeof(float);
   if (smem > 200 * 1024) return B200_ERR_TOO_LARGE;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
@@ -227,11 +323,11 @@ extern "C" int b200_qk_norm_rope_write(
   if (d <= 0 || nq < 0 || nkv < 0 || rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) ||
       page_size <= 0)
     return B200_ERR_BAD_SIZE;
-  const int warps = 4;
-  const size_t smem = (static_cast<size_t>(rotary_dim) + static_cast<size_t>(warps) * d) * sizeof(float);
-  if (smem > 48 * 1024) return B200_ERR_TOO_LARGE;
+  if (rotary_dim / 2 > 32 * kMaxPairs || d > 32 * kMaxTail) return B200_ERR_TOO_LARGE;
+  dim3 grid(n, (nq + 2 * nkv + 3) / 4);
+  if (grid.y > 65535) return B200_ERR_TOO_LARGE;
   B200_DISPATCH_DTYPE(dtype, T,
-      qk_norm_rope_write_kernel<T><<<n, warps * 32, smem, stream>>>(
+      qk_norm_rope_write_kernel<T><<<grid, 128, 0, stream>>>(
           static_cast<const T*>(qkv), static_cast<T*>(q_out), q_weight, k_weight, eps, inv_freq,
           rotary_dim, positions, token_entry, block_table, table_stride, page_size,
           static_cast<T*>(k_pool), static_cast<T*>(v_pool), nq, nkv, d, qkv_stride));

@@ -69,12 +69,13 @@ constexpr int kParamWords = 6;
 
 __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, int ld, int vocab, const int* __restrict__ params,
-              int* __restrict__ out) {
+              int* __restrict__ out, int filtered_only) {
   __shared__ ArgMax arg_scratch[32];
   __shared__ float sum_scratch[32];
   const int row = blockIdx.x;
   const float* x = logits + static_cast<size_t>(row) * ld;
   const int* p = params + row * kParamWords;
+  if (filtered_only && !(__int_as_float(p[0]) != 0.f && ((p[1] > 0 && p[1] < vocab) || __int_as_float(p[2]) < 1.f))) return;
   const float temperature = __int_as_float(p[0]);
   const int top_k = p[1];
   const float top_p = __int_as_float(p[2]);
@@ -144,6 +145,67 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const int* __
   if (threadIdx.x == 0) out[row] = best.index;
 }
 
+// ---------------------------------------------------------------- two-stage selection
+// Rows without top_k / top_p need one pass only (argmax of the logits, or of the logits
+// plus Gumbel noise), so the vocabulary is cut into `chunks` parts handled by different
+// CTAs; the second stage picks the best of the partial results.  Rows with filters take
+// the single-CTA kernel above.
+__device__ __forceinline__ bool row_is_filtered(const int* p, int vocab) {
+  const float temperature = __int_as_float(p[0]);
+  return temperature != 0.f && ((p[1] > 0 && p[1] < vocab) || __int_as_float(p[2]) < 1.f);
+}
+
+__global__ void __launch_bounds__(256)
+sample_partial_kernel(const float* __restrict__ logits, int ld, int vocab, const int* __restrict__ params,
+                      float* __restrict__ part_value, int* __restrict__ part_index, int chunks) {
+  __shared__ ArgMax arg_scratch[32];
+  __shared__ float sum_scratch[32];
+  const int row = blockIdx.y, chunk = blockIdx.x;
+  const int* p = params + row * kParamWords;
+  if (row_is_filtered(p, vocab)) return;
+  const float* x = logits + static_cast<size_t>(row) * ld;
+  const float temperature = __int_as_float(p[0]);
+  const uint64_t seed = (static_cast<uint64_t>(static_cast<uint32_t>(p[4])) << 32) | static_cast<uint32_t>(p[3]);
+  const uint64_t stream = splitmix64(seed ^ splitmix64(static_cast<uint64_t>(static_cast<uint32_t>(p[5]))));
+  const int per = (vocab + chunks - 1) / chunks;
+  const int begin = chunk * per, end = min(vocab, begin + per);
+  ArgMax best{-INFINITY, 0x7fffffff};
+  float bad = 0.f;
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    const float raw = x[i];
+    bad += isfinite(raw) ? 0.f : 1.f;
+    float v = raw;
+    if (temperature != 0.f) v = raw / temperature - logf(-logf(uniform23(stream, static_cast<uint32_t>(i))));
+    best = better(best, ArgMax{v, i});
+  }
+  best = block_argmax(best, arg_scratch);
+  bad = block_sum(bad, sum_scratch);
+  if (threadIdx.x == 0) {
+    part_value[row * chunks + chunk] = best.value;
+    part_index[row * chunks + chunk] = bad > 0.f ? -1 : best.index;
+  }
+}
+
+__global__ void sample_final_kernel(const float* __restrict__ part_value, const int* __restrict__ part_index,
+                                    const int* __restrict__ params, int vocab, int* __restrict__ out, int chunks) {
+  const int row = blockIdx.x;
+  if (row_is_filtered(params + row * kParamWords, vocab)) return;   // written by sample_kernel
+  ArgMax best{-INFINITY, 0x7fffffff};
+  bool bad = false;
+  for (int c = threadIdx.x; c < chunks; c += 32) {
+    const int index = part_index[row * chunks + c];
+    if (index < 0) bad = true;
+    else best = better(best, ArgMax{part_value[row * chunks + c], index});
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
+    best = better(best, other);
+  }
+  bad = __any_sync(0xffffffffu, bad);
+  if (threadIdx.x == 0) out[row] = bad ? -1 : best.index;
+}
+
 }  // namespace b200
 
 extern "C" int b200_sample(const float* logits, int ld, int vocab, const int* params, int* out,
@@ -151,6 +213,25 @@ extern "C" int b200_sample(const float* logits, int ld, int vocab, const int* pa
   if (rows <= 0) return 0;
   if (vocab <= 0 || ld < vocab) return B200_ERR_BAD_SIZE;
   const int threads = vocab >= 8192 ? 1024 : (vocab >= 1024 ? 256 : 128);
-  b200::sample_kernel<<<rows, threads, 0, stream>>>(logits, ld, vocab, params, out);
+  b200::sample_kernel<<<rows, threads, 0, stream>>>(logits, ld, vocab, params, out, 0);
+  return b200::launch_status();
+}
+
+// Two-stage variant.  `scratch` holds rows * chunks floats followed by rows * chunks ints;
+// `any_filtered` tells whether some row uses top_k / top_p (then the single-CTA kernel also
+// runs, for those rows only).
+extern "C" int b200_sample_chunked(const float* logits, int ld, int vocab, const int* params, int* out, int rows,
+                                   int chunks, void* scratch, int any_filtered, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || ld < vocab || chunks <= 0 || rows > 65535) return B200_ERR_BAD_SIZE;
+  float* part_value = static_cast<float*>(scratch);
+  int* part_index = reinterpret_cast<int*>(part_value + static_cast<size_t>(rows) * chunks);
+  dim3 grid(chunks, rows);
+  b200::sample_partial_kernel<<<grid, 256, 0, stream>>>(logits, ld, vocab, params, part_value, part_index, chunks);
+  b200::sample_final_kernel<<<rows, 32, 0, stream>>>(part_value, part_index, params, vocab, out, chunks);
+  if (any_filtered) {
+    const int threads = vocab >= 8192 ? 1024 : (vocab >= 1024 ? 256 : 128);
+    b200::sample_kernel<<<rows, threads, 0, stream>>>(logits, ld, vocab, params, out, 1);
+  }
   return b200::launch_status();
 }

@@ -15,9 +15,15 @@ from .config import SamplingConfig
 
 native.register_library(
     "b200_sampling", ("sampling.cu",),
-    {"b200_sample": [native.c_void_p, native.c_int, native.c_int, native.c_void_p, native.c_void_p,
-                     native.c_int, native.c_void_p]},
+    {
+        "b200_sample": [native.c_void_p, native.c_int, native.c_int, native.c_void_p, native.c_void_p,
+                        native.c_int, native.c_void_p],
+        "b200_sample_chunked": [native.c_void_p, native.c_int, native.c_int, native.c_void_p, native.c_void_p,
+                                native.c_int, native.c_int, native.c_void_p, native.c_int, native.c_void_p],
+    },
 )
+
+CHUNKS = 64   # parts a row's vocabulary is cut into for the one-pass selections
 
 PARAM_WORDS = 6
 _MASK64 = (1 << 64) - 1
@@ -57,6 +63,7 @@ class Sampler:
         self._dev = torch.empty(max_rows * PARAM_WORDS, dtype=torch.int32, device=device)
         self._out = torch.empty(max_rows, dtype=torch.int32, device=device)
         self._out_host = torch.empty(max_rows, dtype=torch.int32, pin_memory=True)
+        self._scratch = torch.empty(max_rows * CHUNKS * 2, dtype=torch.int32, device=device)
         self.max_rows = max_rows
 
     def sample(self, logits: torch.Tensor, rows: Sequence[tuple[SamplingConfig, int, int]]) -> list[int]:
@@ -75,8 +82,12 @@ class Sampler:
         packed = np.asarray([w for config, seed, counter in rows for w in pack_row(config, seed, counter)], dtype=np.int32)
         self._host[: packed.shape[0]].numpy()[:] = packed
         self._dev[: packed.shape[0]].copy_(self._host[: packed.shape[0]], non_blocking=True)
-        native.call("b200_sample", logits.data_ptr(), logits.stride(0), vocab, self._dev.data_ptr(),
-                    self._out.data_ptr(), n, native.stream_ptr())
+        filtered = any(c.temperature > 0 and ((c.top_k is not None and c.top_k < vocab) or c.top_p < 1.0)
+                       for c, _, _ in rows)
+        chunks = CHUNKS if vocab >= 4096 else 1
+        native.call("b200_sample_chunked", logits.data_ptr(), logits.stride(0), vocab, self._dev.data_ptr(),
+                    self._out.data_ptr(), n, chunks, self._scratch.data_ptr(), 1 if filtered else 0,
+                    native.stream_ptr(), launches=3 if filtered else 2)
         self._out_host[:n].copy_(self._out[:n], non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
         tokens = self._out_host[:n].tolist()

@@ -41,7 +41,7 @@ def test_embedding(dtype, hidden, vocab):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden", [1, 100, 4104, 13000])
+@pytest.mark.parametrize("hidden", [1, 100, 4102, 4104, 13000, 40000])
 def test_add_rmsnorm(dtype, hidden):
     torch.manual_seed(1)
     n, eps = 7, 3e-5
