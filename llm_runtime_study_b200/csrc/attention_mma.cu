@@ -185,6 +185,8 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(AttnParam
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* ks = reinterpret_cast<bf16*>(smem_raw);
   bf16* vs = ks + 2 * BN * LDS;
+  pdl_trigger();
+  pdl_wait();
   const int tile = blockIdx.x;
   const int kvh = blockIdx.y / p.slices, slice = blockIdx.y % p.slices;
   const int entry = p.tile_entry[tile], tok0 = p.tile_start[tile], ntok = p.tile_count[tile];
@@ -252,6 +254,8 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* ks = reinterpret_cast<bf16*>(smem_raw);
   bf16* vs = ks + 2 * BN * LDS;
+  pdl_trigger();
+  pdl_wait();
   const int split = blockIdx.x, b = blockIdx.z;
   const int kvh = blockIdx.y / p.slices, slice = blockIdx.y % p.slices;
   const int* table = p.block_table + static_cast<size_t>(b) * p.table_stride;
@@ -358,6 +362,8 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
 // grid (nq, requests), D threads: combine the splits of one (request, head)
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int nq, int num_splits) {
+  pdl_trigger();
+  pdl_wait();
   const long base = (static_cast<long>(blockIdx.y) * nq + blockIdx.x) * num_splits;
   float M = -INFINITY;
   for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
@@ -373,6 +379,7 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
   }
 }
 
+constexpr int kMergeThreads = D < 128 ? D : 128;
 static int heads_per_cta(int group) { return group < 16 ? group : 16; }
 
 }  // namespace b200
@@ -426,7 +433,7 @@ extern "C" int b200_attention_prefill_bf16(const void* q, const void* k_pool, co
   }
   dim3 grid(num_tiles, nkv * p.slices);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
-  prefill_attention_kernel<4><<<grid, 128, kSmemBytes, stream>>>(p);
+  launch(prefill_attention_kernel<4>, dim3(grid), dim3(128), kSmemBytes, stream, p);
   return launch_status();
 }
 
@@ -454,11 +461,11 @@ extern "C" int b200_attention_decode_bf16(const void* q, const void* k_pool, con
     configured = true;
   }
   dim3 grid(num_splits, nkv * p.slices, requests);
-  decode_attention_kernel<<<grid, 128, kSmemBytes, stream>>>(p);
+  launch(decode_attention_kernel, dim3(grid), dim3(128), kSmemBytes, stream, p);
   if (int e = launch_status()) return e;
   if (num_splits > 1) {
     dim3 mgrid(nq, requests);
-    decode_merge_kernel<<<mgrid, D < 128 ? D : 128, 0, stream>>>(p.part_o, p.part_ml, p.out, nq, num_splits);
+    launch(decode_merge_kernel, dim3(mgrid), dim3(kMergeThreads), 0, stream, p.part_o, p.part_ml, p.out, nq, num_splits);
   }
   return launch_status();
 }

@@ -22,6 +22,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
                             const int* __restrict__ block_table, int table_stride, int page_size,
                             int nq, int nkv, int d, float scale, int window) {
   extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int token = blockIdx.x;
   const int head = blockIdx.y * 4 + warp;
@@ -104,7 +106,7 @@ extern "C" int b200_paged_attention_simt(
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
   const size_t smem = static_cast<size_t>(4) * d * sizeof(float);
   B200_DISPATCH_DTYPE(dtype, T,
-      paged_attention_simt_kernel<T><<<grid, 128, smem, stream>>>(
+      launch(paged_attention_simt_kernel<T>, dim3(grid), dim3(128), smem, stream, 
           static_cast<const T*>(q), static_cast<const T*>(k_pool), static_cast<const T*>(v_pool),
           static_cast<T*>(out), positions, token_entry, block_table, table_stride, page_size, nq,
           nkv, d, scale, window));

@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace b200 {
 
@@ -83,6 +84,41 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 // Launch status for the C entry points: 0 on success, else the cudaError value.
 inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
+
+// ---------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel started through launch() may begin while the
+// kernel before it in the stream is still draining: everything it does before pdl_wait()
+// (index arithmetic, fetching weights, which no kernel ever writes) overlaps that tail.
+// pdl_wait() returns once the preceding kernels have completed and their writes are
+// visible, so every read of an activation and every write must come after it.
+// Every kernel started through launch() must call pdl_wait() on all paths that touch memory.
+// LLM_RUNTIME_STUDY_B200_PDL=0 turns the overlap off (plain stream order).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("LLM_RUNTIME_STUDY_B200_PDL");
+    enabled = e ? (atoi(e) != 0 ? 1 : 0) : 1;
+  }
+  return enabled == 1;
+}
+
+template <typename... Params, typename... Args>
+inline void launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
 
 }  // namespace b200
 

@@ -19,6 +19,8 @@ namespace b200 {
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab, float scale) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const int id = ids[row];
   float* dst = out + static_cast<size_t>(row) * hidden;
@@ -36,6 +38,8 @@ __global__ void embedding_vec_kernel(const int* __restrict__ ids, const T* __res
                                      float* __restrict__ out, int hidden, int vocab, float scale) {
   constexpr int VN = Vec<T>::n;
   using V = typename Vec<T>::type;
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const int id = ids[row];
   const bool ok = id >= 0 && id < vocab;
@@ -63,6 +67,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const float* __res
   extern __shared__ float smem[];
   float* x = smem;            // [hidden]
   float* scratch = smem + hidden;  // [32]
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const size_t src = static_cast<size_t>(rows ? rows[row] : row) * hidden;
   float ss = 0.f;
@@ -88,6 +94,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const float* _
                                        const float* __restrict__ weight, OutT* __restrict__ out,
                                        const int* __restrict__ rows, int hidden, float eps, int write_resid) {
   __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const size_t src = static_cast<size_t>(rows ? rows[row] : row) * hidden;
   const int nvec = hidden >> 2;
@@ -131,6 +139,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const float* _
 // ------------------------------------------------------------------ SiLU * up
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+  pdl_trigger();
+  pdl_wait();
   const size_t row = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= inter) return;
@@ -145,6 +155,8 @@ template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
   constexpr int VN = Vec<T>::n;
   using V = typename Vec<T>::type;
+  pdl_trigger();
+  pdl_wait();
   const size_t row = blockIdx.y;
   const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VN;
   if (i >= inter) return;
@@ -170,6 +182,8 @@ __global__ void __launch_bounds__(128) qk_norm_rope_write_kernel(
     int rotary_dim, const int* __restrict__ positions, const int* __restrict__ token_entry,
     const int* __restrict__ block_table, int table_stride, int page_size,
     T* __restrict__ k_pool, T* __restrict__ v_pool, int nq, int nkv, int d, int qkv_stride) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int token = blockIdx.x;
   const int h = blockIdx.y * 4 + warp;
@@ -239,13 +253,13 @@ template <typename T>
 static void launch_norm_vec(float* resid, const float* delta, const float* weight, T* out, const int* rows, int n,
                             int hidden, float eps, int write_resid, cudaStream_t stream) {
   const int nvec = hidden / 4;
-  if (nvec <= 128) add_rmsnorm_vec_kernel<T, 1><<<n, 128, 0, stream>>>(resid, delta, weight, out, rows, hidden, eps, write_resid);
-  else if (nvec <= 256) add_rmsnorm_vec_kernel<T, 1><<<n, 256, 0, stream>>>(resid, delta, weight, out, rows, hidden, eps, write_resid);
-  else if (nvec <= 512) add_rmsnorm_vec_kernel<T, 2><<<n, 256, 0, stream>>>(resid, delta, weight, out, rows, hidden, eps, write_resid);
-  else if (nvec <= 1024) add_rmsnorm_vec_kernel<T, 4><<<n, 256, 0, stream>>>(resid, delta, weight, out, rows, hidden, eps, write_resid);
-  else if (nvec <= 2048) add_rmsnorm_vec_kernel<T, 4><<<n, 512, 0, stream>>>(resid, delta, weight, out, rows, hidden, eps, write_resid);
-  else if (nvec <= 4096) add_rmsnorm_vec_kernel<T, 4><<<n, 1024, 0, stream>>>(resid, delta, weight, out, rows, hidden, eps, write_resid);
-  else add_rmsnorm_vec_kernel<T, 8><<<n, 1024, 0, stream>>>(resid, delta, weight, out, rows, hidden, eps, write_resid);
+  if (nvec <= 128) launch(add_rmsnorm_vec_kernel<T, 1>, dim3(n), dim3(128), 0, stream, resid, delta, weight, out, rows, hidden, eps, write_resid);
+  else if (nvec <= 256) launch(add_rmsnorm_vec_kernel<T, 1>, dim3(n), dim3(256), 0, stream, resid, delta, weight, out, rows, hidden, eps, write_resid);
+  else if (nvec <= 512) launch(add_rmsnorm_vec_kernel<T, 2>, dim3(n), dim3(256), 0, stream, resid, delta, weight, out, rows, hidden, eps, write_resid);
+  else if (nvec <= 1024) launch(add_rmsnorm_vec_kernel<T, 4>, dim3(n), dim3(256), 0, stream, resid, delta, weight, out, rows, hidden, eps, write_resid);
+  else if (nvec <= 2048) launch(add_rmsnorm_vec_kernel<T, 4>, dim3(n), dim3(512), 0, stream, resid, delta, weight, out, rows, hidden, eps, write_resid);
+  else if (nvec <= 4096) launch(add_rmsnorm_vec_kernel<T, 4>, dim3(n), dim3(1024), 0, stream, resid, delta, weight, out, rows, hidden, eps, write_resid);
+  else launch(add_rmsnorm_vec_kernel<T, 8>, dim3(n), dim3(1024), 0, stream, resid, delta, weight, out, rows, hidden, eps, write_resid);
 }
 
 }  // namespace b200
@@ -260,9 +274,9 @@ extern "C" int b200_embedding(const int* ids, const void* table, float* out, int
   const bool aligned = ((reinterpret_cast<uintptr_t>(table) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
   B200_DISPATCH_DTYPE(dtype, T, {
     if (aligned && hidden % Vec<T>::n == 0)
-      embedding_vec_kernel<T><<<n, threads, 0, stream>>>(ids, static_cast<const T*>(table), out, hidden, vocab, scale);
+      launch(embedding_vec_kernel<T>, dim3(n), dim3(threads), 0, stream, ids, static_cast<const T*>(table), out, hidden, vocab, scale);
     else
-      embedding_kernel<T><<<n, threads, 0, stream>>>(ids, static_cast<const T*>(table), out, hidden, vocab, scale);
+      launch(embedding_kernel<T>, dim3(n), dim3(threads), 0, stream, ids, static_cast<const T*>(table), out, hidden, vocab, scale);
   });
   return launch_status();
 }
@@ -289,7 +303,7 @@ extern "C" int b200_add_rmsnorm(float* resid, const float* delta, const float* w
                                            static_cast<int>(smem));
       if (e != cudaSuccess) return static_cast<int>(e);
     }
-    add_rmsnorm_kernel<T><<<n, threads, smem, stream>>>(resid, delta, weight, static_cast<T*>(out),
+    launch(add_rmsnorm_kernel<T>, dim3(n), dim3(threads), smem, stream, resid, delta, weight, static_cast<T*>(out),
                                                          rows, hidden, eps, write_resid);
   });
   return launch_status();
@@ -305,10 +319,10 @@ extern "C" int b200_silu_mul(const void* gate_up, void* out, int n, int inter, i
     const bool aligned = ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
     if (inter % VN == 0 && aligned) {
       dim3 grid((inter / VN + 255) / 256, n);
-      silu_mul_vec_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(gate_up), static_cast<T*>(out), inter);
+      launch(silu_mul_vec_kernel<T>, dim3(grid), dim3(256), 0, stream, static_cast<const T*>(gate_up), static_cast<T*>(out), inter);
     } else {
       dim3 grid((inter + 255) / 256, n);
-      silu_mul_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(gate_up), static_cast<T*>(out), inter);
+      launch(silu_mul_kernel<T>, dim3(grid), dim3(256), 0, stream, static_cast<const T*>(gate_up), static_cast<T*>(out), inter);
     }
   });
   return launch_status();
@@ -327,7 +341,7 @@ extern "C" int b200_qk_norm_rope_write(
   dim3 grid(n, (nq + 2 * nkv + 3) / 4);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
   B200_DISPATCH_DTYPE(dtype, T,
-      qk_norm_rope_write_kernel<T><<<grid, 128, 0, stream>>>(
+      launch(qk_norm_rope_write_kernel<T>, dim3(grid), dim3(128), 0, stream, 
           static_cast<const T*>(qkv), static_cast<T*>(q_out), q_weight, k_weight, eps, inv_freq,
           rotary_dim, positions, token_entry, block_table, table_stride, page_size,
           static_cast<T*>(k_pool), static_cast<T*>(v_pool), nq, nkv, d, qkv_stride));

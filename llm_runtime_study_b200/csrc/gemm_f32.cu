@@ -15,6 +15,8 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W,
                 int lda, int ldc) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
+  pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int tx = tid & 15, ty = tid >> 4;  // 16 x 16 threads, each 4 x 4 outputs
@@ -64,6 +66,6 @@ extern "C" int b200_gemm_f32(const float* A, const float* W, const float* bias, 
   if (K <= 0 || lda < K || ldc < N) return B200_ERR_BAD_SIZE;
   dim3 grid((N + b200::BN - 1) / b200::BN, (M + b200::BM - 1) / b200::BM);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
-  b200::gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, W, bias, C, M, N, K, lda, ldc);
+  b200::launch(b200::gemm_f32_kernel, dim3(grid), dim3(256), 0, stream, A, W, bias, C, M, N, K, lda, ldc);
   return b200::launch_status();
 }

@@ -43,16 +43,33 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
     for (int e = 0; e < 4; ++e) c[j][e] = 0.f;
 
   const uint4 zero = make_uint4(0, 0, 0, 0);
+  // The weights do not depend on the kernel before this one: fetch the first piece of them
+  // while that kernel is still finishing, and only then wait for the activations.
+  pdl_trigger();
+  uint4 a[UNROLL], b[UNROLL];
+  {
+    const int k0 = warp * kChunk;
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = k0 + u * 32;
+      const bool ok = k + t * 8 < K;
+      a[u] = ok ? ldg_stream(wa + k) : zero;
+      b[u] = ok ? ldg_stream(wb + k) : zero;
+    }
+  }
+  pdl_wait();
   for (int k0 = warp * kChunk; k0 < K; k0 += kSkinnyWarps * kChunk) {
 #pragma unroll
     for (int h = 0; h < kChunk / 32; h += UNROLL) {
-      uint4 a[UNROLL], b[UNROLL], x[NT][UNROLL];
+      uint4 x[NT][UNROLL];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const int k = k0 + (h + u) * 32;
         const bool ok = k + t * 8 < K;
-        a[u] = ok ? ldg_stream(wa + k) : zero;
-        b[u] = ok ? ldg_stream(wb + k) : zero;
+        if (h != 0 || k0 != warp * kChunk) {   // the very first piece is already in registers
+          a[u] = ok ? ldg_stream(wa + k) : zero;
+          b[u] = ok ? ldg_stream(wb + k) : zero;
+        }
 #pragma unroll
         for (int j = 0; j < NT; ++j) x[j][u] = ok ? *reinterpret_cast<const uint4*>(xr[j] + k) : zero;
       }
@@ -102,11 +119,11 @@ extern "C" int b200_gemm_skinny(const void* X, const void* W, const float* bias,
   const auto* w = static_cast<const __nv_bfloat16*>(W);
   const auto* x = static_cast<const __nv_bfloat16*>(X);
   if (M <= 8) {
-    if (out_f32) gemm_skinny_kernel<1, 8, float><<<grid, kSkinnyWarps * 32, 0, stream>>>(w, x, bias, static_cast<float*>(C), M, N, K, ldc);
-    else gemm_skinny_kernel<1, 8, __nv_bfloat16><<<grid, kSkinnyWarps * 32, 0, stream>>>(w, x, bias, static_cast<__nv_bfloat16*>(C), M, N, K, ldc);
+    if (out_f32) launch(gemm_skinny_kernel<1, 8, float>, dim3(grid), dim3(kSkinnyWarps * 32), 0, stream, w, x, bias, static_cast<float*>(C), M, N, K, ldc);
+    else launch(gemm_skinny_kernel<1, 8, __nv_bfloat16>, dim3(grid), dim3(kSkinnyWarps * 32), 0, stream, w, x, bias, static_cast<__nv_bfloat16*>(C), M, N, K, ldc);
   } else {
-    if (out_f32) gemm_skinny_kernel<2, 4, float><<<grid, kSkinnyWarps * 32, 0, stream>>>(w, x, bias, static_cast<float*>(C), M, N, K, ldc);
-    else gemm_skinny_kernel<2, 4, __nv_bfloat16><<<grid, kSkinnyWarps * 32, 0, stream>>>(w, x, bias, static_cast<__nv_bfloat16*>(C), M, N, K, ldc);
+    if (out_f32) launch(gemm_skinny_kernel<2, 4, float>, dim3(grid), dim3(kSkinnyWarps * 32), 0, stream, w, x, bias, static_cast<float*>(C), M, N, K, ldc);
+    else launch(gemm_skinny_kernel<2, 4, __nv_bfloat16>, dim3(grid), dim3(kSkinnyWarps * 32), 0, stream, w, x, bias, static_cast<__nv_bfloat16*>(C), M, N, K, ldc);
   }
   return launch_status();
 }

@@ -72,6 +72,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const int* __
               int* __restrict__ out, int filtered_only) {
   __shared__ ArgMax arg_scratch[32];
   __shared__ float sum_scratch[32];
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const float* x = logits + static_cast<size_t>(row) * ld;
   const int* p = params + row * kParamWords;
@@ -160,6 +162,8 @@ sample_partial_kernel(const float* __restrict__ logits, int ld, int vocab, const
                       float* __restrict__ part_value, int* __restrict__ part_index, int chunks) {
   __shared__ ArgMax arg_scratch[32];
   __shared__ float sum_scratch[32];
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.y, chunk = blockIdx.x;
   const int* p = params + row * kParamWords;
   if (row_is_filtered(p, vocab)) return;
@@ -188,6 +192,8 @@ sample_partial_kernel(const float* __restrict__ logits, int ld, int vocab, const
 
 __global__ void sample_final_kernel(const float* __restrict__ part_value, const int* __restrict__ part_index,
                                     const int* __restrict__ params, int vocab, int* __restrict__ out, int chunks) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   if (row_is_filtered(params + row * kParamWords, vocab)) return;   // written by sample_kernel
   ArgMax best{-INFINITY, 0x7fffffff};
@@ -213,7 +219,7 @@ extern "C" int b200_sample(const float* logits, int ld, int vocab, const int* pa
   if (rows <= 0) return 0;
   if (vocab <= 0 || ld < vocab) return B200_ERR_BAD_SIZE;
   const int threads = vocab >= 8192 ? 1024 : (vocab >= 1024 ? 256 : 128);
-  b200::sample_kernel<<<rows, threads, 0, stream>>>(logits, ld, vocab, params, out, 0);
+  b200::launch(b200::sample_kernel, dim3(rows), dim3(threads), 0, stream, logits, ld, vocab, params, out, 0);
   return b200::launch_status();
 }
 
@@ -227,11 +233,11 @@ extern "C" int b200_sample_chunked(const float* logits, int ld, int vocab, const
   float* part_value = static_cast<float*>(scratch);
   int* part_index = reinterpret_cast<int*>(part_value + static_cast<size_t>(rows) * chunks);
   dim3 grid(chunks, rows);
-  b200::sample_partial_kernel<<<grid, 256, 0, stream>>>(logits, ld, vocab, params, part_value, part_index, chunks);
-  b200::sample_final_kernel<<<rows, 32, 0, stream>>>(part_value, part_index, params, vocab, out, chunks);
+  b200::launch(b200::sample_partial_kernel, dim3(grid), dim3(256), 0, stream, logits, ld, vocab, params, part_value, part_index, chunks);
+  b200::launch(b200::sample_final_kernel, dim3(rows), dim3(32), 0, stream, part_value, part_index, params, vocab, out, chunks);
   if (any_filtered) {
     const int threads = vocab >= 8192 ? 1024 : (vocab >= 1024 ? 256 : 128);
-    b200::sample_kernel<<<rows, threads, 0, stream>>>(logits, ld, vocab, params, out, 1);
+    b200::launch(b200::sample_kernel, dim3(rows), dim3(threads), 0, stream, logits, ld, vocab, params, out, 1);
   }
   return b200::launch_status();
 }

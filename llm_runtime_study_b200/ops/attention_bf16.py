@@ -13,7 +13,7 @@ from .native import c_float, c_int, c_void_p
 
 c_long = native.ctypes.c_long
 MAX_HEAD_DIM = 256
-_TARGET_CTAS = 592       # four CTAs on each of 148 SMs
+_CTA_SLOTS = 3 * 148     # resident CTAs of the decode kernel (shared memory allows three per SM)
 _MIN_KEYS_PER_SPLIT = 128
 
 _TABLE = {
@@ -46,12 +46,19 @@ def build(head_dim: int) -> None:
 
 
 def decode_splits(requests: int, kv_heads: int, slices: int, longest: int) -> int:
-    """Into how many parts each sequence is cut so that the GPU is filled."""
+    """Into how many parts each sequence is cut.  The decode kernel keeps three CTAs on
+    each of the 148 SMs; the CTAs of all parts should fill those slots in as few, as full
+    rounds as possible, and a part should not be shorter than two tiles of keys."""
 
     ctas = max(1, requests * kv_heads * slices)
-    by_occupancy = -(-_TARGET_CTAS // ctas)
-    by_length = max(1, -(-longest // _MIN_KEYS_PER_SPLIT))
-    return max(1, min(by_occupancy, by_length))
+    most = max(1, -(-longest // _MIN_KEYS_PER_SPLIT))
+    best, best_cost = 1, None
+    for s in range(1, min(most, 64) + 1):
+        rounds = -(-(ctas * s) // _CTA_SLOTS)
+        cost = rounds / s + 0.02 * s          # time of the rounds + what each further part costs to merge
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 def tile_map(q_lens, tokens_per_tile: int, device) -> tuple[torch.Tensor, int]:
