@@ -136,7 +136,8 @@ def run_ours(args) -> dict:
     max_batch = max(args.batch, 64)
     engine = Engine.from_random_weights(
         cfg, seed=0, device="cuda:0", dtype="bfloat16", max_seq_len=cfg["max_position_embeddings"],
-        max_batch_size=max_batch, page_size=PAGE_SIZE, max_cache_tokens=max_batch * (CONTEXT + 64),
+        max_batch_size=max_batch, page_size=PAGE_SIZE,
+        max_cache_tokens=max_batch * (CONTEXT + args.steps + max(args.warmup, 3) + 2 * PAGE_SIZE),
         max_tokens_per_step=PREFILL_TOKENS, use_cuda_graph=True)
     runner, manager = engine.runner, engine.cache_manager
     sampler = engine._sampler
@@ -385,7 +386,7 @@ def run_reference(args) -> dict:
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--steps", type=int, default=128)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--batch", type=int, default=8)

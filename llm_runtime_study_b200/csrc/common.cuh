@@ -94,7 +94,14 @@ inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
 // Every kernel started through launch() must call pdl_wait() on all paths that touch memory.
 // LLM_RUNTIME_STUDY_B200_PDL=0 turns the overlap off (plain stream order).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+// The next kernel is released when a CTA exits (the implicit trigger).  Releasing it
+// earlier, at the top of every CTA, was measured slower on the decode step: the
+// dependent's CTAs then take SM slots while they wait.
+__device__ __forceinline__ void pdl_trigger() {
+#ifdef B200_PDL_EARLY_TRIGGER
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+#endif
+}
 
 inline bool pdl_enabled() {
   static int enabled = -1;

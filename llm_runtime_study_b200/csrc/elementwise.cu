@@ -175,77 +175,86 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict
 constexpr int kMaxPairs = 4;   // rotary_dim / 2 <= 128
 constexpr int kMaxTail = 8;    // head_dim <= 256
 
+constexpr int kRopeWarps = 8;
+
 template <typename T>
-__global__ void __launch_bounds__(128) qk_norm_rope_write_kernel(
+__global__ void __launch_bounds__(kRopeWarps * 32) qk_norm_rope_write_kernel(
     const T* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ q_weight,
     const float* __restrict__ k_weight, float eps, const float* __restrict__ inv_freq,
     int rotary_dim, const int* __restrict__ positions, const int* __restrict__ token_entry,
     const int* __restrict__ block_table, int table_stride, int page_size,
     T* __restrict__ k_pool, T* __restrict__ v_pool, int nq, int nkv, int d, int qkv_stride) {
+  __shared__ float cs[32 * kMaxPairs], sn[32 * kMaxPairs];
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int token = blockIdx.x;
-  const int h = blockIdx.y * 4 + warp;
-  if (h >= nq + 2 * nkv) return;
-  const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
   const int pos = positions[token];
-  const T* src = qkv + static_cast<size_t>(token) * qkv_stride + static_cast<size_t>(h) * d;
-  T* dst;
-  if (is_q) {
-    dst = q_out + (static_cast<size_t>(token) * nq + h) * d;
-  } else {
+  const int rot_half = inv_freq ? rotary_dim / 2 : 0;
+  // sine and cosine once per token, shared by all its heads
+  for (int j = threadIdx.x; j < rot_half; j += blockDim.x)
+    sincosf(static_cast<float>(pos) * inv_freq[j], &sn[j], &cs[j]);
+  __syncthreads();
+  int64_t kv_base = -1;   // element offset of this token's slot for kv head 0
+  if (nkv > 0) {
     const int page = block_table[static_cast<size_t>(token_entry[token]) * table_stride + pos / page_size];
-    if (page < 0) return;
-    const int kvh = is_k ? h - nq : h - nq - nkv;
-    dst = (is_k ? k_pool : v_pool) +
-          ((static_cast<int64_t>(page) * nkv + kvh) * page_size + pos % page_size) * static_cast<int64_t>(d);
+    if (page >= 0) kv_base = (static_cast<int64_t>(page) * nkv * page_size + pos % page_size) * d;
   }
-  const bool rotate = inv_freq != nullptr && (is_q || is_k);
-  const int half = rotate ? rotary_dim / 2 : 0;
-  const int tail0 = 2 * half;
-  float lo[kMaxPairs], hi[kMaxPairs], tail[kMaxTail];
-  float ss = 0.f;
-#pragma unroll
-  for (int p = 0; p < kMaxPairs; ++p) {
-    const int j = lane + 32 * p;
-    lo[p] = hi[p] = 0.f;
-    if (j < half) {
-      lo[p] = to_float(src[j]);
-      hi[p] = to_float(src[j + half]);
-      ss += lo[p] * lo[p] + hi[p] * hi[p];
+  // gridDim.y blocks share a token's heads (few tokens: more blocks, one head per warp)
+  for (int h = blockIdx.y * kRopeWarps + warp; h < nq + 2 * nkv; h += gridDim.y * kRopeWarps) {
+    const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+    const T* src = qkv + static_cast<size_t>(token) * qkv_stride + static_cast<size_t>(h) * d;
+    T* dst;
+    if (is_q) {
+      dst = q_out + (static_cast<size_t>(token) * nq + h) * d;
+    } else {
+      if (kv_base < 0) continue;
+      const int kvh = is_k ? h - nq : h - nq - nkv;
+      dst = (is_k ? k_pool : v_pool) + kv_base + static_cast<int64_t>(kvh) * page_size * d;
     }
-  }
+    const int half = (is_q || is_k) ? rot_half : 0;
+    const int tail0 = 2 * half;
+    float lo[kMaxPairs], hi[kMaxPairs], tail[kMaxTail];
+    float ss = 0.f;
 #pragma unroll
-  for (int q = 0; q < kMaxTail; ++q) {
-    const int i = tail0 + lane + 32 * q;
-    tail[q] = 0.f;
-    if (i < d) {
-      tail[q] = to_float(src[i]);
-      ss += tail[q] * tail[q];
+    for (int p = 0; p < kMaxPairs; ++p) {
+      const int j = lane + 32 * p;
+      lo[p] = hi[p] = 0.f;
+      if (j < half) {
+        lo[p] = to_float(src[j]);
+        hi[p] = to_float(src[j + half]);
+        ss += lo[p] * lo[p] + hi[p] * hi[p];
+      }
     }
-  }
-  const float* w = is_q ? q_weight : (is_k ? k_weight : nullptr);
-  const float r = w ? rsqrtf(warp_sum(ss) / static_cast<float>(d) + eps) : 1.f;
 #pragma unroll
-  for (int p = 0; p < kMaxPairs; ++p) {
-    const int j = lane + 32 * p;
-    if (j >= half) continue;
-    float a = lo[p], b = hi[p];
-    if (w) {
-      a *= r * w[j];
-      b *= r * w[j + half];
+    for (int q = 0; q < kMaxTail; ++q) {
+      const int i = tail0 + lane + 32 * q;
+      tail[q] = 0.f;
+      if (i < d) {
+        tail[q] = to_float(src[i]);
+        ss += tail[q] * tail[q];
+      }
     }
-    float sn, cs;
-    sincosf(static_cast<float>(pos) * inv_freq[j], &sn, &cs);
-    dst[j] = from_float<T>(a * cs - b * sn);
-    dst[j + half] = from_float<T>(b * cs + a * sn);
-  }
+    const float* w = is_q ? q_weight : (is_k ? k_weight : nullptr);
+    const float r = w ? rsqrtf(warp_sum(ss) / static_cast<float>(d) + eps) : 1.f;
 #pragma unroll
-  for (int q = 0; q < kMaxTail; ++q) {
-    const int i = tail0 + lane + 32 * q;
-    if (i >= d) continue;
-    dst[i] = from_float<T>(w ? tail[q] * r * w[i] : tail[q]);
+    for (int p = 0; p < kMaxPairs; ++p) {
+      const int j = lane + 32 * p;
+      if (j >= half) continue;
+      float a = lo[p], b = hi[p];
+      if (w) {
+        a *= r * w[j];
+        b *= r * w[j + half];
+      }
+      dst[j] = from_float<T>(a * cs[j] - b * sn[j]);
+      dst[j + half] = from_float<T>(b * cs[j] + a * sn[j]);
+    }
+#pragma unroll
+    for (int q = 0; q < kMaxTail; ++q) {
+      const int i = tail0 + lane + 32 * q;
+      if (i >= d) continue;
+      dst[i] = from_float<T>(w ? tail[q] * r * w[i] : tail[q]);
+    }
   }
 }
 
@@ -338,10 +347,10 @@ extern "C" int b200_qk_norm_rope_write(
       page_size <= 0)
     return B200_ERR_BAD_SIZE;
   if (rotary_dim / 2 > 32 * kMaxPairs || d > 32 * kMaxTail) return B200_ERR_TOO_LARGE;
-  dim3 grid(n, (nq + 2 * nkv + 3) / 4);
-  if (grid.y > 65535) return B200_ERR_TOO_LARGE;
+  const int heads = nq + 2 * nkv;
+  const int head_blocks = n >= 512 ? 1 : (heads + kRopeWarps - 1) / kRopeWarps;
   B200_DISPATCH_DTYPE(dtype, T,
-      launch(qk_norm_rope_write_kernel<T>, dim3(grid), dim3(128), 0, stream, 
+      launch(qk_norm_rope_write_kernel<T>, dim3(n, head_blocks), dim3(kRopeWarps * 32), 0, stream, 
           static_cast<const T*>(qkv), static_cast<T*>(q_out), q_weight, k_weight, eps, inv_freq,
           rotary_dim, positions, token_entry, block_table, table_stride, page_size,
           static_cast<T*>(k_pool), static_cast<T*>(v_pool), nq, nkv, d, qkv_stride));
