@@ -469,3 +469,50 @@ extern "C" int b200_attention_decode_bf16(const void* q, const void* k_pool, con
   }
   return launch_status();
 }
+
+// --------------------------------------------------------------------------------------
+// Allocation-free variant of the decode entry point (see attention_noalloc.h for the
+// contract and for who needs it).  The scratch that b200_attention_decode_bf16 takes from
+// its caller lives here, in the library image.
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[B200_NOALLOC_SCRATCH_FLOATS];
+
+// `g_noalloc_scratch` in host code is only a handle for the runtime, not an address a
+// kernel could use; the device address is asked for once per device and kept.
+static float* noalloc_scratch_address(int* status) {
+  constexpr int kMaxDevices = 64;
+  static float* address[kMaxDevices] = {};
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= kMaxDevices) {
+    *status = e != cudaSuccess ? static_cast<int>(e) : B200_ERR_NOALLOC_SETUP;
+    return nullptr;
+  }
+  if (address[device] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      *status = e != cudaSuccess ? static_cast<int>(e) : B200_ERR_NOALLOC_SETUP;
+      return nullptr;
+    }
+    address[device] = p;
+  }
+  *status = 0;
+  return address[device];
+}
+
+extern "C" int b200_attention_decode_bf16_noalloc(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                                  const int* kv_len, const int* block_table, int table_stride,
+                                                  int page_size, int requests, int nq, int nkv, float scale,
+                                                  int window, int num_splits, cudaStream_t stream) {
+  if (requests <= 0) return 0;
+  if (num_splits < 1) return B200_ERR_BAD_SIZE;
+  const long needed = b200_attention_decode_scratch_floats(requests, nq, num_splits);
+  if (needed > B200_NOALLOC_SCRATCH_FLOATS) return B200_ERR_NOALLOC_TOO_LARGE;
+  int status = 0;
+  float* scratch = noalloc_scratch_address(&status);
+  if (scratch == nullptr) return status;
+  return b200_attention_decode_bf16(q, k_pool, v_pool, out, kv_len, block_table, table_stride, page_size, requests,
+                                    nq, nkv, scale, window, num_splits, scratch, B200_NOALLOC_SCRATCH_FLOATS, stream);
+}

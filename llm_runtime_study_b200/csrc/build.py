@@ -59,7 +59,7 @@ def _build_dir() -> Path:
 
 def _digest(sources: Sequence[Path], flags: Sequence[str]) -> str:
     h = hashlib.sha256()
-    for path in list(sources) + sorted(CSRC_DIR.glob("*.cuh")):
+    for path in list(sources) + sorted(CSRC_DIR.glob("*.cuh")) + sorted(CSRC_DIR.glob("*.h")):
         h.update(path.name.encode())
         h.update(path.read_bytes())
     h.update(" ".join(flags).encode())
