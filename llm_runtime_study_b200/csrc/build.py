@@ -106,6 +106,9 @@ def build_library(name: str, sources: Iterable[str], defines: Sequence[str] = ()
         raise KernelError(f"nvcc failed for {name}:\n{log}")
     (out.with_suffix(".log")).write_text(log)
     os.replace(tmp, out)
+    for stale in out.parent.glob(f"lib{name}-*"):      # builds of earlier versions of the sources
+        if stale.stem != out.stem:
+            stale.unlink(missing_ok=True)
     if verbose:
         print(f"[llm_runtime_study_b200] built {out.name} in {time.time() - started:.1f} s", file=sys.stderr, flush=True)
     return out
