@@ -40,6 +40,7 @@ struct AttnParams {
   const int* positions;
   const int* block_table;
   int table_stride, page_size;
+  int page_shift;                  // log2(page_size) when it is a power of two, else -1
   int nq, nkv, group, gs, slices;  // group = nq / nkv; gs = heads of a group per CTA; slices = ceil(group / gs)
   float scale_log2;
   int window;
@@ -67,9 +68,11 @@ __device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const AttnParam
     const bf16* vsrc = p.v_pool;
     int bytes = 0;
     if (t >= lo && t <= hi) {
-      const int page = table[t / p.page_size];
+      const int index = p.page_shift >= 0 ? t >> p.page_shift : t / p.page_size;
+      const int slot = p.page_shift >= 0 ? t & (p.page_size - 1) : t - index * p.page_size;
+      const int page = table[index];
       if (page >= 0) {
-        const size_t off = ((static_cast<size_t>(page) * p.nkv + kvh) * p.page_size + t % p.page_size) * D + ch * 8;
+        const size_t off = ((static_cast<size_t>(page) * p.nkv + kvh) * p.page_size + slot) * D + ch * 8;
         ksrc += off;
         vsrc += off;
         bytes = 16;
@@ -398,6 +401,9 @@ static int fill_common(AttnParams& p, const void* q, const void* k_pool, const v
   p.block_table = block_table;
   p.table_stride = table_stride;
   p.page_size = page_size;
+  p.page_shift = -1;
+  for (int b = 0; b < 20; ++b)
+    if ((1 << b) == page_size) p.page_shift = b;
   p.nq = nq;
   p.nkv = nkv;
   p.group = nq / nkv;
