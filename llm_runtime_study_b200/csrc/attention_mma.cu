@@ -291,28 +291,58 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[dt][e] = 0.f;
 
-  const int ntiles = c1 >= c0 ? (c1 - c0) / BN + 1 : 0;
-  if (ntiles > 0) {
-    load_kv_tile<128>(ks, vs, p, table, kvh, c0, c0, c1);
+  // Each warp runs a pipeline of its own over 16-key blocks (block w, w + 4, ... of this
+  // CTA's part), with a private pair of shared-memory buffers: no CTA-wide barrier inside
+  // the loop, so the warps drift apart and cover each other's waits.
+  constexpr int WB = 16;                                  // keys per warp block
+  bf16* wk = ks + warp * (2 * WB * LDS);                  // [2][WB][LDS] keys
+  bf16* wv = vs + warp * (2 * WB * LDS);                  // [2][WB][LDS] values
+  const int nblocks = c1 >= c0 ? (c1 - c0) / WB + 1 : 0;  // 16-key blocks in this CTA's part
+  const int hi_here[2] = {min(row_hi[0], c1), min(row_hi[1], c1)};
+  auto load_block = [&](int block, int buf) {
+    constexpr int CH = D / 8;
+    const int t0 = c0 + block * WB;
+#pragma unroll
+    for (int c = lane; c < WB * CH; c += 32) {
+      const int r = c / CH, ch = c - r * CH;
+      const int t = t0 + r;
+      const bf16* ksrc = p.k_pool;
+      const bf16* vsrc = p.v_pool;
+      int bytes = 0;
+      if (t <= c1) {
+        const int index = p.page_shift >= 0 ? t >> p.page_shift : t / p.page_size;
+        const int slot = p.page_shift >= 0 ? t & (p.page_size - 1) : t - index * p.page_size;
+        const int page = table[index];
+        if (page >= 0) {
+          const size_t off = ((static_cast<size_t>(page) * p.nkv + kvh) * p.page_size + slot) * D + ch * 8;
+          ksrc += off;
+          vsrc += off;
+          bytes = 16;
+        }
+      }
+      cp_async_16(wk + (buf * WB + r) * LDS + ch * 8, ksrc, bytes);
+      cp_async_16(wv + (buf * WB + r) * LDS + ch * 8, vsrc, bytes);
+    }
+  };
+  if (warp < nblocks) {
+    load_block(warp, 0);
     cp_async_commit();
   }
-  for (int j = 0; j < ntiles; ++j) {
-    const int buf = j & 1;
-    if (j + 1 < ntiles) {
-      load_kv_tile<128>(ks + (buf ^ 1) * BN * LDS, vs + (buf ^ 1) * BN * LDS, p, table, kvh, c0 + (j + 1) * BN, c0, c1);
+  int buf = 0;
+  for (int block = warp; block < nblocks; block += 4, buf ^= 1) {
+    if (block + 4 < nblocks) {
+      load_block(block + 4, buf ^ 1);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
-    __syncthreads();
-    // keys of this warp beyond c1 are masked through row_hi
-    const int hi_here[2] = {min(row_hi[0], c1), min(row_hi[1], c1)};
-    if (c0 + j * BN + warp * 16 <= c1)
-      warp_attend<2>(ks + buf * BN * LDS, vs + buf * BN * LDS, warp * 16, c0 + j * BN, qf, row_ok, hi_here, row_lo,
-                     p.scale_log2, m, l, o);
-    __syncthreads();
+    __syncwarp();
+    warp_attend<2>(wk + buf * WB * LDS, wv + buf * WB * LDS, 0, c0 + block * WB, qf, row_ok, hi_here, row_lo,
+                   p.scale_log2, m, l, o);
+    __syncwarp();
   }
+  __syncthreads();
 
   // combine the four warps through shared memory (the K/V buffers are free now)
   float* sm_m = reinterpret_cast<float*>(smem_raw);  // [4][16]
