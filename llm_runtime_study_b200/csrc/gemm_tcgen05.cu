@@ -294,6 +294,147 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   }
 }
 
+// ---------------------------------------------------------------------- persistent kernel
+// One CTA per SM walks over the output tiles (tile, tile + gridDim.x, ...; the 128-row blocks
+// of one 256-column panel are neighbours, so a wave of CTAs shares few weight panels in L2).
+// The accumulator is double buffered in TMEM (2 x 256 columns): while the epilogue warps
+// drain tile i, the tensor core already works on tile i + 1.
+template <int STAGES, typename OutT>
+__global__ void __launch_bounds__(kThreads)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
+                               GemmParams p) {
+  constexpr int BN = 256;
+  constexpr uint32_t ROW_BYTES = BM * BK * 2, COL_BYTES = BN * BK * 2, STAGE_BYTES = ROW_BYTES + COL_BYTES;
+  constexpr uint32_t TMEM_COLS = 512;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;    // [2]
+  uint64_t* acc_empty = acc_full + 2;     // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
+  const int tiles = m_tiles * n_tiles;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full + b, 1);
+      mbar_init(acc_empty + b, 4);     // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------------------------------------------------------- producer
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      const int row0 = (tile % m_tiles) * BM, col0 = (tile / m_tiles) * BN;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t phase = (it / STAGES) & 1;
+        if (!mbar_wait(empty + s, phase ^ 1)) { atomicExch(&g_gemm_error, 1); ok = false; break; }
+        mbar_expect_tx(full + s, STAGE_BYTES);
+        unsigned char* stage = smem + s * STAGE_BYTES;
+        tma_load_2d(stage, &map_rows, full + s, kb * BK, row0);
+        tma_load_2d(stage + ROW_BYTES, &map_cols, full + s, kb * BK, col0);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------------------------------------------------------- tensor-core issue
+    constexpr uint32_t idesc = umma_idesc(BN);
+    int it = 0, local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(acc_empty + buf, acc_phase ^ 1)) { atomicExch(&g_gemm_error, 4); ok = false; break; }
+      tcgen05_fence_after();
+      const uint32_t tmem_d = tmem_base + buf * BN;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t phase = (it / STAGES) & 1;
+        if (!mbar_wait(full + s, phase)) { atomicExch(&g_gemm_error, 2); ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t a_addr = smem_addr(smem + s * STAGE_BYTES), b_addr = a_addr + ROW_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma_bf16(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, (kb | k) != 0);
+        umma_commit(empty + s);
+      }
+      umma_commit(acc_full + buf);
+    }
+  } else if (warp >= 2) {
+    // -------------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      const int row0 = (tile % m_tiles) * BM, col0 = (tile / m_tiles) * BN;
+      const bool ok = mbar_wait(acc_full + buf, acc_phase);
+      if (!ok) atomicExch(&g_gemm_error, 3);
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+      const int m = row0 + row;
+      OutT* crow = static_cast<OutT*>(p.c) + static_cast<size_t>(m) * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        float v[32];
+        if (ok) {
+          tmem_load_32(taddr + c, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        if (m < p.M) {
+          const int nb = col0 + c;
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += nb + j < p.N ? p.bias[nb + j] : 0.f;
+          }
+          if (p.vector_ok && nb + 32 <= p.N) {
+            store_row_32(crow + nb, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nb + j < p.N) store_out<OutT>(crow + nb + j, v[j]);
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(acc_empty + buf)) : "memory");
+      }
+      if (!ok) break;
+    }
+  }
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------------ host side
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -352,6 +493,26 @@ static int launch(const CUtensorMap& rows, const CUtensorMap& cols, const GemmPa
   return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
+template <int STAGES, typename OutT>
+static int launch_persistent(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, cudaStream_t stream) {
+  constexpr size_t smem = STAGES * (BM * BK * 2 + 256 * BK * 2) + 1024 + 256;
+  auto kernel = gemm_tcgen05_persistent_kernel<STAGES, OutT>;
+  static bool configured = false;
+  static int sm_count = 0;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+    configured = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  kernel<<<grid, kThreads, smem, stream>>>(rows, cols, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -368,7 +529,8 @@ extern "C" int b200_gemm_tcgen05_error() {
 
 // C[M,N] (ldc) = A[M,K] * W[N,K]^T + bias; out_f32 selects float or bfloat16 output.
 // K must be a multiple of 8 and both bases 16-byte aligned (TMA); refused otherwise.
-// splits > 0 selects the swapped kernel for M <= 64 with the K range cut into `splits` (1..8) parts.
+// splits > 0 selects the swapped kernel for M <= 64 with the K range cut into `splits` (1..8) parts;
+// splits == 0 the persistent kernel; splits < 0 the one-tile-per-CTA kernel.
 extern "C" int b200_gemm_tcgen05(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
                                  int out_f32, int splits, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
@@ -395,8 +557,12 @@ extern "C" int b200_gemm_tcgen05(const void* A, const void* W, const float* bias
   constexpr int BN = 256;
   if (int e = make_map(&rows, A, M, K, BM)) return e;
   if (int e = make_map(&cols, W, N, K, BN)) return e;
-  dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN);
-  if (grid.y > 65535) return B200_ERR_TOO_LARGE;
-  return out_f32 ? launch<BN, 4, false, float>(rows, cols, p, grid, 1, stream)
-                 : launch<BN, 4, false, __nv_bfloat16>(rows, cols, p, grid, 1, stream);
+  if (splits < 0) {   // one CTA per tile, no overlap of epilogue and main loop (kept for comparison)
+    dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN);
+    if (grid.y > 65535) return B200_ERR_TOO_LARGE;
+    return out_f32 ? launch<BN, 4, false, float>(rows, cols, p, grid, 1, stream)
+                   : launch<BN, 4, false, __nv_bfloat16>(rows, cols, p, grid, 1, stream);
+  }
+  return out_f32 ? launch_persistent<4, float>(rows, cols, p, stream)
+                 : launch_persistent<4, __nv_bfloat16>(rows, cols, p, stream);
 }

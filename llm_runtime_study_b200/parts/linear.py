@@ -19,14 +19,16 @@ class Projection:
     float32 runtime: our FFMA kernel.  bfloat16 runtime, float32 accumulation,
     bfloat16 or float32 output:
       * up to 16 rows (decoding): our weight-streaming mma.sync kernel;
-      * more rows: our tcgen05/TMEM/TMA kernel when ``GEMM_BACKEND`` is "tcgen05",
-        else a library product (the reference's projections are ``nn.Linear``,
-        i.e. library products: mini_llm/nn/attention.py:102-111).
+      * 128 rows and more (prompts): our persistent tcgen05/TMEM/TMA kernel;
+      * in between, and everywhere when ``LLM_RUNTIME_STUDY_B200_GEMM=library``: a
+        library product (the reference's projections are ``nn.Linear``, i.e. library
+        products: mini_llm/nn/attention.py:102-111).
     K must be a multiple of 8 for our bfloat16 kernels (16-byte rows); other
     widths go to the library product.
     """
 
-    GEMM_BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_GEMM", "library")
+    GEMM_BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_GEMM", "tcgen05")
+    TCGEN05_MIN_ROWS = 128
 
     def __init__(self, weights: list[torch.Tensor], biases: list[torch.Tensor] | None, runtime: Runtime) -> None:
         self.runtime = runtime
@@ -52,7 +54,7 @@ class Projection:
         if self.in_features % 8 == 0 and x.is_contiguous():
             if m <= gemm_bf16.SKINNY_M:
                 return gemm_bf16.linear_skinny(x, self.weight, self.bias, out_dtype)
-            if self.GEMM_BACKEND == "tcgen05":
+            if self.GEMM_BACKEND == "tcgen05" and m >= self.TCGEN05_MIN_ROWS:
                 return gemm_bf16.linear(x, self.weight, self.bias, out_dtype, splits=0)
         if out_dtype == torch.bfloat16:
             y = torch.mm(x, self.weight.t())

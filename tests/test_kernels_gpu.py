@@ -367,6 +367,7 @@ def test_weight_streaming_projection(m, n, k, bias, out):
 
 @pytest.mark.parametrize("m,n,k,bias,splits", [
     (128, 256, 64, False, 0), (130, 264, 72, True, 0), (300, 1000, 520, True, 0), (2048, 1024, 4096, False, 0),
+    (5000, 4096, 512, True, 0), (130, 264, 72, True, -1), (2048, 1024, 4096, False, -1),
     (8, 4096, 4096, False, 4), (1, 136, 4096, True, 3), (64, 1000, 512, False, 1), (33, 640, 1024, True, 2)])
 @pytest.mark.parametrize("out", [torch.float32, torch.bfloat16])
 def test_tcgen05_projection(m, n, k, bias, splits, out):
