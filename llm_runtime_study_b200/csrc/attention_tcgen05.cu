@@ -1,0 +1,368 @@
+// bfloat16 causal attention over the paged cache on the 5th-generation tensor cores, for
+// batches that hold prompt portions.  Built once per head size (-DHEAD_DIM=64 or 128).
+//
+// One CTA owns 128 rows of S = Q K^T: up to 128 / gs consecutive query tokens of one request
+// times the gs query heads that share one KV head.  Keys are taken 64 at a time:
+//   warp 4     one lane issues TMA loads: the Q tile once (3-D map over [token, head, d]), then
+//              for every key tile the request's pages of K (two stages) and V (one stage), one
+//              box per page and 64-column half, found through the block table;
+//   warp 5     allocates TMEM; one lane issues tcgen05.mma: S = Q K^T (M 128, N 64, K = head size)
+//              into TMEM, and, once P is in shared memory, O += P V (M 128, N = head size, K 64)
+//              with V read as an MN-major operand (no transposition of the cache);
+//   warps 0-3  softmax: thread r owns row r of S (tcgen05.ld gives a thread its whole row, so
+//              the row maximum and sum need no shuffles); it masks, exponentiates in float32,
+//              writes P as bfloat16 into shared memory in the swizzled K-major layout the tensor
+//              core reads, and keeps the running maximum and sum.  O stays in TMEM; it is only
+//              rescaled (tcgen05.ld / st) when a row's maximum has grown by more than 2^8, which
+//              keeps the result exact (the final division uses the same reference maximum).
+// Two CTAs fit on an SM, so one CTA's softmax overlaps the other's matrix products.
+//
+// Formula (mini_llm/nn/attention.py:95-99, 231-248): S = q.k^T * scale, key t visible iff
+// t <= p, P = softmax(S), o = P.v; query head j reads KV head j / (nq / nkv).
+// Every wait on an mbarrier is bounded; a wait that runs out records an error code, the CTA
+// stops issuing work, frees its TMEM and returns.
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=64 or 128"
+#endif
+static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "this kernel is built for head sizes 64 and 128");
+
+namespace b200 {
+
+using bf16 = __nv_bfloat16;
+constexpr int D = HEAD_DIM;
+constexpr int BM = 128;                    // rows per CTA = TMEM lanes
+constexpr int BN = 64;                     // keys per tile
+constexpr int DSUB = D / 64;               // 64-column (128-byte) sub-tiles of the head size
+constexpr uint32_t Q_SUB = BM * 128;       // bytes of one Q sub-tile
+constexpr uint32_t KV_SUB = BN * 128;      // bytes of one K or V sub-tile
+constexpr uint32_t Q_BYTES = DSUB * Q_SUB, KV_BYTES = DSUB * KV_SUB, P_BYTES = BM * 128;
+constexpr int KSTAGES = 2;
+constexpr uint32_t SMEM_TILES = Q_BYTES + KSTAGES * KV_BYTES + KV_BYTES + P_BYTES;
+constexpr uint32_t TMEM_COLS = (64 + D) <= 128 ? 128 : 256;
+constexpr uint32_t S_COL = 0, O_COL = 64;
+constexpr int kTcThreads = 192;
+constexpr float kRescaleStep = 8.f;        // log2 units a row maximum may lag behind
+
+__device__ int g_attn_error = 0;
+
+struct TcAttnParams {
+  bf16* out;
+  const int* positions;
+  const int* block_table;
+  int table_stride, page_size, page_shift;
+  int nq, nkv, group, gs, slices;
+  float scale_log2;
+  const int* tile_entry;
+  const int* tile_start;
+  const int* tile_count;
+};
+
+__global__ void __launch_bounds__(kTcThreads)
+prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                 const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  unsigned char* q_smem = smem;
+  unsigned char* k_smem = q_smem + Q_BYTES;                 // [KSTAGES]
+  unsigned char* v_smem = k_smem + KSTAGES * KV_BYTES;
+  unsigned char* p_smem = v_smem + KV_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_TILES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;       // [2]
+  uint64_t* k_empty = bars + 3;      // [2]
+  uint64_t* v_full = bars + 5;
+  uint64_t* v_empty = bars + 6;
+  uint64_t* s_full = bars + 7;
+  uint64_t* p_full = bars + 8;
+  uint64_t* o_done = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x;
+  const int kvh = blockIdx.y / p.slices, slice = blockIdx.y % p.slices;
+  const int entry = p.tile_entry[tile], tok0 = p.tile_start[tile], ntok = p.tile_count[tile];
+  const int* table = p.block_table + static_cast<size_t>(entry) * p.table_stride;
+  const int p_first = p.positions[tok0], p_last = p_first + ntok - 1;   // an entry's positions are consecutive
+  const int ntiles = p_last / BN + 1;
+  const int head0 = kvh * p.group + slice * p.gs;
+  const int tokens_per_cta = BM / p.gs;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < KSTAGES; ++s) {
+      mbar_init(k_full + s, 1);
+      mbar_init(k_empty + s, 1);
+    }
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, BM);
+    mbar_init(o_done, 1);
+    fence_barrier_init();
+  }
+  if (warp == 5) tmem_alloc(tmem_slot, TMEM_COLS);
+  // Rows of the V stage that no page is ever copied into must hold finite numbers: a masked
+  // key has probability 0, and 0 * NaN would still be NaN.
+  for (uint32_t i = threadIdx.x; i < KV_BYTES / 16; i += kTcThreads)
+    reinterpret_cast<uint4*>(v_smem)[i] = make_uint4(0, 0, 0, 0);
+  fence_async_shared();
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4 && lane == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    mbar_expect_tx(q_full, DSUB * 128u * p.gs * tokens_per_cta);
+    for (int sub = 0; sub < DSUB; ++sub) tma_load_3d(q_smem + sub * Q_SUB, &map_q, q_full, sub * 64, head0, tok0);
+    const int pages_per_tile = BN / p.page_size;
+    auto load_pages = [&](unsigned char* dst, const CUtensorMap* map, uint64_t* bar, int j) {
+      int loaded = 0;
+      int ids[8];
+      for (int i = 0; i < pages_per_tile; ++i) {
+        const int t0 = j * BN + i * p.page_size;
+        ids[i] = t0 <= p_last ? table[t0 >> p.page_shift] : -1;
+        loaded += ids[i] >= 0;
+      }
+      mbar_expect_tx(bar, static_cast<uint32_t>(loaded) * p.page_size * 128u * DSUB);
+      for (int i = 0; i < pages_per_tile; ++i) {
+        if (ids[i] < 0) continue;
+        const int y = (ids[i] * p.nkv + kvh) * p.page_size;
+        for (int sub = 0; sub < DSUB; ++sub)
+          tma_load_2d(dst + sub * KV_SUB + i * p.page_size * 128, map, bar, sub * 64, y);
+      }
+    };
+    for (int j = 0; j < ntiles; ++j) {
+      const int s = j & 1;
+      if (!mbar_wait(k_empty + s, ((j >> 1) & 1) ^ 1)) { atomicExch(&g_attn_error, 1); break; }
+      load_pages(k_smem + s * KV_BYTES, &map_k, k_full + s, j);
+      if (!mbar_wait(v_empty, (j & 1) ^ 1)) { atomicExch(&g_attn_error, 1); break; }
+      load_pages(v_smem, &map_v, v_full, j);
+    }
+  } else if (warp == 5 && lane == 0) {
+    // ------------------------------------------------------------------ tensor-core issue
+    constexpr uint32_t idesc_s = umma_idesc_bf16(BM, BN, 0);
+    constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, D, 1);
+    bool ok = mbar_wait(q_full, 0);
+    if (!ok) atomicExch(&g_attn_error, 2);
+    const uint32_t q_addr = smem_addr(q_smem), p_addr = smem_addr(p_smem), v_addr = smem_addr(v_smem);
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int s = j & 1;
+      if (!mbar_wait(k_full + s, (j >> 1) & 1)) { atomicExch(&g_attn_error, 2); break; }
+      tcgen05_fence_after();
+      const uint32_t k_addr = smem_addr(k_smem + s * KV_BYTES);
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k)
+        umma_bf16_ss(tmem_base + S_COL, umma_desc_sw128(q_addr + (k >> 2) * Q_SUB + (k & 3) * 32, 16, 1024),
+                     umma_desc_sw128(k_addr + (k >> 2) * KV_SUB + (k & 3) * 32, 16, 1024), idesc_s, k != 0);
+      umma_commit_to(s_full);
+      umma_commit_to(k_empty + s);
+      if (!mbar_wait(p_full, j & 1) || !mbar_wait(v_full, j & 1)) { atomicExch(&g_attn_error, 3); break; }
+      tcgen05_fence_after();
+#pragma unroll
+      for (int k = 0; k < BN / 16; ++k)
+        umma_bf16_ss(tmem_base + O_COL, umma_desc_sw128(p_addr + k * 32, 16, 1024),
+                     umma_desc_sw128(v_addr + k * 2048, KV_SUB, 1024), idesc_pv, (j | k) != 0);
+      umma_commit_to(o_done);
+      umma_commit_to(v_empty);
+    }
+  } else if (warp < 4) {
+    // ------------------------------------------------------------------ softmax, one row per thread
+    const int row = threadIdx.x;
+    const int tl = row / p.gs, g = row - tl * p.gs;
+    const bool row_ok = tl < ntok && slice * p.gs + g < p.group;
+    const int row_hi = p_first + tl;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < ntiles; ++j) {
+      if (!mbar_wait(s_full, j & 1)) { atomicExch(&g_attn_error, 4); ok = false; break; }
+      tcgen05_fence_after();
+      float sv[BN];
+      {
+        uint32_t r[32];
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          tmem_ld_32(lane_base + S_COL + c * 32, r);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sv[c * 32 + i] = __uint_as_float(r[i]) * p.scale_log2;
+        }
+      }
+      const int t0 = j * BN;
+      float m_tile = -INFINITY;
+      if (t0 + BN - 1 <= p_first) {          // every key of the tile is visible to every row of this CTA
+#pragma unroll
+        for (int i = 0; i < BN; ++i) m_tile = fmaxf(m_tile, sv[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) {
+          sv[i] = t0 + i <= row_hi ? sv[i] : -INFINITY;
+          m_tile = fmaxf(m_tile, sv[i]);
+        }
+      }
+      const float m_new = fmaxf(m_used, m_tile);
+      const bool grow = m_new > m_used + kRescaleStep;      // also true on the first tile (m_used = -inf)
+      if (j == 0) {
+        m_used = m_new;
+      } else if (__any_sync(0xffffffffu, grow)) {
+        // O of the tiles so far is complete: S of this tile was issued after their P.V products.
+        const float factor = grow ? exp2f(m_used - m_new) : 1.f;
+        if (grow) m_used = m_new;
+        uint32_t r[32];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          tmem_ld_32(lane_base + O_COL + c * 32, r);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+          tmem_st_32(lane_base + O_COL + c * 32, r);
+        }
+        l *= factor;
+      }
+      const float ref = m_used == -INFINITY ? 0.f : m_used;
+      unsigned char* prow = p_smem + row * 128;
+#pragma unroll
+      for (int c = 0; c < BN / 8; ++c) {
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          e[i] = exp2f(sv[c * 8 + i] - ref);
+          l += e[i];
+        }
+        uint4 packed;
+        packed.x = pack_bf16(e[0], e[1]);
+        packed.y = pack_bf16(e[2], e[3]);
+        packed.z = pack_bf16(e[4], e[5]);
+        packed.w = pack_bf16(e[6], e[7]);
+        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = packed;
+      }
+      fence_async_shared();
+      tcgen05_fence_before();
+      mbar_arrive(p_full);
+    }
+    if (ok) {
+      if (!mbar_wait(o_done, (ntiles - 1) & 1)) {
+        atomicExch(&g_attn_error, 5);
+      } else {
+        tcgen05_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        bf16* dst = p.out + (static_cast<size_t>(tok0 + tl) * p.nq + head0 + g) * D;
+        uint32_t r[32];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          tmem_ld_32(lane_base + O_COL + c * 32, r);   // warp-collective: every lane takes part
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 q;
+              q.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+              q.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+              q.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+              q.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + i) = q;
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// rows x cols bf16 matrix with `row_bytes` between rows; box = [box_rows, 64 columns], 128-byte swizzle
+static int make_map_2d(CUtensorMap* map, const void* base, uint64_t rows, int cols, int box_rows) {
+  EncodeTiledFn fn = tensor_map_encoder();
+  if (!fn) return 10005;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), rows};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : 10006;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_attention_tcgen05_error() {
+  int v = 0, zero = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(int));
+  cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int));
+  return v;
+}
+
+// Tokens per CTA for a group of `group` query heads per KV head: the caller cuts entries into
+// tiles of that many consecutive tokens.
+extern "C" int b200_attention_tcgen05_tokens_per_tile(int group) {
+  const int gs = group < 16 ? group : 16;
+  return BM / gs;
+}
+
+// q, out: [tokens, nq, D]; pools: [pages, nkv, page_size, D].  page_size must be 8, 16, 32 or 64.
+extern "C" int b200_attention_prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                              const int* positions, const int* block_table, int table_stride,
+                                              int page_size, int num_pages, int tokens, int nq, int nkv, float scale,
+                                              const int* tile_entry, const int* tile_start, const int* tile_count,
+                                              int num_tiles, cudaStream_t stream) {
+  if (num_tiles <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || table_stride <= 0 || tokens <= 0) return B200_ERR_BAD_SIZE;
+  if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return B200_ERR_BAD_SIZE;
+  TcAttnParams p{};
+  p.out = static_cast<bf16*>(out);
+  p.positions = positions;
+  p.block_table = block_table;
+  p.table_stride = table_stride;
+  p.page_size = page_size;
+  p.page_shift = page_size == 8 ? 3 : (page_size == 16 ? 4 : (page_size == 32 ? 5 : 6));
+  p.nq = nq;
+  p.nkv = nkv;
+  p.group = nq / nkv;
+  p.gs = p.group < 16 ? p.group : 16;
+  p.slices = (p.group + p.gs - 1) / p.gs;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.tile_entry = tile_entry;
+  p.tile_start = tile_start;
+  p.tile_count = tile_count;
+
+  CUtensorMap map_q, map_k, map_v;
+  {
+    EncodeTiledFn fn = tensor_map_encoder();
+    if (!fn) return 10005;
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(nq), static_cast<cuuint64_t>(tokens)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(nq) * D * 2};
+    const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(p.gs), static_cast<cuuint32_t>(BM / p.gs)};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    if (fn(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return 10006;
+  }
+  const uint64_t pool_rows = static_cast<uint64_t>(num_pages) * nkv * page_size;
+  if (int e = make_map_2d(&map_k, k_pool, pool_rows, D, page_size)) return e;
+  if (int e = make_map_2d(&map_v, v_pool, pool_rows, D, page_size)) return e;
+
+  constexpr size_t smem = SMEM_TILES + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  dim3 grid(num_tiles, nkv * p.slices);
+  if (grid.y > 65535) return B200_ERR_TOO_LARGE;
+  launch(prefill_attention_tcgen05_kernel, grid, dim3(kTcThreads), smem, stream, map_q, map_k, map_v, p);
+  return launch_status();
+}

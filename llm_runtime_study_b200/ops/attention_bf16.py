@@ -4,6 +4,8 @@ from __future__ import annotations
 
 from typing import Any
 
+import os
+
 import numpy as np
 import torch
 
@@ -25,6 +27,30 @@ _TABLE = {
 }
 
 
+_TC_TABLE = {
+    "b200_attention_tcgen05_error": [],
+    "b200_attention_tcgen05_tokens_per_tile": [c_int],
+    "b200_attention_prefill_tcgen05": [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_int, c_int, c_float] + [c_void_p] * 3 + [c_int, c_void_p],
+}
+TC_HEAD_DIMS = (64, 128)
+TC_PAGE_SIZES = (8, 16, 32, 64)
+TC_MIN_PORTION = 32     # shorter portions only: the mma.sync kernel wastes fewer rows
+PREFILL_BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_ATTENTION", "tcgen05")
+
+
+def tc_library_name(head_dim: int) -> str:
+    name = f"b200_attention_tcgen05_d{head_dim}"
+    if name not in native.library_specs():
+        native.register_library(name, ("attention_tcgen05.cu",), _TC_TABLE, defines=(f"HEAD_DIM={head_dim}",))
+    return name
+
+
+def tc_supported(head_dim: int, page_size: int, window: int) -> bool:
+    """The tcgen05 kernel takes head sizes 64 and 128, pages of 8 to 64 tokens, no window."""
+
+    return head_dim in TC_HEAD_DIMS and page_size in TC_PAGE_SIZES and not window
+
+
 def library_name(head_dim: int) -> str:
     name = f"b200_attention_mma_d{head_dim}"
     if name not in native.library_specs():
@@ -43,6 +69,9 @@ def build(head_dim: int) -> None:
 
     name = library_name(head_dim)
     build_library(name, ("attention_mma.cu",), native.library_defines(name))
+    if head_dim in TC_HEAD_DIMS:
+        name = tc_library_name(head_dim)
+        build_library(name, ("attention_tcgen05.cu",), native.library_defines(name))
 
 
 def decode_splits(requests: int, kv_heads: int, slices: int, longest: int) -> int:
@@ -106,6 +135,39 @@ def prefill_attention(
     return out
 
 
+def prefill_attention_tcgen05(
+    q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, *, positions: torch.Tensor, block_table: torch.Tensor,
+    q_lens, scale: float, tiles: tuple[torch.Tensor, int] | None = None,
+) -> torch.Tensor:
+    """The same contract as ``prefill_attention`` (no window), on tcgen05 tensor cores with
+    TMEM accumulators and TMA loads of the pages."""
+
+    for t, name in ((q, "q"), (keys, "keys"), (values, "values")):
+        native.require(t, name, dtype=torch.bfloat16)
+    n, nq, d, nkv, page_size, gs, _ = _geometry(q, keys)
+    if not tc_supported(d, page_size, 0):
+        raise KernelError(f"the tcgen05 attention kernel does not take head size {d} with pages of {page_size}")
+    lib = tc_library_name(d)
+    if tiles is None:
+        tiles = tile_map(q_lens, 128 // gs, q.device)
+    table, count = tiles
+    out = torch.empty_like(q)
+    native.call(
+        "b200_attention_prefill_tcgen05", q.data_ptr(), keys.data_ptr(), values.data_ptr(), out.data_ptr(),
+        positions.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, keys.shape[0], n, nq, nkv,
+        float(scale), table[0].data_ptr(), table[1].data_ptr(), table[2].data_ptr(), count, native.stream_ptr(),
+        library=lib)
+    return out
+
+
+def check_tcgen05_error(head_dim: int) -> None:
+    """Synchronise and raise if a bounded wait inside the tcgen05 attention kernel ran out."""
+
+    code = native.query("b200_attention_tcgen05_error", library=tc_library_name(head_dim))
+    if code:
+        raise KernelError(f"tcgen05 attention: a bounded wait ran out (code {code})")
+
+
 def decode_attention(
     q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, *, kv_len: torch.Tensor, block_table: torch.Tensor,
     scale: float, window: int = 0, splits: int = 1,
@@ -141,6 +203,14 @@ def try_paged_attention(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Tens
         return decode_attention(q, cache.keys, cache.values, kv_len=ctx.kv_len, block_table=table, scale=scale,
                                 window=window, splits=decode_splits(n, nkv, slices, ctx.max_kv_len))
     maps = ctx.__dict__.setdefault("_tile_maps", {})
+    page_size = cache.keys.shape[2]
+    if PREFILL_BACKEND == "tcgen05" and tc_supported(d, page_size, window) and ctx.max_q_len >= TC_MIN_PORTION:
+        per_tile = 128 // gs
+        key = ("tc", per_tile)
+        if key not in maps:
+            maps[key] = tile_map(ctx.q_lens, per_tile, q.device)
+        return prefill_attention_tcgen05(q, cache.keys, cache.values, positions=ctx.positions, block_table=table,
+                                         q_lens=ctx.q_lens, scale=scale, tiles=maps[key])
     per_tile = 64 // gs
     if per_tile not in maps:
         maps[per_tile] = tile_map(ctx.q_lens, per_tile, q.device)

@@ -386,3 +386,42 @@ def test_projections_refuse_unaligned_widths():
         _gemm().linear_skinny(x, w)
     with pytest.raises(KernelError, match="multiple of 8"):
         _gemm().linear(x, w)
+
+
+# ------------------------------------------------------------- tcgen05 prefill attention
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (32, 8, 128, 16), (4, 4, 64, 8), (6, 1, 64, 32), (5, 1, 128, 64),
+                                           (32, 1, 64, 16), (12, 2, 128, 8)])
+def test_prefill_attention_tcgen05(nq, nkv, d, page):
+    q, kp, vp, pos, ent, table, want = _attention_case(
+        torch.bfloat16, nq, nkv, d, page, [(1, 1), (33, 33), (70, 5), (131, 1), (64, 2), (200, 200), (129, 65), (513, 300)])
+    out = _mma().prefill_attention_tcgen05(dev(q), dev(kp), dev(vp), positions=dev(pos), block_table=dev(table),
+                                           q_lens=_q_lens(ent), scale=1 / math.sqrt(d))
+    _mma().check_tcgen05_error(d)
+    torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
+
+
+@pytest.mark.parametrize("boost", [0, 15, 16, 63, 64, -2, 300, 511, 512])
+def test_tcgen05_attention_finds_a_far_key(boost):
+    nq, nkv, d, page = 8, 2, 64, 16
+    q, kp, vp, pos, ent, table, want = _attention_case(torch.bfloat16, nq, nkv, d, page, [(700, 3)], boost=boost)
+    out = _mma().prefill_attention_tcgen05(dev(q), dev(kp), dev(vp), positions=dev(pos), block_table=dev(table),
+                                           q_lens=[3], scale=1 / math.sqrt(d))
+    _mma().check_tcgen05_error(d)
+    torch.testing.assert_close(out.cpu().double(), want, atol=3e-2, rtol=2e-2)
+
+
+def test_tcgen05_attention_rescales_when_the_maximum_grows():
+    """Scores that keep growing along the sequence force the lazy rescaling of O in TMEM."""
+
+    torch.manual_seed(11)
+    nq, nkv, d, page, L = 4, 1, 64, 16, 400
+    q, k, v = torch.randn(L, nq, d), torch.randn(L, nkv, d), torch.randn(L, nkv, d)
+    k[:, :, 0] = torch.linspace(0, 40, L).view(L, 1)       # later keys score ever higher for positive q
+    q[:, :, 0] = 4.0
+    q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    want = plain.causal_attention(q.double(), k.double(), v.double(), 1 / math.sqrt(d))
+    kp, vp, ids = _scatter_to_pages(k, v, page, nkv, d, torch.bfloat16, seed=3)
+    out = _mma().prefill_attention_tcgen05(dev(q), dev(kp), dev(vp), positions=dev(torch.arange(L, dtype=torch.int32)),
+                                           block_table=dev(ids.view(1, -1)), q_lens=[L], scale=1 / math.sqrt(d))
+    _mma().check_tcgen05_error(d)
+    torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
