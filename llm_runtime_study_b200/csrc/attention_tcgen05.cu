@@ -4,11 +4,13 @@
 // One CTA owns 128 rows of S = Q K^T: up to 128 / gs consecutive query tokens of one request
 // times the gs query heads that share one KV head.  Keys are taken 64 at a time:
 //   warp 4     one lane issues TMA loads: the Q tile once (3-D map over [token, head, d]), then
-//              for every key tile the request's pages of K (two stages) and V (one stage), one
-//              box per page and 64-column half, found through the block table;
+//              for every key tile the request's pages of K and V (two stages each, running two
+//              tiles ahead), one box per page and 64-column half, found through the block table;
 //   warp 5     allocates TMEM; one lane issues tcgen05.mma: S = Q K^T (M 128, N 64, K = head size)
-//              into TMEM, and, once P is in shared memory, O += P V (M 128, N = head size, K 64)
-//              with V read as an MN-major operand (no transposition of the cache);
+//              into one of two S buffers in TMEM - the product for the next tile is issued before
+//              the softmax of the current one is awaited - and, once P is in shared memory,
+//              O += P V (M 128, N = head size, K 64) with V read as an MN-major operand (no
+//              transposition of the cache);
 //   warps 0-3  softmax: thread r owns row r of S (tcgen05.ld gives a thread its whole row, so
 //              the row maximum and sum need no shuffles); it masks, exponentiates in float32,
 //              writes P as bfloat16 into shared memory in the swizzled K-major layout the tensor
@@ -40,13 +42,21 @@ constexpr uint32_t Q_SUB = BM * 128;       // bytes of one Q sub-tile
 constexpr uint32_t KV_SUB = BN * 128;      // bytes of one K or V sub-tile
 constexpr uint32_t Q_BYTES = DSUB * Q_SUB, KV_BYTES = DSUB * KV_SUB, P_BYTES = BM * 128;
 constexpr int KSTAGES = 2;
-constexpr uint32_t SMEM_TILES = Q_BYTES + KSTAGES * KV_BYTES + KV_BYTES + P_BYTES;
-constexpr uint32_t TMEM_COLS = (64 + D) <= 128 ? 128 : 256;
-constexpr uint32_t S_COL = 0, O_COL = 64;
+constexpr uint32_t SMEM_TILES = Q_BYTES + 2 * KSTAGES * KV_BYTES + P_BYTES;
+constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t S_COL = 0, O_COL = 2 * BN;   // two S buffers of 64 columns, then O
 constexpr int kTcThreads = 192;
 constexpr float kRescaleStep = 8.f;        // log2 units a row maximum may lag behind
 
 __device__ int g_attn_error = 0;
+
+// 2^x for x <= 0 in one MUFU instruction (exp2f() adds range handling that is not needed here:
+// results below the normal range may flush to zero, which is what a vanishing weight should do)
+__device__ __forceinline__ float exp2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 
 struct TcAttnParams {
   bf16* out;
@@ -63,24 +73,27 @@ struct TcAttnParams {
 __global__ void __launch_bounds__(kTcThreads)
 prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* q_smem = smem;
   unsigned char* k_smem = q_smem + Q_BYTES;                 // [KSTAGES]
-  unsigned char* v_smem = k_smem + KSTAGES * KV_BYTES;
-  unsigned char* p_smem = v_smem + KV_BYTES;
+  unsigned char* v_smem = k_smem + KSTAGES * KV_BYTES;      // [KSTAGES]
+  unsigned char* p_smem = v_smem + KSTAGES * KV_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_TILES);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;       // [2]
   uint64_t* k_empty = bars + 3;      // [2]
-  uint64_t* v_full = bars + 5;
-  uint64_t* v_empty = bars + 6;
-  uint64_t* s_full = bars + 7;
-  uint64_t* p_full = bars + 8;
-  uint64_t* o_done = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* v_full = bars + 5;       // [2]
+  uint64_t* v_empty = bars + 7;      // [2]
+  uint64_t* s_full = bars + 9;       // [2]
+  uint64_t* p_full = bars + 11;      // [2]
+  uint64_t* o_done = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
 
   pdl_wait();
+  if ((smem_addr(smem) & 1023u) != 0) {      // the swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicExch(&g_attn_error, 9);
+    return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x;
   const int kvh = blockIdx.y / p.slices, slice = blockIdx.y % p.slices;
@@ -93,21 +106,21 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < KSTAGES; ++s) {
+    for (int s = 0; s < 2; ++s) {
       mbar_init(k_full + s, 1);
       mbar_init(k_empty + s, 1);
+      mbar_init(v_full + s, 1);
+      mbar_init(v_empty + s, 1);
+      mbar_init(s_full + s, 1);
+      mbar_init(p_full + s, BM);
     }
-    mbar_init(v_full, 1);
-    mbar_init(v_empty, 1);
-    mbar_init(s_full, 1);
-    mbar_init(p_full, BM);
     mbar_init(o_done, 1);
     fence_barrier_init();
   }
   if (warp == 5) tmem_alloc(tmem_slot, TMEM_COLS);
-  // Rows of the V stage that no page is ever copied into must hold finite numbers: a masked
+  // Rows of the V stages that no page is ever copied into must hold finite numbers: a masked
   // key has probability 0, and 0 * NaN would still be NaN.
-  for (uint32_t i = threadIdx.x; i < KV_BYTES / 16; i += kTcThreads)
+  for (uint32_t i = threadIdx.x; i < KSTAGES * KV_BYTES / 16; i += kTcThreads)
     reinterpret_cast<uint4*>(v_smem)[i] = make_uint4(0, 0, 0, 0);
   fence_async_shared();
   tcgen05_fence_before();
@@ -120,28 +133,42 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     mbar_expect_tx(q_full, DSUB * 128u * p.gs * tokens_per_cta);
     for (int sub = 0; sub < DSUB; ++sub) tma_load_3d(q_smem + sub * Q_SUB, &map_q, q_full, sub * 64, head0, tok0);
     const int pages_per_tile = BN / p.page_size;
-    auto load_pages = [&](unsigned char* dst, const CUtensorMap* map, uint64_t* bar, int j) {
-      int loaded = 0;
-      int ids[8];
-      for (int i = 0; i < pages_per_tile; ++i) {
+    // Page ids of a tile are fetched from the block table one tile ahead, so that the global
+    // load is in flight while this thread waits for a free stage.
+    auto fetch_ids = [&](int j, int (&ids)[8]) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
         const int t0 = j * BN + i * p.page_size;
-        ids[i] = t0 <= p_last ? table[t0 >> p.page_shift] : -1;
-        loaded += ids[i] >= 0;
+        ids[i] = (i < pages_per_tile && t0 <= p_last) ? table[t0 >> p.page_shift] : -1;
       }
+    };
+    auto load_pages = [&](unsigned char* dst, const CUtensorMap* map, uint64_t* bar, const int (&ids)[8]) {
+      int loaded = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) loaded += ids[i] >= 0;
       mbar_expect_tx(bar, static_cast<uint32_t>(loaded) * p.page_size * 128u * DSUB);
-      for (int i = 0; i < pages_per_tile; ++i) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
         if (ids[i] < 0) continue;
         const int y = (ids[i] * p.nkv + kvh) * p.page_size;
         for (int sub = 0; sub < DSUB; ++sub)
           tma_load_2d(dst + sub * KV_SUB + i * p.page_size * 128, map, bar, sub * 64, y);
       }
     };
+    // K and V of tile j go to stage j & 1; a stage is free again when the product that read it
+    // has completed (S(j-2) for K, P.V(j-2) for V): the first two tiles find their stages free.
+    int ids[8], next_ids[8];
+    fetch_ids(0, ids);
     for (int j = 0; j < ntiles; ++j) {
       const int s = j & 1;
-      if (!mbar_wait(k_empty + s, ((j >> 1) & 1) ^ 1)) { atomicExch(&g_attn_error, 1); break; }
-      load_pages(k_smem + s * KV_BYTES, &map_k, k_full + s, j);
-      if (!mbar_wait(v_empty, (j & 1) ^ 1)) { atomicExch(&g_attn_error, 1); break; }
-      load_pages(v_smem, &map_v, v_full, j);
+      const uint32_t parity = ((j >> 1) & 1) ^ 1;
+      if (j + 1 < ntiles) fetch_ids(j + 1, next_ids);
+      if (!mbar_wait(k_empty + s, parity)) { atomicExch(&g_attn_error, 1); break; }
+      load_pages(k_smem + s * KV_BYTES, &map_k, k_full + s, ids);
+      if (!mbar_wait(v_empty + s, parity)) { atomicExch(&g_attn_error, 1); break; }
+      load_pages(v_smem + s * KV_BYTES, &map_v, v_full + s, ids);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ids[i] = next_ids[i];
     }
   } else if (warp == 5 && lane == 0) {
     // ------------------------------------------------------------------ tensor-core issue
@@ -149,26 +176,36 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, D, 1);
     bool ok = mbar_wait(q_full, 0);
     if (!ok) atomicExch(&g_attn_error, 2);
-    const uint32_t q_addr = smem_addr(q_smem), p_addr = smem_addr(p_smem), v_addr = smem_addr(v_smem);
-    for (int j = 0; j < ntiles && ok; ++j) {
+    const uint32_t q_addr = smem_addr(q_smem), p_addr = smem_addr(p_smem);
+    auto issue_s = [&](int j) -> bool {        // S(j) = Q K_j^T into S buffer j & 1
       const int s = j & 1;
-      if (!mbar_wait(k_full + s, (j >> 1) & 1)) { atomicExch(&g_attn_error, 2); break; }
+      if (!mbar_wait(k_full + s, (j >> 1) & 1)) return false;
       tcgen05_fence_after();
       const uint32_t k_addr = smem_addr(k_smem + s * KV_BYTES);
 #pragma unroll
       for (int k = 0; k < D / 16; ++k)
-        umma_bf16_ss(tmem_base + S_COL, umma_desc_sw128(q_addr + (k >> 2) * Q_SUB + (k & 3) * 32, 16, 1024),
+        umma_bf16_ss(tmem_base + S_COL + s * BN, umma_desc_sw128(q_addr + (k >> 2) * Q_SUB + (k & 3) * 32, 16, 1024),
                      umma_desc_sw128(k_addr + (k >> 2) * KV_SUB + (k & 3) * 32, 16, 1024), idesc_s, k != 0);
-      umma_commit_to(s_full);
+      umma_commit_to(s_full + s);
       umma_commit_to(k_empty + s);
-      if (!mbar_wait(p_full, j & 1) || !mbar_wait(v_full, j & 1)) { atomicExch(&g_attn_error, 3); break; }
+      return true;
+    };
+    if (ok && !issue_s(0)) { atomicExch(&g_attn_error, 2); ok = false; }
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int s = j & 1;
+      // S of the next tile first: its buffer was read by the softmax of tile j - 1, which has
+      // arrived on p_full (waited for in the previous round); the tensor core then has work
+      // while the softmax of tile j runs.
+      if (j + 1 < ntiles && !issue_s(j + 1)) { atomicExch(&g_attn_error, 2); break; }
+      if (!mbar_wait(p_full, j & 1) || !mbar_wait(v_full + s, (j >> 1) & 1)) { atomicExch(&g_attn_error, 3); break; }
       tcgen05_fence_after();
+      const uint32_t v_addr = smem_addr(v_smem + s * KV_BYTES);
 #pragma unroll
       for (int k = 0; k < BN / 16; ++k)
         umma_bf16_ss(tmem_base + O_COL, umma_desc_sw128(p_addr + k * 32, 16, 1024),
                      umma_desc_sw128(v_addr + k * 2048, KV_SUB, 1024), idesc_pv, (j | k) != 0);
       umma_commit_to(o_done);
-      umma_commit_to(v_empty);
+      umma_commit_to(v_empty + s);
     }
   } else if (warp < 4) {
     // ------------------------------------------------------------------ softmax, one row per thread
@@ -177,39 +214,43 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const bool row_ok = tl < ntok && slice * p.gs + g < p.group;
     const int row_hi = p_first + tl;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    float m_used = -INFINITY, l = 0.f;
+    float m_used = -INFINITY, l = 0.f;       // m_used in units of log2, after scaling
     bool ok = true;
     for (int j = 0; j < ntiles; ++j) {
-      if (!mbar_wait(s_full, j & 1)) { atomicExch(&g_attn_error, 4); ok = false; break; }
+      if (!mbar_wait(s_full + (j & 1), (j >> 1) & 1)) { atomicExch(&g_attn_error, 4); ok = false; break; }
       tcgen05_fence_after();
       float sv[BN];
       {
         uint32_t r[32];
 #pragma unroll
         for (int c = 0; c < BN / 32; ++c) {
-          tmem_ld_32(lane_base + S_COL + c * 32, r);
+          tmem_ld_32(lane_base + S_COL + (j & 1) * BN + c * 32, r);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) sv[c * 32 + i] = __uint_as_float(r[i]) * p.scale_log2;
+          for (int i = 0; i < 32; ++i) sv[c * 32 + i] = __uint_as_float(r[i]);
         }
       }
       const int t0 = j * BN;
-      float m_tile = -INFINITY;
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (t0 + BN - 1 <= p_first) {          // every key of the tile is visible to every row of this CTA
 #pragma unroll
-        for (int i = 0; i < BN; ++i) m_tile = fmaxf(m_tile, sv[i]);
+        for (int i = 0; i < BN; ++i) mx[i & 3] = fmaxf(mx[i & 3], sv[i]);
       } else {
 #pragma unroll
         for (int i = 0; i < BN; ++i) {
           sv[i] = t0 + i <= row_hi ? sv[i] : -INFINITY;
-          m_tile = fmaxf(m_tile, sv[i]);
+          mx[i & 3] = fmaxf(mx[i & 3], sv[i]);
         }
       }
-      const float m_new = fmaxf(m_used, m_tile);
-      const bool grow = m_new > m_used + kRescaleStep;      // also true on the first tile (m_used = -inf)
+      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      const float m_new = fmaxf(m_used, m_tile * p.scale_log2);   // the scale is positive
+      const bool grow = m_new > m_used + kRescaleStep;            // also true on the first tile (m_used = -inf)
       if (j == 0) {
         m_used = m_new;
       } else if (__any_sync(0xffffffffu, grow)) {
-        // O of the tiles so far is complete: S of this tile was issued after their P.V products.
+        // O must hold every product issued so far and no later one: P.V(j-1) has been issued
+        // (it follows S(j), which is complete) and P.V(j) waits for this thread's arrival.
+        if (!mbar_wait(o_done, (j - 1) & 1)) { atomicExch(&g_attn_error, 5); ok = false; break; }
+        tcgen05_fence_after();
         const float factor = grow ? exp2f(m_used - m_new) : 1.f;
         if (grow) m_used = m_new;
         uint32_t r[32];
@@ -222,30 +263,35 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
         l *= factor;
       }
-      const float ref = m_used == -INFINITY ? 0.f : m_used;
-      unsigned char* prow = p_smem + row * 128;
+      const float neg_ref = m_used == -INFINITY ? 0.f : -m_used;
+      uint4 packed[BN / 8];
+      float lsum[4] = {0.f, 0.f, 0.f, 0.f};      // four chains instead of one long dependent sum
 #pragma unroll
       for (int c = 0; c < BN / 8; ++c) {
         float e[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          e[i] = exp2f(sv[c * 8 + i] - ref);
-          l += e[i];
+          e[i] = exp2_fast(fmaf(sv[c * 8 + i], p.scale_log2, neg_ref));
+          lsum[i & 3] += e[i];
         }
-        uint4 packed;
-        packed.x = pack_bf16(e[0], e[1]);
-        packed.y = pack_bf16(e[2], e[3]);
-        packed.z = pack_bf16(e[4], e[5]);
-        packed.w = pack_bf16(e[6], e[7]);
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = packed;
+        packed[c].x = pack_bf16(e[0], e[1]);
+        packed[c].y = pack_bf16(e[2], e[3]);
+        packed[c].z = pack_bf16(e[4], e[5]);
+        packed[c].w = pack_bf16(e[6], e[7]);
       }
+      l += (lsum[0] + lsum[1]) + (lsum[2] + lsum[3]);
+      // P is single buffered: the product that read the previous P must have completed.
+      if (j > 0 && !mbar_wait(o_done, (j - 1) & 1)) { atomicExch(&g_attn_error, 6); ok = false; break; }
+      unsigned char* prow = p_smem + row * 128;
+#pragma unroll
+      for (int c = 0; c < BN / 8; ++c) *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = packed[c];
       fence_async_shared();
       tcgen05_fence_before();
       mbar_arrive(p_full);
     }
     if (ok) {
       if (!mbar_wait(o_done, (ntiles - 1) & 1)) {
-        atomicExch(&g_attn_error, 5);
+        atomicExch(&g_attn_error, 7);
       } else {
         tcgen05_fence_after();
         const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -353,7 +399,7 @@ extern "C" int b200_attention_prefill_tcgen05(const void* q, const void* k_pool,
   if (int e = make_map_2d(&map_k, k_pool, pool_rows, D, page_size)) return e;
   if (int e = make_map_2d(&map_v, v_pool, pool_rows, D, page_size)) return e;
 
-  constexpr size_t smem = SMEM_TILES + 1024 + 256;
+  constexpr size_t smem = SMEM_TILES + 256;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(prefill_attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

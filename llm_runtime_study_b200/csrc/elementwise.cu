@@ -258,6 +258,91 @@ __global__ void __launch_bounds__(kRopeWarps * 32) qk_norm_rope_write_kernel(
   }
 }
 
+// The common case - the whole head is rotated (or none of it) and the head size is a multiple
+// of 4 - with two neighbouring pairs per lane: 4- or 8-byte loads and stores, no unused loop
+// iterations.  PITER = ceil(head_dim / 128).
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+  using type = float2;
+  __device__ static float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  __device__ static void store(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+};
+template <> struct Pair<__nv_bfloat16> {
+  using type = float2;
+  __device__ static float2 load(const __nv_bfloat16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+  __device__ static void store(__nv_bfloat16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
+};
+
+template <typename T, int PITER>
+__global__ void __launch_bounds__(kRopeWarps * 32) qk_norm_rope_write_vec_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ q_weight,
+    const float* __restrict__ k_weight, float eps, const float* __restrict__ inv_freq,
+    const int* __restrict__ positions, const int* __restrict__ token_entry,
+    const int* __restrict__ block_table, int table_stride, int page_size,
+    T* __restrict__ k_pool, T* __restrict__ v_pool, int nq, int nkv, int d, int qkv_stride) {
+  __shared__ float cs[32 * kMaxPairs], sn[32 * kMaxPairs];
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int token = blockIdx.x;
+  const int pos = positions[token];
+  const int half = d / 2;
+  if (inv_freq) {
+    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(static_cast<float>(pos) * inv_freq[j], &sn[j], &cs[j]);
+  }
+  __syncthreads();
+  int64_t kv_base = -1;
+  if (nkv > 0) {
+    const int page = block_table[static_cast<size_t>(token_entry[token]) * table_stride + pos / page_size];
+    if (page >= 0) kv_base = (static_cast<int64_t>(page) * nkv * page_size + pos % page_size) * d;
+  }
+  for (int h = blockIdx.y * kRopeWarps + warp; h < nq + 2 * nkv; h += gridDim.y * kRopeWarps) {
+    const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+    const T* src = qkv + static_cast<size_t>(token) * qkv_stride + static_cast<size_t>(h) * d;
+    T* dst;
+    if (is_q) {
+      dst = q_out + (static_cast<size_t>(token) * nq + h) * d;
+    } else {
+      if (kv_base < 0) continue;
+      const int kvh = is_k ? h - nq : h - nq - nkv;
+      dst = (is_k ? k_pool : v_pool) + kv_base + static_cast<int64_t>(kvh) * page_size * d;
+    }
+    float2 lo[PITER], hi[PITER];
+    float ss = 0.f;
+#pragma unroll
+    for (int p = 0; p < PITER; ++p) {
+      const int j = 2 * lane + 64 * p;
+      lo[p] = hi[p] = make_float2(0.f, 0.f);
+      if (j < half) {
+        lo[p] = Pair<T>::load(src + j);
+        hi[p] = Pair<T>::load(src + j + half);
+        ss += lo[p].x * lo[p].x + lo[p].y * lo[p].y + hi[p].x * hi[p].x + hi[p].y * hi[p].y;
+      }
+    }
+    const float* w = is_q ? q_weight : (is_k ? k_weight : nullptr);
+    const float r = w ? rsqrtf(warp_sum(ss) / static_cast<float>(d) + eps) : 1.f;
+    const bool rotate = inv_freq != nullptr && (is_q || is_k);
+#pragma unroll
+    for (int p = 0; p < PITER; ++p) {
+      const int j = 2 * lane + 64 * p;
+      if (j >= half) continue;
+      float2 a = lo[p], b = hi[p];
+      if (w) {
+        a.x *= r * w[j]; a.y *= r * w[j + 1];
+        b.x *= r * w[j + half]; b.y *= r * w[j + half + 1];
+      }
+      if (rotate) {
+        const float c0 = cs[j], s0 = sn[j], c1 = cs[j + 1], s1 = sn[j + 1];
+        Pair<T>::store(dst + j, a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+        Pair<T>::store(dst + j + half, b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+      } else {
+        Pair<T>::store(dst + j, a.x, a.y);
+        Pair<T>::store(dst + j + half, b.x, b.y);
+      }
+    }
+  }
+}
+
 template <typename T>
 static void launch_norm_vec(float* resid, const float* delta, const float* weight, T* out, const int* rows, int n,
                             int hidden, float eps, int write_resid, cudaStream_t stream) {
@@ -349,6 +434,24 @@ extern "C" int b200_qk_norm_rope_write(
   if (rotary_dim / 2 > 32 * kMaxPairs || d > 32 * kMaxTail) return B200_ERR_TOO_LARGE;
   const int heads = nq + 2 * nkv;
   const int head_blocks = n >= 512 ? 1 : (heads + kRopeWarps - 1) / kRopeWarps;
+  const bool whole_head = inv_freq == nullptr || rotary_dim == d;
+  const bool aligned4 = ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                          reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool)) & 7) == 0;
+  if (whole_head && d % 4 == 0 && d <= 256 && qkv_stride % 2 == 0 && aligned4) {
+    B200_DISPATCH_DTYPE(dtype, T, {
+      auto* in = static_cast<const T*>(qkv);
+      auto* qo = static_cast<T*>(q_out);
+      auto* kp = static_cast<T*>(k_pool);
+      auto* vp = static_cast<T*>(v_pool);
+      if (d <= 128)
+        launch(qk_norm_rope_write_vec_kernel<T, 1>, dim3(n, head_blocks), dim3(kRopeWarps * 32), 0, stream, in, qo, q_weight,
+               k_weight, eps, inv_freq, positions, token_entry, block_table, table_stride, page_size, kp, vp, nq, nkv, d, qkv_stride);
+      else
+        launch(qk_norm_rope_write_vec_kernel<T, 2>, dim3(n, head_blocks), dim3(kRopeWarps * 32), 0, stream, in, qo, q_weight,
+               k_weight, eps, inv_freq, positions, token_entry, block_table, table_stride, page_size, kp, vp, nq, nkv, d, qkv_stride);
+    });
+    return launch_status();
+  }
   B200_DISPATCH_DTYPE(dtype, T,
       launch(qk_norm_rope_write_kernel<T>, dim3(n, head_blocks), dim3(kRopeWarps * 32), 0, stream, 
           static_cast<const T*>(qkv), static_cast<T*>(q_out), q_weight, k_weight, eps, inv_freq,

@@ -90,15 +90,22 @@ def decode_splits(requests: int, kv_heads: int, slices: int, longest: int) -> in
     return best
 
 
-def tile_map(q_lens, tokens_per_tile: int, device) -> tuple[torch.Tensor, int]:
-    """Cut every entry into tiles of consecutive tokens: rows [entry, first token, count]."""
+def tile_map(q_lens, tokens_per_tile: int, device, kv_lens=None) -> tuple[torch.Tensor, int]:
+    """Cut every entry into tiles of consecutive tokens: rows [entry, first token, count].
+    With ``kv_lens`` (each entry's length after this step) the tiles are ordered by
+    falling number of keys they attend to, so that the longest start first and the
+    short ones fill the tail of the launch."""
 
     rows, first = [], 0
     for entry, n in enumerate(q_lens):
+        before = 0 if kv_lens is None else kv_lens[entry] - n
         for s in range(0, n, tokens_per_tile):
-            rows.append((entry, first + s, min(tokens_per_tile, n - s)))
+            count = min(tokens_per_tile, n - s)
+            rows.append((before + s + count, entry, first + s, count))
         first += n
-    table = np.ascontiguousarray(np.asarray(rows, dtype=np.int32).T)
+    if kv_lens is not None:
+        rows.sort(key=lambda r: -r[0])
+    table = np.ascontiguousarray(np.asarray([r[1:] for r in rows], dtype=np.int32).T)
     return torch.from_numpy(table).to(device), len(rows)
 
 
@@ -208,11 +215,11 @@ def try_paged_attention(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Tens
         per_tile = 128 // gs
         key = ("tc", per_tile)
         if key not in maps:
-            maps[key] = tile_map(ctx.q_lens, per_tile, q.device)
+            maps[key] = tile_map(ctx.q_lens, per_tile, q.device, ctx.kv_lens)
         return prefill_attention_tcgen05(q, cache.keys, cache.values, positions=ctx.positions, block_table=table,
                                          q_lens=ctx.q_lens, scale=scale, tiles=maps[key])
     per_tile = 64 // gs
     if per_tile not in maps:
-        maps[per_tile] = tile_map(ctx.q_lens, per_tile, q.device)
+        maps[per_tile] = tile_map(ctx.q_lens, per_tile, q.device, ctx.kv_lens)
     return prefill_attention(q, cache.keys, cache.values, positions=ctx.positions, block_table=table,
                              q_lens=ctx.q_lens, scale=scale, window=window, tiles=maps[per_tile])

@@ -18,7 +18,10 @@ native.register_library(
 
 native.register_library(
     "b200_gemm_skinny", ("gemm_skinny.cu",),
-    {"b200_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]},
+    {
+        "b200_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "b200_gemm_skinny_variant": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    },
 )
 
 SKINNY_M = 16         # up to here weights are streamed straight into mma.sync fragments
@@ -78,7 +81,7 @@ def check_error() -> None:
 
 
 def linear_skinny(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
-                  out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+                  out_dtype: torch.dtype = torch.bfloat16, *, variant: int = 0) -> torch.Tensor:
     """``x @ weight.T (+ bias)`` for at most 16 rows of ``x``: the weight-streaming kernel."""
 
     native.require(x, "x", dtype=torch.bfloat16, dims=2)
@@ -92,6 +95,6 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
     if bias is not None:
         native.require(bias, "bias", dtype=torch.float32, shape=(n,))
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-    native.call("b200_gemm_skinny", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k, n,
-                1 if out_dtype == torch.float32 else 0, native.stream_ptr())
+    native.call("b200_gemm_skinny_variant", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k, n,
+                1 if out_dtype == torch.float32 else 0, variant, native.stream_ptr())
     return out
