@@ -221,12 +221,14 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       tcgen05_fence_after();
       float sv[BN];
       {
-        uint32_t r[32];
+        uint32_t r0[32], r1[32];            // both halves in flight, one wait
+        tmem_ld_32_nowait(lane_base + S_COL + (j & 1) * BN, r0);
+        tmem_ld_32_nowait(lane_base + S_COL + (j & 1) * BN + 32, r1);
+        tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          tmem_ld_32(lane_base + S_COL + (j & 1) * BN + c * 32, r);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) sv[c * 32 + i] = __uint_as_float(r[i]);
+        for (int i = 0; i < 32; ++i) {
+          sv[i] = __uint_as_float(r0[i]);
+          sv[32 + i] = __uint_as_float(r1[i]);
         }
       }
       const int t0 = j * BN;
