@@ -258,6 +258,32 @@ __global__ void __launch_bounds__(kRopeWarps * 32) qk_norm_rope_write_kernel(
   }
 }
 
+// Gate and up columns interleaved in blocks of eight: [g0..g7 | u0..u7 | g8..g15 | u8..u15 | ...],
+// the layout in which the stacked gate/up projection is stored so that a projection kernel
+// can apply SiLU * up in its epilogue.  `inter` is a multiple of 8.
+template <typename T>
+__global__ void silu_mul_interleaved_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = blockIdx.y;
+  const int block8 = blockIdx.x * blockDim.x + threadIdx.x;     // which group of eight features
+  if (block8 * 8 >= inter) return;
+  const T* src = gate_up + row * 2 * inter + static_cast<size_t>(block8) * 16;
+  T* dst = out + row * inter + static_cast<size_t>(block8) * 8;
+  constexpr int VN = Vec<T>::n;
+  using V = typename Vec<T>::type;
+  float g[8], u[8];
+#pragma unroll
+  for (int i = 0; i < 8; i += VN) {
+    Vec<T>::unpack(*reinterpret_cast<const V*>(src + i), g + i);
+    Vec<T>::unpack(*reinterpret_cast<const V*>(src + 8 + i), u + i);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) g[i] = g[i] / (1.f + expf(-g[i])) * u[i];
+#pragma unroll
+  for (int i = 0; i < 8; i += VN) *reinterpret_cast<V*>(dst + i) = Vec<T>::pack(g + i);
+}
+
 // The common case - the whole head is rotated (or none of it) and the head size is a multiple
 // of 4 - with two neighbouring pairs per lane: 4- or 8-byte loads and stores, no unused loop
 // iterations.  PITER = ceil(head_dim / 128).
@@ -419,6 +445,18 @@ extern "C" int b200_silu_mul(const void* gate_up, void* out, int n, int inter, i
       launch(silu_mul_kernel<T>, dim3(grid), dim3(256), 0, stream, static_cast<const T*>(gate_up), static_cast<T*>(out), inter);
     }
   });
+  return launch_status();
+}
+
+extern "C" int b200_silu_mul_interleaved(const void* gate_up, void* out, int n, int inter, int dtype,
+                                         cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (inter <= 0 || inter % 8 != 0 || n > 65535) return B200_ERR_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) return B200_ERR_BAD_SIZE;
+  dim3 grid((inter / 8 + 127) / 128, n);
+  B200_DISPATCH_DTYPE(dtype, T,
+      launch(silu_mul_interleaved_kernel<T>, grid, dim3(128), 0, stream, static_cast<const T*>(gate_up),
+             static_cast<T*>(out), inter));
   return launch_status();
 }
 

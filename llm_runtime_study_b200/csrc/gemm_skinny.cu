@@ -23,7 +23,7 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   return v;
 }
 
-template <int NT, int UNROLL, int kSkinnyWarps, typename OutT>
+template <int NT, int UNROLL, int kSkinnyWarps, bool SWIGLU, typename OutT>
 __global__ void __launch_bounds__(kSkinnyWarps * 32)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
                    const float* __restrict__ bias, OutT* __restrict__ C, int M, int N, int K, int ldc) {
@@ -92,15 +92,35 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
     red[warp][g + 8][j * 8 + 2 * t + 1] = c[j][3];
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += kSkinnyWarps * 32) {
-    const int m = idx >> 4, row = idx & 15;   // consecutive threads -> consecutive output features
-    const int n = n0 + row;
-    if (m >= M || n >= N) continue;
-    float acc = 0.f;
+  if constexpr (SWIGLU) {
+    // rows 0..7 of the tile are gate features, rows 8..15 the matching up features
+    for (int idx = threadIdx.x; idx < 8 * NT * 8; idx += kSkinnyWarps * 32) {
+      const int m = idx >> 3, f = idx & 7;
+      const int n = n0 + f;                      // gate row in W; the output feature is n0 / 2 + f
+      if (m >= M || n + 8 >= N) continue;
+      float gate = 0.f, up = 0.f;
 #pragma unroll
-    for (int w = 0; w < kSkinnyWarps; ++w) acc += red[w][row][m];
-    acc += bias ? bias[n] : 0.f;
-    C[static_cast<size_t>(m) * ldc + n] = from_float<OutT>(acc);
+      for (int w = 0; w < kSkinnyWarps; ++w) {
+        gate += red[w][f][m];
+        up += red[w][f + 8][m];
+      }
+      if (bias) {
+        gate += bias[n];
+        up += bias[n + 8];
+      }
+      C[static_cast<size_t>(m) * ldc + (n0 >> 1) + f] = from_float<OutT>(gate / (1.f + expf(-gate)) * up);
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += kSkinnyWarps * 32) {
+      const int m = idx >> 4, row = idx & 15;   // consecutive threads -> consecutive output features
+      const int n = n0 + row;
+      if (m >= M || n >= N) continue;
+      float acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < kSkinnyWarps; ++w) acc += red[w][row][m];
+      acc += bias ? bias[n] : 0.f;
+      C[static_cast<size_t>(m) * ldc + n] = from_float<OutT>(acc);
+    }
   }
 }
 
@@ -111,22 +131,34 @@ using namespace b200;
 // M <= 16, K a multiple of 8, W and X 16-byte aligned; otherwise refused.
 template <int NT, int UNROLL, int WARPS>
 static void launch_skinny(const __nv_bfloat16* w, const __nv_bfloat16* x, const float* bias, void* C, int M, int N, int K,
-                          int ldc, int out_f32, cudaStream_t stream) {
+                          int ldc, int out_f32, int swiglu, cudaStream_t stream) {
   const int grid = (N + 15) / 16;
+  if (swiglu) {
+    if (out_f32)
+      launch(gemm_skinny_kernel<NT, UNROLL, WARPS, true, float>, dim3(grid), dim3(WARPS * 32), 0, stream, w, x, bias,
+             static_cast<float*>(C), M, N, K, ldc);
+    else
+      launch(gemm_skinny_kernel<NT, UNROLL, WARPS, true, __nv_bfloat16>, dim3(grid), dim3(WARPS * 32), 0, stream, w, x, bias,
+             static_cast<__nv_bfloat16*>(C), M, N, K, ldc);
+    return;
+  }
   if (out_f32)
-    launch(gemm_skinny_kernel<NT, UNROLL, WARPS, float>, dim3(grid), dim3(WARPS * 32), 0, stream, w, x, bias,
+    launch(gemm_skinny_kernel<NT, UNROLL, WARPS, false, float>, dim3(grid), dim3(WARPS * 32), 0, stream, w, x, bias,
            static_cast<float*>(C), M, N, K, ldc);
   else
-    launch(gemm_skinny_kernel<NT, UNROLL, WARPS, __nv_bfloat16>, dim3(grid), dim3(WARPS * 32), 0, stream, w, x, bias,
+    launch(gemm_skinny_kernel<NT, UNROLL, WARPS, false, __nv_bfloat16>, dim3(grid), dim3(WARPS * 32), 0, stream, w, x, bias,
            static_cast<__nv_bfloat16*>(C), M, N, K, ldc);
 }
 
 // M <= 16, K a multiple of 8, W and X 16-byte aligned; otherwise refused.
 // `variant` picks the shape of a CTA (0: the default for the size; 1..3: experiments).
+// `swiglu` = 1: W holds gate and up rows interleaved in blocks of eight (N a multiple of 16);
+// the output is silu(gate) * up, N / 2 columns wide (ldc >= N / 2).
 extern "C" int b200_gemm_skinny_variant(const void* X, const void* W, const float* bias, void* C, int M, int N, int K,
-                                        int ldc, int out_f32, int variant, cudaStream_t stream) {
+                                        int ldc, int out_f32, int variant, int swiglu, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (M > 16 || K <= 0 || K % 8 != 0 || ldc < N) return B200_ERR_BAD_SIZE;
+  if (M > 16 || K <= 0 || K % 8 != 0 || ldc < (swiglu ? N / 2 : N)) return B200_ERR_BAD_SIZE;
+  if (swiglu && N % 16 != 0) return B200_ERR_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W)) & 15) return B200_ERR_BAD_SIZE;
   const auto* w = static_cast<const __nv_bfloat16*>(W);
   const auto* x = static_cast<const __nv_bfloat16*>(X);
@@ -139,16 +171,16 @@ extern "C" int b200_gemm_skinny_variant(const void* X, const void* W, const floa
   }
   if (M <= 8) {
     switch (variant) {
-      case 1: launch_skinny<1, 8, 4>(w, x, bias, C, M, N, K, ldc, out_f32, stream); break;
-      case 2: launch_skinny<1, 4, 8>(w, x, bias, C, M, N, K, ldc, out_f32, stream); break;
-      case 3: launch_skinny<1, 4, 4>(w, x, bias, C, M, N, K, ldc, out_f32, stream); break;
-      default: launch_skinny<1, 8, 8>(w, x, bias, C, M, N, K, ldc, out_f32, stream); break;
+      case 1: launch_skinny<1, 8, 4>(w, x, bias, C, M, N, K, ldc, out_f32, swiglu, stream); break;
+      case 2: launch_skinny<1, 4, 8>(w, x, bias, C, M, N, K, ldc, out_f32, swiglu, stream); break;
+      case 3: launch_skinny<1, 4, 4>(w, x, bias, C, M, N, K, ldc, out_f32, swiglu, stream); break;
+      default: launch_skinny<1, 8, 8>(w, x, bias, C, M, N, K, ldc, out_f32, swiglu, stream); break;
     }
   } else {
     switch (variant) {
-      case 1: launch_skinny<2, 4, 4>(w, x, bias, C, M, N, K, ldc, out_f32, stream); break;
-      case 2: launch_skinny<2, 2, 8>(w, x, bias, C, M, N, K, ldc, out_f32, stream); break;
-      default: launch_skinny<2, 4, 8>(w, x, bias, C, M, N, K, ldc, out_f32, stream); break;
+      case 1: launch_skinny<2, 4, 4>(w, x, bias, C, M, N, K, ldc, out_f32, swiglu, stream); break;
+      case 2: launch_skinny<2, 2, 8>(w, x, bias, C, M, N, K, ldc, out_f32, swiglu, stream); break;
+      default: launch_skinny<2, 4, 8>(w, x, bias, C, M, N, K, ldc, out_f32, swiglu, stream); break;
     }
   }
   return launch_status();
@@ -156,5 +188,5 @@ extern "C" int b200_gemm_skinny_variant(const void* X, const void* W, const floa
 
 extern "C" int b200_gemm_skinny(const void* X, const void* W, const float* bias, void* C, int M, int N, int K,
                                 int ldc, int out_f32, cudaStream_t stream) {
-  return b200_gemm_skinny_variant(X, W, bias, C, M, N, K, ldc, out_f32, 0, stream);
+  return b200_gemm_skinny_variant(X, W, bias, C, M, N, K, ldc, out_f32, 0, 0, stream);
 }

@@ -136,6 +136,19 @@ __device__ __forceinline__ void store_row_32(__nv_bfloat16* dst, const float (&v
   }
 }
 
+__device__ __forceinline__ void store_row_8(float* dst, const float* v) {
+  *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store_row_8(__nv_bfloat16* dst, const float* v) {
+  uint4 q;
+  q.x = pack_bf16(v[0], v[1]);
+  q.y = pack_bf16(v[2], v[3]);
+  q.z = pack_bf16(v[4], v[5]);
+  q.w = pack_bf16(v[6], v[7]);
+  *reinterpret_cast<uint4*>(dst) = q;
+}
+
 struct GemmParams {
   void* c;
   const float* bias;
@@ -299,7 +312,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
 // of one 256-column panel are neighbours, so a wave of CTAs shares few weight panels in L2).
 // The accumulator is double buffered in TMEM (2 x 256 columns): while the epilogue warps
 // drain tile i, the tensor core already works on tile i + 1.
-template <int STAGES, typename OutT>
+// SWIGLU: the weight holds gate and up rows interleaved in blocks of eight; the epilogue
+// writes silu(gate) * up, N / 2 columns wide, and the [M, N] intermediate never exists.
+template <int STAGES, bool SWIGLU, typename OutT>
 __global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
                                GemmParams p) {
@@ -409,7 +424,28 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, con
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] += nb + j < p.N ? p.bias[nb + j] : 0.f;
           }
-          if (p.vector_ok && nb + 32 <= p.N) {
+          if constexpr (SWIGLU) {
+            // [g0..7 | u0..7 | g8..15 | u8..15] -> 16 outputs at column nb / 2 (N is a multiple of 16)
+            float h[16];
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float gate = v[b * 16 + j], up = v[b * 16 + 8 + j];
+                h[b * 8 + j] = gate / (1.f + __expf(-gate)) * up;
+              }
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+              if (nb + b * 16 + 16 > p.N) continue;
+              OutT* dst = crow + (nb >> 1) + b * 8;
+              if (p.vector_ok) {
+                store_row_8(dst, h + b * 8);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) store_out<OutT>(dst + j, h[b * 8 + j]);
+              }
+            }
+          } else if (p.vector_ok && nb + 32 <= p.N) {
             store_row_32(crow + nb, v);
           } else {
 #pragma unroll
@@ -493,10 +529,10 @@ static int launch(const CUtensorMap& rows, const CUtensorMap& cols, const GemmPa
   return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
-template <int STAGES, typename OutT>
+template <int STAGES, bool SWIGLU, typename OutT>
 static int launch_persistent(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, cudaStream_t stream) {
   constexpr size_t smem = STAGES * (BM * BK * 2 + 256 * BK * 2) + 1024 + 256;
-  auto kernel = gemm_tcgen05_persistent_kernel<STAGES, OutT>;
+  auto kernel = gemm_tcgen05_persistent_kernel<STAGES, SWIGLU, OutT>;
   static bool configured = false;
   static int sm_count = 0;
   if (!configured) {
@@ -531,10 +567,26 @@ extern "C" int b200_gemm_tcgen05_error() {
 // K must be a multiple of 8 and both bases 16-byte aligned (TMA); refused otherwise.
 // splits > 0 selects the swapped kernel for M <= 64 with the K range cut into `splits` (1..8) parts;
 // splits == 0 the persistent kernel; splits < 0 the one-tile-per-CTA kernel.
+static int gemm_tcgen05_impl(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
+                             int out_f32, int splits, int swiglu, cudaStream_t stream);
+
 extern "C" int b200_gemm_tcgen05(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
                                  int out_f32, int splits, cudaStream_t stream) {
+  return gemm_tcgen05_impl(A, W, bias, C, M, N, K, ldc, out_f32, splits, 0, stream);
+}
+
+// The persistent kernel with the SwiGLU epilogue: W = gate and up rows interleaved in blocks of
+// eight (N a multiple of 16), C = silu(gate) * up with N / 2 columns (ldc >= N / 2).
+extern "C" int b200_gemm_tcgen05_swiglu(const void* A, const void* W, const float* bias, void* C, int M, int N, int K,
+                                        int ldc, int out_f32, cudaStream_t stream) {
+  if (N % 16 != 0) return B200_ERR_BAD_SIZE;
+  return gemm_tcgen05_impl(A, W, bias, C, M, N, K, ldc, out_f32, 0, 1, stream);
+}
+
+static int gemm_tcgen05_impl(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
+                             int out_f32, int splits, int swiglu, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 != 0 || ldc < N) return B200_ERR_BAD_SIZE;
+  if (K <= 0 || K % 8 != 0 || ldc < (swiglu ? N / 2 : N)) return B200_ERR_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return B200_ERR_BAD_SIZE;
   GemmParams p{C, bias, M, N, K, ldc, (ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0, 0};
   CUtensorMap rows, cols;
@@ -563,6 +615,9 @@ extern "C" int b200_gemm_tcgen05(const void* A, const void* W, const float* bias
     return out_f32 ? launch<BN, 4, false, float>(rows, cols, p, grid, 1, stream)
                    : launch<BN, 4, false, __nv_bfloat16>(rows, cols, p, grid, 1, stream);
   }
-  return out_f32 ? launch_persistent<4, float>(rows, cols, p, stream)
-                 : launch_persistent<4, __nv_bfloat16>(rows, cols, p, stream);
+  if (swiglu)
+    return out_f32 ? launch_persistent<4, true, float>(rows, cols, p, stream)
+                   : launch_persistent<4, true, __nv_bfloat16>(rows, cols, p, stream);
+  return out_f32 ? launch_persistent<4, false, float>(rows, cols, p, stream)
+                 : launch_persistent<4, false, __nv_bfloat16>(rows, cols, p, stream);
 }

@@ -39,6 +39,7 @@ class Engine:
     max_cache_tokens: int | None = None
     page_policy: str = "on_demand"
     tokenizer: Any = None
+    source: Any = None   # how the weights were obtained: ("dir", path) or ("random", config, seed, on_device)
     _runner: StepRunner | None = field(default=None, init=False, repr=False)
     _sampler: Sampler | None = field(default=None, init=False, repr=False)
 
@@ -68,7 +69,8 @@ class Engine:
 
             tokenizer = load_tokenizer(model_dir)
         engine = cls(loaded=loaded, max_seq_len=max_seq_len, max_batch_size=max_batch_size,
-                     cache_backend=cache_backend, use_cuda_graph=use_cuda_graph, tokenizer=tokenizer, **options)
+                     cache_backend=cache_backend, use_cuda_graph=use_cuda_graph, tokenizer=tokenizer,
+                     source=("dir", Path(model_dir)), **options)
         engine.synchronize()
         engine.load_seconds = time.perf_counter() - started
         return engine
@@ -84,7 +86,7 @@ class Engine:
         started = time.perf_counter()
         loaded = load_random(config, seed, device=device, dtype=dtype, on_device=on_device)
         engine = cls(loaded=loaded, max_seq_len=max_seq_len, max_batch_size=max_batch_size,
-                     use_cuda_graph=use_cuda_graph, **options)
+                     use_cuda_graph=use_cuda_graph, source=("random", dict(config), seed, on_device), **options)
         engine.synchronize()
         engine.load_seconds = time.perf_counter() - started
         return engine
@@ -142,6 +144,49 @@ class Engine:
 
     def synchronize(self) -> None:
         torch.cuda.synchronize(self.device)
+
+    def allocate_cache(self, capacity: int):
+        """A request's hold on the cache with pages for ``capacity`` tokens
+        (mini_llm/engine.py:298-299)."""
+
+        manager = self.cache_manager
+        request = manager.admit()
+        try:
+            manager.grow(request, capacity)
+        except Exception:
+            manager.release(request)
+            raise
+        return request
+
+    def release_cache(self, cache) -> None:
+        self.cache_manager.release(cache)
+
+    def to(self, *, device: str | torch.device | None = None, dtype: str | torch.dtype | None = None) -> "Engine":
+        """Place the model on another CUDA device or in the other run type
+        (mini_llm/engine.py:304-347).  The reference converts the resident weights in
+        place, which loses precision when widening after a downcast; here the weights
+        are read (or drawn) again from their source, so ``float32`` after ``bfloat16``
+        has the checkpoint's own values.  Captured graphs and the cache pool are dropped."""
+
+        from .runtime import resolve_device, resolve_dtype
+
+        new_device = self.device if device is None else resolve_device(device)
+        new_dtype = self.dtype if dtype is None else resolve_dtype(dtype)
+        if new_device == self.device and new_dtype == self.dtype:
+            return self
+        if self._runner is not None and self._runner.manager.active_sequences:
+            raise EngineError("cannot move an engine while request caches are active")
+        if self.source is None:
+            raise EngineError("this engine does not know where its weights came from and cannot be moved")
+        if self.source[0] == "dir":
+            self.loaded = load(self.source[1], device=new_device, dtype=new_dtype)
+        else:
+            _, config, seed, on_device = self.source
+            self.loaded = load_random(config, seed, device=new_device, dtype=new_dtype, on_device=on_device)
+        self._runner = None
+        self._sampler = None
+        self.synchronize()
+        return self
 
     # ------------------------------------------------------------ generation
     def create_scheduler(self) -> Scheduler:

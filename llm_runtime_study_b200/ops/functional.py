@@ -77,6 +77,19 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def silu_mul_interleaved(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` for rows laid out in blocks of eight, ``[g0..g7 | u0..u7 | g8..g15 | ...]``
+    (the layout of a stacked gate/up projection whose kernels can apply the activation themselves)."""
+
+    require(gate_up, "gate_up", dims=2)
+    n, two_i = gate_up.shape
+    if two_i % 16:
+        raise KernelError("silu_mul_interleaved: row width must be a multiple of 16")
+    out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    call("b200_silu_mul_interleaved", ptr(gate_up), ptr(out), n, two_i // 2, tag(gate_up.dtype), stream_ptr())
+    return out
+
+
 def qk_norm_rope_write(
     qkv: torch.Tensor, *, num_q_heads: int, num_kv_heads: int, head_dim: int,
     q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,

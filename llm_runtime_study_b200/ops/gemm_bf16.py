@@ -12,6 +12,7 @@ native.register_library(
     "b200_gemm_tcgen05", ("gemm_tcgen05.cu",),
     {
         "b200_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "b200_gemm_tcgen05_swiglu": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "b200_gemm_tcgen05_error": [],
     },
 )
@@ -20,7 +21,7 @@ native.register_library(
     "b200_gemm_skinny", ("gemm_skinny.cu",),
     {
         "b200_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
-        "b200_gemm_skinny_variant": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "b200_gemm_skinny_variant": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     },
 )
 
@@ -48,8 +49,10 @@ def pick_splits(m: int, n: int, k: int) -> int:
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
-           out_dtype: torch.dtype = torch.bfloat16, *, splits: int | None = None) -> torch.Tensor:
-    """``x @ weight.T (+ bias)``; float32 accumulation; bfloat16 or float32 output."""
+           out_dtype: torch.dtype = torch.bfloat16, *, splits: int | None = None, swiglu: bool = False) -> torch.Tensor:
+    """``x @ weight.T (+ bias)``; float32 accumulation; bfloat16 or float32 output.
+    With ``swiglu`` the weight holds gate and up rows interleaved in blocks of eight and
+    the result is ``silu(gate) * up``, half as wide (persistent kernel only)."""
 
     native.require(x, "x", dtype=torch.bfloat16, dims=2)
     native.require(weight, "weight", dtype=torch.bfloat16, dims=2)
@@ -63,6 +66,13 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
         raise KernelError(f"unsupported output type {out_dtype}")
     if bias is not None:
         native.require(bias, "bias", dtype=torch.float32, shape=(n,))
+    if swiglu:
+        if n % 16:
+            raise KernelError("the SwiGLU epilogue needs an even number of 8-feature blocks")
+        out = torch.empty((m, n // 2), dtype=out_dtype, device=x.device)
+        native.call("b200_gemm_tcgen05_swiglu", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k,
+                    n // 2, 1 if out_dtype == torch.float32 else 0, native.stream_ptr())
+        return out
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     if splits is None:
         splits = pick_splits(m, n, k)
@@ -81,8 +91,9 @@ def check_error() -> None:
 
 
 def linear_skinny(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
-                  out_dtype: torch.dtype = torch.bfloat16, *, variant: int = 0) -> torch.Tensor:
-    """``x @ weight.T (+ bias)`` for at most 16 rows of ``x``: the weight-streaming kernel."""
+                  out_dtype: torch.dtype = torch.bfloat16, *, variant: int = 0, swiglu: bool = False) -> torch.Tensor:
+    """``x @ weight.T (+ bias)`` for at most 16 rows of ``x``: the weight-streaming kernel.
+    ``swiglu``: see ``linear``."""
 
     native.require(x, "x", dtype=torch.bfloat16, dims=2)
     native.require(weight, "weight", dtype=torch.bfloat16, dims=2)
@@ -94,7 +105,10 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
         raise KernelError(f"the weight-streaming kernel takes at most {SKINNY_M} rows and K a multiple of 8; got {m}, {k}")
     if bias is not None:
         native.require(bias, "bias", dtype=torch.float32, shape=(n,))
-    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-    native.call("b200_gemm_skinny_variant", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k, n,
-                1 if out_dtype == torch.float32 else 0, variant, native.stream_ptr())
+    if swiglu and n % 16:
+        raise KernelError("the SwiGLU epilogue needs an even number of 8-feature blocks")
+    width = n // 2 if swiglu else n
+    out = torch.empty((m, width), dtype=out_dtype, device=x.device)
+    native.call("b200_gemm_skinny_variant", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k, width,
+                1 if out_dtype == torch.float32 else 0, variant, 1 if swiglu else 0, native.stream_ptr())
     return out

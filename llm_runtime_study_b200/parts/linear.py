@@ -40,6 +40,20 @@ class Projection:
             b = biases[0] if len(biases) == 1 else torch.cat(list(biases), dim=0)
             self.bias = b.to(device=runtime.device, dtype=torch.float32).contiguous()
 
+    def swiglu(self, x: torch.Tensor) -> torch.Tensor:
+        """For a projection whose rows are gate and up features interleaved in blocks of
+        eight: ``silu(gate(x)) * up(x)`` in the activation type.  Our bfloat16 kernels apply
+        the activation in their epilogue, so the ``[tokens, 2 I]`` intermediate is never
+        written; the other paths run the projection and then the interleaved SiLU kernel."""
+
+        if self.runtime.dtype == torch.bfloat16 and self.in_features % 8 == 0 and x.is_contiguous():
+            m = x.shape[0]
+            if m <= gemm_bf16.SKINNY_M:
+                return gemm_bf16.linear_skinny(x, self.weight, self.bias, torch.bfloat16, swiglu=True)
+            if self.GEMM_BACKEND == "tcgen05" and m >= self.TCGEN05_MIN_ROWS:
+                return gemm_bf16.linear(x, self.weight, self.bias, torch.bfloat16, swiglu=True)
+        return F.silu_mul_interleaved(self(x))
+
     def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         out_dtype = out_dtype or self.runtime.dtype
         if x.shape[-1] != self.in_features:

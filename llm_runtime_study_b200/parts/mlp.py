@@ -33,8 +33,19 @@ class SwiGLU(FeedForward):
 
     def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         self.runtime = runtime
-        self.gate_up_proj = Projection([tensors["gate_proj.weight"], tensors["up_proj.weight"]], None, runtime)
+        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        # When the width allows, gate and up rows are interleaved in blocks of eight
+        # ([g0..g7, u0..u7, g8..g15, ...]): a projection kernel then holds matching gate and
+        # up features in one tile and can apply SiLU * up before it writes anything.
+        self.interleaved = self.intermediate_size % 8 == 0
+        if self.interleaved:
+            blocks = self.intermediate_size // 8
+            stacked = torch.stack((gate.view(blocks, 8, -1), up.view(blocks, 8, -1)), dim=1).reshape(2 * self.intermediate_size, -1)
+            self.gate_up_proj = Projection([stacked], None, runtime)
+        else:
+            self.gate_up_proj = Projection([gate, up], None, runtime)
         self.down_proj = Projection([tensors["down_proj.weight"]], None, runtime)
 
     def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
-        return self.down_proj(F.silu_mul(self.gate_up_proj(x)), torch.float32)
+        hidden = self.gate_up_proj.swiglu(x) if self.interleaved else F.silu_mul(self.gate_up_proj(x))
+        return self.down_proj(hidden, torch.float32)

@@ -144,3 +144,31 @@ def test_cuda_graph_decode_equals_eager(tmp_path, dtype):
 
     eager, captured = run(False), run(True)
     assert torch.equal(eager, captured)
+
+
+def test_engine_to_and_cache_handles(tmp_path):
+    from llm_runtime_study_b200.engine.engine import Engine
+    from llm_runtime_study_b200.errors import EngineError, KVCacheError
+
+    raw, seed, page = helpers.TINY["A"]
+    path, weights = helpers.make_model_dir(tmp_path / "m", raw, seed)
+    engine = Engine.from_model_dir(path, device="cuda:0", dtype="bfloat16", max_seq_len=64, max_batch_size=2, page_size=page)
+    prompt = [5, 17, 3, 9]
+    first = [e.token_id for _, e in engine.generate([prompt], max_new_tokens=4)]
+    handle = engine.allocate_cache(10)
+    assert engine.last_cache_capacity == 12 and engine.last_cache_num_bytes > 0      # three pages of four
+    with pytest.raises(EngineError, match="active"):
+        engine.to(dtype="float32")
+    engine.release_cache(handle)
+    engine.release_cache(handle)
+    assert engine.to(dtype="bfloat16") is engine
+    engine.to(dtype="float32")
+    assert engine.dtype == torch.float32
+    want, gaps = plain_generate(weights, raw, prompt, 4, eos=[raw["eos_token_id"]])
+    got = [e.token_id for _, e in engine.generate([prompt], max_new_tokens=4)]
+    assert_same_until_a_tie(got, want, gaps, 1e-5)
+    assert_same_until_a_tie(first, want, gaps, 3e-2)
+    with pytest.raises(EngineError):
+        engine.to(device="cpu")
+    with pytest.raises(KVCacheError):
+        engine.allocate_cache(10_000)

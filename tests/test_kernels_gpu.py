@@ -425,3 +425,37 @@ def test_tcgen05_attention_rescales_when_the_maximum_grows():
                                            block_table=dev(ids.view(1, -1)), q_lens=[L], scale=1 / math.sqrt(d))
     _mma().check_tcgen05_error(d)
     torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
+
+
+# ----------------------------------------------------------- fused SwiGLU epilogues
+def _interleave(gate, up):
+    blocks = gate.shape[0] // 8
+    return torch.stack((gate.view(blocks, 8, -1), up.view(blocks, 8, -1)), dim=1).reshape(2 * gate.shape[0], -1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter", [8, 272, 1000])
+def test_silu_mul_interleaved(dtype, inter):
+    torch.manual_seed(12)
+    g, u = (torch.randn(5, inter) * 3).to(dtype), (torch.randn(5, inter) * 3).to(dtype)
+    packed = _interleave(g.T.contiguous(), u.T.contiguous()).T.contiguous()      # columns in blocks of eight
+    out = F().silu_mul_interleaved(dev(packed))
+    want = g.double() / (1 + torch.exp(-g.double())) * u.double()
+    torch.testing.assert_close(out.cpu().double(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("m,inter,k", [(1, 16, 64), (8, 272, 96), (16, 1000, 520), (130, 272, 96), (2048, 1536, 1024), (300, 8, 4096)])
+def test_projection_with_swiglu_epilogue(m, inter, k):
+    torch.manual_seed(13)
+    x = torch.randn(m, k).bfloat16()
+    gate, up = (torch.randn(inter, k) * 0.08).bfloat16(), (torch.randn(inter, k) * 0.08).bfloat16()
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    want = g / (1 + torch.exp(-g)) * u
+    w = dev(_interleave(gate, up))
+    if m <= 16:
+        got = _gemm().linear_skinny(dev(x), w, None, torch.bfloat16, swiglu=True)
+    else:
+        got = _gemm().linear(dev(x), w, None, torch.bfloat16, swiglu=True)
+        _gemm().check_error()
+    assert got.shape == (m, inter)
+    torch.testing.assert_close(got.cpu().double(), want, atol=2e-2 * float(want.abs().max()), rtol=0)
