@@ -144,3 +144,76 @@ def test_unknown_kind_and_bad_sizes():
         MIXERS.build({"kind": "gqa_attention", "hidden_size": 8, "num_heads": 3, "num_kv_heads": 2, "head_dim": 16})
     with pytest.raises(ValueError):
         FEED_FORWARDS.build({"kind": "swiglu", "hidden_size": 0, "intermediate_size": 4})
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_and_head_parts(dtype):
+    from llm_runtime_study_b200.parts import OutputHead, TokenEmbedding
+
+    torch.manual_seed(3)
+    rt = runtime(dtype)
+    emb = TokenEmbedding(vocab_size=37, hidden_size=24, scale=2.0)
+    table = torch.randn(37, 24).to(dtype)
+    emb.load({"weight": table}, rt)
+    ids = torch.tensor([5, 0, 36, 5], dtype=torch.int32)
+    out = emb.forward(ids.cuda())
+    assert out.dtype == torch.float32
+    torch.testing.assert_close(out.cpu(), table[ids.long()].float() * 2.0, atol=0, rtol=0)
+
+    x = torch.randn(4, 24).to(dtype)
+    untied = OutputHead(vocab_size=37, hidden_size=24, tied=False)
+    assert not untied.tensor_specs()["weight"].optional
+    w = (torch.randn(37, 24) * 0.2).to(dtype)
+    untied.load({"weight": w}, rt, embedding=emb)
+    logits = untied.forward(x.cuda())
+    assert logits.dtype == torch.float32
+    torch.testing.assert_close(logits.cpu().double(), x.double() @ w.double().T, **TOL[dtype])
+    tied = OutputHead(vocab_size=37, hidden_size=24, tied=True)
+    assert tied.tensor_specs()["weight"].optional
+    tied.load({}, rt, embedding=emb)
+    torch.testing.assert_close(tied.forward(x.cuda()).cpu().double(), x.double() @ table.double().T, **TOL[dtype])
+    tied.load({"weight": w}, rt, embedding=emb)          # a stored head wins over the tie
+    torch.testing.assert_close(tied.forward(x.cuda()).cpu().double(), x.double() @ w.double().T, **TOL[dtype])
+    with pytest.raises(KeyError):
+        untied.load({}, rt, embedding=emb)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_pre_norm_block_composition(dtype):
+    """h = h + mixer(norm1(h)); h = h + ffn(norm2(h)), the additions carried in float32 by the next norm."""
+
+    from llm_runtime_study_b200.cache import CacheLayout, CacheManager
+    from llm_runtime_study_b200.engine.step import StepEntry, StepRunner
+    from llm_runtime_study_b200.parts import BLOCKS, ResidualStream
+
+    hidden, nq, nkv, d, inter, eps, theta, T = 40, 2, 1, 16, 56, 1e-5, 1e4, 9
+    norm = {"kind": "rms_norm", "dim": hidden, "eps": eps}
+    block = BLOCKS.build({
+        "kind": "pre_norm", "mixer_norm": norm, "ffn_norm": norm,
+        "mixer": {"kind": "gqa_attention", "hidden_size": hidden, "num_heads": nq, "num_kv_heads": nkv, "head_dim": d,
+                  "qk_norm": {"kind": "rms_norm", "dim": d, "eps": eps}, "position": {"kind": "rope", "head_dim": d, "theta": theta}},
+        "feed_forward": {"kind": "swiglu", "hidden_size": hidden, "intermediate_size": inter},
+    })
+    torch.manual_seed(4)
+    w = {n: ((1 + 0.1 * torch.randn(s.shape)) if "norm" in n else torch.randn(s.shape) * 0.2).to(dtype)
+         for n, s in block.tensor_specs().items()}
+    assert "self_attn.q_proj.weight" in w and "post_attention_layernorm.weight" in w and "mlp.down_proj.weight" in w
+    rt = runtime(dtype)
+    block.load(w, rt)
+    h0 = torch.randn(T, hidden)
+    cfg = {"num_attention_heads": nq, "num_key_value_heads": nkv, "head_dim": d, "rms_norm_eps": eps,
+           "num_hidden_layers": 1, "rope_theta": theta}
+    pw = {f"model.layers.0.{n}": t.double() for n, t in w.items()}
+    cos, sin = plain.rotary_tables(torch.arange(T), d, theta, torch.float64)
+    want = plain.decoder_layer(h0.double(), pw, 0, cfg, cos, sin)
+    manager = CacheManager(CacheLayout.from_requirements([block.mixer.cache_requirement()]), max_tokens=32, page_size=4,
+                           max_requests=1, dtype=dtype, device="cuda:0")
+
+    def run(ctx, cache):
+        stream = ResidualStream(h0.cuda().clone())
+        block.forward(stream, ctx, cache)
+        return stream.resid + stream.delta
+
+    runner = StepRunner(OnePart(run), manager, rt, vocab_size=10, max_positions=32)
+    got = runner.step([StepEntry(manager.admit(), [0] * T, [])])
+    torch.testing.assert_close(got.double().cpu(), want, **TOL[dtype])
