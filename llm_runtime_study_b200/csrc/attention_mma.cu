@@ -392,6 +392,217 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
   }
 }
 
+// --------------------------------------------------------------------------- decode, transposed
+// The same split-sequence scheme with the roles of the matrix dimensions exchanged, which
+// suits a handful of query heads much better: keys are the 16-row (M) side and the query
+// heads of the group the 8-wide (N) side,
+//     S^T[16 keys x 8 heads]  = K[16 keys x d]   . Q^T[d x 8 heads]
+//     O^T[d x 8 heads]       += V^T[d x 16 keys] . P^T[16 keys x 8 heads]
+// so that half of an accumulator is real work instead of a quarter (or less), the softmax
+// touches 4 values per thread instead of 32, and K never goes through shared memory: like
+// the weight-streaming projection, each lane fetches 16 contiguous bytes of "its" key row
+// straight into the A fragments (the order of the head-size index inside a 32-wide slab is
+// permuted identically in K and Q).  V goes through shared memory (cp.async, a private
+// two-stage buffer per warp) and is read transposed by ldmatrix.trans; P^T reaches the
+// B-fragment layout with movmatrix.trans.
+// grid (splits, nkv * slices, requests); at most 8 query heads of a group per CTA.
+#if HEAD_DIM % 32 == 0
+constexpr int kTGs = 8;                       // query heads per CTA = the N side of one mma
+constexpr int TLDS = D + 8;                   // padded V row
+constexpr int kTSmemBytes = 4 * 2 * 16 * TLDS * 2 > (2 * 4 * 8 + 4 * 8 * D) * 4 ? 4 * 2 * 16 * TLDS * 2 : (2 * 4 * 8 + 4 * 8 * D) * 4;
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+__global__ void __launch_bounds__(128) decode_attention_t_kernel(AttnParams p) {
+  constexpr int SLABS = D / 32;               // 32-wide slabs of the head size (two k-steps each)
+  constexpr int MT = D / 16;                  // 16-row tiles of O^T
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  pdl_trigger();
+  pdl_wait();
+  const int split = blockIdx.x, b = blockIdx.z;
+  const int kvh = blockIdx.y / p.slices, slice = blockIdx.y % p.slices;
+  const int* table = p.block_table + static_cast<size_t>(b) * p.table_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int len = p.kv_len[b];
+  const int lo = p.window > 0 ? max(0, len - p.window) : 0;
+  int chunk = (len - lo + p.num_splits - 1) / p.num_splits;
+  chunk = ((chunk + 63) / 64) * 64;
+  const int c0 = lo + split * chunk;
+  const int c1 = min(c0 + chunk, len) - 1;    // last key of this CTA's part (c1 < c0: nothing to do)
+  const int head0 = kvh * p.group + slice * p.gs;
+  const int heads_here = min(p.gs, p.group - slice * p.gs);
+
+  // Q^T fragments: lane (g, t) holds Q[head g][32 s + 8 t .. + 7] for every slab s
+  uint4 qv[SLABS];
+#pragma unroll
+  for (int s = 0; s < SLABS; ++s) {
+    qv[s] = make_uint4(0, 0, 0, 0);
+    if (g < heads_here)
+      qv[s] = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(b) * p.nq + head0 + g) * D + 32 * s + 8 * t);
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};   // heads 2t and 2t + 1
+  float o[MT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[mt][e] = 0.f;
+
+  bf16* wv = reinterpret_cast<bf16*>(smem_raw) + warp * (2 * 16 * TLDS);   // [2][16][TLDS] values of this warp
+  const int nblocks = c1 >= c0 ? (c1 - c0) / 16 + 1 : 0;
+  auto key_offset = [&](int key) -> long {          // element offset of a key's row in the pools; -1: none
+    if (key > c1) return -1;
+    const int index = p.page_shift >= 0 ? key >> p.page_shift : key / p.page_size;
+    const int slot = p.page_shift >= 0 ? key & (p.page_size - 1) : key - index * p.page_size;
+    const int page = table[index];
+    if (page < 0) return -1;
+    return ((static_cast<long>(page) * p.nkv + kvh) * p.page_size + slot) * D;
+  };
+  auto load_values = [&](int block, int buf) {
+    constexpr int CH = D / 8;
+    const int t0 = c0 + block * 16;
+#pragma unroll
+    for (int c = lane; c < 16 * CH; c += 32) {
+      const int r = c / CH, ch = c - r * CH;
+      const long off = key_offset(t0 + r);
+      cp_async_16(wv + (buf * 16 + r) * TLDS + ch * 8, off >= 0 ? p.v_pool + off + ch * 8 : p.v_pool, off >= 0 ? 16 : 0);
+    }
+  };
+  if (warp < nblocks) {
+    load_values(warp, 0);
+    cp_async_commit();
+  }
+  int buf = 0;
+  for (int block = warp; block < nblocks; block += 4, buf ^= 1) {
+    const int t0 = c0 + block * 16;
+    // keys of this block straight into the A fragments
+    uint4 ka[SLABS], kb[SLABS];
+    {
+      const long offa = key_offset(t0 + g), offb = key_offset(t0 + g + 8);
+#pragma unroll
+      for (int s = 0; s < SLABS; ++s) {
+        ka[s] = offa >= 0 ? ldg_stream16(p.k_pool + offa + 32 * s + 8 * t) : make_uint4(0, 0, 0, 0);
+        kb[s] = offb >= 0 ? ldg_stream16(p.k_pool + offb + 32 * s + 8 * t) : make_uint4(0, 0, 0, 0);
+      }
+    }
+    if (block + 4 < nblocks) {
+      load_values(block + 4, buf ^ 1);
+      cp_async_commit();
+    }
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int s = 0; s < SLABS; ++s) {
+      const uint32_t a_lo[4] = {ka[s].x, kb[s].x, ka[s].y, kb[s].y};
+      const uint32_t a_hi[4] = {ka[s].z, kb[s].z, ka[s].w, kb[s].w};
+      mma_bf16(c, a_lo, qv[s].x, qv[s].y);
+      mma_bf16(c, a_hi, qv[s].z, qv[s].w);
+    }
+    // c0, c1: key t0 + g, heads 2t, 2t+1;  c2, c3: key t0 + g + 8
+    const bool vis_a = t0 + g <= c1, vis_b = t0 + g + 8 <= c1;     // the whole part lies inside [lo, len)
+    c[0] = vis_a ? c[0] * p.scale_log2 : -INFINITY;
+    c[1] = vis_a ? c[1] * p.scale_log2 : -INFINITY;
+    c[2] = vis_b ? c[2] * p.scale_log2 : -INFINITY;
+    c[3] = vis_b ? c[3] * p.scale_log2 : -INFINITY;
+    float mx[2] = {fmaxf(c[0], c[2]), fmaxf(c[1], c[3])};
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+      mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], off));
+      mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], off));
+    }
+    float corr[2], ref[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float m_new = fmaxf(m[h], mx[h]);
+      ref[h] = m_new == -INFINITY ? 0.f : m_new;
+      corr[h] = exp2f(m[h] - ref[h]);
+      m[h] = m_new;
+      l[h] *= corr[h];
+    }
+    const float p0 = exp2f(c[0] - ref[0]), p1 = exp2f(c[1] - ref[1]), p2 = exp2f(c[2] - ref[0]), p3 = exp2f(c[3] - ref[1]);
+    l[0] += p0 + p2;
+    l[1] += p1 + p3;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      o[mt][0] *= corr[0];
+      o[mt][1] *= corr[1];
+      o[mt][2] *= corr[0];
+      o[mt][3] *= corr[1];
+    }
+    // P^T [keys x heads] -> B fragments [k = keys][n = heads]
+    const uint32_t pb0 = movmatrix_trans(pack_bf16(p0, p1));
+    const uint32_t pb1 = movmatrix_trans(pack_bf16(p2, p3));
+    if (block + 4 < nblocks) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncwarp();
+    const bf16* vbuf = wv + buf * 16 * TLDS;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      uint32_t vf[4];
+      ldmatrix_x4_trans(vf, vbuf + ((lane & 7) + ((lane >> 4) & 1) * 8) * TLDS + mt * 16 + ((lane >> 3) & 1) * 8);
+      mma_bf16(o[mt], vf, pb0, pb1);
+    }
+    __syncwarp();
+  }
+  __syncthreads();
+
+  // combine the four warps through shared memory
+  float* sm_m = reinterpret_cast<float*>(smem_raw);   // [4][8]
+  float* sm_l = sm_m + 32;                            // [4][8]
+  float* sm_o = sm_l + 32;                            // [4][8 heads][D]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float total = l[h];
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+    if (g == 0) {
+      sm_m[warp * 8 + 2 * t + h] = m[h];
+      sm_l[warp * 8 + 2 * t + h] = total;
+    }
+  }
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    sm_o[(warp * 8 + 2 * t) * D + mt * 16 + g] = o[mt][0];
+    sm_o[(warp * 8 + 2 * t + 1) * D + mt * 16 + g] = o[mt][1];
+    sm_o[(warp * 8 + 2 * t) * D + mt * 16 + g + 8] = o[mt][2];
+    sm_o[(warp * 8 + 2 * t + 1) * D + mt * 16 + g + 8] = o[mt][3];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < heads_here * D; idx += 128) {
+    const int h = idx / D, col = idx - h * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * 8 + h]);
+    const float base = M == -INFINITY ? 0.f : M;
+    float acc = 0.f, L = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(sm_m[w * 8 + h] - base);
+      acc += sm_o[(w * 8 + h) * D + col] * f;
+      L += sm_l[w * 8 + h] * f;
+    }
+    const int head = head0 + h;
+    if (p.num_splits == 1) {
+      p.out[(static_cast<long>(b) * p.nq + head) * D + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    } else {
+      const long slot = (static_cast<long>(b) * p.nq + head) * p.num_splits + split;
+      p.part_o[slot * D + col] = acc;
+      if (col == 0) {
+        p.part_ml[slot * 2] = M;
+        p.part_ml[slot * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+#endif  // HEAD_DIM % 32 == 0
+
 // grid (nq, requests), D threads: combine the splits of one (request, head)
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int nq, int num_splits) {
@@ -490,14 +701,37 @@ extern "C" int b200_attention_decode_bf16(const void* q, const void* k_pool, con
   p.num_splits = num_splits;
   p.part_o = scratch;
   p.part_ml = scratch + static_cast<long>(requests) * nq * num_splits * D;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+#if HEAD_DIM % 32 == 0
+  // The transposed kernel, unless LLM_RUNTIME_STUDY_B200_DECODE_ATTENTION=rows asks for the
+  // older one with the query heads on the 16-row side (kept for head sizes like 48 and 80).
+  static int use_rows = -1;
+  if (use_rows < 0) {
+    const char* e = getenv("LLM_RUNTIME_STUDY_B200_DECODE_ATTENTION");
+    use_rows = (e && e[0] == 'r') ? 1 : 0;
   }
-  dim3 grid(num_splits, nkv * p.slices, requests);
-  launch(decode_attention_kernel, dim3(grid), dim3(128), kSmemBytes, stream, p);
+  if (!use_rows) {
+    p.gs = p.group < kTGs ? p.group : kTGs;
+    p.slices = (p.group + p.gs - 1) / p.gs;
+    static bool configured_t = false;
+    if (!configured_t) {
+      cudaError_t e = cudaFuncSetAttribute(decode_attention_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmemBytes);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured_t = true;
+    }
+    dim3 tgrid(num_splits, nkv * p.slices, requests);
+    launch(decode_attention_t_kernel, tgrid, dim3(128), kTSmemBytes, stream, p);
+  } else
+#endif
+  {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured = true;
+    }
+    dim3 grid(num_splits, nkv * p.slices, requests);
+    launch(decode_attention_kernel, dim3(grid), dim3(128), kSmemBytes, stream, p);
+  }
   if (int e = launch_status()) return e;
   if (num_splits > 1) {
     dim3 mgrid(nq, requests);

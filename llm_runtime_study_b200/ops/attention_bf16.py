@@ -15,7 +15,7 @@ from .native import c_float, c_int, c_void_p
 
 c_long = native.ctypes.c_long
 MAX_HEAD_DIM = 256
-_CTA_SLOTS = 3 * 148     # resident CTAs of the decode kernel (shared memory allows three per SM)
+_CTA_SLOTS = 4 * 148     # resident CTAs of the decode kernel (registers allow four per SM)
 _MIN_KEYS_PER_SPLIT = 128
 
 _TABLE = {
