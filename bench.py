@@ -221,7 +221,7 @@ def run_ours(args) -> dict:
     torch.cuda.synchronize()
     e2e_seconds = time.perf_counter() - t0
     scheduler.abort_all()
-    graph = runner._graphs._graphs.get(args.batch) if runner._graphs else None
+    graph = runner._graphs._graphs.get(runner._graphs.bucket(args.batch)) if runner._graphs else None
     h2d = (graph.dev.numel() * 4 if graph else 0) + args.batch * 6 * 4
     d2h = args.batch * 4
 

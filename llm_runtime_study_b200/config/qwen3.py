@@ -7,7 +7,6 @@ and constant the model uses comes from here; nothing is hard-coded elsewhere.
 
 from __future__ import annotations
 
-import warnings
 from dataclasses import asdict, dataclass
 from typing import Any, Mapping
 
@@ -56,20 +55,19 @@ class Qwen3Config:
             raise ConfigError(
                 "quantization_config is present: quantized checkpoints are not supported"
             )
-        # The reference never reads these keys (its attention is always full and
-        # its rotary angles are never rescaled), so a value here cannot change
-        # the result; say so instead of silently looking as if it were honoured.
+        # The reference never reads these keys (its attention is always full and its rotary
+        # angles are never rescaled, mini_llm/config.py:137-188), so honouring them is not
+        # possible and ignoring them would compute something else than the file asks for:
+        # a null or disabled value is accepted, anything else is refused.
         if raw.get("use_sliding_window") is True and raw.get("sliding_window") is not None:
-            warnings.warn(
-                "use_sliding_window is set but Qwen3 dense attends to the full "
-                "context here, as in the reference runtime",
-                stacklevel=2,
+            raise ConfigError(
+                "use_sliding_window is enabled: Qwen3 dense attends to the full context in this "
+                "engine, as in the reference runtime; sliding-window checkpoints are not supported"
             )
         if raw.get("rope_scaling") is not None:
-            warnings.warn(
-                "rope_scaling is set but not applied: rotary angles are "
-                "position * theta^(-2i/d), as in the reference runtime",
-                stacklevel=2,
+            raise ConfigError(
+                "rope_scaling is set: rotary angles are position * theta^(-2i/d) in this engine, as in "
+                "the reference runtime; scaled rotary embeddings are not supported"
             )
         config = cls(
             architectures=tuple(architectures),

@@ -45,10 +45,11 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
   constexpr int VN = Vec<T>::n;
   for (int t0 = (w0 / 32) * 32; t0 <= p; t0 += 32) {
     const int t = t0 + lane;
-    const bool valid = t <= p && t >= w0;
+    bool valid = t <= p && t >= w0;
     float s = -INFINITY;
+    const int page = valid ? table[t / page_size] : -1;
+    valid = valid && page >= 0;      // a page given back (window) or a padding row without pages
     if (valid) {
-      const int page = table[t / page_size];
       const T* krow = k_pool + ((static_cast<size_t>(page) * nkv + kvh) * page_size + t % page_size) * d;
       float dot = 0.f;
       for (int i = 0; i < d; i += VN) {
@@ -83,7 +84,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_poo
     m = m_new;
   }
   T* orow = out + (static_cast<size_t>(token) * nq + head) * d;
-  const float inv = 1.f / l;
+  const float inv = l > 0.f ? 1.f / l : 0.f;   // a row without any visible key (padding) gives zeros
 #pragma unroll
   for (int c = 0; c < kMaxChunks; ++c) {
     const int i = lane + 32 * c;

@@ -2,10 +2,13 @@
 
 The reference captures the decoder stack once per batch size over a block table
 of fixed width and leaves the output head outside (mini_llm/cuda_graph.py:89-187).
-Here the whole step is captured (embedding to logits) once per batch size: all
-metadata lives in one persistent device buffer whose layout is fixed by the batch
-size and the table width, so a replay is one host-to-device copy plus one graph
-launch.  Steps that hold prompt portions run eagerly.
+Here the whole step is captured (embedding to logits) once per batch-size *bucket*
+(1, 2, 4, 8, ... and the largest batch): a batch is padded up to its bucket with
+rows that hold no request (length 0, no pages: the cache-write and the attention
+kernels skip them), so a batch that shrinks or grows by one does not pay a new
+capture.  All metadata lives in one persistent device buffer whose layout is fixed
+by the bucket and the table width, so a replay is one host-to-device copy plus one
+graph launch.  Steps that hold prompt portions run eagerly.
 """
 
 from __future__ import annotations
@@ -63,9 +66,12 @@ class DecodeGraph:
         return ctx
 
     def _fill(self, entries: Sequence[StepEntry]) -> list[int]:
-        """Write this step's metadata into the persistent buffer."""
+        """Write this step's metadata into the persistent buffer.  Rows beyond the
+        entries are padding: token 0 at position 0 of a sequence of length 0 whose block
+        table is empty."""
 
         b, w = self.batch, self.table_width
+        n = len(entries)
         self.turn ^= 1
         event = self.events[self.turn]
         if event is not None:
@@ -74,12 +80,13 @@ class DecodeGraph:
         starts = [e.request.length for e in entries]
         kv_lens = [s + 1 for s in starts]
         o = self.offsets
-        host[o[0] : o[0] + b] = [int(e.tokens[0]) for e in entries]
-        host[o[1] : o[1] + b] = starts
+        pad = [0] * (b - n)
+        host[o[0] : o[0] + b] = [int(e.tokens[0]) for e in entries] + pad
+        host[o[1] : o[1] + b] = starts + pad
         host[o[2] : o[2] + b] = np.arange(b)
         host[o[3] : o[3] + b + 1] = np.arange(b + 1)
-        host[o[4] : o[4] + b] = kv_lens
-        host[o[5] : o[5] + b] = [e.request.slot for e in entries]
+        host[o[4] : o[4] + b] = kv_lens + pad
+        host[o[5] : o[5] + b] = [e.request.slot for e in entries] + pad
         host[o[6] : o[6] + b] = np.arange(b)
         for g in range(self.groups):
             table = host[o[7 + g] : o[7 + g] + b * w].reshape(b, w)
@@ -115,11 +122,11 @@ class DecodeGraph:
             self.graph = graph
         self.graph.replay()
         native.add_launches(self.kernel_launches)
-        return self.logits, kv_lens
+        return self.logits[: len(entries)], kv_lens
 
 
 class DecodeGraphs:
-    """Graphs by batch size, captured on first use."""
+    """Graphs by batch-size bucket, captured on first use."""
 
     def __init__(self, runner: Any) -> None:
         self.runner = runner
@@ -128,8 +135,18 @@ class DecodeGraphs:
     def eligible(self, entries: Sequence[StepEntry]) -> bool:
         return all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
 
+    def bucket(self, batch: int) -> int:
+        """The smallest power of two that holds the batch, but never more rows than
+        the cache has request slots."""
+
+        size = 1
+        while size < batch:
+            size *= 2
+        return max(batch, min(size, self.runner.manager.max_requests))
+
     def run(self, entries: Sequence[StepEntry]) -> tuple[torch.Tensor, list[int]]:
-        graph = self._graphs.get(len(entries))
+        size = self.bucket(len(entries))
+        graph = self._graphs.get(size)
         if graph is None:
-            graph = self._graphs[len(entries)] = DecodeGraph(self.runner, len(entries))
+            graph = self._graphs[size] = DecodeGraph(self.runner, size)
         return graph.run(entries)

@@ -61,10 +61,19 @@ def test_bool_is_not_an_int():
     ({"attention_dropout": 1.0}, "attention_dropout"),
     ({"num_hidden_layers": 0}, "num_hidden_layers"),
     ({"quantization_config": {"bits": 4}}, "quantiz"),
+    ({"rope_scaling": {"type": "yarn", "factor": 4.0}}, "rope_scaling"),
+    ({"use_sliding_window": True, "sliding_window": 128}, "sliding"),
 ])
 def test_rejections(patch, match):
     with pytest.raises(ConfigError, match=match):
         Qwen3Config.from_dict({**TINY_A, **patch})
+
+
+def test_keys_the_engine_does_not_use_may_be_present_when_off():
+    cfg = Qwen3Config.from_dict({**TINY_A, "rope_scaling": None, "use_sliding_window": False, "sliding_window": None,
+                                 "max_window_layers": 2, "use_cache": True, "transformers_version": "4.51.0"})
+    assert cfg.hidden_size == 64
+    Qwen3Config.from_dict({**TINY_A, "use_sliding_window": False, "sliding_window": 4096})   # off: the size does not matter
 
 
 def test_context_length_and_cache_bytes():

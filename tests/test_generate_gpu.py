@@ -137,13 +137,26 @@ def test_cuda_graph_decode_equals_eager(tmp_path, dtype):
         runner.step([StepEntry(r, p, []) for r, p in zip(requests, prompts)])
         rows = []
         for t in range(12):
-            live = requests if t < 8 else requests[:2]             # the batch shrinks: another graph
+            live = requests if t < 6 else (requests[:3] if t < 9 else requests[:2])   # 4, then 3 (padded to 4), then 2
             logits = runner.step([StepEntry(r, [f[t]], [0]) for r, f in zip(live, follow)])
             rows.append(logits.clone())
         return torch.cat(rows)
 
     eager, captured = run(False), run(True)
     assert torch.equal(eager, captured)
+
+
+def test_graph_buckets_pad_with_empty_rows(tmp_path):
+    from llm_runtime_study_b200.engine.graph import DecodeGraphs
+
+    class Manager:
+        max_requests = 48
+
+    class Runner:
+        manager = Manager()
+
+    graphs = DecodeGraphs(Runner())
+    assert [graphs.bucket(n) for n in (1, 2, 3, 5, 8, 9, 33, 48)] == [1, 2, 4, 8, 8, 16, 48, 48]
 
 
 def test_engine_to_and_cache_handles(tmp_path):
