@@ -271,6 +271,129 @@ class _IdsTokenizer:
         return messages[-1].content
 
 
+QWEN3_14B = {**QWEN3_8B, "hidden_size": 5120, "intermediate_size": 17408, "num_hidden_layers": 40,
+             "num_attention_heads": 40, "num_key_value_heads": 8, "max_position_embeddings": 8192}
+QWEN3_32B = {**QWEN3_8B, "hidden_size": 5120, "intermediate_size": 25600, "num_hidden_layers": 64,
+             "num_attention_heads": 64, "num_key_value_heads": 8, "max_position_embeddings": 4096}
+
+
+def run_staggered_14b(args) -> dict:
+    """Qwen3-14B shape: 32 requests arriving 50 ms apart, prompt lengths uniform in [128, 4096], 256 new
+    tokens each, continuous batching of at most 16 (the reference's staggered benchmark, doc/batch.md:45-53,
+    at this model size).  Wall-clock figures through the scheduler."""
+
+    import random
+
+    import torch
+
+    from llm_runtime_study_b200.engine.engine import Engine
+
+    cfg = dict(QWEN3_14B)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    torch.cuda.set_device(0)
+    rng = random.Random(0)
+    generator = torch.Generator().manual_seed(0)
+    requests, new_tokens, interval, max_batch = 32, 256, 0.050, 16
+    prompts = [torch.randint(0, cfg["vocab_size"], (rng.randint(128, 4096),), generator=generator).tolist()
+               for _ in range(requests)]
+    engine = Engine.from_random_weights(
+        cfg, seed=0, device="cuda:0", dtype="bfloat16", max_seq_len=8192, max_batch_size=max_batch, page_size=PAGE_SIZE,
+        max_cache_tokens=max_batch * (4096 + new_tokens + PAGE_SIZE), max_tokens_per_step=4096, use_cuda_graph=True)
+    # warm-up: kernels built and loaded, decode graphs of every bucket captured
+    warm = engine.create_scheduler()
+    for n in (1, 2, 4, 8, 16):
+        for _ in range(n - warm.num_running):
+            warm.add_request(prompts[0][:128], max_new_tokens=4)
+        while warm.has_unfinished:
+            warm.step()
+    scheduler = engine.create_scheduler()
+    engine.synchronize()
+    start = time.perf_counter()
+    arrival, first, done, index_of = {}, {}, {}, {}
+    submitted = produced = 0
+    while submitted < requests or scheduler.has_unfinished:
+        now = time.perf_counter() - start
+        while submitted < requests and now >= submitted * interval:
+            index_of[scheduler.add_request(prompts[submitted], max_new_tokens=new_tokens)] = submitted
+            arrival[submitted] = submitted * interval
+            submitted += 1
+        if not scheduler.has_unfinished:
+            time.sleep(max(0.0, submitted * interval - now))
+            continue
+        for index, event in scheduler.step():
+            stamp = time.perf_counter() - start
+            r = index_of[index]
+            first.setdefault(r, stamp)
+            produced += event.token_id is not None
+            if event.finish_reason is not None:
+                done[r] = stamp
+    makespan = time.perf_counter() - start
+
+    def pct(values, q):
+        values = sorted(values)
+        return values[min(len(values) - 1, int(round(q * (len(values) - 1))))]
+
+    ttft = [first[r] - arrival[r] for r in range(requests)]
+    latency = [done[r] - arrival[r] for r in range(requests)]
+    return {
+        "metric": "staggered arrivals, continuous batching: output tok/s (Qwen3-14B shape)", "impl": "ours",
+        "value": round(produced / makespan, 1), "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
+        "data": "synthetic: random weights, uniform random token ids", "makespan_s": round(makespan, 3),
+        "ttft_ms": {"p50": round(pct(ttft, 0.5) * 1e3, 1), "p95": round(pct(ttft, 0.95) * 1e3, 1)},
+        "latency_ms": {"p50": round(pct(latency, 0.5) * 1e3, 1), "p95": round(pct(latency, 0.95) * 1e3, 1)},
+        "config": {"model": "Qwen3-14B shape", "layers": cfg["num_hidden_layers"], "layers_full": 40, "requests": requests,
+                   "prompt_tokens": "uniform 128..4096", "new_tokens": new_tokens, "arrival_interval_ms": 50,
+                   "max_batch_size": max_batch, "max_tokens_per_step": 4096, "page_size": PAGE_SIZE,
+                   "preemptions": scheduler.stats["preemptions"], "steps": scheduler.stats["steps"]},
+    }
+
+
+def run_decode_32b(args) -> dict:
+    """Qwen3-32B shape: decode at batch 1 and 16 after 1,024-token prompts, 128 new tokens, CUDA-graph decode step."""
+
+    import torch
+
+    from llm_runtime_study_b200.engine.engine import Engine
+
+    cfg = dict(QWEN3_32B)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    layers = cfg["num_hidden_layers"]
+    torch.cuda.set_device(0)
+    generator = torch.Generator().manual_seed(0)
+    engine = Engine.from_random_weights(
+        cfg, seed=0, device="cuda:0", dtype="bfloat16", max_seq_len=4096, max_batch_size=16, page_size=PAGE_SIZE,
+        max_cache_tokens=16 * (1024 + 128 + 64), max_tokens_per_step=2048, use_cuda_graph=True)
+    pk = peaks()
+    out = {}
+    for batch in (1, 16):
+        scheduler = engine.create_scheduler()
+        for _ in range(batch):
+            scheduler.add_request(torch.randint(0, cfg["vocab_size"], (1024,), generator=generator).tolist(), max_new_tokens=129)
+        while scheduler.num_waiting or any(r.prefilling for r in scheduler._running):
+            scheduler.step()
+        for _ in range(8):
+            scheduler.step()
+        engine.synchronize()
+        started = time.perf_counter()
+        produced, steps = 0, 0
+        while scheduler.has_unfinished and steps < 100:
+            produced += len(scheduler.step())
+            steps += 1
+        engine.synchronize()
+        seconds = time.perf_counter() - started
+        scheduler.abort_all()
+        step_bytes = model_bytes(cfg, layers) + batch * 1088 * kv_bytes_per_token(cfg, layers)
+        out[f"decode_b{batch}"] = {"tokens_per_s": round(produced / seconds, 1), "ms_per_step": round(seconds / steps * 1e3, 3),
+                                   "hbm_frac": round(step_bytes / (seconds / steps) / 1e9 / pk["hbm_gbs"], 4)}
+    return {"metric": "decode tok/s at batch 1 and 16 (Qwen3-32B shape, 1,024-token prompts, CUDA-graph decode)", "impl": "ours",
+            "value": out["decode_b16"]["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic: random weights, uniform random token ids", "points": out,
+            "config": {"model": "Qwen3-32B shape", "layers": layers, "layers_full": 64, "prompt_tokens": 1024, "new_tokens": 128,
+                       "page_size": PAGE_SIZE, "timing": "wall clock through the scheduler", "peaks": pk["source"]}}
+
+
 def run_reference(args) -> dict:
     """The unmodified reference from baseline/_ref: its own Qwen3ForCausalLM, paged cache,
     CUDA-graph decode and BatchScheduler, driven through Engine.create_scheduler()."""
@@ -391,13 +514,20 @@ def main() -> int:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
+    parser.add_argument("--workload", choices=("default", "staggered14b", "decode32b"), default="default",
+                        help="default: Qwen3-8B decode/prefill; the others are the larger configurations (ours only)")
     parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
                         help="run only the decode steps or only the prefill (for profiler captures of a small case)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: --gpus {args.gpus} is not supported by this engine (single-GPU tier)")
         return 2
-    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.workload == "staggered14b":
+        result = run_staggered_14b(args)
+    elif args.workload == "decode32b":
+        result = run_decode_32b(args)
+    else:
+        result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
     return 0
 
