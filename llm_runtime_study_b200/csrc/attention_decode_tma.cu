@@ -1,0 +1,449 @@
+// Decode attention over the paged cache with the pages streamed by TMA (sm_100a).
+//
+// One query token per request.  A CTA owns one (request, KV head, part of the sequence) and up to
+// eight query heads of that KV head's group; its four warps take the 16-key blocks of the part in
+// turn.  Every warp runs its own ring of DEPTH stages: lane 0 asks the TMA unit for the K and V
+// rows of a block (two or four 2 KB boxes, 128-byte swizzle, found through the block table) and the
+// warp waits on the stage's mbarrier, so the bytes in flight do not cost registers or instructions.
+// The products are the transposed ones: S^T = K Q^T (keys on the 16-row side of mma.sync m16n8k16,
+// query heads on the 8-column side) and O^T += V^T P^T, with softmax statistics in float32.
+// When the sequence is cut into parts, each CTA writes (max, sum, unnormalised output) of its part
+// and takes a ticket; the CTA that draws the last ticket of its (request, KV head) adds the parts
+// in their fixed order, so no second launch is needed and the result does not depend on which CTA
+// came last.
+//
+// Sizes: head sizes that are multiples of 64 (HEAD_DIM at compile time), pages of a multiple of 16
+// tokens, any number of heads and groups, no window.  Other shapes use the kernels of
+// attention_mma.cu.
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+#include "mma.cuh"
+#include "tcgen05.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=<multiple of 64>"
+#endif
+#ifndef DECODE_DEPTH
+#define DECODE_DEPTH 3
+#endif
+
+namespace b200 {
+
+using bf16 = __nv_bfloat16;
+
+constexpr int D = HEAD_DIM;
+static_assert(D % 64 == 0 && D >= 64 && D <= 256, "head size must be a multiple of 64, at most 256");
+constexpr int BOXES = D / 64;                 // 64-column TMA boxes per row of K or V
+constexpr int KEYS = 16;                      // keys per block
+constexpr int BOX_BYTES = KEYS * 128;         // 2 KB
+constexpr int TENSOR_BYTES = BOXES * BOX_BYTES;
+constexpr int STAGE_BYTES = 2 * TENSOR_BYTES; // K then V
+constexpr int DEPTH = DECODE_DEPTH;
+constexpr int WARPS = 4;
+constexpr int RING_BYTES = WARPS * DEPTH * STAGE_BYTES;
+constexpr int HEADS = 8;                      // query heads per CTA (the n side of the mma)
+constexpr int MAX_SPLITS = 64;
+constexpr int COMBINE_FLOATS = 2 * WARPS * HEADS + WARPS * HEADS * D;
+static_assert(COMBINE_FLOATS * 4 <= RING_BYTES, "the combine buffers reuse the ring");
+constexpr int SMEM_BYTES = RING_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+
+struct DecodeParams {
+  const bf16* q;
+  bf16* out;
+  const int* kv_len;
+  const int* block_table;
+  int table_stride, page_size, page_shift;
+  int nq, nkv, group, gs, slices;
+  float scale_log2;
+  int num_splits;
+  float* part_o;        // [requests][nq][num_splits][D]
+  float* part_ml;       // [requests][nq][num_splits][2]
+  unsigned* tickets;    // [requests][nkv][slices], zero between launches
+  int* error;
+};
+
+__device__ int g_decode_error = 0;
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ void ldmatrix_x4_addr(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans_addr(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+__global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_constant__ CUtensorMap kmap,
+                                                                   const __grid_constant__ CUtensorMap vmap,
+                                                                   DecodeParams p) {
+  constexpr int KS = D / 16;                  // k-steps of S^T = K Q^T
+  constexpr int MT = D / 16;                  // 16-row tiles of O^T
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + RING_BYTES);
+  __shared__ float sm_pm[HEADS][MAX_SPLITS], sm_pl[HEADS][MAX_SPLITS];
+  __shared__ int sm_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < WARPS * DEPTH; ++i) mbar_init(&bars[i], 1);
+    fence_barrier_init();
+  }
+  const int split = blockIdx.x, b = blockIdx.z;
+  const int kvh = blockIdx.y / p.slices, slice = blockIdx.y % p.slices;
+  const int head0 = kvh * p.group + slice * p.gs;
+  const int heads_here = min(p.gs, p.group - slice * p.gs);
+  const int* table = p.block_table + static_cast<size_t>(b) * p.table_stride;
+  __syncthreads();
+
+  // Lengths and block tables are uploaded before the step's first kernel; the pages of all keys but
+  // the newest were written by earlier steps.  Only q, the newest key and the outputs depend on the
+  // kernel before this one, so the first blocks can be asked for before the dependency wait.
+  const int len = p.kv_len[b];
+  int chunk = (len + p.num_splits - 1) / p.num_splits;
+  chunk = ((chunk + 63) / 64) * 64;
+  const int c0 = split * chunk;
+  const int c1 = min(c0 + chunk, len) - 1;    // last key of this CTA's part (c1 < c0: nothing to do)
+  const int nblocks = c1 >= c0 ? (c1 - c0) / KEYS + 1 : 0;
+  const int my_count = nblocks > warp ? (nblocks - warp + WARPS - 1) / WARPS : 0;
+  unsigned char* ring = base + warp * DEPTH * STAGE_BYTES;
+  uint64_t* full = bars + warp * DEPTH;
+
+  auto page_row = [&](int t0) -> int {        // row of the block's first key in the pool seen as [rows][D]; -1: no page
+    const int index = p.page_shift >= 0 ? t0 >> p.page_shift : t0 / p.page_size;
+    const int slot = p.page_shift >= 0 ? t0 & (p.page_size - 1) : t0 - index * p.page_size;
+    const int page = table[index];
+    return page < 0 ? -1 : (page * p.nkv + kvh) * p.page_size + slot;
+  };
+  auto issue = [&](int i) {                   // lane 0: ask for the K and V rows of this warp's i-th block
+    const int row = page_row(c0 + (warp + WARPS * i) * KEYS);
+    unsigned char* stage = ring + (i % DEPTH) * STAGE_BYTES;
+    uint64_t* bar = &full[i % DEPTH];
+    if (row < 0) {                            // no page (never the case for a live sequence): complete the phase empty-handed
+      mbar_arrive(bar);
+      return;
+    }
+    mbar_expect_tx(bar, STAGE_BYTES);
+#pragma unroll
+    for (int box = 0; box < BOXES; ++box) {
+      tma_load_2d(stage + box * BOX_BYTES, &kmap, bar, box * 64, row);
+      tma_load_2d(stage + TENSOR_BYTES + box * BOX_BYTES, &vmap, bar, box * 64, row);
+    }
+  };
+  // blocks that cannot hold the newest key (index len - 1) go out before the wait
+  const int newest_block = (len - 1 - c0) / KEYS;            // block of this part holding key len - 1, if it is here
+  const bool newest_here = len - 1 >= c0 && len - 1 <= c1;
+  int issued = 0;
+  if (lane == 0) {
+    while (issued < my_count && issued < DEPTH && !(newest_here && warp + WARPS * issued == newest_block)) issue(issued++);
+  }
+  pdl_wait();
+  if (lane == 0) {
+    while (issued < my_count && issued < DEPTH) issue(issued++);
+  }
+
+  // Q^T as B fragments: lane (g, t) holds Q[head g][16 ks + 2t, +1] and Q[head g][16 ks + 8 + 2t, +1]
+  uint32_t qb[KS][2];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    qb[ks][0] = qb[ks][1] = 0u;
+    if (g < heads_here) {
+      const bf16* src = p.q + (static_cast<size_t>(b) * p.nq + head0 + g) * D + 16 * ks + 2 * t;
+      qb[ks][0] = *reinterpret_cast<const uint32_t*>(src);
+      qb[ks][1] = *reinterpret_cast<const uint32_t*>(src + 8);
+    }
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};   // heads 2t and 2t + 1
+  float o[MT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[mt][e] = 0.f;
+
+  // ldmatrix lane roles: K (A operand, rows = keys): row (lane & 7) + 8 ((lane >> 3) & 1), 16-byte chunk 2 ks + (lane >> 4);
+  // V^T (A operand through .trans, rows of the tile = keys): key (lane & 7) + 8 ((lane >> 4) & 1), chunk 2 mt + ((lane >> 3) & 1)
+  const int k_row = (lane & 7) + ((lane >> 3) & 1) * 8, k_half = lane >> 4;
+  const int v_key = (lane & 7) + ((lane >> 4) & 1) * 8, v_half = (lane >> 3) & 1;
+
+  for (int i = 0; i < my_count; ++i) {
+    const int t0 = c0 + (warp + WARPS * i) * KEYS;
+    if (!mbar_wait(&full[i % DEPTH], (i / DEPTH) & 1)) {
+      if (lane == 0) atomicExch(p.error, 1);
+      break;
+    }
+    if (page_row(t0) >= 0) {
+    const uint32_t kbase = smem_addr(ring + (i % DEPTH) * STAGE_BYTES), vbase = kbase + TENSOR_BYTES;
+    if (t0 + KEYS - 1 > c1) {
+      // rows past the end of the sequence hold whatever the page held before: their scores are
+      // masked below, their values are cleared here so that 0 x (stale) cannot become NaN
+      const int first = c1 - t0 + 1;
+      for (int c = lane; c < (KEYS - first) * (D / 8); c += 32) {
+        const int r = first + c / (D / 8), ch = c % (D / 8);
+        *reinterpret_cast<uint4*>(ring + (i % DEPTH) * STAGE_BYTES + TENSOR_BYTES + (ch >> 3) * BOX_BYTES + r * 128 + (ch & 7) * 16) =
+            make_uint4(0, 0, 0, 0);
+      }
+      __syncwarp();
+    }
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int chunk16 = 2 * ks + k_half;
+      uint32_t a[4];
+      ldmatrix_x4_addr(a, kbase + (chunk16 >> 3) * BOX_BYTES + k_row * 128 + (((chunk16 & 7) ^ (k_row & 7)) << 4));
+      mma_bf16(c, a, qb[ks][0], qb[ks][1]);
+    }
+    // c0, c1: key t0 + g, heads 2t, 2t+1;  c2, c3: key t0 + g + 8
+    const bool vis_a = t0 + g <= c1, vis_b = t0 + g + 8 <= c1;
+    c[0] = vis_a ? c[0] * p.scale_log2 : -INFINITY;
+    c[1] = vis_a ? c[1] * p.scale_log2 : -INFINITY;
+    c[2] = vis_b ? c[2] * p.scale_log2 : -INFINITY;
+    c[3] = vis_b ? c[3] * p.scale_log2 : -INFINITY;
+    float mx[2] = {fmaxf(c[0], c[2]), fmaxf(c[1], c[3])};
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+      mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], off));
+      mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], off));
+    }
+    float corr[2], ref[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float m_new = fmaxf(m[h], mx[h]);
+      ref[h] = m_new == -INFINITY ? 0.f : m_new;
+      corr[h] = exp2f(m[h] - ref[h]);
+      m[h] = m_new;
+      l[h] *= corr[h];
+    }
+    const float p0 = exp2f(c[0] - ref[0]), p1 = exp2f(c[1] - ref[1]), p2 = exp2f(c[2] - ref[0]), p3 = exp2f(c[3] - ref[1]);
+    l[0] += p0 + p2;
+    l[1] += p1 + p3;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      o[mt][0] *= corr[0];
+      o[mt][1] *= corr[1];
+      o[mt][2] *= corr[0];
+      o[mt][3] *= corr[1];
+    }
+    // P^T [keys x heads] -> B fragments [k = keys][n = heads]
+    const uint32_t pb0 = movmatrix_trans(pack_bf16(p0, p1));
+    const uint32_t pb1 = movmatrix_trans(pack_bf16(p2, p3));
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const int chunk16 = 2 * mt + v_half;
+      uint32_t vf[4];
+      ldmatrix_x4_trans_addr(vf, vbase + (chunk16 >> 3) * BOX_BYTES + v_key * 128 + (((chunk16 & 7) ^ (v_key & 7)) << 4));
+      mma_bf16(o[mt], vf, pb0, pb1);
+    }
+    }
+    __syncwarp();
+    if (lane == 0 && i + DEPTH < my_count) {
+      fence_async_shared();
+      issue(i + DEPTH);
+    }
+  }
+  __syncthreads();
+
+  // combine the four warps through shared memory (the ring is idle now)
+  float* sm_m = reinterpret_cast<float*>(base);       // [4][8]
+  float* sm_l = sm_m + WARPS * HEADS;                 // [4][8]
+  float* sm_o = sm_l + WARPS * HEADS;                 // [4][8 heads][D]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float total = l[h];
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+    if (g == 0) {
+      sm_m[warp * HEADS + 2 * t + h] = m[h];
+      sm_l[warp * HEADS + 2 * t + h] = total;
+    }
+  }
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    sm_o[(warp * HEADS + 2 * t) * D + mt * 16 + g] = o[mt][0];
+    sm_o[(warp * HEADS + 2 * t + 1) * D + mt * 16 + g] = o[mt][1];
+    sm_o[(warp * HEADS + 2 * t) * D + mt * 16 + g + 8] = o[mt][2];
+    sm_o[(warp * HEADS + 2 * t + 1) * D + mt * 16 + g + 8] = o[mt][3];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < heads_here * D; idx += 128) {
+    const int h = idx / D, col = idx - h * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) M = fmaxf(M, sm_m[w * HEADS + h]);
+    const float ref = M == -INFINITY ? 0.f : M;
+    float acc = 0.f, L = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float f = exp2f(sm_m[w * HEADS + h] - ref);
+      acc += sm_o[(w * HEADS + h) * D + col] * f;
+      L += sm_l[w * HEADS + h] * f;
+    }
+    const int head = head0 + h;
+    if (p.num_splits == 1) {
+      p.out[(static_cast<long>(b) * p.nq + head) * D + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    } else {
+      const long slot = (static_cast<long>(b) * p.nq + head) * p.num_splits + split;
+      p.part_o[slot * D + col] = acc;
+      if (col == 0) {
+        p.part_ml[slot * 2] = M;
+        p.part_ml[slot * 2 + 1] = L;
+      }
+    }
+  }
+  if (p.num_splits == 1) return;
+
+  // ticket: the CTA that finishes last among the parts of this (request, KV head, slice) adds them up
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned old = atomicInc(&p.tickets[(static_cast<size_t>(b) * p.nkv + kvh) * p.slices + slice], p.num_splits - 1);
+    sm_last = old == static_cast<unsigned>(p.num_splits - 1);   // atomicInc wraps to zero: ready for the next launch
+  }
+  __syncthreads();
+  if (!sm_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < heads_here * p.num_splits; idx += 128) {
+    const int h = idx / p.num_splits, s = idx - h * p.num_splits;
+    const long slot = (static_cast<long>(b) * p.nq + head0 + h) * p.num_splits + s;
+    sm_pm[h][s] = __ldcg(p.part_ml + slot * 2);
+    sm_pl[h][s] = __ldcg(p.part_ml + slot * 2 + 1);
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < heads_here * D; idx += 128) {
+    const int h = idx / D, col = idx - h * D;
+    float M = -INFINITY;
+    for (int s = 0; s < p.num_splits; ++s) M = fmaxf(M, sm_pm[h][s]);
+    const float ref = M == -INFINITY ? 0.f : M;
+    const long slot0 = (static_cast<long>(b) * p.nq + head0 + h) * p.num_splits;
+    float acc = 0.f, L = 0.f;
+    for (int s = 0; s < p.num_splits; ++s) {
+      const float f = exp2f(sm_pm[h][s] - ref);
+      acc += __ldcg(p.part_o + (slot0 + s) * D + col) * f;
+      L += sm_pl[h][s] * f;
+    }
+    p.out[(static_cast<long>(b) * p.nq + head0 + h) * D + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  }
+}
+
+// Tensor maps over a pool seen as [rows][D] bfloat16, boxes of 16 rows x 64 columns, 128-byte swizzle.
+// Encoding costs a microsecond or two on the host, so the maps of the pools seen so far are kept.
+struct CachedMap {
+  const void* base;
+  uint64_t rows;
+  CUtensorMap map;
+};
+static int pool_map(const void* base, uint64_t rows, CUtensorMap* out) {
+  constexpr int kSlots = 1024;
+  static CachedMap cache[kSlots];
+  static int used = 0;
+  for (int i = 0; i < used; ++i)
+    if (cache[i].base == base && cache[i].rows == rows) {
+      *out = cache[i].map;
+      return 0;
+    }
+  EncodeTiledFn fn = tensor_map_encoder();
+  if (!fn) return 10005;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(D), rows};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(D) * 2};
+  const cuuint32_t box[2] = {64, KEYS};
+  const cuuint32_t elem[2] = {1, 1};
+  if (fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return 10006;
+  if (used < kSlots) {
+    cache[used].base = base;
+    cache[used].rows = rows;
+    cache[used].map = *out;
+    ++used;
+  }
+  return 0;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_attention_decode_tma_head_dim() { return HEAD_DIM; }
+extern "C" int b200_attention_decode_tma_ctas_per_sm() { return (227 * 1024) / (SMEM_BYTES + 1024 + 2 * HEADS * MAX_SPLITS * 4); }
+
+extern "C" long b200_attention_decode_tma_scratch_floats(int requests, int nq, int num_splits) {
+  return num_splits <= 1 ? 0 : static_cast<long>(requests) * nq * num_splits * (D + 2);
+}
+// Tickets the caller keeps, zeroed once: one per (request, KV head, slice of the group).
+extern "C" long b200_attention_decode_tma_tickets(int requests, int nq, int nkv) {
+  if (nq <= 0 || nkv <= 0 || nq % nkv) return -1;
+  const int group = nq / nkv, gs = group < HEADS ? group : HEADS;
+  return static_cast<long>(requests) * nkv * ((group + gs - 1) / gs);
+}
+
+// 0: no wait of the kernel ever gave up; 1: a TMA copy did not arrive within the poll limit.
+extern "C" int b200_attention_decode_tma_error() {
+  int value = 0;
+  if (cudaMemcpyFromSymbol(&value, g_decode_error, sizeof(int)) != cudaSuccess) return -1;
+  return value;
+}
+
+extern "C" int b200_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, void* out, const int* kv_len,
+                                         const int* block_table, int table_stride, int page_size, int num_pages, int requests,
+                                         int nq, int nkv, float scale, int num_splits, float* scratch, long scratch_floats,
+                                         unsigned* tickets, long ticket_count, cudaStream_t stream) {
+  if (requests <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || page_size % KEYS != 0 || table_stride <= 0 || num_pages <= 0)
+    return B200_ERR_BAD_SIZE;
+  if (num_splits < 1 || num_splits > MAX_SPLITS || requests > 65535) return B200_ERR_BAD_SIZE;
+  const uint64_t rows = static_cast<uint64_t>(num_pages) * nkv * page_size;
+  if (rows >= (1ull << 31)) return B200_ERR_TOO_LARGE;
+  if (scratch_floats < b200_attention_decode_tma_scratch_floats(requests, nq, num_splits)) return 10004;
+  if (num_splits > 1 && (tickets == nullptr || ticket_count < b200_attention_decode_tma_tickets(requests, nq, nkv))) return 10004;
+  DecodeParams p{};
+  p.q = static_cast<const bf16*>(q);
+  p.out = static_cast<bf16*>(out);
+  p.kv_len = kv_len;
+  p.block_table = block_table;
+  p.table_stride = table_stride;
+  p.page_size = page_size;
+  p.page_shift = -1;
+  for (int s = 0; s < 20; ++s)
+    if ((1 << s) == page_size) p.page_shift = s;
+  p.nq = nq;
+  p.nkv = nkv;
+  p.group = nq / nkv;
+  p.gs = p.group < HEADS ? p.group : HEADS;
+  p.slices = (p.group + p.gs - 1) / p.gs;
+  if (static_cast<long>(nkv) * p.slices > 65535) return B200_ERR_TOO_LARGE;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.num_splits = num_splits;
+  p.part_o = scratch;
+  p.part_ml = scratch + static_cast<long>(requests) * nq * num_splits * D;
+  p.tickets = tickets;
+  constexpr int kMaxDevices = 64;
+  static int* error_address[kMaxDevices] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return 10007;
+  if (!error_address[device] &&
+      cudaGetSymbolAddress(reinterpret_cast<void**>(&error_address[device]), g_decode_error) != cudaSuccess)
+    return 10007;
+  p.error = error_address[device];
+  CUtensorMap kmap, vmap;
+  if (int e = pool_map(k_pool, rows, &kmap)) return e;
+  if (int e = pool_map(v_pool, rows, &vmap)) return e;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  dim3 grid(num_splits, nkv * p.slices, requests);
+  launch(decode_attention_tma_kernel, grid, dim3(128), SMEM_BYTES, stream, kmap, vmap, p);
+  return launch_status();
+}

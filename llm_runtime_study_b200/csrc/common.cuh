@@ -103,6 +103,12 @@ __device__ __forceinline__ void pdl_trigger() {
 #endif
 }
 
+// Unconditional release of the next kernel, for small kernels whose CTAs are all resident at once
+// and whose successor does useful work before its own pdl_wait() (fetching weights, asking for
+// cache pages of earlier steps).  What the successor does before its wait must not depend on this
+// kernel or on any kernel before it.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
 inline bool pdl_enabled() {
   static int enabled = -1;
   if (enabled < 0) {

@@ -20,6 +20,9 @@ template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab, float scale) {
   pdl_trigger();
+#ifdef B200_EARLY_EMBED
+  pdl_launch_dependents();
+#endif
   pdl_wait();
   const int row = blockIdx.x;
   const int id = ids[row];
@@ -39,6 +42,9 @@ __global__ void embedding_vec_kernel(const int* __restrict__ ids, const T* __res
   constexpr int VN = Vec<T>::n;
   using V = typename Vec<T>::type;
   pdl_trigger();
+#ifdef B200_EARLY_EMBED
+  pdl_launch_dependents();
+#endif
   pdl_wait();
   const int row = blockIdx.x;
   const int id = ids[row];
@@ -68,6 +74,9 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const float* __res
   float* x = smem;            // [hidden]
   float* scratch = smem + hidden;  // [32]
   pdl_trigger();
+#ifdef B200_EARLY_NORM
+  pdl_launch_dependents();
+#endif
   pdl_wait();
   const int row = blockIdx.x;
   const size_t src = static_cast<size_t>(rows ? rows[row] : row) * hidden;
@@ -95,6 +104,9 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const float* _
                                        const int* __restrict__ rows, int hidden, float eps, int write_resid) {
   __shared__ float scratch[32];
   pdl_trigger();
+#ifdef B200_EARLY_NORM
+  pdl_launch_dependents();
+#endif
   pdl_wait();
   const int row = blockIdx.x;
   const size_t src = static_cast<size_t>(rows ? rows[row] : row) * hidden;
@@ -186,6 +198,9 @@ __global__ void __launch_bounds__(kRopeWarps * 32) qk_norm_rope_write_kernel(
     T* __restrict__ k_pool, T* __restrict__ v_pool, int nq, int nkv, int d, int qkv_stride) {
   __shared__ float cs[32 * kMaxPairs], sn[32 * kMaxPairs];
   pdl_trigger();
+#ifdef B200_EARLY_ROPE
+  pdl_launch_dependents();
+#endif
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int token = blockIdx.x;
@@ -308,6 +323,9 @@ __global__ void __launch_bounds__(kRopeWarps * 32) qk_norm_rope_write_vec_kernel
     T* __restrict__ k_pool, T* __restrict__ v_pool, int nq, int nkv, int d, int qkv_stride) {
   __shared__ float cs[32 * kMaxPairs], sn[32 * kMaxPairs];
   pdl_trigger();
+#ifdef B200_EARLY_ROPE
+  pdl_launch_dependents();
+#endif
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int token = blockIdx.x;

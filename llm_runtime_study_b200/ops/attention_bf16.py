@@ -27,6 +27,24 @@ _TABLE = {
 }
 
 
+_TMA_TABLE = {
+    "b200_attention_decode_tma_head_dim": [],
+    "b200_attention_decode_tma_ctas_per_sm": [],
+    "b200_attention_decode_tma_scratch_floats": [c_int, c_int, c_int],
+    "b200_attention_decode_tma_tickets": [c_int, c_int, c_int],
+    "b200_attention_decode_tma_error": [],
+    "b200_attention_decode_tma": [c_void_p] * 6 + [c_int] * 6 + [c_float, c_int, c_void_p, c_long, c_void_p, c_long, c_void_p],
+}
+# "tma": pages streamed by TMA, parts merged in the same launch; "mma": the cp.async kernels of attention_mma.cu
+DECODE_BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_DECODE_ATTENTION", "tma")
+# Stages of each warp's ring: 3 keeps most bytes in flight when few CTAs share the machine; with one
+# stage more CTAs (and warps) fit on an SM, which is what a batch that fills every SM several times
+# needs.  LLM_RUNTIME_STUDY_B200_DECODE_DEPTH forces one value.
+DECODE_DEPTHS = (1, 3)
+_FORCED_DEPTH = int(os.environ.get("LLM_RUNTIME_STUDY_B200_DECODE_DEPTH", "0"))
+DEEP_RING_MAX_CTAS = int(os.environ.get("LLM_RUNTIME_STUDY_B200_DECODE_DEEP_MAX", "296"))
+TMA_MAX_SPLITS = 64
+
 _TC_TABLE = {
     "b200_attention_tcgen05_error": [],
     "b200_attention_tcgen05_tokens_per_tile": [c_int],
@@ -51,6 +69,28 @@ def tc_supported(head_dim: int, page_size: int, window: int) -> bool:
     return head_dim in TC_HEAD_DIMS and page_size in TC_PAGE_SIZES and not window
 
 
+def tma_library_name(head_dim: int, depth: int = 3) -> str:
+    name = f"b200_attention_decode_tma_d{head_dim}_s{depth}"
+    if name not in native.library_specs():
+        native.register_library(name, ("attention_decode_tma.cu",), _TMA_TABLE,
+                                defines=(f"HEAD_DIM={head_dim}", f"DECODE_DEPTH={depth}"))
+    return name
+
+
+def tma_depth(ctas: int) -> int:
+    """Ring depth for a launch whose (request, KV head, slice) triples number ``ctas``."""
+
+    if _FORCED_DEPTH:
+        return _FORCED_DEPTH
+    return DECODE_DEPTHS[1] if ctas <= DEEP_RING_MAX_CTAS else DECODE_DEPTHS[0]
+
+
+def tma_supported(head_dim: int, page_size: int, window: int) -> bool:
+    """The TMA decode kernel takes head sizes that are multiples of 64, pages of a multiple of 16 tokens, no window."""
+
+    return head_dim % 64 == 0 and head_dim <= MAX_HEAD_DIM and page_size % 16 == 0 and not window
+
+
 def library_name(head_dim: int) -> str:
     name = f"b200_attention_mma_d{head_dim}"
     if name not in native.library_specs():
@@ -72,18 +112,24 @@ def build(head_dim: int) -> None:
     if head_dim in TC_HEAD_DIMS:
         name = tc_library_name(head_dim)
         build_library(name, ("attention_tcgen05.cu",), native.library_defines(name))
+    if head_dim % 64 == 0:
+        for depth in DECODE_DEPTHS:
+            name = tma_library_name(head_dim, depth)
+            build_library(name, ("attention_decode_tma.cu",), native.library_defines(name))
 
 
-def decode_splits(requests: int, kv_heads: int, slices: int, longest: int) -> int:
-    """Into how many parts each sequence is cut.  The decode kernel keeps three CTAs on
-    each of the 148 SMs; the CTAs of all parts should fill those slots in as few, as full
-    rounds as possible, and a part should not be shorter than two tiles of keys."""
+def decode_splits(requests: int, kv_heads: int, slices: int, longest: int, slots: int = 0) -> int:
+    """Into how many parts each sequence is cut.  The decode kernel keeps a few CTAs on
+    each of the 148 SMs (``slots`` in all); the CTAs of all parts should fill those slots
+    in as few, as full rounds as possible, and a part should not be shorter than two tiles
+    of keys."""
 
+    slots = slots or _CTA_SLOTS
     ctas = max(1, requests * kv_heads * slices)
     most = max(1, -(-longest // _MIN_KEYS_PER_SPLIT))
     best, best_cost = 1, None
     for s in range(1, min(most, 64) + 1):
-        rounds = -(-(ctas * s) // _CTA_SLOTS)
+        rounds = -(-(ctas * s) // slots)
         cost = rounds / s + 0.02 * s          # time of the rounds + what each further part costs to merge
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
@@ -177,15 +223,18 @@ def check_tcgen05_error(head_dim: int) -> None:
 
 def decode_attention(
     q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, *, kv_len: torch.Tensor, block_table: torch.Tensor,
-    scale: float, window: int = 0, splits: int = 1,
+    scale: float, window: int = 0, splits: int = 1, backend: str | None = None,
 ) -> torch.Tensor:
     """One query token per request (row ``i`` of ``q`` belongs to row ``i`` of
     ``block_table``) over its ``kv_len[i]`` cached keys, the sequence cut into
-    ``splits`` parts that are merged afterwards."""
+    ``splits`` parts that are merged afterwards.  ``backend``: "tma" or "mma";
+    by default the TMA kernel wherever it takes the shape."""
 
     for t, name in ((q, "q"), (keys, "keys"), (values, "values")):
         native.require(t, name, dtype=torch.bfloat16)
     n, nq, d, nkv, page_size, _, _ = _geometry(q, keys)
+    if (backend or DECODE_BACKEND) == "tma" and tma_supported(d, page_size, window) and splits <= TMA_MAX_SPLITS:
+        return _decode_attention_tma(q, keys, values, kv_len, block_table, scale, splits)
     lib = library_name(d)
     floats = native.query("b200_attention_decode_scratch_floats", n, nq, splits, library=lib)
     scratch = torch.empty(max(floats, 1), dtype=torch.float32, device=q.device)
@@ -198,6 +247,55 @@ def decode_attention(
     return out
 
 
+_TICKETS: dict[tuple, list[torch.Tensor]] = {}
+
+
+def _tickets(device: torch.device, count: int) -> torch.Tensor:
+    """Zeroed counters that the TMA decode kernel leaves at zero after every launch; one buffer
+    per device, made on first use.  A larger one replaces it when needed, and the old ones are
+    kept for good: a captured graph may still hold their address."""
+
+    made = _TICKETS.setdefault((device.type, device.index), [])
+    if not made or made[-1].numel() < count:
+        made.append(torch.zeros(max(count, 4096), dtype=torch.int32, device=device))
+    return made[-1]
+
+
+def decode_slots(head_dim: int, page_size: int, window: int, ctas: int = 1) -> int:
+    """CTAs of the decode kernel that fit on the GPU at once."""
+
+    if DECODE_BACKEND == "tma" and tma_supported(head_dim, page_size, window):
+        return 148 * native.query("b200_attention_decode_tma_ctas_per_sm", library=tma_library_name(head_dim, tma_depth(ctas)))
+    return _CTA_SLOTS
+
+
+def _decode_attention_tma(q, keys, values, kv_len, block_table, scale, splits) -> torch.Tensor:
+    n, nq, d, nkv, page_size, _, _ = _geometry(q, keys)
+    count = native.query("b200_attention_decode_tma_tickets", n, nq, nkv, library=tma_library_name(d))
+    lib = tma_library_name(d, tma_depth(count))
+    floats = native.query("b200_attention_decode_tma_scratch_floats", n, nq, splits, library=lib)
+    scratch = torch.empty(max(floats, 1), dtype=torch.float32, device=q.device)
+    tickets = _tickets(q.device, count)
+    out = torch.empty_like(q)
+    native.call(
+        "b200_attention_decode_tma", q.data_ptr(), keys.data_ptr(), values.data_ptr(), out.data_ptr(), kv_len.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], page_size, keys.shape[0], n, nq, nkv, float(scale), splits,
+        scratch.data_ptr(), floats, tickets.data_ptr(), tickets.numel(), native.stream_ptr(), library=lib)
+    return out
+
+
+def check_decode_tma_error(head_dim: int) -> None:
+    """Raise if a wait inside the TMA decode kernel ever gave up (synchronises the device)."""
+
+    for depth in DECODE_DEPTHS + ((_FORCED_DEPTH,) if _FORCED_DEPTH else ()):
+        name = tma_library_name(head_dim, depth)
+        if not native.library_loaded(name):
+            continue
+        code = native.query("b200_attention_decode_tma_error", library=name)
+        if code:
+            raise KernelError(f"TMA decode attention: a copy did not arrive within the poll limit (code {code})")
+
+
 def try_paged_attention(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Tensor, *, scale: float, window: int):
     """Return the attention output, or ``None`` when no tensor-core kernel takes
     this head size (the caller then uses the CUDA-core kernel)."""
@@ -207,8 +305,12 @@ def try_paged_attention(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Tens
         return None
     _, _, _, nkv, _, gs, slices = _geometry(q, cache.keys)
     if ctx.all_decode and n == ctx.num_entries:
+        if DECODE_BACKEND == "tma" and tma_supported(d, cache.keys.shape[2], window):
+            slices = -(-(nq // nkv) // 8)        # that kernel takes eight query heads of a group per CTA
         return decode_attention(q, cache.keys, cache.values, kv_len=ctx.kv_len, block_table=table, scale=scale,
-                                window=window, splits=decode_splits(n, nkv, slices, ctx.max_kv_len))
+                                window=window,
+                                splits=decode_splits(n, nkv, slices, ctx.max_kv_len,
+                                                     decode_slots(d, cache.keys.shape[2], window, n * nkv * slices)))
     maps = ctx.__dict__.setdefault("_tile_maps", {})
     page_size = cache.keys.shape[2]
     if PREFILL_BACKEND == "tcgen05" and tc_supported(d, page_size, window) and ctx.max_q_len >= TC_MIN_PORTION:

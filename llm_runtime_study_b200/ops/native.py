@@ -10,6 +10,7 @@ raised.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Sequence
 
 import torch
@@ -62,12 +63,23 @@ _functions: dict[str, ctypes._CFuncPtr] = {}
 
 
 _DEFINES: dict[str, tuple[str, ...]] = {}
+# Which small kernels release their successor at their first instruction (see pdl_launch_dependents
+# in csrc/common.cuh): the norms (a projection follows and fetches weights meanwhile) and the rotary
+# write (decode attention follows and asks for the pages of earlier steps meanwhile).
+_early = os.environ.get("LLM_RUNTIME_STUDY_B200_EARLY", "norm,rope")
+_DEFINES["b200_elementwise"] = tuple(f"B200_EARLY_{w.upper()}" for w in _early.split(",") if w and w != "none")
 
 
 def library_specs() -> dict:
     """Sources of every library, for the build-everything entry point."""
 
     return {name: sources for name, (sources, _) in _LIBRARIES.items()}
+
+
+def library_loaded(name: str) -> bool:
+    """Whether any function of this library has been looked up (and the library therefore loaded)."""
+
+    return any(key.startswith(name + ":") or (key in _LIBRARIES.get(name, ((), {}))[1]) for key in _functions)
 
 
 def library_defines(name: str) -> tuple[str, ...]:

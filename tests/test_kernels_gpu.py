@@ -292,7 +292,7 @@ def test_decode_attention_mma(nq, nkv, d, page, splits):
     lens = [1, 33, 70, 131, 64, 700, 65]
     q, kp, vp, pos, ent, table, want = _attention_case(torch.bfloat16, nq, nkv, d, page, [(L, 1) for L in lens])
     out = _mma().decode_attention(dev(q), dev(kp), dev(vp), kv_len=dev(torch.tensor(lens, dtype=torch.int32)),
-                                  block_table=dev(table), scale=1 / math.sqrt(d), splits=splits)
+                                  block_table=dev(table), scale=1 / math.sqrt(d), splits=splits, backend="mma")
     torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
 
 
@@ -315,7 +315,7 @@ def test_mma_attention_finds_a_far_key(boost):
                                    q_lens=[3], scale=1 / math.sqrt(d))
     torch.testing.assert_close(out.cpu().double(), want, atol=3e-2, rtol=2e-2)
     last = _mma().decode_attention(dev(q[-1:]), dev(kp), dev(vp), kv_len=dev(torch.tensor([700], dtype=torch.int32)),
-                                   block_table=dev(table), scale=1 / math.sqrt(d), splits=4)
+                                   block_table=dev(table), scale=1 / math.sqrt(d), splits=4, backend="mma")
     torch.testing.assert_close(last.cpu().double(), want[-1:], atol=3e-2, rtol=2e-2)
 
 
@@ -333,6 +333,56 @@ def test_masked_cache_rows_may_hold_anything():
     last = _mma().decode_attention(dev(q[-1:]), dev(kp), dev(vp), kv_len=dev(torch.tensor([37], dtype=torch.int32)),
                                    block_table=dev(table), scale=1 / math.sqrt(d), splits=2)
     torch.testing.assert_close(last.cpu().double(), want[-1:], **BF16_TOL)
+
+
+# ------------------------------------------- decode attention with pages streamed by TMA
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (32, 8, 128, 16), (5, 1, 64, 16), (24, 2, 64, 32), (3, 3, 192, 16),
+                                           (2, 1, 256, 64), (7, 7, 128, 48)])
+@pytest.mark.parametrize("splits", [1, 2, 5, 16, 64])
+def test_decode_attention_tma(nq, nkv, d, page, splits):
+    """Lengths around the edges of blocks, pages and parts; twice in a row, so that the tickets of
+    the first launch must have come back to zero; and the same bits as the first time."""
+
+    mma = _mma()
+    assert mma.DECODE_BACKEND == "tma" and mma.tma_supported(d, page, 0)
+    lens = [1, 15, 16, 17, 33, 64, 65, 131, 700, 1024]
+    q, kp, vp, pos, ent, table, want = _attention_case(torch.bfloat16, nq, nkv, d, page, [(L, 1) for L in lens])
+    args = (dev(q), dev(kp), dev(vp))
+    kw = dict(kv_len=dev(torch.tensor(lens, dtype=torch.int32)), block_table=dev(table), scale=1 / math.sqrt(d), splits=splits)
+    first = mma.decode_attention(*args, **kw)
+    second = mma.decode_attention(*args, **kw)
+    torch.testing.assert_close(first.cpu().double(), want, **BF16_TOL)
+    assert torch.equal(first, second)
+    mma.check_decode_tma_error(d)
+
+
+def test_decode_attention_tma_ignores_stale_rows_and_padding():
+    """Slots past a request's length hold NaN; a padded row has length 0 and no pages."""
+
+    mma = _mma()
+    nq, nkv, d, page = 8, 2, 128, 16
+    lens = [37, 100]
+    q, kp, vp, pos, ent, table, want = _attention_case(torch.bfloat16, nq, nkv, d, page, [(L, 1) for L in lens])
+    kp[table[0, 2].long(), :, 37 - 32:] = float("nan")
+    vp[table[0, 2].long(), :, 37 - 32:] = float("nan")
+    q3 = torch.cat([q, torch.zeros(1, nq, d, dtype=q.dtype)])
+    table3 = torch.cat([table, torch.full((1, table.shape[1]), -1, dtype=torch.int32)])
+    out = mma.decode_attention(dev(q3), dev(kp), dev(vp), kv_len=dev(torch.tensor(lens + [0], dtype=torch.int32)),
+                               block_table=dev(table3), scale=1 / math.sqrt(d), splits=3)
+    torch.testing.assert_close(out[:2].cpu().double(), want, **BF16_TOL)
+    assert float(out[2].abs().max()) == 0.0
+    mma.check_decode_tma_error(d)
+
+
+@pytest.mark.parametrize("boost", [0, 15, 16, 255, 256, -2, -1, 300])
+def test_decode_attention_tma_finds_a_far_key(boost):
+    mma = _mma()
+    nq, nkv, d, page = 8, 2, 128, 16
+    q, kp, vp, pos, ent, table, want = _attention_case(torch.bfloat16, nq, nkv, d, page, [(700, 1)], boost=boost)
+    assert float(want[-1].abs().mean()) > 3.0
+    out = mma.decode_attention(dev(q), dev(kp), dev(vp), kv_len=dev(torch.tensor([700], dtype=torch.int32)),
+                               block_table=dev(table), scale=1 / math.sqrt(d), splits=3)
+    torch.testing.assert_close(out.cpu().double(), want, atol=3e-2, rtol=2e-2)
 
 
 # ------------------------------------------------------------ bfloat16 projections

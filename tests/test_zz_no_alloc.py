@@ -59,7 +59,7 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point():
     for seed, lens, splits in ((1, [700, 33, 64, 129, 1], 5), (2, [95, 300], 3)):
         q, keys, values, kv_len, table = _case(seed, lens)
         want = attention_bf16.decode_attention(q, keys, values, kv_len=kv_len, block_table=table,
-                                               scale=1 / math.sqrt(HEAD_DIM), splits=splits)
+                                               scale=1 / math.sqrt(HEAD_DIM), splits=splits, backend="mma")
         status, got = _call(fn, q, keys, values, kv_len, table, splits)
         assert status == 0
         torch.cuda.synchronize()
