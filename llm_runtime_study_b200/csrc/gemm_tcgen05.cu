@@ -34,6 +34,7 @@ constexpr int BK = 64;    // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr int kThreads = 192;
+constexpr int kStreamKMaxCtas = 256;   // slots of the stream-K workspace the caller provides
 
 __device__ int g_gemm_error = 0;
 
@@ -155,6 +156,9 @@ struct GemmParams {
   int M, N, K, ldc;
   int vector_ok;      // rows of C start on 16-byte boundaries
   int kb_per_split;   // 64-wide K blocks per CTA of a cluster (swapped mode); all of them otherwise
+  int accumulate;     // float output only: C += A W^T + bias instead of C = ...
+  float* partials;    // stream-K: [grid][128][256] partial accumulators
+  unsigned* flags;    // stream-K: [grid], zero between launches
 };
 
 // SWAP = false: rows operand = A (activations), columns operand = W; tile (m0, n0) = (blockIdx.x*128, blockIdx.y*BN).
@@ -445,12 +449,29 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, con
                 for (int j = 0; j < 8; ++j) store_out<OutT>(dst + j, h[b * 8 + j]);
               }
             }
-          } else if (p.vector_ok && nb + 32 <= p.N) {
-            store_row_32(crow + nb, v);
           } else {
+            if constexpr (sizeof(OutT) == 4) {
+              if (p.accumulate) {
+                if (p.vector_ok && nb + 32 <= p.N) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nb + j < p.N) store_out<OutT>(crow + nb + j, v[j]);
+                  for (int j = 0; j < 32; j += 4) {
+                    const float4 e = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(crow) + nb + j);
+                    v[j] += e.x; v[j + 1] += e.y; v[j + 2] += e.z; v[j + 3] += e.w;
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (nb + j < p.N) v[j] += reinterpret_cast<const float*>(crow)[nb + j];
+                }
+              }
+            }
+            if (p.vector_ok && nb + 32 <= p.N) {
+              store_row_32(crow + nb, v);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < p.N) store_out<OutT>(crow + nb + j, v[j]);
+            }
           }
         }
       }
@@ -461,6 +482,305 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, con
       }
       if (!ok) break;
     }
+  }
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------ stream-K kernel
+// One CTA per SM.  The tiles that fill whole rounds of gridDim.x CTAs are computed whole, round
+// by round (tile = round * gridDim.x + CTA, so the CTAs of a round share few weight panels in L2).
+// The tiles that are left, fewer than gridDim.x, would keep only some SMs busy for a whole tile's
+// time; instead their (tile, 64-wide K block) pairs, tile-major, are cut into equal contiguous
+// ranges, one per CTA, so that every SM does the same number of tensor-core steps.  Such a range
+// may begin in the middle of a tile and end in the middle of another.  The CTA that holds K block
+// 0 of a tile owns it: it runs that piece last, then adds what the CTAs after it computed for the
+// rest of the tile's K range, and writes the result.  Those CTAs ran their piece first (it is the
+// head of their range), wrote the accumulator to `partials` and raised their flag; the owner
+// lowers the flags again, so they are zero when the kernel ends.  Nobody waits for an owner, so
+// no wait depends on a CTA that has not started; the owner's wait for a flag is bounded.
+// The partial sums of a tile are added in the order of the CTAs: the result depends on the shape
+// of the product only, never on timing.
+__device__ __forceinline__ unsigned load_acquire(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void store_release(unsigned* p, unsigned v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
+
+struct StreamKPlan {
+  int num_kb, ctas, rounds, first_left, sharers;   // sharers: CTAs that take part in the left-over tiles
+  long long left_units;
+  __device__ long long begin_of(int cta) const { return cta >= sharers ? left_units : left_units * cta / sharers; }
+  // Calls f(tile, kb0, kb1, last_partner): the K blocks [kb0, kb1) of `tile`; for an owned tile whose K range
+  // continues in other CTAs, those are blockIdx.x + 1 .. last_partner (else last_partner == blockIdx.x).
+  template <typename F> __device__ __forceinline__ void for_each_piece(int cta, F&& f) const {
+    for (int r = 0; r < rounds; ++r) f(r * ctas + cta, 0, num_kb, cta);
+    const long long begin = begin_of(cta), end = begin_of(cta + 1);
+    for (long long u = begin; u < end;) {
+      const int t = static_cast<int>(u / num_kb), kb0 = static_cast<int>(u - static_cast<long long>(t) * num_kb);
+      const int kb1 = static_cast<int>(min(static_cast<long long>(num_kb), kb0 + (end - u)));
+      int last = cta;
+      if (kb0 == 0 && kb1 < num_kb) {
+        const long long tile_end = static_cast<long long>(t + 1) * num_kb;
+        while (last + 1 < sharers && begin_of(last + 1) < tile_end) ++last;
+      }
+      f(first_left + t, kb0, kb1, last);
+      u += kb1 - kb0;
+    }
+  }
+};
+
+// Element (row, column c) of a partial accumulator: 16-byte groups of four columns, the 128 rows of a
+// group next to each other, so that a warp (32 rows) moves 512 contiguous bytes.
+__device__ __forceinline__ float4* partial_group(float* base, int cta, int group, int row) {
+  return reinterpret_cast<float4*>(base) + (static_cast<size_t>(cta) * 64 + group) * BM + row;
+}
+
+template <int STAGES, bool SWIGLU, typename OutT>
+__global__ void __launch_bounds__(kThreads)
+gemm_tcgen05_streamk_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
+                            GemmParams p) {
+  constexpr int BN = 256;
+  constexpr uint32_t ROW_BYTES = BM * BK * 2, COL_BYTES = BN * BK * 2, STAGE_BYTES = ROW_BYTES + COL_BYTES;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t kFlagSpins = 1u << 22;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;    // [2]
+  uint64_t* acc_empty = acc_full + 2;     // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
+  const int tiles = m_tiles * n_tiles;
+  StreamKPlan plan;
+  plan.num_kb = (p.K + BK - 1) / BK;
+  plan.ctas = gridDim.x;
+  plan.rounds = tiles / plan.ctas;
+  plan.first_left = plan.rounds * plan.ctas;
+  const int left = tiles - plan.first_left;
+  plan.left_units = static_cast<long long>(left) * plan.num_kb;
+  // at most three CTAs per left-over tile: each further one costs the owner a pass over 128 KB
+  plan.sharers = static_cast<int>(min(static_cast<long long>(min(plan.ctas, 3 * left)), plan.left_units));
+  const int cta = blockIdx.x;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full + b, 1);
+      mbar_init(acc_empty + b, 4);     // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------------------------------------------------------- producer
+    int it = 0;
+    bool ok = true;
+    plan.for_each_piece(cta, [&](int tile, int kb0, int kb1, int) {
+      const int row0 = (tile % m_tiles) * BM, col0 = (tile / m_tiles) * BN;
+      for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t phase = (it / STAGES) & 1;
+        if (!mbar_wait(empty + s, phase ^ 1)) { atomicExch(&g_gemm_error, 1); ok = false; break; }
+        mbar_expect_tx(full + s, STAGE_BYTES);
+        unsigned char* stage = smem + s * STAGE_BYTES;
+        tma_load_2d(stage, &map_rows, full + s, kb * BK, row0);
+        tma_load_2d(stage + ROW_BYTES, &map_cols, full + s, kb * BK, col0);
+      }
+    });
+  } else if (warp == 1 && lane == 0) {
+    // ---------------------------------------------------------------- tensor-core issue
+    constexpr uint32_t idesc = umma_idesc(BN);
+    int it = 0, local = 0;
+    bool ok = true;
+    plan.for_each_piece(cta, [&](int, int kb0, int kb1, int) {
+      if (!ok) return;
+      const int buf = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      ++local;
+      if (!mbar_wait(acc_empty + buf, acc_phase ^ 1)) { atomicExch(&g_gemm_error, 4); ok = false; return; }
+      tcgen05_fence_after();
+      const uint32_t tmem_d = tmem_base + buf * BN;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t phase = (it / STAGES) & 1;
+        if (!mbar_wait(full + s, phase)) { atomicExch(&g_gemm_error, 2); ok = false; return; }
+        tcgen05_fence_after();
+        const uint32_t a_addr = smem_addr(smem + s * STAGE_BYTES), b_addr = a_addr + ROW_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma_bf16(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, ((kb - kb0) | k) != 0);
+        umma_commit(empty + s);
+      }
+      umma_commit(acc_full + buf);
+    });
+  } else if (warp >= 2) {
+    // -------------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    int local = 0;
+    bool alive = true;
+    plan.for_each_piece(cta, [&](int tile, int kb0, int kb1, int last_partner) {
+      if (!alive) return;
+      const int buf = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      ++local;
+      const int row0 = (tile % m_tiles) * BM, col0 = (tile / m_tiles) * BN;
+      const bool ok = mbar_wait(acc_full + buf, acc_phase);
+      if (!ok) { atomicExch(&g_gemm_error, 3); alive = false; }
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+      if (kb0 > 0) {
+        // the rest of a tile that an earlier CTA owns: hand the accumulator over
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          float v[32];
+          if (ok) {
+            tmem_load_32(taddr + c, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            __stcg(partial_group(p.partials, cta, (c + j) >> 2, row), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(acc_empty + buf)) : "memory");
+        __threadfence();
+        epilogue_barrier();
+        if (warp == 2 && lane == 0) store_release(p.flags + cta, 1u);
+        return;
+      }
+      // owner: the CTAs cta + 1 .. last_partner hold the rest of the tile's K range
+      for (int q = cta + 1; q <= last_partner; ++q) {
+        uint32_t spins = 0;
+        while (load_acquire(p.flags + q) == 0u) {
+          if (++spins > kFlagSpins) { atomicExch(&g_gemm_error, 5); break; }
+          __nanosleep(32);
+        }
+      }
+      const int m = row0 + row;
+      OutT* crow = static_cast<OutT*>(p.c) + static_cast<size_t>(m) * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        float v[32];
+        float4 t[2][8];
+        const int partners = last_partner - cta;
+        // the loads of up to two partners are in flight while the accumulator comes out of TMEM
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+          if (q < partners) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t[q][j] = __ldcg(partial_group(p.partials, cta + 1 + q, (c >> 2) + j, row));
+          }
+        if (ok) {
+          tmem_load_32(taddr + c, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+          if (q < partners) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              v[4 * j] += t[q][j].x; v[4 * j + 1] += t[q][j].y; v[4 * j + 2] += t[q][j].z; v[4 * j + 3] += t[q][j].w;
+            }
+          }
+        for (int q = cta + 3; q <= last_partner; ++q) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 e = __ldcg(partial_group(p.partials, q, (c >> 2) + j, row));
+            v[4 * j] += e.x; v[4 * j + 1] += e.y; v[4 * j + 2] += e.z; v[4 * j + 3] += e.w;
+          }
+        }
+        if (m < p.M) {
+          const int nb = col0 + c;
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += nb + j < p.N ? p.bias[nb + j] : 0.f;
+          }
+          if constexpr (SWIGLU) {
+            // [g0..7 | u0..7 | g8..15 | u8..15] -> 16 outputs at column nb / 2 (N is a multiple of 16)
+            float h[16];
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float gate = v[b * 16 + j], up = v[b * 16 + 8 + j];
+                h[b * 8 + j] = gate / (1.f + __expf(-gate)) * up;
+              }
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+              if (nb + b * 16 + 16 > p.N) continue;
+              OutT* dst = crow + (nb >> 1) + b * 8;
+              if (p.vector_ok) {
+                store_row_8(dst, h + b * 8);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) store_out<OutT>(dst + j, h[b * 8 + j]);
+              }
+            }
+          } else {
+            if constexpr (sizeof(OutT) == 4) {
+              if (p.accumulate) {
+                if (p.vector_ok && nb + 32 <= p.N) {
+#pragma unroll
+                  for (int j = 0; j < 32; j += 4) {
+                    const float4 e = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(crow) + nb + j);
+                    v[j] += e.x; v[j + 1] += e.y; v[j + 2] += e.z; v[j + 3] += e.w;
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (nb + j < p.N) v[j] += reinterpret_cast<const float*>(crow)[nb + j];
+                }
+              }
+            }
+            if (p.vector_ok && nb + 32 <= p.N) {
+              store_row_32(crow + nb, v);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < p.N) store_out<OutT>(crow + nb + j, v[j]);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(acc_empty + buf)) : "memory");
+      if (last_partner > cta) {
+        epilogue_barrier();      // every epilogue thread has read the partners' sums
+        if (warp == 2 && lane == 0)
+          for (int q = cta + 1; q <= last_partner; ++q) p.flags[q] = 0u;
+      }
+    });
   }
   __syncwarp();
   tcgen05_fence_before();
@@ -549,6 +869,29 @@ static int launch_persistent(const CUtensorMap& rows, const CUtensorMap& cols, c
   return static_cast<int>(cudaGetLastError());
 }
 
+template <int STAGES, bool SWIGLU, typename OutT>
+static int launch_streamk(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, cudaStream_t stream) {
+  constexpr size_t smem = STAGES * (BM * BK * 2 + 256 * BK * 2) + 1024 + 256;
+  auto kernel = gemm_tcgen05_streamk_kernel<STAGES, SWIGLU, OutT>;
+  static bool configured = false;
+  static int sm_count = 0;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+    configured = true;
+  }
+  const long long units = static_cast<long long>((p.M + BM - 1) / BM) * ((p.N + 255) / 256) * ((p.K + BK - 1) / BK);
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
+  int grid = sm_count < kStreamKMaxCtas ? sm_count : kStreamKMaxCtas;
+  if (3 * tiles < grid) grid = 3 * tiles;              // at most three CTAs share a tile
+  if (units < grid) grid = static_cast<int>(units);
+  kernel<<<grid, kThreads, smem, stream>>>(rows, cols, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -568,7 +911,13 @@ extern "C" int b200_gemm_tcgen05_error() {
 // splits > 0 selects the swapped kernel for M <= 64 with the K range cut into `splits` (1..8) parts;
 // splits == 0 the persistent kernel; splits < 0 the one-tile-per-CTA kernel.
 static int gemm_tcgen05_impl(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
-                             int out_f32, int splits, int swiglu, cudaStream_t stream);
+                             int out_f32, int splits, int swiglu, cudaStream_t stream, int accumulate = 0);
+
+// The persistent kernel with C (float32) += A W^T + bias: the residual sum done where the product is.
+extern "C" int b200_gemm_tcgen05_add(const void* A, const void* W, const float* bias, float* C, int M, int N, int K, int ldc,
+                                     cudaStream_t stream) {
+  return gemm_tcgen05_impl(A, W, bias, C, M, N, K, ldc, 1, 0, 0, stream, 1);
+}
 
 extern "C" int b200_gemm_tcgen05(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
                                  int out_f32, int splits, cudaStream_t stream) {
@@ -583,12 +932,36 @@ extern "C" int b200_gemm_tcgen05_swiglu(const void* A, const void* W, const floa
   return gemm_tcgen05_impl(A, W, bias, C, M, N, K, ldc, out_f32, 0, 1, stream);
 }
 
+// Stream-K kernel.  `partials` holds b200_gemm_tcgen05_streamk_partial_floats() floats, `flags`
+// b200_gemm_tcgen05_streamk_flags() 32-bit words that are zero before the first launch (the kernel
+// leaves them zero).  Launches that share them must not overlap.  accumulate (float output, no
+// SwiGLU): C += A W^T + bias.
+extern "C" long b200_gemm_tcgen05_streamk_partial_floats() { return static_cast<long>(kStreamKMaxCtas) * BM * 256; }
+extern "C" int b200_gemm_tcgen05_streamk_flags() { return kStreamKMaxCtas; }
+
+extern "C" int b200_gemm_tcgen05_streamk(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
+                                         int out_f32, int swiglu, int accumulate, float* partials, unsigned* flags,
+                                         cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || ldc < (swiglu ? N / 2 : N) || (swiglu && N % 16 != 0)) return B200_ERR_BAD_SIZE;
+  if (accumulate && (!out_f32 || swiglu)) return B200_ERR_BAD_SIZE;
+  if (!partials || !flags) return 10004;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(partials)) & 15) return B200_ERR_BAD_SIZE;
+  GemmParams p{C, bias, M, N, K, ldc, (ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0, 0, accumulate, partials, flags};
+  CUtensorMap rows, cols;
+  if (int e = make_map(&rows, A, M, K, BM)) return e;
+  if (int e = make_map(&cols, W, N, K, 256)) return e;
+  if (swiglu)
+    return out_f32 ? launch_streamk<4, true, float>(rows, cols, p, stream) : launch_streamk<4, true, __nv_bfloat16>(rows, cols, p, stream);
+  return out_f32 ? launch_streamk<4, false, float>(rows, cols, p, stream) : launch_streamk<4, false, __nv_bfloat16>(rows, cols, p, stream);
+}
+
 static int gemm_tcgen05_impl(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
-                             int out_f32, int splits, int swiglu, cudaStream_t stream) {
+                             int out_f32, int splits, int swiglu, cudaStream_t stream, int accumulate) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ldc < (swiglu ? N / 2 : N)) return B200_ERR_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return B200_ERR_BAD_SIZE;
-  GemmParams p{C, bias, M, N, K, ldc, (ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0, 0};
+  GemmParams p{C, bias, M, N, K, ldc, (ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0, 0, accumulate, nullptr, nullptr};
   CUtensorMap rows, cols;
   const int total_kb = (K + BK - 1) / BK;
   if (splits > 0) {

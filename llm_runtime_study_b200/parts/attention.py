@@ -92,7 +92,9 @@ class GroupedQueryAttention(Mixer):
         return None if self.shares_kv else PagedKV(self.num_kv_heads, self.head_dim, self.window)
 
     # ------------------------------------------------------------- forward
-    def forward(self, x: torch.Tensor, ctx: Any, cache: Any) -> torch.Tensor:
+    adds_to_residual = True
+
+    def forward(self, x: torch.Tensor, ctx: Any, cache: Any, residual: torch.Tensor | None = None) -> torch.Tensor | None:
         qkv = self.qkv_proj(x)
         rotary = self.position.rotary_parameters() if self.position is not None else None
         table = ctx.block_table(cache.group)
@@ -113,4 +115,4 @@ class GroupedQueryAttention(Mixer):
             k_pool=None if self.shares_kv else cache.keys, v_pool=None if self.shares_kv else cache.values,
         )
         out = ctx.attention(q, cache, scale=self.scale, window=self.window or 0)
-        return self.o_proj(out.view(out.shape[0], -1), torch.float32)
+        return self.o_proj(out.view(out.shape[0], -1), torch.float32, add_to=residual)

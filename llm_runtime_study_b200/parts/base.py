@@ -105,6 +105,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # A part that sets this takes a keyword ``residual`` (the float32 residual rows, already
+    # holding everything before this part) and may add its output to them in place, returning
+    # ``None`` instead of the output; the block then has nothing left to add.
+    adds_to_residual = False
+
     def cache_requirement(self) -> PagedKV | FixedState | None:
         return None
 
@@ -113,6 +118,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    adds_to_residual = False    # as for Mixer
+
     def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
         raise NotImplementedError
 

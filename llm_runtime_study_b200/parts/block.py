@@ -54,6 +54,12 @@ class PreNormBlock(Block):
 
     def forward(self, stream: ResidualStream, ctx: Any, cache: Any) -> None:
         x = self.mixer_norm.add_norm(stream.resid, stream.delta)
-        stream.delta = self.mixer.forward(x, ctx, cache)
+        if self.mixer.adds_to_residual:
+            stream.delta = self.mixer.forward(x, ctx, cache, residual=stream.resid)
+        else:
+            stream.delta = self.mixer.forward(x, ctx, cache)
         x = self.ffn_norm.add_norm(stream.resid, stream.delta)
-        stream.delta = self.feed_forward.forward(x, ctx)
+        if self.feed_forward.adds_to_residual:
+            stream.delta = self.feed_forward.forward(x, ctx, residual=stream.resid)
+        else:
+            stream.delta = self.feed_forward.forward(x, ctx)

@@ -29,6 +29,7 @@ class Projection:
 
     GEMM_BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_GEMM", "tcgen05")
     TCGEN05_MIN_ROWS = 128
+    FUSE_RESIDUAL = os.environ.get("LLM_RUNTIME_STUDY_B200_FUSE_RESIDUAL", "1") != "0"
 
     def __init__(self, weights: list[torch.Tensor], biases: list[torch.Tensor] | None, runtime: Runtime) -> None:
         self.runtime = runtime
@@ -54,7 +55,12 @@ class Projection:
                 return gemm_bf16.linear(x, self.weight, self.bias, torch.bfloat16, swiglu=True)
         return F.silu_mul_interleaved(self(x))
 
-    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, *,
+                 add_to: torch.Tensor | None = None) -> torch.Tensor | None:
+        """The projection of ``x``.  ``add_to`` (the float32 residual rows): where the kernel that takes
+        this shape can add its result to them in its epilogue it does so and ``None`` is returned;
+        otherwise the result is returned as always and the caller adds it."""
+
         out_dtype = out_dtype or self.runtime.dtype
         if x.shape[-1] != self.in_features:
             raise KernelError(f"projection expects width {self.in_features}, got {x.shape[-1]}")
@@ -69,7 +75,10 @@ class Projection:
             if m <= gemm_bf16.SKINNY_M:
                 return gemm_bf16.linear_skinny(x, self.weight, self.bias, out_dtype)
             if self.GEMM_BACKEND == "tcgen05" and m >= self.TCGEN05_MIN_ROWS:
-                return gemm_bf16.linear(x, self.weight, self.bias, out_dtype, splits=0)
+                if add_to is not None and out_dtype == torch.float32 and self.FUSE_RESIDUAL:
+                    gemm_bf16.linear(x, self.weight, self.bias, torch.float32, add_to=add_to)
+                    return None
+                return gemm_bf16.linear(x, self.weight, self.bias, out_dtype)
         if out_dtype == torch.bfloat16:
             y = torch.mm(x, self.weight.t())
         else:

@@ -46,6 +46,8 @@ class SwiGLU(FeedForward):
             self.gate_up_proj = Projection([gate, up], None, runtime)
         self.down_proj = Projection([tensors["down_proj.weight"]], None, runtime)
 
-    def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
+    adds_to_residual = True
+
+    def forward(self, x: torch.Tensor, ctx: Any, residual: torch.Tensor | None = None) -> torch.Tensor | None:
         hidden = self.gate_up_proj.swiglu(x) if self.interleaved else F.silu_mul(self.gate_up_proj(x))
-        return self.down_proj(hidden, torch.float32)
+        return self.down_proj(hidden, torch.float32, add_to=residual)

@@ -428,6 +428,39 @@ def test_tcgen05_projection(m, n, k, bias, splits, out):
     torch.testing.assert_close(got.cpu().double(), want, atol=(1e-2 if out == torch.bfloat16 else 2e-5) * scale, rtol=0)
 
 
+@pytest.mark.parametrize("m,n,k,bias", [
+    (128, 256, 64, False), (130, 264, 72, True), (300, 1000, 520, True), (2048, 1024, 4096, False), (5000, 4096, 512, True),
+    (17, 4096, 4096, False), (129, 24, 12288, True), (640, 520, 8, False), (1, 8, 8, True), (2048, 4096, 12288, False),
+])
+@pytest.mark.parametrize("out", [torch.float32, torch.bfloat16])
+def test_tcgen05_stream_k_projection(m, n, k, bias, out):
+    """Tile counts below, at and far above the number of SMs; K ranges cut inside tiles; three
+    calls in a row, the last two with the flags the first one left."""
+
+    x, w, b, want = _gemm_case(m, n, k, bias)
+    args = (dev(x), dev(w), dev(b) if bias else None, out)
+    got = _gemm().linear_streamk(*args)
+    again = _gemm().linear_streamk(*args)
+    third = _gemm().linear_streamk(*args)
+    _gemm().check_error()
+    scale = float(want.abs().max())
+    torch.testing.assert_close(got.cpu().double(), want, atol=(1e-2 if out == torch.bfloat16 else 2e-5) * scale, rtol=0)
+    assert torch.equal(got, again) and torch.equal(got, third)        # partial sums are added in a fixed order
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 1000, 520), (2048, 4096, 4096)])
+def test_tcgen05_stream_k_adds_to_the_residual(m, n, k):
+    x, w, b, want = _gemm_case(m, n, k, True)
+    torch.manual_seed(3)
+    resid = torch.randn(m, n)
+    target = dev(resid.clone())
+    delta = _gemm().linear_streamk(dev(x), dev(w), dev(b), torch.float32)
+    out = _gemm().linear_streamk(dev(x), dev(w), dev(b), add_to=target)
+    _gemm().check_error()
+    assert out.data_ptr() == target.data_ptr()
+    assert torch.equal(out, dev(resid) + delta)                       # the same single float32 addition
+
+
 def test_projections_refuse_unaligned_widths():
     from llm_runtime_study_b200.errors import KernelError
 
@@ -507,5 +540,8 @@ def test_projection_with_swiglu_epilogue(m, inter, k):
     else:
         got = _gemm().linear(dev(x), w, None, torch.bfloat16, swiglu=True)
         _gemm().check_error()
+        streamed = _gemm().linear_streamk(dev(x), w, None, torch.bfloat16, swiglu=True)
+        _gemm().check_error()
+        torch.testing.assert_close(streamed.cpu().double(), want, atol=2e-2 * float(want.abs().max()), rtol=0)
     assert got.shape == (m, inter)
     torch.testing.assert_close(got.cpu().double(), want, atol=2e-2 * float(want.abs().max()), rtol=0)
