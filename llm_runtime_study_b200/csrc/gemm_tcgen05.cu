@@ -492,6 +492,237 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, con
   }
 }
 
+// ------------------------------------------------------------------------ 2-CTA kernel
+// A pair of CTAs (a cluster of two, on neighbouring SMs) computes one 256 x 256 tile with
+// tcgen05.mma.cta_group::2.  Each CTA brings in 128 rows of A and 128 of the 256 weight rows per
+// 64-wide K block (32 KB instead of the 48 KB a CTA of the one-CTA kernel needs for the same
+// 128 x 256 outputs) and keeps its 128 x 256 half of the accumulator in its own TMEM; the tensor
+// core of the pair reads both halves of B.  Only the even CTA (the leader) issues MMAs.  Protocol
+// per stage: both CTAs' TMA copies complete on the leader's `full` barrier (armed by the leader
+// for the bytes of both); the leader's commit arrives on `empty` in both CTAs.  Per tile: the
+// leader's commit arrives on `acc_full` in both CTAs; the eight epilogue warps of the pair arrive
+// on the leader's `acc_empty`.
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_address, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(out) : "r"(smem_address), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// TMA copy into this CTA's shared memory whose bytes are counted on a barrier of the pair's leader
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(
+          smem_addr(dst)),
+      "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives, once the MMAs issued so far have finished, on the barrier at this address in both CTAs of the pair
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(
+                   smem_addr(bar)),
+               "h"(both)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_address) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_address) : "memory");
+}
+// instruction descriptor for the pair: M = 256 (128 rows per CTA)
+__host__ __device__ constexpr uint32_t umma_idesc_pair(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
+}
+
+template <int STAGES, bool SWIGLU, typename OutT>
+__global__ void __launch_bounds__(kThreads)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols, GemmParams p) {
+  constexpr int BN = 256, HALF_N = 128, PAIR_M = 256;
+  constexpr uint32_t ROW_BYTES = BM * BK * 2, COL_BYTES = HALF_N * BK * 2, STAGE_BYTES = ROW_BYTES + COL_BYTES;
+  constexpr uint32_t TMEM_COLS = 512;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;    // [2]
+  uint64_t* acc_empty = acc_full + 2;     // [2], used in the leader
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int m_tiles = (p.M + PAIR_M - 1) / PAIR_M, n_tiles = (p.N + BN - 1) / BN;
+  const int tiles = m_tiles * n_tiles;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full + b, 1);
+      mbar_init(acc_empty + b, 8);     // one arrival per epilogue warp of the pair
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();                     // both CTAs' barriers exist before anything arrives on them
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------------------------------------------------------- producer (both CTAs)
+    int it = 0;
+    bool ok = true;
+    for (int tile = pair; tile < tiles && ok; tile += pairs) {
+      const int row0 = (tile % m_tiles) * PAIR_M + static_cast<int>(rank) * BM;
+      const int col0 = (tile / m_tiles) * BN + static_cast<int>(rank) * HALF_N;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t phase = (it / STAGES) & 1;
+        if (!mbar_wait(empty + s, phase ^ 1)) { atomicExch(&g_gemm_error, 1); ok = false; break; }
+        if (leader) mbar_expect_tx(full + s, 2 * STAGE_BYTES);
+        const uint32_t leader_full = map_to_cta(smem_addr(full + s), 0);
+        unsigned char* stage = smem + s * STAGE_BYTES;
+        tma_load_2d_pair(stage, &map_rows, leader_full, kb * BK, row0);
+        tma_load_2d_pair(stage + ROW_BYTES, &map_cols, leader_full, kb * BK, col0);
+      }
+    }
+  } else if (warp == 1 && lane == 0 && leader) {
+    // ---------------------------------------------------------------- tensor-core issue (leader)
+    constexpr uint32_t idesc = umma_idesc_pair(BN);
+    int it = 0, local = 0;
+    bool ok = true;
+    for (int tile = pair; tile < tiles && ok; tile += pairs, ++local) {
+      const int buf = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(acc_empty + buf, acc_phase ^ 1)) { atomicExch(&g_gemm_error, 4); ok = false; break; }
+      tcgen05_fence_after();
+      const uint32_t tmem_d = tmem_base + buf * BN;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t phase = (it / STAGES) & 1;
+        if (!mbar_wait(full + s, phase)) { atomicExch(&g_gemm_error, 2); ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t a_addr = smem_addr(smem + s * STAGE_BYTES), b_addr = a_addr + ROW_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma_bf16_pair(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, (kb | k) != 0);
+        umma_commit_pair(empty + s);
+      }
+      umma_commit_pair(acc_full + buf);
+    }
+  } else if (warp >= 2) {
+    // -------------------------------------------------------------------- epilogue (both CTAs)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    int local = 0;
+    for (int tile = pair; tile < tiles; tile += pairs, ++local) {
+      const int buf = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      const int row0 = (tile % m_tiles) * PAIR_M + static_cast<int>(rank) * BM, col0 = (tile / m_tiles) * BN;
+      const bool ok = mbar_wait(acc_full + buf, acc_phase);
+      if (!ok) atomicExch(&g_gemm_error, 3);
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+      const int m = row0 + row;
+      OutT* crow = static_cast<OutT*>(p.c) + static_cast<size_t>(m) * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        float v[32];
+        if (ok) {
+          tmem_load_32(taddr + c, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        if (m < p.M) {
+          const int nb = col0 + c;
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += nb + j < p.N ? p.bias[nb + j] : 0.f;
+          }
+          if constexpr (SWIGLU) {
+            float h[16];
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float gate = v[b * 16 + j], up = v[b * 16 + 8 + j];
+                h[b * 8 + j] = gate / (1.f + __expf(-gate)) * up;
+              }
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+              if (nb + b * 16 + 16 > p.N) continue;
+              OutT* dst = crow + (nb >> 1) + b * 8;
+              if (p.vector_ok) {
+                store_row_8(dst, h + b * 8);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) store_out<OutT>(dst + j, h[b * 8 + j]);
+              }
+            }
+          } else {
+            if constexpr (sizeof(OutT) == 4) {
+              if (p.accumulate) {
+                if (p.vector_ok && nb + 32 <= p.N) {
+#pragma unroll
+                  for (int j = 0; j < 32; j += 4) {
+                    const float4 e = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(crow) + nb + j);
+                    v[j] += e.x; v[j + 1] += e.y; v[j + 2] += e.z; v[j + 3] += e.w;
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (nb + j < p.N) v[j] += reinterpret_cast<const float*>(crow)[nb + j];
+                }
+              }
+            }
+            if (p.vector_ok && nb + 32 <= p.N) {
+              store_row_32(crow + nb, v);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (nb + j < p.N) store_out<OutT>(crow + nb + j, v[j]);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_addr(acc_empty + buf), 0));
+      if (!ok) break;
+    }
+  }
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();                     // the leader's MMAs read this CTA's shared memory until its last commit
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------------ stream-K kernel
 // One CTA per SM.  The tiles that fill whole rounds of gridDim.x CTAs are computed whole, round
 // by round (tile = round * gridDim.x + CTA, so the CTAs of a round share few weight panels in L2).
@@ -892,6 +1123,39 @@ static int launch_streamk(const CUtensorMap& rows, const CUtensorMap& cols, cons
   return static_cast<int>(cudaGetLastError());
 }
 
+template <int STAGES, bool SWIGLU, typename OutT>
+static int launch_pair(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, cudaStream_t stream) {
+  constexpr size_t smem = STAGES * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256;
+  auto kernel = gemm_tcgen05_pair_kernel<STAGES, SWIGLU, OutT>;
+  static bool configured = false;
+  static int sm_count = 0;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+    configured = true;
+  }
+  const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
+  int pairs = sm_count / 2;
+  if (tiles < pairs) pairs = tiles;
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(2 * pairs);
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, rows, cols, p);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -930,6 +1194,22 @@ extern "C" int b200_gemm_tcgen05_swiglu(const void* A, const void* W, const floa
                                         int ldc, int out_f32, cudaStream_t stream) {
   if (N % 16 != 0) return B200_ERR_BAD_SIZE;
   return gemm_tcgen05_impl(A, W, bias, C, M, N, K, ldc, out_f32, 0, 1, stream);
+}
+
+// The 2-CTA kernel (256 x 256 tiles on pairs of SMs).  swiglu / accumulate as in the other entry points.
+extern "C" int b200_gemm_tcgen05_pair(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
+                                      int out_f32, int swiglu, int accumulate, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || ldc < (swiglu ? N / 2 : N) || (swiglu && N % 16 != 0)) return B200_ERR_BAD_SIZE;
+  if (accumulate && (!out_f32 || swiglu)) return B200_ERR_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return B200_ERR_BAD_SIZE;
+  GemmParams p{C, bias, M, N, K, ldc, (ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0, 0, accumulate, nullptr, nullptr};
+  CUtensorMap rows, cols;
+  if (int e = make_map(&rows, A, M, K, BM)) return e;
+  if (int e = make_map(&cols, W, N, K, 128)) return e;
+  if (swiglu)
+    return out_f32 ? launch_pair<6, true, float>(rows, cols, p, stream) : launch_pair<6, true, __nv_bfloat16>(rows, cols, p, stream);
+  return out_f32 ? launch_pair<6, false, float>(rows, cols, p, stream) : launch_pair<6, false, __nv_bfloat16>(rows, cols, p, stream);
 }
 
 // Stream-K kernel.  `partials` holds b200_gemm_tcgen05_streamk_partial_floats() floats, `flags`

@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..errors import KernelError
@@ -15,6 +17,7 @@ native.register_library(
         "b200_gemm_tcgen05_swiglu": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "b200_gemm_tcgen05_error": [],
         "b200_gemm_tcgen05_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "b200_gemm_tcgen05_pair": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "b200_gemm_tcgen05_streamk_partial_floats": [],
         "b200_gemm_tcgen05_streamk_flags": [],
         "b200_gemm_tcgen05_streamk": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -30,6 +33,8 @@ native.register_library(
     },
 )
 
+PAIR_MIN_ROWS = 256   # from here on pairs of SMs work on 256 x 256 tiles (tcgen05 cta_group::2)
+PAIR_ENABLED = os.environ.get("LLM_RUNTIME_STUDY_B200_GEMM_PAIR", "1") != "0"
 SKINNY_M = 16         # up to here weights are streamed straight into mma.sync fragments
 SMALL_M = 64          # up to here the weight is the row operand ("swapped")
 _SM_COUNT = 148
@@ -106,6 +111,37 @@ def pick_splits(m: int, n: int, k: int) -> int:
     return splits
 
 
+def linear_pair(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+                out_dtype: torch.dtype = torch.bfloat16, *, swiglu: bool = False,
+                add_to: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ weight.T (+ bias)`` on pairs of SMs (tcgen05 ``cta_group::2``, 256 x 256 tiles).
+    ``swiglu`` and ``add_to`` as in :func:`linear`."""
+
+    native.require(x, "x", dtype=torch.bfloat16, dims=2)
+    native.require(weight, "weight", dtype=torch.bfloat16, dims=2)
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k:
+        raise KernelError(f"linear: x has width {k}, weight expects {weight.shape[1]}")
+    if not supported(m, n, k):
+        raise KernelError(f"tcgen05 projection needs K to be a multiple of 8, got {k}")
+    if bias is not None:
+        native.require(bias, "bias", dtype=torch.float32, shape=(n,))
+    if swiglu and (n % 16 or add_to is not None):
+        raise KernelError("the SwiGLU epilogue needs an even number of 8-feature blocks and excludes add_to")
+    if add_to is not None:
+        native.require(add_to, "add_to", dtype=torch.float32, shape=(m, n))
+        out, out_dtype = add_to, torch.float32
+    else:
+        if out_dtype not in (torch.bfloat16, torch.float32):
+            raise KernelError(f"unsupported output type {out_dtype}")
+        out = torch.empty((m, n // 2 if swiglu else n), dtype=out_dtype, device=x.device)
+    native.call("b200_gemm_tcgen05_pair", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k,
+                out.shape[1], 1 if out_dtype == torch.float32 else 0, 1 if swiglu else 0, 0 if add_to is None else 1,
+                native.stream_ptr())
+    return out
+
+
 def few_tiles(m: int, n: int, k: int) -> bool:
     """Products whose 128 x 256 tiles would occupy a third of the SMs or fewer, with a K range
     long enough to share: the stream-K kernel lets up to three SMs work on one tile."""
@@ -122,9 +158,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     the result is ``silu(gate) * up``, half as wide (persistent kernel only).
     ``add_to`` (float32 ``[M, N]``): the product is added to it in place and it is returned."""
 
-    if splits is None and x.dim() == 2 and weight.dim() == 2 and few_tiles(x.shape[0], weight.shape[0], x.shape[1]) \
-            and x.shape[0] > SMALL_M:
-        return linear_streamk(x, weight, bias, out_dtype, swiglu=swiglu, add_to=add_to)
+    if splits is None and x.dim() == 2 and weight.dim() == 2 and x.shape[0] > SMALL_M:
+        if few_tiles(x.shape[0], weight.shape[0], x.shape[1]):
+            return linear_streamk(x, weight, bias, out_dtype, swiglu=swiglu, add_to=add_to)
+        if x.shape[0] >= PAIR_MIN_ROWS and PAIR_ENABLED:
+            return linear_pair(x, weight, bias, out_dtype, swiglu=swiglu, add_to=add_to)
 
     native.require(x, "x", dtype=torch.bfloat16, dims=2)
     native.require(weight, "weight", dtype=torch.bfloat16, dims=2)

@@ -448,6 +448,37 @@ def test_tcgen05_stream_k_projection(m, n, k, bias, out):
     assert torch.equal(got, again) and torch.equal(got, third)        # partial sums are added in a fixed order
 
 
+@pytest.mark.parametrize("m,n,k,bias", [
+    (256, 256, 64, False), (130, 264, 72, True), (300, 1000, 520, True), (2048, 1024, 4096, False), (5000, 4096, 512, True),
+    (257, 24, 12288, True), (640, 520, 8, False), (1, 8, 8, True), (2048, 4096, 12288, False), (4096, 6144, 4096, False),
+])
+@pytest.mark.parametrize("out", [torch.float32, torch.bfloat16])
+def test_tcgen05_pair_projection(m, n, k, bias, out):
+    """The 2-CTA kernel: 256 x 256 tiles on pairs of SMs, ragged edges in every dimension."""
+
+    x, w, b, want = _gemm_case(m, n, k, bias)
+    args = (dev(x), dev(w), dev(b) if bias else None, out)
+    got = _gemm().linear_pair(*args)
+    again = _gemm().linear_pair(*args)
+    _gemm().check_error()
+    scale = float(want.abs().max())
+    torch.testing.assert_close(got.cpu().double(), want, atol=(1e-2 if out == torch.bfloat16 else 2e-5) * scale, rtol=0)
+    assert torch.equal(got, again)
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 1000, 520), (2048, 4096, 4096)])
+def test_tcgen05_pair_adds_to_the_residual(m, n, k):
+    x, w, b, want = _gemm_case(m, n, k, True)
+    torch.manual_seed(3)
+    resid = torch.randn(m, n)
+    target = dev(resid.clone())
+    delta = _gemm().linear_pair(dev(x), dev(w), dev(b), torch.float32)
+    out = _gemm().linear_pair(dev(x), dev(w), dev(b), add_to=target)
+    _gemm().check_error()
+    assert out.data_ptr() == target.data_ptr()
+    assert torch.equal(out, dev(resid) + delta)
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 1000, 520), (2048, 4096, 4096)])
 def test_tcgen05_stream_k_adds_to_the_residual(m, n, k):
     x, w, b, want = _gemm_case(m, n, k, True)
@@ -540,8 +571,9 @@ def test_projection_with_swiglu_epilogue(m, inter, k):
     else:
         got = _gemm().linear(dev(x), w, None, torch.bfloat16, swiglu=True)
         _gemm().check_error()
-        streamed = _gemm().linear_streamk(dev(x), w, None, torch.bfloat16, swiglu=True)
-        _gemm().check_error()
-        torch.testing.assert_close(streamed.cpu().double(), want, atol=2e-2 * float(want.abs().max()), rtol=0)
+        for variant in (_gemm().linear_streamk, _gemm().linear_pair):
+            other = variant(dev(x), w, None, torch.bfloat16, swiglu=True)
+            _gemm().check_error()
+            torch.testing.assert_close(other.cpu().double(), want, atol=2e-2 * float(want.abs().max()), rtol=0)
     assert got.shape == (m, inter)
     torch.testing.assert_close(got.cpu().double(), want, atol=2e-2 * float(want.abs().max()), rtol=0)
