@@ -387,6 +387,105 @@ __global__ void __launch_bounds__(kRopeWarps * 32) qk_norm_rope_write_vec_kernel
   }
 }
 
+// Head sizes 64, 128 and 256 with the whole head rotated (or none of it): LANES = d / 16 lanes hold
+// one head, eight neighbouring elements of its lower half and the matching eight of its upper half
+// each (16-byte loads and stores for bfloat16), so a warp works on 32 / LANES heads at once.  A
+// task is such a group of heads; the tasks of a token may be spread over several CTAs (grid.y)
+// when there are few tokens.  The arithmetic of a head does not depend on that spread.
+template <typename T> __device__ __forceinline__ void load8(const T* p, float* f);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* f) {
+  Vec<float>::unpack(*reinterpret_cast<const float4*>(p), f);
+  Vec<float>::unpack(*reinterpret_cast<const float4*>(p + 4), f + 4);
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* f) {
+  Vec<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(p), f);
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float* f);
+template <> __device__ __forceinline__ void store8<float>(float* p, const float* f) {
+  *reinterpret_cast<float4*>(p) = Vec<float>::pack(f);
+  *reinterpret_cast<float4*>(p + 4) = Vec<float>::pack(f + 4);
+}
+template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float* f) {
+  *reinterpret_cast<uint4*>(p) = Vec<__nv_bfloat16>::pack(f);
+}
+
+template <typename T, int LANES>
+__global__ void __launch_bounds__(512) qk_norm_rope_write_wide_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ q_weight,
+    const float* __restrict__ k_weight, float eps, const float* __restrict__ inv_freq,
+    const int* __restrict__ positions, const int* __restrict__ token_entry,
+    const int* __restrict__ block_table, int table_stride, int page_size,
+    T* __restrict__ k_pool, T* __restrict__ v_pool, int nq, int nkv, int qkv_stride) {
+  constexpr int D = 16 * LANES, HALF = D / 2, HEADS_PER_WARP = 32 / LANES;
+  __shared__ float cs[HALF], sn[HALF];
+  pdl_trigger();
+#ifdef B200_EARLY_ROPE
+  pdl_launch_dependents();
+#endif
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int token = blockIdx.x;
+  const int pos = positions[token];
+  if (inv_freq) {
+    for (int j = threadIdx.x; j < HALF; j += blockDim.x) sincosf(static_cast<float>(pos) * inv_freq[j], &sn[j], &cs[j]);
+  }
+  __syncthreads();
+  int64_t kv_base = -1;
+  if (nkv > 0) {
+    const int page = block_table[static_cast<size_t>(token_entry[token]) * table_stride + pos / page_size];
+    if (page >= 0) kv_base = (static_cast<int64_t>(page) * nkv * page_size + pos % page_size) * D;
+  }
+  const int heads = nq + 2 * nkv;
+  const int sub = lane / LANES, li = lane % LANES;
+  for (int task = blockIdx.y * warps + warp; task * HEADS_PER_WARP < heads; task += gridDim.y * warps) {
+    const int h = task * HEADS_PER_WARP + sub;
+    const bool is_q = h < nq, is_k = !is_q && h < nq + nkv, is_v = !is_q && !is_k && h < heads;
+    T* dst = nullptr;
+    if (is_q) {
+      dst = q_out + (static_cast<size_t>(token) * nq + h) * D;
+    } else if ((is_k || is_v) && kv_base >= 0) {
+      const int kvh = is_k ? h - nq : h - nq - nkv;
+      dst = (is_k ? k_pool : v_pool) + kv_base + static_cast<int64_t>(kvh) * page_size * D;
+    }
+    float lo[8], hi[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) lo[i] = hi[i] = 0.f;
+    if (dst) {
+      const T* src = qkv + static_cast<size_t>(token) * qkv_stride + static_cast<size_t>(h) * D + 8 * li;
+      load8<T>(src, lo);
+      load8<T>(src + HALF, hi);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += lo[i] * lo[i];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += hi[i] * hi[i];
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (!dst) continue;
+    const float* w = is_q ? q_weight : (is_k ? k_weight : nullptr);
+    if (w) {
+      const float r = rsqrtf(ss / static_cast<float>(D) + eps);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        lo[i] *= r * w[8 * li + i];
+        hi[i] *= r * w[8 * li + i + HALF];
+      }
+    }
+    if (inv_freq != nullptr && (is_q || is_k)) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float c = cs[8 * li + i], sine = sn[8 * li + i];
+        const float a = lo[i], b = hi[i];
+        lo[i] = a * c - b * sine;
+        hi[i] = b * c + a * sine;
+      }
+    }
+    store8<T>(dst + 8 * li, lo);
+    store8<T>(dst + 8 * li + HALF, hi);
+  }
+}
+
 template <typename T>
 static void launch_norm_vec(float* resid, const float* delta, const float* weight, T* out, const int* rows, int n,
                             int hidden, float eps, int write_resid, cudaStream_t stream) {
@@ -493,6 +592,30 @@ extern "C" int b200_qk_norm_rope_write(
   const bool whole_head = inv_freq == nullptr || rotary_dim == d;
   const bool aligned4 = ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
                           reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool)) & 7) == 0;
+  const bool aligned16 = ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                           reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool)) & 15) == 0;
+  if (whole_head && (d == 64 || d == 128 || d == 256) && qkv_stride % 8 == 0 && aligned16) {
+    const int heads_per_warp = 32 / (d / 16);
+    const int tasks = (heads + heads_per_warp - 1) / heads_per_warp;
+    const int warps = tasks < (n >= 256 ? 16 : 2) ? tasks : (n >= 256 ? 16 : 2);
+    const dim3 grid(n, n >= 256 ? 1 : (tasks + warps - 1) / warps);
+    B200_DISPATCH_DTYPE(dtype, T, {
+      auto* in = static_cast<const T*>(qkv);
+      auto* qo = static_cast<T*>(q_out);
+      auto* kp = static_cast<T*>(k_pool);
+      auto* vp = static_cast<T*>(v_pool);
+      if (d == 64)
+        launch(qk_norm_rope_write_wide_kernel<T, 4>, grid, dim3(warps * 32), 0, stream, in, qo, q_weight, k_weight, eps, inv_freq,
+               positions, token_entry, block_table, table_stride, page_size, kp, vp, nq, nkv, qkv_stride);
+      else if (d == 128)
+        launch(qk_norm_rope_write_wide_kernel<T, 8>, grid, dim3(warps * 32), 0, stream, in, qo, q_weight, k_weight, eps, inv_freq,
+               positions, token_entry, block_table, table_stride, page_size, kp, vp, nq, nkv, qkv_stride);
+      else
+        launch(qk_norm_rope_write_wide_kernel<T, 16>, grid, dim3(warps * 32), 0, stream, in, qo, q_weight, k_weight, eps, inv_freq,
+               positions, token_entry, block_table, table_stride, page_size, kp, vp, nq, nkv, qkv_stride);
+    });
+    return launch_status();
+  }
   if (whole_head && d % 4 == 0 && d <= 256 && qkv_stride % 2 == 0 && aligned4) {
     B200_DISPATCH_DTYPE(dtype, T, {
       auto* in = static_cast<const T*>(qkv);

@@ -357,6 +357,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, con
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                             // set-up above overlaps the kernel before; its results are read below
 
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer
@@ -588,6 +589,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __g
   cluster_sync_all();                     // both CTAs' barriers exist before anything arrives on them
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                             // set-up above overlaps the kernel before; its results are read below
 
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer (both CTAs)
@@ -825,6 +827,7 @@ gemm_tcgen05_streamk_kernel(const __grid_constant__ CUtensorMap map_rows, const 
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                             // set-up above overlaps the kernel before; its results are read below
 
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- producer
@@ -1096,7 +1099,7 @@ static int launch_persistent(const CUtensorMap& rows, const CUtensorMap& cols, c
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
   const int grid = tiles < sm_count ? tiles : sm_count;
-  kernel<<<grid, kThreads, smem, stream>>>(rows, cols, p);
+  b200::launch(kernel, dim3(grid), dim3(kThreads), smem, stream, rows, cols, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -1119,7 +1122,7 @@ static int launch_streamk(const CUtensorMap& rows, const CUtensorMap& cols, cons
   int grid = sm_count < kStreamKMaxCtas ? sm_count : kStreamKMaxCtas;
   if (3 * tiles < grid) grid = 3 * tiles;              // at most three CTAs share a tile
   if (units < grid) grid = static_cast<int>(units);
-  kernel<<<grid, kThreads, smem, stream>>>(rows, cols, p);
+  b200::launch(kernel, dim3(grid), dim3(kThreads), smem, stream, rows, cols, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -1145,13 +1148,15 @@ static int launch_pair(const CUtensorMap& rows, const CUtensorMap& cols, const G
   config.blockDim = dim3(kThreads);
   config.dynamicSmemBytes = smem;
   config.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
-  config.numAttrs = 1;
+  config.numAttrs = pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&config, kernel, rows, cols, p);
   return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }

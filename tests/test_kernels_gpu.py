@@ -112,7 +112,8 @@ def _scatter_to_pages(k, v, page_size, nkv, d, dtype, seed=0, extra_pages=3):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nq,nkv,d,page,rot", [(4, 2, 16, 4, 16), (6, 1, 32, 8, 32), (5, 5, 48, 16, 48), (8, 2, 128, 16, 64)])
+@pytest.mark.parametrize("nq,nkv,d,page,rot", [(4, 2, 16, 4, 16), (6, 1, 32, 8, 32), (5, 5, 48, 16, 48), (8, 2, 128, 16, 64),
+                                               (8, 2, 128, 16, 128), (5, 3, 64, 16, 64), (3, 1, 256, 32, 256), (32, 8, 128, 16, 128)])
 def test_qk_norm_rope_write(dtype, nq, nkv, d, page, rot):
     torch.manual_seed(4)
     eps, theta = 1e-5, 1e6
@@ -151,6 +152,39 @@ def test_qk_norm_rope_write(dtype, nq, nkv, d, page, rot):
         written[pg, slot] = True
     assert float(kp.permute(0, 2, 1, 3)[~written].abs().max()) == 0.0        # nothing else was touched
     assert float(vp.permute(0, 2, 1, 3)[~written].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d", [(8, 2, 128), (5, 3, 64), (6, 1, 32)])
+def test_qk_norm_rope_write_many_tokens_same_bits_as_few(dtype, nq, nkv, d):
+    """A long portion (one CTA per token) and the same tokens a few at a time (a token's heads spread
+    over several CTAs) give the same bits, and both agree with the plain formulas."""
+
+    torch.manual_seed(9)
+    eps, theta, page, n = 1e-6, 1e4, 16, 300
+    positions = torch.arange(n, dtype=torch.int32)
+    entry = torch.zeros(n, dtype=torch.int32)
+    qkv = torch.randn(n, (nq + 2 * nkv) * d).to(dtype)
+    qw, kw = 1 + 0.1 * torch.randn(d), 1 + 0.1 * torch.randn(d)
+    pages = -(-n // page)
+    table = torch.randperm(pages).to(torch.int32).view(1, pages)
+    inv_freq = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+
+    def run(lo, hi, kp, vp):
+        return F().qk_norm_rope_write(
+            dev(qkv[lo:hi]), num_q_heads=nq, num_kv_heads=nkv, head_dim=d, q_weight=dev(qw), k_weight=dev(kw), eps=eps,
+            inv_freq=dev(inv_freq), rotary_dim=d, positions=dev(positions[lo:hi]), token_entry=dev(entry[lo:hi]),
+            block_table=dev(table), page_size=page, k_pool=kp, v_pool=vp)
+
+    kp1, vp1 = dev(torch.zeros(pages, nkv, page, d, dtype=dtype)), dev(torch.zeros(pages, nkv, page, d, dtype=dtype))
+    kp2, vp2 = torch.zeros_like(kp1), torch.zeros_like(vp1)
+    whole = run(0, n, kp1, vp1)
+    pieces = torch.cat([run(lo, min(lo + 7, n), kp2, vp2) for lo in range(0, n, 7)])
+    assert torch.equal(whole, pieces) and torch.equal(kp1, kp2) and torch.equal(vp1, vp2)
+    x = qkv.double()
+    q = plain.rms_norm(x[:, : nq * d].view(n, nq, d), qw.double(), eps)
+    cos, sin = plain.rotary_tables(positions, d, theta, torch.float64)
+    torch.testing.assert_close(whole.cpu().double(), plain.rotate(q, cos, sin), **tol(dtype))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
