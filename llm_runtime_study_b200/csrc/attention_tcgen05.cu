@@ -128,47 +128,45 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4 && lane == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    mbar_expect_tx(q_full, DSUB * 128u * p.gs * tokens_per_cta);
-    for (int sub = 0; sub < DSUB; ++sub) tma_load_3d(q_smem + sub * Q_SUB, &map_q, q_full, sub * 64, head0, tok0);
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer (one warp)
+    if (lane == 0) {
+      mbar_expect_tx(q_full, DSUB * 128u * p.gs * tokens_per_cta);
+      for (int sub = 0; sub < DSUB; ++sub) tma_load_3d(q_smem + sub * Q_SUB, &map_q, q_full, sub * 64, head0, tok0);
+    }
+    // A key tile is pages_per_tile pages of K and as many of V, DSUB boxes (64 columns) each.  Lane
+    // i of the warp owns box i of a tensor: page i / DSUB, half i % DSUB.  All lanes issue their
+    // copies at once, so a tile of small pages costs the time of one copy instruction, not sixteen.
     const int pages_per_tile = BN / p.page_size;
-    // Page ids of a tile are fetched from the block table one tile ahead, so that the global
-    // load is in flight while this thread waits for a free stage.
-    auto fetch_ids = [&](int j, int (&ids)[8]) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int t0 = j * BN + i * p.page_size;
-        ids[i] = (i < pages_per_tile && t0 <= p_last) ? table[t0 >> p.page_shift] : -1;
-      }
+    const int boxes = pages_per_tile * DSUB;
+    const int my_page = lane / DSUB, my_sub = lane % DSUB;
+    const bool has_box = lane < boxes;
+    // the page id of tile j for this lane, fetched one tile ahead of its use
+    auto fetch_id = [&](int j) -> int {
+      const int t0 = j * BN + my_page * p.page_size;
+      return (has_box && t0 <= p_last) ? table[t0 >> p.page_shift] : -1;
     };
-    auto load_pages = [&](unsigned char* dst, const CUtensorMap* map, uint64_t* bar, const int (&ids)[8]) {
-      int loaded = 0;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) loaded += ids[i] >= 0;
-      mbar_expect_tx(bar, static_cast<uint32_t>(loaded) * p.page_size * 128u * DSUB);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (ids[i] < 0) continue;
-        const int y = (ids[i] * p.nkv + kvh) * p.page_size;
-        for (int sub = 0; sub < DSUB; ++sub)
-          tma_load_2d(dst + sub * KV_SUB + i * p.page_size * 128, map, bar, sub * 64, y);
-      }
+    auto load_boxes = [&](unsigned char* dst, const CUtensorMap* map, uint64_t* bar, int id) {
+      const unsigned valid = __ballot_sync(0xffffffffu, id >= 0);
+      if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(__popc(valid)) * p.page_size * 128u);
+      __syncwarp();
+      if (id >= 0)
+        tma_load_2d(dst + my_sub * KV_SUB + my_page * p.page_size * 128, map, bar, my_sub * 64, (id * p.nkv + kvh) * p.page_size);
     };
     // K and V of tile j go to stage j & 1; a stage is free again when the product that read it
     // has completed (S(j-2) for K, P.V(j-2) for V): the first two tiles find their stages free.
-    int ids[8], next_ids[8];
-    fetch_ids(0, ids);
+    int id = fetch_id(0);
     for (int j = 0; j < ntiles; ++j) {
       const int s = j & 1;
       const uint32_t parity = ((j >> 1) & 1) ^ 1;
-      if (j + 1 < ntiles) fetch_ids(j + 1, next_ids);
-      if (!mbar_wait(k_empty + s, parity)) { atomicExch(&g_attn_error, 1); break; }
-      load_pages(k_smem + s * KV_BYTES, &map_k, k_full + s, ids);
-      if (!mbar_wait(v_empty + s, parity)) { atomicExch(&g_attn_error, 1); break; }
-      load_pages(v_smem + s * KV_BYTES, &map_v, v_full + s, ids);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) ids[i] = next_ids[i];
+      const int next_id = j + 1 < ntiles ? fetch_id(j + 1) : -1;
+      bool free_k = mbar_wait(k_empty + s, parity);
+      if (!__all_sync(0xffffffffu, free_k)) { if (lane == 0) atomicExch(&g_attn_error, 1); break; }
+      load_boxes(k_smem + s * KV_BYTES, &map_k, k_full + s, id);
+      bool free_v = mbar_wait(v_empty + s, parity);
+      if (!__all_sync(0xffffffffu, free_v)) { if (lane == 0) atomicExch(&g_attn_error, 1); break; }
+      load_boxes(v_smem + s * KV_BYTES, &map_v, v_full + s, id);
+      id = next_id;
     }
   } else if (warp == 5 && lane == 0) {
     // ------------------------------------------------------------------ tensor-core issue
