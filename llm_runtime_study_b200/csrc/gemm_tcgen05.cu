@@ -1,31 +1,25 @@
 // bfloat16 matrix product on the 5th-generation tensor cores: C[M,N] = A[M,K] * W[N,K]^T (+ bias)
-// with float32 accumulation in tensor memory (TMEM).
-//
-// One CTA computes one 128 x BN tile.  Roles, one per warp:
-//   warp 0   producer: one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of a
-//            128 x 64 tile of the row operand and a BN x 64 tile of the column operand into a
-//            ring of shared-memory stages, signalling a "full" mbarrier per stage;
-//   warp 1   allocates TMEM; one lane issues tcgen05.mma (M = 128, N = BN, K = 16, four per
-//            stage) and commits each stage's completion to its "empty" mbarrier;
+// with float32 accumulation in tensor memory (TMEM).  Three kernels share the roles below and
+// differ in how tiles are handed to SMs: one CTA per 128 x 256 tile (persistent), pairs of CTAs
+// on 256 x 256 tiles (cta_group::2), and stream-K for products with few tiles.
+//   warp 0   producer: one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the
+//            operands' 64-wide K blocks into a ring of shared-memory stages, signalling a "full"
+//            mbarrier per stage;
+//   warp 1   allocates TMEM; one lane issues tcgen05.mma (K = 16, four per stage) and commits
+//            each stage's completion to its "empty" mbarrier and each tile's to "acc_full";
 //   warps 2-5  epilogue: tcgen05.ld of the accumulator (each warp its quarter of the 128 TMEM
-//            lanes), bias, conversion, store.
+//            lanes), bias, SwiGLU or residual sum where asked for, conversion, store.  The
+//            accumulator is double buffered, so the epilogue of a tile runs under the products
+//            of the next.
 // Both operands are K-major ("row . row^T"), which is how nn.Linear stores its weight
 // (mini_llm/nn/attention.py:102-111), so no transposition is needed anywhere.
 //
-// "Swapped" mode serves small M (decoding): the weight is the row operand (128 output
-// features per CTA), the tokens are the column operand (BN = tokens rounded up to 16), and the
-// K range may be split over the CTAs of a thread-block cluster whose partial tiles are summed
-// through distributed shared memory in rank order (deterministic, no atomics, no scratch).
-//
-// Every wait on an mbarrier is bounded: after kSpinLimit polls the kernel records an error
-// code, stops issuing work, frees its TMEM and returns.
-#include <cooperative_groups.h>
+// Every wait on an mbarrier or a flag is bounded: after its limit of polls the kernel records an
+// error code, stops issuing work, frees its TMEM and returns.
 #include <cuda.h>
 
 #include "common.cuh"
 #include "mma.cuh"
-
-namespace cg = cooperative_groups;
 
 namespace b200 {
 
@@ -155,159 +149,66 @@ struct GemmParams {
   const float* bias;
   int M, N, K, ldc;
   int vector_ok;      // rows of C start on 16-byte boundaries
-  int kb_per_split;   // 64-wide K blocks per CTA of a cluster (swapped mode); all of them otherwise
   int accumulate;     // float output only: C += A W^T + bias instead of C = ...
   float* partials;    // stream-K: [grid][128][256] partial accumulators
   unsigned* flags;    // stream-K: [grid], zero between launches
 };
 
-// SWAP = false: rows operand = A (activations), columns operand = W; tile (m0, n0) = (blockIdx.x*128, blockIdx.y*BN).
-// SWAP = true : rows operand = W, columns operand = A (all M <= BN tokens); n0 = blockIdx.x*128; blockIdx.y = K split.
-template <int BN, int STAGES, bool SWAP, typename OutT>
-__global__ void __launch_bounds__(kThreads)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols, GemmParams p) {
-  constexpr uint32_t ROW_BYTES = BM * BK * 2, COL_BYTES = BN * BK * 2, STAGE_BYTES = ROW_BYTES + COL_BYTES;
-  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : (BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256)));
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
-  uint64_t* empty = full + STAGES;
-  uint64_t* acc_full = empty + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
-  int* failed = reinterpret_cast<int*>(tmem_slot + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row0 = blockIdx.x * BM;
-  const int col0 = SWAP ? 0 : blockIdx.y * BN;
-  const int total_kb = (p.K + BK - 1) / BK;
-  const int kb_begin = SWAP ? blockIdx.y * p.kb_per_split : 0;
-  const int kb_end = SWAP ? min(total_kb, kb_begin + p.kb_per_split) : total_kb;
-  const int num_kb = max(0, kb_end - kb_begin);
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full + s, 1);
-      mbar_init(empty + s, 1);
-    }
-    mbar_init(acc_full, 1);
-    *failed = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(tmem_slot)), "r"(TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-  }
-  tcgen05_fence_before();
-  __syncthreads();
-  tcgen05_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0 && lane == 0) {
-    // ---------------------------------------------------------------- producer
-    for (int i = 0; i < num_kb; ++i) {
-      const int s = i % STAGES;
-      const uint32_t phase = (i / STAGES) & 1;
-      if (!mbar_wait(empty + s, phase ^ 1)) { *failed = 1; atomicExch(&g_gemm_error, 1); break; }
-      mbar_expect_tx(full + s, STAGE_BYTES);
-      unsigned char* stage = smem + s * STAGE_BYTES;
-      const int k = (kb_begin + i) * BK;
-      tma_load_2d(stage, &map_rows, full + s, k, row0);
-      tma_load_2d(stage + ROW_BYTES, &map_cols, full + s, k, col0);
-    }
-  } else if (warp == 1 && lane == 0) {
-    // ---------------------------------------------------------------- tensor-core issue
-    constexpr uint32_t idesc = umma_idesc(BN);
-    bool ok = true;
-    for (int i = 0; i < num_kb && ok; ++i) {
-      const int s = i % STAGES;
-      const uint32_t phase = (i / STAGES) & 1;
-      if (!mbar_wait(full + s, phase)) { *failed = 1; atomicExch(&g_gemm_error, 2); ok = false; break; }
-      tcgen05_fence_after();
-      const uint32_t a_addr = smem_addr(smem + s * STAGE_BYTES), b_addr = a_addr + ROW_BYTES;
+// What the epilogue does with 32 consecutive accumulator columns of one row, starting at column nb of
+// the product: bias, then either SiLU(gate) * up on interleaved blocks of eight, or the optional sum
+// with what C holds, then conversion and 16-byte stores where the row allows them.
+template <bool SWIGLU, typename OutT>
+__device__ __forceinline__ void finish_chunk(float (&v)[32], const GemmParams& p, OutT* crow, int nb) {
+  if (p.bias) {
 #pragma unroll
-      for (int k = 0; k < BK / UMMA_K; ++k)
-        umma_bf16(tmem_base, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, (i | k) != 0);
-      umma_commit(empty + s);
-    }
-    umma_commit(acc_full);   // arrives when every MMA issued so far has finished (also when none was issued)
+    for (int j = 0; j < 32; ++j) v[j] += nb + j < p.N ? p.bias[nb + j] : 0.f;
   }
-  __syncwarp();
-
-  // -------------------------------------------------------------------- epilogue
-  float* partial = reinterpret_cast<float*>(smem);   // swapped mode: [BN tokens][128 features] float, over the stage ring
-  if (warp >= 2) {
-    const int quarter = warp & 3;              // TMEM lanes this warp may read
-    const int row = quarter * 32 + lane;       // row of the tile = TMEM lane
-    bool ok = mbar_wait(acc_full, 0);
-    if (!ok) { *failed = 1; atomicExch(&g_gemm_error, 3); }
-    tcgen05_fence_after();
-    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    if (!SWAP) {
-      const int m = row0 + row;
-      OutT* crow = static_cast<OutT*>(p.c) + static_cast<size_t>(m) * p.ldc;
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        float v[32];
-        if (ok && num_kb > 0) {
-          tmem_load_32(taddr + c, v);
+  if constexpr (SWIGLU) {
+    // [g0..7 | u0..7 | g8..15 | u8..15] -> 16 outputs at column nb / 2 (N is a multiple of 16)
+    float h[16];
+#pragma unroll
+    for (int b = 0; b < 2; ++b)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gate = v[b * 16 + j], up = v[b * 16 + 8 + j];
+        h[b * 8 + j] = gate / (1.f + __expf(-gate)) * up;
+      }
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      if (nb + b * 16 + 16 > p.N) continue;
+      OutT* dst = crow + (nb >> 1) + b * 8;
+      if (p.vector_ok) {
+        store_row_8(dst, h + b * 8);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) store_out<OutT>(dst + j, h[b * 8 + j]);
+      }
+    }
+  } else {
+    const bool whole = p.vector_ok && nb + 32 <= p.N;
+    if constexpr (sizeof(OutT) == 4) {
+      if (p.accumulate) {
+        const float* have = reinterpret_cast<const float*>(crow) + nb;
+        if (whole) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const float4 e = *reinterpret_cast<const float4*>(have + j);
+            v[j] += e.x; v[j + 1] += e.y; v[j + 2] += e.z; v[j + 3] += e.w;
+          }
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0.f;
-        }
-        if (m < p.M) {
-          const int nb = col0 + c;
-          if (p.bias) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += nb + j < p.N ? p.bias[nb + j] : 0.f;
-          }
-          if (p.vector_ok && nb + 32 <= p.N) {
-            store_row_32(crow + nb, v);     // 16-byte stores
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (nb + j < p.N) store_out<OutT>(crow + nb + j, v[j]);
-          }
+          for (int j = 0; j < 32; ++j)
+            if (nb + j < p.N) v[j] += have[j];
         }
       }
+    }
+    if (whole) {
+      store_row_32(crow + nb, v);
     } else {
-      // lane = output feature, TMEM column = token.  Park the partial tile in shared memory.
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        float v[16];
-        if (ok && num_kb > 0) {
-          tmem_load_16(taddr + c, v);
-        } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) partial[(c + j) * BM + row] = v[j];
-      }
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < p.N) store_out<OutT>(crow + nb + j, v[j]);
     }
-  }
-  if (SWAP) {
-    cg::cluster_group cluster = cg::this_cluster();
-    const unsigned splits = cluster.num_blocks(), rank = cluster.block_rank();
-    cluster.sync();                                    // every CTA's partial tile is in its shared memory
-    if (rank == 0 && warp >= 2) {
-      const int quarter = warp & 3, row = quarter * 32 + lane;
-      const int n = row0 + row;
-      if (n < p.N) {
-        const float b = p.bias ? p.bias[n] : 0.f;
-        for (int m = 0; m < p.M; ++m) {
-          float acc = partial[m * BM + row];
-          for (unsigned r = 1; r < splits; ++r) acc += cluster.map_shared_rank(partial, r)[m * BM + row];
-          store_out<OutT>(static_cast<OutT*>(p.c) + static_cast<size_t>(m) * p.ldc + n, acc + b);
-        }
-      }
-    }
-    cluster.sync();                                    // nobody leaves while its memory may still be read
-  }
-  tcgen05_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    __syncwarp();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -423,58 +324,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, con
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.f;
         }
-        if (m < p.M) {
-          const int nb = col0 + c;
-          if (p.bias) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += nb + j < p.N ? p.bias[nb + j] : 0.f;
-          }
-          if constexpr (SWIGLU) {
-            // [g0..7 | u0..7 | g8..15 | u8..15] -> 16 outputs at column nb / 2 (N is a multiple of 16)
-            float h[16];
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float gate = v[b * 16 + j], up = v[b * 16 + 8 + j];
-                h[b * 8 + j] = gate / (1.f + __expf(-gate)) * up;
-              }
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {
-              if (nb + b * 16 + 16 > p.N) continue;
-              OutT* dst = crow + (nb >> 1) + b * 8;
-              if (p.vector_ok) {
-                store_row_8(dst, h + b * 8);
-              } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) store_out<OutT>(dst + j, h[b * 8 + j]);
-              }
-            }
-          } else {
-            if constexpr (sizeof(OutT) == 4) {
-              if (p.accumulate) {
-                if (p.vector_ok && nb + 32 <= p.N) {
-#pragma unroll
-                  for (int j = 0; j < 32; j += 4) {
-                    const float4 e = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(crow) + nb + j);
-                    v[j] += e.x; v[j + 1] += e.y; v[j + 2] += e.z; v[j + 3] += e.w;
-                  }
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 32; ++j)
-                    if (nb + j < p.N) v[j] += reinterpret_cast<const float*>(crow)[nb + j];
-                }
-              }
-            }
-            if (p.vector_ok && nb + 32 <= p.N) {
-              store_row_32(crow + nb, v);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < p.N) store_out<OutT>(crow + nb + j, v[j]);
-            }
-          }
-        }
+        if (m < p.M) finish_chunk<SWIGLU, OutT>(v, p, crow, col0 + c);
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -657,57 +507,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __g
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.f;
         }
-        if (m < p.M) {
-          const int nb = col0 + c;
-          if (p.bias) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += nb + j < p.N ? p.bias[nb + j] : 0.f;
-          }
-          if constexpr (SWIGLU) {
-            float h[16];
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float gate = v[b * 16 + j], up = v[b * 16 + 8 + j];
-                h[b * 8 + j] = gate / (1.f + __expf(-gate)) * up;
-              }
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {
-              if (nb + b * 16 + 16 > p.N) continue;
-              OutT* dst = crow + (nb >> 1) + b * 8;
-              if (p.vector_ok) {
-                store_row_8(dst, h + b * 8);
-              } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) store_out<OutT>(dst + j, h[b * 8 + j]);
-              }
-            }
-          } else {
-            if constexpr (sizeof(OutT) == 4) {
-              if (p.accumulate) {
-                if (p.vector_ok && nb + 32 <= p.N) {
-#pragma unroll
-                  for (int j = 0; j < 32; j += 4) {
-                    const float4 e = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(crow) + nb + j);
-                    v[j] += e.x; v[j + 1] += e.y; v[j + 2] += e.z; v[j + 3] += e.w;
-                  }
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 32; ++j)
-                    if (nb + j < p.N) v[j] += reinterpret_cast<const float*>(crow)[nb + j];
-                }
-              }
-            }
-            if (p.vector_ok && nb + 32 <= p.N) {
-              store_row_32(crow + nb, v);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < p.N) store_out<OutT>(crow + nb + j, v[j]);
-            }
-          }
-        }
+        if (m < p.M) finish_chunk<SWIGLU, OutT>(v, p, crow, col0 + c);
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -953,58 +753,7 @@ gemm_tcgen05_streamk_kernel(const __grid_constant__ CUtensorMap map_rows, const 
             v[4 * j] += e.x; v[4 * j + 1] += e.y; v[4 * j + 2] += e.z; v[4 * j + 3] += e.w;
           }
         }
-        if (m < p.M) {
-          const int nb = col0 + c;
-          if (p.bias) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += nb + j < p.N ? p.bias[nb + j] : 0.f;
-          }
-          if constexpr (SWIGLU) {
-            // [g0..7 | u0..7 | g8..15 | u8..15] -> 16 outputs at column nb / 2 (N is a multiple of 16)
-            float h[16];
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float gate = v[b * 16 + j], up = v[b * 16 + 8 + j];
-                h[b * 8 + j] = gate / (1.f + __expf(-gate)) * up;
-              }
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {
-              if (nb + b * 16 + 16 > p.N) continue;
-              OutT* dst = crow + (nb >> 1) + b * 8;
-              if (p.vector_ok) {
-                store_row_8(dst, h + b * 8);
-              } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) store_out<OutT>(dst + j, h[b * 8 + j]);
-              }
-            }
-          } else {
-            if constexpr (sizeof(OutT) == 4) {
-              if (p.accumulate) {
-                if (p.vector_ok && nb + 32 <= p.N) {
-#pragma unroll
-                  for (int j = 0; j < 32; j += 4) {
-                    const float4 e = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(crow) + nb + j);
-                    v[j] += e.x; v[j + 1] += e.y; v[j + 2] += e.z; v[j + 3] += e.w;
-                  }
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 32; ++j)
-                    if (nb + j < p.N) v[j] += reinterpret_cast<const float*>(crow)[nb + j];
-                }
-              }
-            }
-            if (p.vector_ok && nb + 32 <= p.N) {
-              store_row_32(crow + nb, v);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (nb + j < p.N) store_out<OutT>(crow + nb + j, v[j]);
-            }
-          }
-        }
+        if (m < p.M) finish_chunk<SWIGLU, OutT>(v, p, crow, col0 + c);
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -1054,33 +803,6 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : 10006;
-}
-
-template <int BN, int STAGES, bool SWAP, typename OutT>
-static int launch(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, dim3 grid, int cluster_y, cudaStream_t stream) {
-  constexpr size_t smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
-  static_assert(!SWAP || STAGES * (BM * BK * 2 + BN * BK * 2) >= BN * BM * 4, "partial tile must fit in the stage ring");
-  auto kernel = gemm_tcgen05_kernel<BN, STAGES, SWAP, OutT>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
-  cudaLaunchConfig_t config{};
-  config.gridDim = grid;
-  config.blockDim = dim3(kThreads);
-  config.dynamicSmemBytes = smem;
-  config.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = cluster_y;
-  attr[0].val.clusterDim.z = 1;
-  config.attrs = attr;
-  config.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&config, kernel, rows, cols, p);
-  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 template <int STAGES, bool SWIGLU, typename OutT>
@@ -1177,105 +899,46 @@ extern "C" int b200_gemm_tcgen05_error() {
 
 // C[M,N] (ldc) = A[M,K] * W[N,K]^T + bias; out_f32 selects float or bfloat16 output.
 // K must be a multiple of 8 and both bases 16-byte aligned (TMA); refused otherwise.
-// splits > 0 selects the swapped kernel for M <= 64 with the K range cut into `splits` (1..8) parts;
-// splits == 0 the persistent kernel; splits < 0 the one-tile-per-CTA kernel.
-static int gemm_tcgen05_impl(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
-                             int out_f32, int splits, int swiglu, cudaStream_t stream, int accumulate = 0);
-
-// The persistent kernel with C (float32) += A W^T + bias: the residual sum done where the product is.
-extern "C" int b200_gemm_tcgen05_add(const void* A, const void* W, const float* bias, float* C, int M, int N, int K, int ldc,
-                                     cudaStream_t stream) {
-  return gemm_tcgen05_impl(A, W, bias, C, M, N, K, ldc, 1, 0, 0, stream, 1);
-}
-
-extern "C" int b200_gemm_tcgen05(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
-                                 int out_f32, int splits, cudaStream_t stream) {
-  return gemm_tcgen05_impl(A, W, bias, C, M, N, K, ldc, out_f32, splits, 0, stream);
-}
-
-// The persistent kernel with the SwiGLU epilogue: W = gate and up rows interleaved in blocks of
-// eight (N a multiple of 16), C = silu(gate) * up with N / 2 columns (ldc >= N / 2).
-extern "C" int b200_gemm_tcgen05_swiglu(const void* A, const void* W, const float* bias, void* C, int M, int N, int K,
-                                        int ldc, int out_f32, cudaStream_t stream) {
-  if (N % 16 != 0) return B200_ERR_BAD_SIZE;
-  return gemm_tcgen05_impl(A, W, bias, C, M, N, K, ldc, out_f32, 0, 1, stream);
-}
-
-// The 2-CTA kernel (256 x 256 tiles on pairs of SMs).  swiglu / accumulate as in the other entry points.
-extern "C" int b200_gemm_tcgen05_pair(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
-                                      int out_f32, int swiglu, int accumulate, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 != 0 || ldc < (swiglu ? N / 2 : N) || (swiglu && N % 16 != 0)) return B200_ERR_BAD_SIZE;
-  if (accumulate && (!out_f32 || swiglu)) return B200_ERR_BAD_SIZE;
-  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return B200_ERR_BAD_SIZE;
-  GemmParams p{C, bias, M, N, K, ldc, (ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0, 0, accumulate, nullptr, nullptr};
-  CUtensorMap rows, cols;
-  if (int e = make_map(&rows, A, M, K, BM)) return e;
-  if (int e = make_map(&cols, W, N, K, 128)) return e;
-  if (swiglu)
-    return out_f32 ? launch_pair<6, true, float>(rows, cols, p, stream) : launch_pair<6, true, __nv_bfloat16>(rows, cols, p, stream);
-  return out_f32 ? launch_pair<6, false, float>(rows, cols, p, stream) : launch_pair<6, false, __nv_bfloat16>(rows, cols, p, stream);
-}
-
-// Stream-K kernel.  `partials` holds b200_gemm_tcgen05_streamk_partial_floats() floats, `flags`
-// b200_gemm_tcgen05_streamk_flags() 32-bit words that are zero before the first launch (the kernel
-// leaves them zero).  Launches that share them must not overlap.  accumulate (float output, no
-// SwiGLU): C += A W^T + bias.
+//   swiglu      W holds gate and up rows interleaved in blocks of eight (N a multiple of 16);
+//               C = silu(gate) * up with N / 2 columns (ldc >= N / 2)
+//   accumulate  float output without swiglu: C += A W^T + bias (the residual sum done where the product is)
+//   kind        0: one CTA per 128 x 256 tile, persistent; 1: pairs of CTAs on 256 x 256 tiles
+//               (cta_group::2); 2: stream-K (left-over tiles shared between CTAs)
+//   partials, flags  stream-K only: b200_gemm_tcgen05_streamk_partial_floats() floats and
+//               b200_gemm_tcgen05_streamk_flags() 32-bit words that are zero before the first launch
+//               (the kernel leaves them zero); launches that share them must not overlap
 extern "C" long b200_gemm_tcgen05_streamk_partial_floats() { return static_cast<long>(kStreamKMaxCtas) * BM * 256; }
 extern "C" int b200_gemm_tcgen05_streamk_flags() { return kStreamKMaxCtas; }
 
-extern "C" int b200_gemm_tcgen05_streamk(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
-                                         int out_f32, int swiglu, int accumulate, float* partials, unsigned* flags,
-                                         cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 != 0 || ldc < (swiglu ? N / 2 : N) || (swiglu && N % 16 != 0)) return B200_ERR_BAD_SIZE;
-  if (accumulate && (!out_f32 || swiglu)) return B200_ERR_BAD_SIZE;
-  if (!partials || !flags) return 10004;
-  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(partials)) & 15) return B200_ERR_BAD_SIZE;
-  GemmParams p{C, bias, M, N, K, ldc, (ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0, 0, accumulate, partials, flags};
-  CUtensorMap rows, cols;
-  if (int e = make_map(&rows, A, M, K, BM)) return e;
-  if (int e = make_map(&cols, W, N, K, 256)) return e;
+template <int KIND, int STAGES, bool SWIGLU, typename OutT>
+static int launch_kind(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, cudaStream_t stream) {
+  if constexpr (KIND == 0) return launch_persistent<STAGES, SWIGLU, OutT>(rows, cols, p, stream);
+  else if constexpr (KIND == 1) return launch_pair<STAGES, SWIGLU, OutT>(rows, cols, p, stream);
+  else return launch_streamk<STAGES, SWIGLU, OutT>(rows, cols, p, stream);
+}
+template <int KIND, int STAGES>
+static int launch_variant(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, int out_f32, int swiglu,
+                          cudaStream_t stream) {
   if (swiglu)
-    return out_f32 ? launch_streamk<4, true, float>(rows, cols, p, stream) : launch_streamk<4, true, __nv_bfloat16>(rows, cols, p, stream);
-  return out_f32 ? launch_streamk<4, false, float>(rows, cols, p, stream) : launch_streamk<4, false, __nv_bfloat16>(rows, cols, p, stream);
+    return out_f32 ? launch_kind<KIND, STAGES, true, float>(rows, cols, p, stream)
+                   : launch_kind<KIND, STAGES, true, __nv_bfloat16>(rows, cols, p, stream);
+  return out_f32 ? launch_kind<KIND, STAGES, false, float>(rows, cols, p, stream)
+                 : launch_kind<KIND, STAGES, false, __nv_bfloat16>(rows, cols, p, stream);
 }
 
-static int gemm_tcgen05_impl(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
-                             int out_f32, int splits, int swiglu, cudaStream_t stream, int accumulate) {
+extern "C" int b200_gemm_tcgen05(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
+                                 int out_f32, int swiglu, int accumulate, int kind, float* partials, unsigned* flags,
+                                 cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 != 0 || ldc < (swiglu ? N / 2 : N)) return B200_ERR_BAD_SIZE;
+  if (K <= 0 || K % 8 != 0 || ldc < (swiglu ? N / 2 : N) || (swiglu && N % 16 != 0) || kind < 0 || kind > 2) return B200_ERR_BAD_SIZE;
+  if (accumulate && (!out_f32 || swiglu)) return B200_ERR_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return B200_ERR_BAD_SIZE;
-  GemmParams p{C, bias, M, N, K, ldc, (ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0, 0, accumulate, nullptr, nullptr};
+  if (kind == 2 && (!partials || !flags || (reinterpret_cast<uintptr_t>(partials) & 15))) return 10004;
+  GemmParams p{C, bias, M, N, K, ldc, (ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0, accumulate, partials, flags};
   CUtensorMap rows, cols;
-  const int total_kb = (K + BK - 1) / BK;
-  if (splits > 0) {
-    if (M > 64 || splits > 8) return B200_ERR_BAD_SIZE;
-    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-    if (int e = make_map(&rows, W, N, K, BM)) return e;
-    if (int e = make_map(&cols, A, M, K, bn)) return e;
-    p.kb_per_split = (total_kb + splits - 1) / splits;
-    dim3 grid((N + BM - 1) / BM, splits);
-#define B200_SWAP(BN_)                                                                               \
-  return out_f32 ? launch<BN_, 8, true, float>(rows, cols, p, grid, splits, stream)                 \
-                 : launch<BN_, 8, true, __nv_bfloat16>(rows, cols, p, grid, splits, stream)
-    if (bn == 16) { B200_SWAP(16); }
-    if (bn == 32) { B200_SWAP(32); }
-    B200_SWAP(64);
-#undef B200_SWAP
-  }
-  constexpr int BN = 256;
   if (int e = make_map(&rows, A, M, K, BM)) return e;
-  if (int e = make_map(&cols, W, N, K, BN)) return e;
-  if (splits < 0) {   // one CTA per tile, no overlap of epilogue and main loop (kept for comparison)
-    dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN);
-    if (grid.y > 65535) return B200_ERR_TOO_LARGE;
-    return out_f32 ? launch<BN, 4, false, float>(rows, cols, p, grid, 1, stream)
-                   : launch<BN, 4, false, __nv_bfloat16>(rows, cols, p, grid, 1, stream);
-  }
-  if (swiglu)
-    return out_f32 ? launch_persistent<4, true, float>(rows, cols, p, stream)
-                   : launch_persistent<4, true, __nv_bfloat16>(rows, cols, p, stream);
-  return out_f32 ? launch_persistent<4, false, float>(rows, cols, p, stream)
-                 : launch_persistent<4, false, __nv_bfloat16>(rows, cols, p, stream);
+  if (int e = make_map(&cols, W, N, K, kind == 1 ? 128 : 256)) return e;
+  if (kind == 1) return launch_variant<1, 6>(rows, cols, p, out_f32, swiglu, stream);
+  if (kind == 2) return launch_variant<2, 4>(rows, cols, p, out_f32, swiglu, stream);
+  return launch_variant<0, 4>(rows, cols, p, out_f32, swiglu, stream);
 }

@@ -13,15 +13,11 @@ from .native import c_int, c_void_p
 native.register_library(
     "b200_gemm_tcgen05", ("gemm_tcgen05.cu",),
     {
-        "b200_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
-        "b200_gemm_tcgen05_swiglu": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "b200_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                              c_void_p, c_void_p, c_void_p],
         "b200_gemm_tcgen05_error": [],
-        "b200_gemm_tcgen05_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-        "b200_gemm_tcgen05_pair": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "b200_gemm_tcgen05_streamk_partial_floats": [],
         "b200_gemm_tcgen05_streamk_flags": [],
-        "b200_gemm_tcgen05_streamk": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                      c_void_p, c_void_p, c_void_p],
     },
 )
 
@@ -36,9 +32,8 @@ native.register_library(
 PAIR_MIN_ROWS = 256   # from here on pairs of SMs work on 256 x 256 tiles (tcgen05 cta_group::2)
 PAIR_ENABLED = os.environ.get("LLM_RUNTIME_STUDY_B200_GEMM_PAIR", "1") != "0"
 SKINNY_M = 16         # up to here weights are streamed straight into mma.sync fragments
-SMALL_M = 64          # up to here the weight is the row operand ("swapped")
 _SM_COUNT = 148
-
+KERNELS = {"persistent": 0, "pair": 1, "streamk": 2}
 
 _STREAMK_WORKSPACE: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
 
@@ -58,64 +53,39 @@ def _streamk_workspace(device: torch.device) -> tuple[torch.Tensor, torch.Tensor
     return have
 
 
-def linear_streamk(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
-                   out_dtype: torch.dtype = torch.bfloat16, *, swiglu: bool = False,
-                   add_to: torch.Tensor | None = None) -> torch.Tensor:
-    """``x @ weight.T (+ bias)`` with the (tile, K block) pairs spread evenly over the SMs.
-    ``swiglu``: as in :func:`linear`.  ``add_to`` (float32 ``[M, N]``): the product is added to it
-    in place and it is returned."""
-
-    native.require(x, "x", dtype=torch.bfloat16, dims=2)
-    native.require(weight, "weight", dtype=torch.bfloat16, dims=2)
-    m, k = x.shape
-    n = weight.shape[0]
-    if weight.shape[1] != k:
-        raise KernelError(f"linear: x has width {k}, weight expects {weight.shape[1]}")
-    if not supported(m, n, k):
-        raise KernelError(f"tcgen05 projection needs K to be a multiple of 8, got {k}")
-    if bias is not None:
-        native.require(bias, "bias", dtype=torch.float32, shape=(n,))
-    if swiglu and n % 16:
-        raise KernelError("the SwiGLU epilogue needs an even number of 8-feature blocks")
-    if add_to is not None:
-        if swiglu:
-            raise KernelError("add_to and swiglu exclude each other")
-        native.require(add_to, "add_to", dtype=torch.float32, shape=(m, n))
-        out, out_dtype = add_to, torch.float32
-    else:
-        if out_dtype not in (torch.bfloat16, torch.float32):
-            raise KernelError(f"unsupported output type {out_dtype}")
-        out = torch.empty((m, n // 2 if swiglu else n), dtype=out_dtype, device=x.device)
-    partials, flags = _streamk_workspace(x.device)
-    native.call("b200_gemm_tcgen05_streamk", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k,
-                out.shape[1], 1 if out_dtype == torch.float32 else 0, 1 if swiglu else 0, 0 if add_to is None else 1,
-                partials.data_ptr(), flags.data_ptr(), native.stream_ptr())
-    return out
-
-
 def supported(m: int, n: int, k: int) -> bool:
     """TMA needs rows that start on 16-byte boundaries: K a multiple of 8."""
 
     return k % 8 == 0 and m > 0 and n > 0
 
 
-def pick_splits(m: int, n: int, k: int) -> int:
-    """Parts the K range is cut into (a cluster of that many CTAs) so that a
-    small-M product still puts a CTA on every SM.  0: the large-M kernel."""
+def few_tiles(m: int, n: int, k: int) -> bool:
+    """Products whose 128 x 256 tiles would occupy a third of the SMs or fewer, with a K range
+    long enough to share: the stream-K kernel lets up to three SMs work on one tile."""
 
-    if m > SMALL_M:
-        return 0
-    tiles = -(-n // 128)
-    k_blocks = -(-k // 64)
-    splits = max(1, min(8, _SM_COUNT // tiles, k_blocks // 8))
-    return splits
+    tiles = -(-m // 128) * -(-n // 256)
+    return 3 * tiles <= _SM_COUNT + 2 and k >= 48 * 64
 
 
-def linear_pair(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
-                out_dtype: torch.dtype = torch.bfloat16, *, swiglu: bool = False,
-                add_to: torch.Tensor | None = None) -> torch.Tensor:
-    """``x @ weight.T (+ bias)`` on pairs of SMs (tcgen05 ``cta_group::2``, 256 x 256 tiles).
-    ``swiglu`` and ``add_to`` as in :func:`linear`."""
+def pick_kernel(m: int, n: int, k: int) -> str:
+    if few_tiles(m, n, k):
+        return "streamk"
+    if m >= PAIR_MIN_ROWS and PAIR_ENABLED:
+        return "pair"
+    return "persistent"
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+           out_dtype: torch.dtype = torch.bfloat16, *, swiglu: bool = False, add_to: torch.Tensor | None = None,
+           kernel: str | None = None) -> torch.Tensor:
+    """``x @ weight.T (+ bias)`` on the tcgen05 tensor cores; float32 accumulation; bfloat16 or
+    float32 output.
+
+    ``swiglu``: the weight holds gate and up rows interleaved in blocks of eight and the result is
+    ``silu(gate) * up``, half as wide.  ``add_to`` (float32 ``[M, N]``): the product is added to it
+    in place and it is returned.  ``kernel``: "persistent" (one CTA per 128 x 256 tile), "pair"
+    (two CTAs per 256 x 256 tile) or "streamk" (few tiles: up to three SMs share a tile's K range);
+    chosen by shape when not given."""
 
     native.require(x, "x", dtype=torch.bfloat16, dims=2)
     native.require(weight, "weight", dtype=torch.bfloat16, dims=2)
@@ -136,63 +106,13 @@ def linear_pair(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
         if out_dtype not in (torch.bfloat16, torch.float32):
             raise KernelError(f"unsupported output type {out_dtype}")
         out = torch.empty((m, n // 2 if swiglu else n), dtype=out_dtype, device=x.device)
-    native.call("b200_gemm_tcgen05_pair", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k,
+    kernel = kernel or pick_kernel(m, n, k)
+    if kernel not in KERNELS:
+        raise KernelError(f"unknown projection kernel {kernel!r}; expected one of {sorted(KERNELS)}")
+    partials, flags = _streamk_workspace(x.device) if kernel == "streamk" else (None, None)
+    native.call("b200_gemm_tcgen05", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k,
                 out.shape[1], 1 if out_dtype == torch.float32 else 0, 1 if swiglu else 0, 0 if add_to is None else 1,
-                native.stream_ptr())
-    return out
-
-
-def few_tiles(m: int, n: int, k: int) -> bool:
-    """Products whose 128 x 256 tiles would occupy a third of the SMs or fewer, with a K range
-    long enough to share: the stream-K kernel lets up to three SMs work on one tile."""
-
-    tiles = -(-m // 128) * -(-n // 256)
-    return 3 * tiles <= _SM_COUNT + 2 and k >= 48 * 64
-
-
-def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
-           out_dtype: torch.dtype = torch.bfloat16, *, splits: int | None = None, swiglu: bool = False,
-           add_to: torch.Tensor | None = None) -> torch.Tensor:
-    """``x @ weight.T (+ bias)``; float32 accumulation; bfloat16 or float32 output.
-    With ``swiglu`` the weight holds gate and up rows interleaved in blocks of eight and
-    the result is ``silu(gate) * up``, half as wide (persistent kernel only).
-    ``add_to`` (float32 ``[M, N]``): the product is added to it in place and it is returned."""
-
-    if splits is None and x.dim() == 2 and weight.dim() == 2 and x.shape[0] > SMALL_M:
-        if few_tiles(x.shape[0], weight.shape[0], x.shape[1]):
-            return linear_streamk(x, weight, bias, out_dtype, swiglu=swiglu, add_to=add_to)
-        if x.shape[0] >= PAIR_MIN_ROWS and PAIR_ENABLED:
-            return linear_pair(x, weight, bias, out_dtype, swiglu=swiglu, add_to=add_to)
-
-    native.require(x, "x", dtype=torch.bfloat16, dims=2)
-    native.require(weight, "weight", dtype=torch.bfloat16, dims=2)
-    m, k = x.shape
-    n = weight.shape[0]
-    if weight.shape[1] != k:
-        raise KernelError(f"linear: x has width {k}, weight expects {weight.shape[1]}")
-    if not supported(m, n, k):
-        raise KernelError(f"tcgen05 projection needs K to be a multiple of 8, got {k}")
-    if out_dtype not in (torch.bfloat16, torch.float32):
-        raise KernelError(f"unsupported output type {out_dtype}")
-    if bias is not None:
-        native.require(bias, "bias", dtype=torch.float32, shape=(n,))
-    if swiglu:
-        if n % 16 or add_to is not None:
-            raise KernelError("the SwiGLU epilogue needs an even number of 8-feature blocks and excludes add_to")
-        out = torch.empty((m, n // 2), dtype=out_dtype, device=x.device)
-        native.call("b200_gemm_tcgen05_swiglu", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k,
-                    n // 2, 1 if out_dtype == torch.float32 else 0, native.stream_ptr())
-        return out
-    if add_to is not None:
-        native.require(add_to, "add_to", dtype=torch.float32, shape=(m, n))
-        native.call("b200_gemm_tcgen05_add", x.data_ptr(), weight.data_ptr(), native.ptr(bias), add_to.data_ptr(), m, n, k, n,
-                    native.stream_ptr())
-        return add_to
-    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-    if splits is None:
-        splits = pick_splits(m, n, k)
-    native.call("b200_gemm_tcgen05", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k, n,
-                1 if out_dtype == torch.float32 else 0, splits, native.stream_ptr())
+                KERNELS[kernel], native.ptr(partials), native.ptr(flags), native.stream_ptr())
     return out
 
 
@@ -201,7 +121,8 @@ def check_error() -> None:
 
     code = native.query("b200_gemm_tcgen05_error")
     if code:
-        where = {1: "producer", 2: "tensor-core issue", 3: "epilogue", -1: "device error"}.get(code, str(code))
+        where = {1: "producer", 2: "tensor-core issue", 3: "epilogue", 4: "accumulator buffer", 5: "stream-K flag",
+                 -1: "device error"}.get(code, str(code))
         raise KernelError(f"tcgen05 projection: a bounded wait ran out ({where})")
 
 
