@@ -120,14 +120,22 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
   unsigned char* ring = base + warp * DEPTH * STAGE_BYTES;
   uint64_t* full = bars + warp * DEPTH;
 
-  auto page_row = [&](int t0) -> int {        // row of the block's first key in the pool seen as [rows][D]; -1: no page
-    const int index = p.page_shift >= 0 ? t0 >> p.page_shift : t0 / p.page_size;
-    const int slot = p.page_shift >= 0 ? t0 & (p.page_size - 1) : t0 - index * p.page_size;
-    const int page = table[index];
+  // Page ids of this warp's blocks: lane l holds the id of block (32 r + l) of the warp for the
+  // current round r of 32 blocks, read from the block table in one go instead of one dependent
+  // global load per block; a block's id then comes out of a shuffle.
+  auto load_round = [&](int round) -> int {
+    const int i = 32 * round + lane;
+    if (i >= my_count) return -1;
+    const int t0 = c0 + (warp + WARPS * i) * KEYS;
+    return table[p.page_shift >= 0 ? t0 >> p.page_shift : t0 / p.page_size];
+  };
+  auto row_of = [&](int i, int page) -> int {   // row of block i's first key in the pool seen as [rows][D]; -1: no page
+    const int t0 = c0 + (warp + WARPS * i) * KEYS;
+    const int slot = p.page_shift >= 0 ? t0 & (p.page_size - 1) : t0 % p.page_size;
     return page < 0 ? -1 : (page * p.nkv + kvh) * p.page_size + slot;
   };
-  auto issue = [&](int i) {                   // lane 0: ask for the K and V rows of this warp's i-th block
-    const int row = page_row(c0 + (warp + WARPS * i) * KEYS);
+  auto issue = [&](int i, int page) {         // lane 0: ask for the K and V rows of this warp's i-th block
+    const int row = row_of(i, page);
     unsigned char* stage = ring + (i % DEPTH) * STAGE_BYTES;
     uint64_t* bar = &full[i % DEPTH];
     if (row < 0) {                            // no page (never the case for a live sequence): complete the phase empty-handed
@@ -141,17 +149,27 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
       tma_load_2d(stage + TENSOR_BYTES + box * BOX_BYTES, &vmap, bar, box * 64, row);
     }
   };
+  int ids = load_round(0), ids_round = 0;     // ids of blocks 32 ids_round .. + 31
+  auto page_of = [&](int i) -> int {          // all lanes call this together, i uniform and rising
+    if (i >= 32 * (ids_round + 1)) {
+      ++ids_round;
+      ids = load_round(ids_round);
+    }
+    return __shfl_sync(0xffffffffu, ids, i & 31);
+  };
   // blocks that cannot hold the newest key (index len - 1) go out before the wait
   const int newest_block = (len - 1 - c0) / KEYS;            // block of this part holding key len - 1, if it is here
   const bool newest_here = len - 1 >= c0 && len - 1 <= c1;
   int issued = 0;
-  if (lane == 0) {
-    while (issued < my_count && issued < DEPTH && !(newest_here && warp + WARPS * issued == newest_block)) issue(issued++);
-  }
+  unsigned valid = 0;                         // bit s: the block now in stage s has a page
+  auto start = [&](int i) {                   // all lanes
+    const int page = page_of(i);
+    valid = (valid & ~(1u << (i % DEPTH))) | (page >= 0 ? 1u << (i % DEPTH) : 0u);
+    if (lane == 0) issue(i, page);
+  };
+  while (issued < my_count && issued < DEPTH && !(newest_here && warp + WARPS * issued == newest_block)) start(issued++);
   pdl_wait();
-  if (lane == 0) {
-    while (issued < my_count && issued < DEPTH) issue(issued++);
-  }
+  while (issued < my_count && issued < DEPTH) start(issued++);
 
   // Q^T as B fragments: lane (g, t) holds Q[head g][16 ks + 2t, +1] and Q[head g][16 ks + 8 + 2t, +1]
   uint32_t qb[KS][2];
@@ -182,7 +200,7 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
       if (lane == 0) atomicExch(p.error, 1);
       break;
     }
-    if (page_row(t0) >= 0) {
+    if ((valid >> (i % DEPTH)) & 1u) {        // else: no page, nothing was copied into the stage
     const uint32_t kbase = smem_addr(ring + (i % DEPTH) * STAGE_BYTES), vbase = kbase + TENSOR_BYTES;
     if (t0 + KEYS - 1 > c1) {
       // rows past the end of the sequence hold whatever the page held before: their scores are
@@ -246,9 +264,9 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
     }
     }
     __syncwarp();
-    if (lane == 0 && i + DEPTH < my_count) {
-      fence_async_shared();
-      issue(i + DEPTH);
+    if (i + DEPTH < my_count) {
+      if (lane == 0) fence_async_shared();
+      start(i + DEPTH);
     }
   }
   __syncthreads();
