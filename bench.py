@@ -134,10 +134,14 @@ def run_ours(args) -> dict:
         return torch.randint(0, cfg["vocab_size"], (n,), generator=generator).tolist()
 
     max_batch = max(args.batch, 64)
+    context = CONTEXT
+    if args.only == "decode" and args.context:     # profiling aid: another context length, its own pool size
+        context, max_batch = args.context, args.batch
+        cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], context + 1024)
     engine = Engine.from_random_weights(
         cfg, seed=0, device="cuda:0", dtype="bfloat16", max_seq_len=cfg["max_position_embeddings"],
         max_batch_size=max_batch, page_size=PAGE_SIZE,
-        max_cache_tokens=max_batch * (CONTEXT + args.steps + max(args.warmup, 3) + 2 * PAGE_SIZE),
+        max_cache_tokens=max_batch * (context + args.steps + max(args.warmup, 3) + 2 * PAGE_SIZE),
         max_tokens_per_step=PREFILL_TOKENS, use_cuda_graph=True)
     runner, manager = engine.runner, engine.cache_manager
     sampler = engine._sampler
@@ -175,7 +179,8 @@ def run_ours(args) -> dict:
     def decode_point(batch, steps, warmup, sample_clocks=False):
         requests = [manager.admit() for _ in range(batch)]
         for request in requests:
-            runner.step([StepEntry(request, ids(CONTEXT), [])])
+            for at in range(0, context, PREFILL_TOKENS):
+                runner.step([StepEntry(request, ids(min(PREFILL_TOKENS, context - at)), [])])
         tokens = [ids(1) for _ in range(batch)]
 
         def one_step():
@@ -198,7 +203,8 @@ def run_ours(args) -> dict:
 
     if args.only == "decode":   # profiling aid: nothing but the decode steps of one batch size
         ms, launches, _ = decode_point(args.batch, args.steps, args.warmup)
-        return {"only": "decode", "layers": layers, "batch": args.batch, "ms_per_step": round(ms, 4), "gpu_launches": launches}
+        return {"only": "decode", "layers": layers, "batch": args.batch, "context": context, "ms_per_step": round(ms, 4),
+                "gpu_launches": launches}
     ms_b8, launches, clocks = decode_point(args.batch, args.steps, args.warmup, sample_clocks=True)
     ms_b1, _, _ = decode_point(1, args.steps, args.warmup)
     ms_b64, _, _ = decode_point(64, args.steps, args.warmup)
@@ -513,6 +519,7 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=0, help="with --only decode: cached tokens per request (default 2048)")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
     parser.add_argument("--workload", choices=("default", "staggered14b", "decode32b"), default="default",
                         help="default: Qwen3-8B decode/prefill; the others are the larger configurations (ours only)")

@@ -337,19 +337,36 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
     sm_pl[h][s] = __ldcg(p.part_ml + slot * 2 + 1);
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < heads_here * D; idx += 128) {
-    const int h = idx / D, col = idx - h * D;
+  // four neighbouring columns per thread, the loads of eight parts in flight at a time
+  for (int idx = threadIdx.x; idx < heads_here * (D / 4); idx += 128) {
+    const int h = idx / (D / 4), col = (idx - h * (D / 4)) * 4;
     float M = -INFINITY;
     for (int s = 0; s < p.num_splits; ++s) M = fmaxf(M, sm_pm[h][s]);
     const float ref = M == -INFINITY ? 0.f : M;
-    const long slot0 = (static_cast<long>(b) * p.nq + head0 + h) * p.num_splits;
-    float acc = 0.f, L = 0.f;
-    for (int s = 0; s < p.num_splits; ++s) {
-      const float f = exp2f(sm_pm[h][s] - ref);
-      acc += __ldcg(p.part_o + (slot0 + s) * D + col) * f;
-      L += sm_pl[h][s] * f;
+    const float* part = p.part_o + (static_cast<long>(b) * p.nq + head0 + h) * p.num_splits * D + col;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float L = 0.f;
+    for (int s0 = 0; s0 < p.num_splits; s0 += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (s0 + u < p.num_splits) v[u] = __ldcg(reinterpret_cast<const float4*>(part + static_cast<long>(s0 + u) * D));
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (s0 + u < p.num_splits) {           // parts are added in their order, whatever the order of arrival
+          const float f = exp2f(sm_pm[h][s0 + u] - ref);
+          acc[0] += v[u].x * f;
+          acc[1] += v[u].y * f;
+          acc[2] += v[u].z * f;
+          acc[3] += v[u].w * f;
+          L += sm_pl[h][s0 + u] * f;
+        }
     }
-    p.out[(static_cast<long>(b) * p.nq + head0 + h) * D + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    bf16* dst = p.out + (static_cast<long>(b) * p.nq + head0 + h) * D + col;
+    uint2 packed;
+    packed.x = pack_bf16(L > 0.f ? acc[0] / L : 0.f, L > 0.f ? acc[1] / L : 0.f);
+    packed.y = pack_bf16(L > 0.f ? acc[2] / L : 0.f, L > 0.f ? acc[3] / L : 0.f);
+    *reinterpret_cast<uint2*>(dst) = packed;
   }
 }
 
@@ -392,7 +409,12 @@ static int pool_map(const void* base, uint64_t rows, CUtensorMap* out) {
 using namespace b200;
 
 extern "C" int b200_attention_decode_tma_head_dim() { return HEAD_DIM; }
-extern "C" int b200_attention_decode_tma_ctas_per_sm() { return (227 * 1024) / (SMEM_BYTES + 1024 + 2 * HEADS * MAX_SPLITS * 4); }
+// CTAs of the kernel that fit on an SM: shared memory (ring, static arrays, 1 KB the system keeps per
+// CTA) or registers (128 threads of up to 128 registers: four CTAs), whichever is less.
+extern "C" int b200_attention_decode_tma_ctas_per_sm() {
+  const int by_smem = (227 * 1024) / (SMEM_BYTES + 1024 + 2 * HEADS * MAX_SPLITS * 4);
+  return by_smem < 4 ? by_smem : 4;
+}
 
 extern "C" long b200_attention_decode_tma_scratch_floats(int requests, int nq, int num_splits) {
   return num_splits <= 1 ? 0 : static_cast<long>(requests) * nq * num_splits * (D + 2);

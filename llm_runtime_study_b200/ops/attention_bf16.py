@@ -118,19 +118,23 @@ def build(head_dim: int) -> None:
             build_library(name, ("attention_decode_tma.cu",), native.library_defines(name))
 
 
-def decode_splits(requests: int, kv_heads: int, slices: int, longest: int, slots: int = 0) -> int:
-    """Into how many parts each sequence is cut.  The decode kernel keeps a few CTAs on
-    each of the 148 SMs (``slots`` in all); the CTAs of all parts should fill those slots
-    in as few, as full rounds as possible, and a part should not be shorter than two tiles
-    of keys."""
+def decode_splits(requests: int, kv_heads: int, slices: int, longest: int, slots: int = 0, head_dim: int = 128) -> int:
+    """Into how many parts each sequence is cut, from a small model of the launch's time: the CTAs
+    of all parts run in rounds of ``slots`` (what fits on the GPU at once); a CTA streams its part's
+    keys and values at what one SM can pull (about 40 GB/s) or at its share of the memory
+    bandwidth, whichever is less; every further part costs the merge a fraction of a microsecond.
+    A part is not shorter than two tiles of keys, and there are at most 64."""
 
     slots = slots or _CTA_SLOTS
     ctas = max(1, requests * kv_heads * slices)
     most = max(1, -(-longest // _MIN_KEYS_PER_SPLIT))
+    bytes_per_key = 4 * head_dim                     # K and V rows of one KV head, bfloat16
     best, best_cost = 1, None
     for s in range(1, min(most, 64) + 1):
         rounds = -(-(ctas * s) // slots)
-        cost = rounds / s + 0.02 * s          # time of the rounds + what each further part costs to merge
+        keys = -(-(-(-longest // s)) // 64) * 64     # a part is a multiple of 64 keys
+        rate = min(40.0, 6000.0 / min(ctas * s, slots))                 # GB/s = KB/us per CTA
+        cost = rounds * keys * bytes_per_key / (rate * 1e3) + 0.15 * s  # microseconds
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
     return best
@@ -310,7 +314,7 @@ def try_paged_attention(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Tens
         return decode_attention(q, cache.keys, cache.values, kv_len=ctx.kv_len, block_table=table, scale=scale,
                                 window=window,
                                 splits=decode_splits(n, nkv, slices, ctx.max_kv_len,
-                                                     decode_slots(d, cache.keys.shape[2], window, n * nkv * slices)))
+                                                     decode_slots(d, cache.keys.shape[2], window, n * nkv * slices), d))
     maps = ctx.__dict__.setdefault("_tile_maps", {})
     page_size = cache.keys.shape[2]
     if PREFILL_BACKEND == "tcgen05" and tc_supported(d, page_size, window) and ctx.max_q_len >= TC_MIN_PORTION:
