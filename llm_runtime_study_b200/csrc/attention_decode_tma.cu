@@ -201,67 +201,67 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
       break;
     }
     if ((valid >> (i % DEPTH)) & 1u) {        // else: no page, nothing was copied into the stage
-    const uint32_t kbase = smem_addr(ring + (i % DEPTH) * STAGE_BYTES), vbase = kbase + TENSOR_BYTES;
-    if (t0 + KEYS - 1 > c1) {
-      // rows past the end of the sequence hold whatever the page held before: their scores are
-      // masked below, their values are cleared here so that 0 x (stale) cannot become NaN
-      const int first = c1 - t0 + 1;
-      for (int c = lane; c < (KEYS - first) * (D / 8); c += 32) {
-        const int r = first + c / (D / 8), ch = c % (D / 8);
-        *reinterpret_cast<uint4*>(ring + (i % DEPTH) * STAGE_BYTES + TENSOR_BYTES + (ch >> 3) * BOX_BYTES + r * 128 + (ch & 7) * 16) =
-            make_uint4(0, 0, 0, 0);
+      const uint32_t kbase = smem_addr(ring + (i % DEPTH) * STAGE_BYTES), vbase = kbase + TENSOR_BYTES;
+      if (t0 + KEYS - 1 > c1) {
+        // rows past the end of the sequence hold whatever the page held before: their scores are
+        // masked below, their values are cleared here so that 0 x (stale) cannot become NaN
+        const int first = c1 - t0 + 1;
+        for (int c = lane; c < (KEYS - first) * (D / 8); c += 32) {
+          const int r = first + c / (D / 8), ch = c % (D / 8);
+          *reinterpret_cast<uint4*>(ring + (i % DEPTH) * STAGE_BYTES + TENSOR_BYTES + (ch >> 3) * BOX_BYTES + r * 128 + (ch & 7) * 16) =
+              make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();
       }
-      __syncwarp();
-    }
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-      const int chunk16 = 2 * ks + k_half;
-      uint32_t a[4];
-      ldmatrix_x4_addr(a, kbase + (chunk16 >> 3) * BOX_BYTES + k_row * 128 + (((chunk16 & 7) ^ (k_row & 7)) << 4));
-      mma_bf16(c, a, qb[ks][0], qb[ks][1]);
-    }
-    // c0, c1: key t0 + g, heads 2t, 2t+1;  c2, c3: key t0 + g + 8
-    const bool vis_a = t0 + g <= c1, vis_b = t0 + g + 8 <= c1;
-    c[0] = vis_a ? c[0] * p.scale_log2 : -INFINITY;
-    c[1] = vis_a ? c[1] * p.scale_log2 : -INFINITY;
-    c[2] = vis_b ? c[2] * p.scale_log2 : -INFINITY;
-    c[3] = vis_b ? c[3] * p.scale_log2 : -INFINITY;
-    float mx[2] = {fmaxf(c[0], c[2]), fmaxf(c[1], c[3])};
+      for (int ks = 0; ks < KS; ++ks) {
+        const int chunk16 = 2 * ks + k_half;
+        uint32_t a[4];
+        ldmatrix_x4_addr(a, kbase + (chunk16 >> 3) * BOX_BYTES + k_row * 128 + (((chunk16 & 7) ^ (k_row & 7)) << 4));
+        mma_bf16(c, a, qb[ks][0], qb[ks][1]);
+      }
+      // c0, c1: key t0 + g, heads 2t, 2t+1;  c2, c3: key t0 + g + 8
+      const bool vis_a = t0 + g <= c1, vis_b = t0 + g + 8 <= c1;
+      c[0] = vis_a ? c[0] * p.scale_log2 : -INFINITY;
+      c[1] = vis_a ? c[1] * p.scale_log2 : -INFINITY;
+      c[2] = vis_b ? c[2] * p.scale_log2 : -INFINITY;
+      c[3] = vis_b ? c[3] * p.scale_log2 : -INFINITY;
+      float mx[2] = {fmaxf(c[0], c[2]), fmaxf(c[1], c[3])};
 #pragma unroll
-    for (int off = 4; off < 32; off <<= 1) {
-      mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], off));
-      mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], off));
-    }
-    float corr[2], ref[2];
+      for (int off = 4; off < 32; off <<= 1) {
+        mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], off));
+        mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], off));
+      }
+      float corr[2], ref[2];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const float m_new = fmaxf(m[h], mx[h]);
-      ref[h] = m_new == -INFINITY ? 0.f : m_new;
-      corr[h] = exp2f(m[h] - ref[h]);
-      m[h] = m_new;
-      l[h] *= corr[h];
-    }
-    const float p0 = exp2f(c[0] - ref[0]), p1 = exp2f(c[1] - ref[1]), p2 = exp2f(c[2] - ref[0]), p3 = exp2f(c[3] - ref[1]);
-    l[0] += p0 + p2;
-    l[1] += p1 + p3;
+      for (int h = 0; h < 2; ++h) {
+        const float m_new = fmaxf(m[h], mx[h]);
+        ref[h] = m_new == -INFINITY ? 0.f : m_new;
+        corr[h] = exp2f(m[h] - ref[h]);
+        m[h] = m_new;
+        l[h] *= corr[h];
+      }
+      const float p0 = exp2f(c[0] - ref[0]), p1 = exp2f(c[1] - ref[1]), p2 = exp2f(c[2] - ref[0]), p3 = exp2f(c[3] - ref[1]);
+      l[0] += p0 + p2;
+      l[1] += p1 + p3;
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      o[mt][0] *= corr[0];
-      o[mt][1] *= corr[1];
-      o[mt][2] *= corr[0];
-      o[mt][3] *= corr[1];
-    }
-    // P^T [keys x heads] -> B fragments [k = keys][n = heads]
-    const uint32_t pb0 = movmatrix_trans(pack_bf16(p0, p1));
-    const uint32_t pb1 = movmatrix_trans(pack_bf16(p2, p3));
+      for (int mt = 0; mt < MT; ++mt) {
+        o[mt][0] *= corr[0];
+        o[mt][1] *= corr[1];
+        o[mt][2] *= corr[0];
+        o[mt][3] *= corr[1];
+      }
+      // P^T [keys x heads] -> B fragments [k = keys][n = heads]
+      const uint32_t pb0 = movmatrix_trans(pack_bf16(p0, p1));
+      const uint32_t pb1 = movmatrix_trans(pack_bf16(p2, p3));
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      const int chunk16 = 2 * mt + v_half;
-      uint32_t vf[4];
-      ldmatrix_x4_trans_addr(vf, vbase + (chunk16 >> 3) * BOX_BYTES + v_key * 128 + (((chunk16 & 7) ^ (v_key & 7)) << 4));
-      mma_bf16(o[mt], vf, pb0, pb1);
-    }
+      for (int mt = 0; mt < MT; ++mt) {
+        const int chunk16 = 2 * mt + v_half;
+        uint32_t vf[4];
+        ldmatrix_x4_trans_addr(vf, vbase + (chunk16 >> 3) * BOX_BYTES + v_key * 128 + (((chunk16 & 7) ^ (v_key & 7)) << 4));
+        mma_bf16(o[mt], vf, pb0, pb1);
+      }
     }
     __syncwarp();
     if (i + DEPTH < my_count) {
