@@ -190,8 +190,9 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(AttnParam
   bf16* vs = ks + 2 * BN * LDS;
   pdl_trigger();
   pdl_wait();
-  const int tile = blockIdx.x;
-  const int kvh = blockIdx.y / p.slices, slice = blockIdx.y % p.slices;
+  // grid (KV heads x slices, tiles): CTAs start in the order of the caller's tile list (longest first)
+  const int tile = blockIdx.y;
+  const int kvh = blockIdx.x / p.slices, slice = blockIdx.x % p.slices;
   const int entry = p.tile_entry[tile], tok0 = p.tile_start[tile], ntok = p.tile_count[tile];
   const int* table = p.block_table + static_cast<size_t>(entry) * p.table_stride;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
@@ -678,7 +679,7 @@ extern "C" int b200_attention_prefill_bf16(const void* q, const void* k_pool, co
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  dim3 grid(num_tiles, nkv * p.slices);
+  dim3 grid(nkv * p.slices, num_tiles);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
   launch(prefill_attention_kernel<4>, dim3(grid), dim3(128), kSmemBytes, stream, p);
   return launch_status();

@@ -95,8 +95,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     return;
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x;
-  const int kvh = blockIdx.y / p.slices, slice = blockIdx.y % p.slices;
+  // grid (KV heads x slices, tiles): CTAs start in the order of the tile list, which the caller sorts by
+  // falling length, whatever their KV head - the longest chains start first
+  const int tile = blockIdx.y;
+  const int kvh = blockIdx.x / p.slices, slice = blockIdx.x % p.slices;
   const int entry = p.tile_entry[tile], tok0 = p.tile_start[tile], ntok = p.tile_count[tile];
   const int* table = p.block_table + static_cast<size_t>(entry) * p.table_stride;
   const int p_first = p.positions[tok0], p_last = p_first + ntok - 1;   // an entry's positions are consecutive
@@ -407,7 +409,7 @@ extern "C" int b200_attention_prefill_tcgen05(const void* q, const void* k_pool,
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  dim3 grid(num_tiles, nkv * p.slices);
+  dim3 grid(nkv * p.slices, num_tiles);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
   launch(prefill_attention_tcgen05_kernel, grid, dim3(kTcThreads), smem, stream, map_q, map_k, map_v, p);
   return launch_status();
