@@ -219,13 +219,13 @@ __device__ __forceinline__ void finish_chunk(float (&v)[32], const GemmParams& p
 // drain tile i, the tensor core already works on tile i + 1.
 // SWIGLU: the weight holds gate and up rows interleaved in blocks of eight; the epilogue
 // writes silu(gate) * up, N / 2 columns wide, and the [M, N] intermediate never exists.
-template <int STAGES, bool SWIGLU, typename OutT>
+template <int BN, int STAGES, bool SWIGLU, typename OutT>
 __global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
                                GemmParams p) {
-  constexpr int BN = 256;
+  static_assert(BN == 64 || BN == 128 || BN == 256, "tile widths: 64, 128, 256");
   constexpr uint32_t ROW_BYTES = BM * BK * 2, COL_BYTES = BN * BK * 2, STAGE_BYTES = ROW_BYTES + COL_BYTES;
-  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -578,13 +578,13 @@ __device__ __forceinline__ float4* partial_group(float* base, int cta, int group
   return reinterpret_cast<float4*>(base) + (static_cast<size_t>(cta) * 64 + group) * BM + row;
 }
 
-template <int STAGES, bool SWIGLU, typename OutT>
+template <int BN, int STAGES, bool SWIGLU, typename OutT>
 __global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_streamk_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
                             GemmParams p) {
-  constexpr int BN = 256;
+  static_assert(BN == 64 || BN == 128 || BN == 256, "tile widths: 64, 128, 256");
   constexpr uint32_t ROW_BYTES = BM * BK * 2, COL_BYTES = BN * BK * 2, STAGE_BYTES = ROW_BYTES + COL_BYTES;
-  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
   constexpr uint32_t kFlagSpins = 1u << 22;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -805,10 +805,10 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
   return r == CUDA_SUCCESS ? 0 : 10006;
 }
 
-template <int STAGES, bool SWIGLU, typename OutT>
+template <int BN, int STAGES, bool SWIGLU, typename OutT>
 static int launch_persistent(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, cudaStream_t stream) {
-  constexpr size_t smem = STAGES * (BM * BK * 2 + 256 * BK * 2) + 1024 + 256;
-  auto kernel = gemm_tcgen05_persistent_kernel<STAGES, SWIGLU, OutT>;
+  constexpr size_t smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+  auto kernel = gemm_tcgen05_persistent_kernel<BN, STAGES, SWIGLU, OutT>;
   static bool configured = false;
   static int sm_count = 0;
   if (!configured) {
@@ -819,16 +819,16 @@ static int launch_persistent(const CUtensorMap& rows, const CUtensorMap& cols, c
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
     configured = true;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count ? tiles : sm_count;
   b200::launch(kernel, dim3(grid), dim3(kThreads), smem, stream, rows, cols, p);
   return static_cast<int>(cudaGetLastError());
 }
 
-template <int STAGES, bool SWIGLU, typename OutT>
+template <int BN, int STAGES, bool SWIGLU, typename OutT>
 static int launch_streamk(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, cudaStream_t stream) {
-  constexpr size_t smem = STAGES * (BM * BK * 2 + 256 * BK * 2) + 1024 + 256;
-  auto kernel = gemm_tcgen05_streamk_kernel<STAGES, SWIGLU, OutT>;
+  constexpr size_t smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+  auto kernel = gemm_tcgen05_streamk_kernel<BN, STAGES, SWIGLU, OutT>;
   static bool configured = false;
   static int sm_count = 0;
   if (!configured) {
@@ -839,8 +839,8 @@ static int launch_streamk(const CUtensorMap& rows, const CUtensorMap& cols, cons
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
     configured = true;
   }
-  const long long units = static_cast<long long>((p.M + BM - 1) / BM) * ((p.N + 255) / 256) * ((p.K + BK - 1) / BK);
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
+  const long long units = static_cast<long long>((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * ((p.K + BK - 1) / BK);
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   int grid = sm_count < kStreamKMaxCtas ? sm_count : kStreamKMaxCtas;
   if (3 * tiles < grid) grid = 3 * tiles;              // at most three CTAs share a tile
   if (units < grid) grid = static_cast<int>(units);
@@ -902,43 +902,52 @@ extern "C" int b200_gemm_tcgen05_error() {
 //   swiglu      W holds gate and up rows interleaved in blocks of eight (N a multiple of 16);
 //               C = silu(gate) * up with N / 2 columns (ldc >= N / 2)
 //   accumulate  float output without swiglu: C += A W^T + bias (the residual sum done where the product is)
-//   kind        0: one CTA per 128 x 256 tile, persistent; 1: pairs of CTAs on 256 x 256 tiles
+//   kind        0: one CTA per 128 x tile_n tile, persistent; 1: pairs of CTAs on 256 x 256 tiles
 //               (cta_group::2); 2: stream-K (left-over tiles shared between CTAs)
+//   tile_n      128 or 256 columns per tile (kind 0; the others take 256): narrower tiles put a product
+//               with few rows on more SMs
 //   partials, flags  stream-K only: b200_gemm_tcgen05_streamk_partial_floats() floats and
 //               b200_gemm_tcgen05_streamk_flags() 32-bit words that are zero before the first launch
 //               (the kernel leaves them zero); launches that share them must not overlap
 extern "C" long b200_gemm_tcgen05_streamk_partial_floats() { return static_cast<long>(kStreamKMaxCtas) * BM * 256; }
 extern "C" int b200_gemm_tcgen05_streamk_flags() { return kStreamKMaxCtas; }
 
-template <int KIND, int STAGES, bool SWIGLU, typename OutT>
+template <int KIND, int BN, bool SWIGLU, typename OutT>
 static int launch_kind(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, cudaStream_t stream) {
-  if constexpr (KIND == 0) return launch_persistent<STAGES, SWIGLU, OutT>(rows, cols, p, stream);
-  else if constexpr (KIND == 1) return launch_pair<STAGES, SWIGLU, OutT>(rows, cols, p, stream);
-  else return launch_streamk<STAGES, SWIGLU, OutT>(rows, cols, p, stream);
+  constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);      // 192 KB of stages in every case
+  if constexpr (KIND == 0) return launch_persistent<BN, STAGES, SWIGLU, OutT>(rows, cols, p, stream);
+  else if constexpr (KIND == 1) return launch_pair<6, SWIGLU, OutT>(rows, cols, p, stream);
+  else return launch_streamk<BN, STAGES, SWIGLU, OutT>(rows, cols, p, stream);
 }
-template <int KIND, int STAGES>
+template <int KIND, int BN>
 static int launch_variant(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, int out_f32, int swiglu,
                           cudaStream_t stream) {
   if (swiglu)
-    return out_f32 ? launch_kind<KIND, STAGES, true, float>(rows, cols, p, stream)
-                   : launch_kind<KIND, STAGES, true, __nv_bfloat16>(rows, cols, p, stream);
-  return out_f32 ? launch_kind<KIND, STAGES, false, float>(rows, cols, p, stream)
-                 : launch_kind<KIND, STAGES, false, __nv_bfloat16>(rows, cols, p, stream);
+    return out_f32 ? launch_kind<KIND, BN, true, float>(rows, cols, p, stream)
+                   : launch_kind<KIND, BN, true, __nv_bfloat16>(rows, cols, p, stream);
+  return out_f32 ? launch_kind<KIND, BN, false, float>(rows, cols, p, stream)
+                 : launch_kind<KIND, BN, false, __nv_bfloat16>(rows, cols, p, stream);
 }
 
 extern "C" int b200_gemm_tcgen05(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
-                                 int out_f32, int swiglu, int accumulate, int kind, float* partials, unsigned* flags,
+                                 int out_f32, int swiglu, int accumulate, int kind, int tile_n, float* partials, unsigned* flags,
                                  cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ldc < (swiglu ? N / 2 : N) || (swiglu && N % 16 != 0) || kind < 0 || kind > 2) return B200_ERR_BAD_SIZE;
+  if (kind == 1) tile_n = 256;
+  if (tile_n != 128 && tile_n != 256) return B200_ERR_BAD_SIZE;
   if (accumulate && (!out_f32 || swiglu)) return B200_ERR_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return B200_ERR_BAD_SIZE;
   if (kind == 2 && (!partials || !flags || (reinterpret_cast<uintptr_t>(partials) & 15))) return 10004;
   GemmParams p{C, bias, M, N, K, ldc, (ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0, accumulate, partials, flags};
   CUtensorMap rows, cols;
   if (int e = make_map(&rows, A, M, K, BM)) return e;
-  if (int e = make_map(&cols, W, N, K, kind == 1 ? 128 : 256)) return e;
-  if (kind == 1) return launch_variant<1, 6>(rows, cols, p, out_f32, swiglu, stream);
-  if (kind == 2) return launch_variant<2, 4>(rows, cols, p, out_f32, swiglu, stream);
-  return launch_variant<0, 4>(rows, cols, p, out_f32, swiglu, stream);
+  if (int e = make_map(&cols, W, N, K, kind == 1 ? 128 : tile_n)) return e;
+  if (kind == 1) return launch_variant<1, 256>(rows, cols, p, out_f32, swiglu, stream);
+  if (kind == 2) {                       // stream-K is built for 256 columns
+    if (tile_n != 256) return B200_ERR_BAD_SIZE;
+    return launch_variant<2, 256>(rows, cols, p, out_f32, swiglu, stream);
+  }
+  if (tile_n == 128) return launch_variant<0, 128>(rows, cols, p, out_f32, swiglu, stream);
+  return launch_variant<0, 256>(rows, cols, p, out_f32, swiglu, stream);
 }

@@ -14,7 +14,7 @@ native.register_library(
     "b200_gemm_tcgen05", ("gemm_tcgen05.cu",),
     {
         "b200_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                              c_void_p, c_void_p, c_void_p],
+                              c_int, c_void_p, c_void_p, c_void_p],
         "b200_gemm_tcgen05_error": [],
         "b200_gemm_tcgen05_streamk_partial_floats": [],
         "b200_gemm_tcgen05_streamk_flags": [],
@@ -59,33 +59,35 @@ def supported(m: int, n: int, k: int) -> bool:
     return k % 8 == 0 and m > 0 and n > 0
 
 
-def few_tiles(m: int, n: int, k: int) -> bool:
-    """Products whose 128 x 256 tiles would occupy a third of the SMs or fewer, with a K range
-    long enough to share: the stream-K kernel lets up to three SMs work on one tile."""
+def pick_kernel(m: int, n: int, k: int) -> tuple[str, int]:
+    """Which kernel and which tile width take a product of this shape (chosen from timings at the
+    Qwen3-8B layer widths with 128 to 4,096 rows).  Pairs of SMs on 256 x 256 tiles when those fill
+    most of the 74 pairs; one CTA per 128 x 256 tile when those cover half the SMs or more; stream-K
+    when a third of the SMs or fewer would have a tile and the K range is long enough to share;
+    else one CTA per 128 x 128 tile.  What bounds a product with few tiles is how fast one SM can
+    pull its operands in (about 120 GB/s), so it pays to spread the bytes over more SMs."""
 
+    if m >= PAIR_MIN_ROWS and PAIR_ENABLED and -(-m // 256) * -(-n // 256) >= 60:
+        return "pair", 256
     tiles = -(-m // 128) * -(-n // 256)
-    return 3 * tiles <= _SM_COUNT + 2 and k >= 48 * 64
-
-
-def pick_kernel(m: int, n: int, k: int) -> str:
-    if few_tiles(m, n, k):
-        return "streamk"
-    if m >= PAIR_MIN_ROWS and PAIR_ENABLED:
-        return "pair"
-    return "persistent"
+    if 2 * tiles >= _SM_COUNT:
+        return "persistent", 256
+    if 3 * tiles <= _SM_COUNT + 2 and k >= 48 * 64:
+        return "streamk", 256
+    return "persistent", 128
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
            out_dtype: torch.dtype = torch.bfloat16, *, swiglu: bool = False, add_to: torch.Tensor | None = None,
-           kernel: str | None = None) -> torch.Tensor:
+           kernel: str | None = None, tile_n: int | None = None) -> torch.Tensor:
     """``x @ weight.T (+ bias)`` on the tcgen05 tensor cores; float32 accumulation; bfloat16 or
     float32 output.
 
     ``swiglu``: the weight holds gate and up rows interleaved in blocks of eight and the result is
     ``silu(gate) * up``, half as wide.  ``add_to`` (float32 ``[M, N]``): the product is added to it
-    in place and it is returned.  ``kernel``: "persistent" (one CTA per 128 x 256 tile), "pair"
-    (two CTAs per 256 x 256 tile) or "streamk" (few tiles: up to three SMs share a tile's K range);
-    chosen by shape when not given."""
+    in place and it is returned.  ``kernel``: "persistent" (one CTA per tile of 128 rows and
+    ``tile_n`` = 128 or 256 columns), "pair" (two CTAs per 256 x 256 tile) or "streamk" (few
+    tiles: up to three SMs share a tile's K range); both chosen by shape when not given."""
 
     native.require(x, "x", dtype=torch.bfloat16, dims=2)
     native.require(weight, "weight", dtype=torch.bfloat16, dims=2)
@@ -106,13 +108,16 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
         if out_dtype not in (torch.bfloat16, torch.float32):
             raise KernelError(f"unsupported output type {out_dtype}")
         out = torch.empty((m, n // 2 if swiglu else n), dtype=out_dtype, device=x.device)
-    kernel = kernel or pick_kernel(m, n, k)
-    if kernel not in KERNELS:
-        raise KernelError(f"unknown projection kernel {kernel!r}; expected one of {sorted(KERNELS)}")
+    picked_kernel, picked_width = pick_kernel(m, n, k)
+    kernel = kernel or picked_kernel
+    tile_n = tile_n or (picked_width if kernel == picked_kernel else 256)
+    if kernel not in KERNELS or tile_n not in (128, 256) or (tile_n == 128 and kernel != "persistent"):
+        raise KernelError(f"unknown projection kernel {kernel!r} or tile width {tile_n}: expected one of {sorted(KERNELS)}, "
+                          "256 columns, or 128 with the persistent kernel")
     partials, flags = _streamk_workspace(x.device) if kernel == "streamk" else (None, None)
     native.call("b200_gemm_tcgen05", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k,
                 out.shape[1], 1 if out_dtype == torch.float32 else 0, 1 if swiglu else 0, 0 if add_to is None else 1,
-                KERNELS[kernel], native.ptr(partials), native.ptr(flags), native.stream_ptr())
+                KERNELS[kernel], tile_n, native.ptr(partials), native.ptr(flags), native.stream_ptr())
     return out
 
 

@@ -459,8 +459,8 @@ def test_tcgen05_projection(m, n, k, bias, out):
 
     x, w, b, want = _gemm_case(m, n, k, bias)
     scale = float(want.abs().max())
-    for kernel in ("persistent", None):
-        got = _gemm().linear(dev(x), dev(w), dev(b) if bias else None, out, kernel=kernel)
+    for kernel, tile_n in (("persistent", 256), ("persistent", 128), (None, None)):
+        got = _gemm().linear(dev(x), dev(w), dev(b) if bias else None, out, kernel=kernel, tile_n=tile_n)
         _gemm().check_error()
         torch.testing.assert_close(got.cpu().double(), want, atol=(1e-2 if out == torch.bfloat16 else 2e-5) * scale, rtol=0)
 
