@@ -3,18 +3,18 @@
 //
 // One CTA owns 128 rows of S = Q K^T: up to 128 / gs consecutive query tokens of one request
 // times the gs query heads that share one KV head.  Keys are taken 64 at a time:
-//   warp 4     one lane issues TMA loads: the Q tile once (3-D map over [token, head, d]), then
-//              for every key tile the request's pages of K and V (two stages each, running two
-//              tiles ahead), one box per page and 64-column half, found through the block table;
+//   warp 4     TMA loads: the Q tile once (3-D map over [token, head, d]), then for every key tile
+//              the request's pages of K and V (two stages each, running two tiles ahead), one box
+//              per page and 64-column half, found through the block table, each lane issuing one;
 //   warp 5     allocates TMEM; one lane issues tcgen05.mma: S = Q K^T (M 128, N 64, K = head size)
 //              into one of two S buffers in TMEM - the product for the next tile is issued before
-//              the softmax of the current one is awaited - and, once P is in shared memory,
-//              O += P V (M 128, N = head size, K 64) with V read as an MN-major operand (no
-//              transposition of the cache);
+//              the softmax of the current one is awaited - and, once P is in tensor memory,
+//              O += P V (M 128, N = head size, K 64) with P as the TMEM operand and V read from
+//              shared memory as an MN-major operand (no transposition of the cache);
 //   warps 0-3  softmax: thread r owns row r of S (tcgen05.ld gives a thread its whole row, so
 //              the row maximum and sum need no shuffles); it masks, exponentiates in float32,
-//              writes P as bfloat16 into shared memory in the swizzled K-major layout the tensor
-//              core reads, and keeps the running maximum and sum.  O stays in TMEM; it is only
+//              writes P as bfloat16 over its own row of S in tensor memory (tcgen05.st, two values
+//              per column), and keeps the running maximum and sum.  O stays in TMEM; it is only
 //              rescaled (tcgen05.ld / st) when a row's maximum has grown by more than 2^8, which
 //              keeps the result exact (the final division uses the same reference maximum).
 // Two CTAs fit on an SM, so one CTA's softmax overlaps the other's matrix products.
@@ -40,9 +40,9 @@ constexpr int BN = 64;                     // keys per tile
 constexpr int DSUB = D / 64;               // 64-column (128-byte) sub-tiles of the head size
 constexpr uint32_t Q_SUB = BM * 128;       // bytes of one Q sub-tile
 constexpr uint32_t KV_SUB = BN * 128;      // bytes of one K or V sub-tile
-constexpr uint32_t Q_BYTES = DSUB * Q_SUB, KV_BYTES = DSUB * KV_SUB, P_BYTES = BM * 128;
+constexpr uint32_t Q_BYTES = DSUB * Q_SUB, KV_BYTES = DSUB * KV_SUB;
 constexpr int KSTAGES = 2;
-constexpr uint32_t SMEM_TILES = Q_BYTES + 2 * KSTAGES * KV_BYTES + P_BYTES;
+constexpr uint32_t SMEM_TILES = Q_BYTES + 2 * KSTAGES * KV_BYTES;
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t S_COL = 0, O_COL = 2 * BN;   // two S buffers of 64 columns, then O
 constexpr int kTcThreads = 192;
@@ -77,7 +77,6 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   unsigned char* q_smem = smem;
   unsigned char* k_smem = q_smem + Q_BYTES;                 // [KSTAGES]
   unsigned char* v_smem = k_smem + KSTAGES * KV_BYTES;      // [KSTAGES]
-  unsigned char* p_smem = v_smem + KSTAGES * KV_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_TILES);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;       // [2]
@@ -176,7 +175,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, D, 1);
     bool ok = mbar_wait(q_full, 0);
     if (!ok) atomicExch(&g_attn_error, 2);
-    const uint32_t q_addr = smem_addr(q_smem), p_addr = smem_addr(p_smem);
+    const uint32_t q_addr = smem_addr(q_smem);
     auto issue_s = [&](int j) -> bool {        // S(j) = Q K_j^T into S buffer j & 1
       const int s = j & 1;
       if (!mbar_wait(k_full + s, (j >> 1) & 1)) return false;
@@ -201,8 +200,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       tcgen05_fence_after();
       const uint32_t v_addr = smem_addr(v_smem + s * KV_BYTES);
 #pragma unroll
-      for (int k = 0; k < BN / 16; ++k)
-        umma_bf16_ss(tmem_base + O_COL, umma_desc_sw128(p_addr + k * 32, 16, 1024),
+      for (int k = 0; k < BN / 16; ++k)       // P of this tile lies where its S was: 8 columns per 16 keys
+        umma_bf16_ts(tmem_base + O_COL, tmem_base + S_COL + s * BN + k * 8,
                      umma_desc_sw128(v_addr + k * 2048, KV_SUB, 1024), idesc_pv, (j | k) != 0);
       umma_commit_to(o_done);
       umma_commit_to(v_empty + s);
@@ -282,12 +281,20 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         packed[c].w = pack_bf16(e[6], e[7]);
       }
       l += (lsum[0] + lsum[1]) + (lsum[2] + lsum[3]);
-      // P is single buffered: the product that read the previous P must have completed.
-      if (j > 0 && !mbar_wait(o_done, (j - 1) & 1)) { atomicExch(&g_attn_error, 6); ok = false; break; }
-      unsigned char* prow = p_smem + row * 128;
+      // P goes where this thread's row of S was (it has been read into registers above): 32 columns of
+      // two bfloat16 each.  The product that read the P before the last one there has completed, since
+      // the S that followed it into this buffer has.
+      {
+        uint32_t words[32];
 #pragma unroll
-      for (int c = 0; c < BN / 8; ++c) *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = packed[c];
-      fence_async_shared();
+        for (int c = 0; c < BN / 8; ++c) {
+          words[4 * c] = packed[c].x;
+          words[4 * c + 1] = packed[c].y;
+          words[4 * c + 2] = packed[c].z;
+          words[4 * c + 3] = packed[c].w;
+        }
+        tmem_st_32(lane_base + S_COL + (j & 1) * BN, words);
+      }
       tcgen05_fence_before();
       mbar_arrive(p_full);
     }
