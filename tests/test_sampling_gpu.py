@@ -49,6 +49,23 @@ def test_matches_the_plain_sampler(sampler, vocab, opts):
         assert got[r] == want or abs(float(scores[got[r]] - scores[want])) < 1e-4
 
 
+@pytest.mark.parametrize("rows", [3, 20, 40, 64])
+def test_large_odd_vocabulary_every_cluster_size(sampler, rows):
+    """40,003 entries (rows after the first are not 16-byte aligned) with 3, 20, 40 and 64 rows: clusters
+    of eight, four and two CTAs a row and the single CTA."""
+
+    torch.manual_seed(5)
+    vocab, opts = 40003, dict(temperature=0.9, top_k=40, top_p=0.7)
+    logits = torch.randn(rows, vocab) * 2
+    specs = [(cfg(**opts), 77 + r, r) for r in range(rows)]
+    got = sampler.sample(logits.cuda(), specs)
+    for r in range(0, rows, max(1, rows // 8)):
+        want, scores = plain.sample(logits[r], opts["temperature"], opts["top_k"], opts["top_p"], 77 + r, r)
+        keep = plain.kept_mask(logits[r], opts["temperature"], opts["top_k"], opts["top_p"])
+        assert keep[got[r]], f"row {r}: token {got[r]} is outside the kept set"
+        assert got[r] == want or abs(float(scores[got[r]] - scores[want])) < 1e-4
+
+
 def test_rows_are_independent_of_the_batch(sampler):
     torch.manual_seed(2)
     logits = torch.randn(8, 503).cuda()
