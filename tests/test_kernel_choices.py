@@ -1,0 +1,43 @@
+"""The host-side rules that choose kernels and launch shapes (no GPU needed)."""
+
+import itertools
+
+from llm_runtime_study_b200.ops import attention_bf16, gemm_bf16
+
+
+def test_projection_kernel_choice_is_always_something_the_library_builds():
+    for m, n, k in itertools.product((1, 17, 128, 129, 255, 256, 300, 512, 1000, 2048, 8192),
+                                     (8, 264, 4096, 6144, 24576, 151936), (8, 72, 4096, 12288)):
+        kernel, width = gemm_bf16.pick_kernel(m, n, k)
+        assert kernel in gemm_bf16.KERNELS and width in (128, 256)
+        assert width == 256 or kernel == "persistent"          # 128-column tiles exist for the one-CTA kernel only
+        if kernel == "pair":
+            assert m >= gemm_bf16.PAIR_MIN_ROWS
+        if kernel == "streamk":
+            assert k >= 3072                                   # a K range long enough to share
+
+
+def test_projection_kernel_choice_at_the_benchmark_shapes():
+    layer = ((6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288))
+    assert all(gemm_bf16.pick_kernel(2048, n, k) == ("pair", 256) for n, k in layer)
+    assert gemm_bf16.pick_kernel(512, 4096, 4096) == ("persistent", 128)
+    assert gemm_bf16.pick_kernel(256, 4096, 12288) == ("streamk", 256)
+
+
+def test_decode_parts_are_bounded_and_use_the_gpu():
+    for requests, kv_heads, longest, slots in itertools.product((1, 3, 8, 64, 500), (1, 8), (1, 100, 2048, 32768, 1 << 20), (296, 592)):
+        parts = attention_bf16.decode_splits(requests, kv_heads, 1, longest, slots)
+        assert 1 <= parts <= 64
+        assert parts == 1 or longest // parts >= 64            # a part is never shorter than a few key blocks
+    # one long sequence is cut into many parts, a full batch into none
+    assert attention_bf16.decode_splits(1, 8, 1, 32768, 296) >= 16
+    assert attention_bf16.decode_splits(64, 8, 1, 2048, 592) == 1
+    assert attention_bf16.decode_splits(8, 8, 1, 2048, 296) == 4
+
+
+def test_tile_map_orders_tiles_longest_first():
+    table, count = attention_bf16.tile_map([5, 70, 1], 32, "cpu", kv_lens=[300, 70, 900])
+    rows = table.t().tolist()                                    # [entry, first token, count]
+    assert count == 5 and sorted(r[0] for r in rows) == [0, 1, 1, 1, 2]
+    assert rows[0] == [2, 75, 1] and rows[1] == [0, 0, 5]        # 900 keys, then 300, then the 70-token prompt's tiles
+    assert [r[2] for r in rows if r[0] == 1] == [6, 32, 32]      # its last tile (6 tokens, 70 keys) before the earlier ones
