@@ -169,24 +169,29 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       load_boxes(v_smem + s * KV_BYTES, &map_v, v_full + s, id);
       id = next_id;
     }
-  } else if (warp == 5 && lane == 0) {
+  } else if (warp == 5) {
     // ------------------------------------------------------------------ tensor-core issue
+    // The whole warp runs the loop and waits; one elected lane issues (see elect_one()).
     constexpr uint32_t idesc_s = umma_idesc_bf16(BM, BN, 0);
     constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, D, 1);
-    bool ok = mbar_wait(q_full, 0);
+    auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbar_wait(bar, parity) ? 1 : 0) != 0; };
+    bool ok = wait_all(q_full, 0);
     if (!ok) atomicExch(&g_attn_error, 2);
     const uint32_t q_addr = smem_addr(q_smem);
     auto issue_s = [&](int j) -> bool {        // S(j) = Q K_j^T into S buffer j & 1
       const int s = j & 1;
-      if (!mbar_wait(k_full + s, (j >> 1) & 1)) return false;
+      if (!wait_all(k_full + s, (j >> 1) & 1)) return false;
       tcgen05_fence_after();
       const uint32_t k_addr = smem_addr(k_smem + s * KV_BYTES);
+      if (elect_one()) {
 #pragma unroll
-      for (int k = 0; k < D / 16; ++k)
-        umma_bf16_ss(tmem_base + S_COL + s * BN, umma_desc_sw128(q_addr + (k >> 2) * Q_SUB + (k & 3) * 32, 16, 1024),
-                     umma_desc_sw128(k_addr + (k >> 2) * KV_SUB + (k & 3) * 32, 16, 1024), idesc_s, k != 0);
-      umma_commit_to(s_full + s);
-      umma_commit_to(k_empty + s);
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16_ss(tmem_base + S_COL + s * BN, umma_desc_sw128(q_addr + (k >> 2) * Q_SUB + (k & 3) * 32, 16, 1024),
+                       umma_desc_sw128(k_addr + (k >> 2) * KV_SUB + (k & 3) * 32, 16, 1024), idesc_s, k != 0);
+        umma_commit_to(s_full + s);
+        umma_commit_to(k_empty + s);
+      }
+      __syncwarp();
       return true;
     };
     if (ok && !issue_s(0)) { atomicExch(&g_attn_error, 2); ok = false; }
@@ -196,15 +201,18 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       // arrived on p_full (waited for in the previous round); the tensor core then has work
       // while the softmax of tile j runs.
       if (j + 1 < ntiles && !issue_s(j + 1)) { atomicExch(&g_attn_error, 2); break; }
-      if (!mbar_wait(p_full, j & 1) || !mbar_wait(v_full + s, (j >> 1) & 1)) { atomicExch(&g_attn_error, 3); break; }
+      if (!wait_all(p_full, j & 1) || !wait_all(v_full + s, (j >> 1) & 1)) { atomicExch(&g_attn_error, 3); break; }
       tcgen05_fence_after();
       const uint32_t v_addr = smem_addr(v_smem + s * KV_BYTES);
+      if (elect_one()) {
 #pragma unroll
-      for (int k = 0; k < BN / 16; ++k)       // P of this tile lies where its S was: 8 columns per 16 keys
-        umma_bf16_ts(tmem_base + O_COL, tmem_base + S_COL + s * BN + k * 8,
-                     umma_desc_sw128(v_addr + k * 2048, KV_SUB, 1024), idesc_pv, (j | k) != 0);
-      umma_commit_to(o_done);
-      umma_commit_to(v_empty + s);
+        for (int k = 0; k < BN / 16; ++k)       // P of this tile lies where its S was: 8 columns per 16 keys
+          umma_bf16_ts(tmem_base + O_COL, tmem_base + S_COL + s * BN + k * 8,
+                       umma_desc_sw128(v_addr + k * 2048, KV_SUB, 1024), idesc_pv, (j | k) != 0);
+        umma_commit_to(o_done);
+        umma_commit_to(v_empty + s);
+      }
+      __syncwarp();
     }
   } else if (warp < 4) {
     // ------------------------------------------------------------------ softmax, one row per thread

@@ -109,6 +109,15 @@ __device__ __forceinline__ void pdl_trigger() {
 // kernel or on any kernel before it.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
+// True in exactly one lane of a converged warp.  Code that every lane runs and that only issues its
+// asynchronous instructions under this predicate keeps descriptors, addresses and counters in uniform
+// registers, where the copy, barrier and MMA instructions take them from.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
+  return pred != 0;
+}
+
 inline bool pdl_enabled() {
   static int enabled = -1;
   if (enabled < 0) {

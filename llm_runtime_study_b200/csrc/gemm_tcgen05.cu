@@ -18,6 +18,7 @@
 // error code, stops issuing work, frees its TMEM and returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include "common.cuh"
 #include "mma.cuh"
 
@@ -48,6 +49,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (done) return true;
   }
   return false;
+}
+// The wait as a converged warp runs it: every lane waits, and all lanes get the same answer.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity) ? 1 : 0) != 0;
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
@@ -152,6 +157,9 @@ struct GemmParams {
   int accumulate;     // float output only: C += A W^T + bias instead of C = ...
   float* partials;    // stream-K: [grid][128][256] partial accumulators
   unsigned* flags;    // stream-K: [grid], zero between launches
+  int splits;         // split-K: CTAs (one cluster) that share the K range of a tile, at most 8
+  int a_rows;         // split-K: rows of the row operand's box, a multiple of 8 up to 128
+  int bn, stages;     // split-K: columns per tile (a multiple of 32, at most 256), stages of the operand ring
 };
 
 // What the epilogue does with 32 consecutive accumulator columns of one row, starting at column nb of
@@ -171,7 +179,7 @@ __device__ __forceinline__ void finish_chunk(float (&v)[32], const GemmParams& p
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float gate = v[b * 16 + j], up = v[b * 16 + 8 + j];
-        h[b * 8 + j] = gate / (1.f + __expf(-gate)) * up;
+        h[b * 8 + j] = __fdividef(gate, 1.f + __expf(-gate)) * up;     // 2 ulp; for huge negative gates 0, as the limit is
       }
 #pragma unroll
     for (int b = 0; b < 2; ++b) {
@@ -260,45 +268,53 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, con
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();                             // set-up above overlaps the kernel before; its results are read below
 
-  if (warp == 0 && lane == 0) {
+  // Producer and tensor-core warp run their loops as whole warps and issue under elect_one(): see there.
+  if (warp == 0) {
     // ---------------------------------------------------------------- producer
-    int it = 0;
+    int s = 0;
+    uint32_t phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
       const int row0 = (tile % m_tiles) * BM, col0 = (tile / m_tiles) * BN;
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t phase = (it / STAGES) & 1;
-        if (!mbar_wait(empty + s, phase ^ 1)) { atomicExch(&g_gemm_error, 1); ok = false; break; }
-        mbar_expect_tx(full + s, STAGE_BYTES);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait_warp(empty + s, phase ^ 1)) { atomicExch(&g_gemm_error, 1); ok = false; break; }
         unsigned char* stage = smem + s * STAGE_BYTES;
-        tma_load_2d(stage, &map_rows, full + s, kb * BK, row0);
-        tma_load_2d(stage + ROW_BYTES, &map_cols, full + s, kb * BK, col0);
+        if (elect_one()) {
+          mbar_expect_tx(full + s, STAGE_BYTES);
+          tma_load_2d(stage, &map_rows, full + s, kb * BK, row0);
+          tma_load_2d(stage + ROW_BYTES, &map_cols, full + s, kb * BK, col0);
+        }
+        __syncwarp();
+        if (++s == STAGES) { s = 0; phase ^= 1; }
       }
     }
-  } else if (warp == 1 && lane == 0) {
+  } else if (warp == 1) {
     // ---------------------------------------------------------------- tensor-core issue
     constexpr uint32_t idesc = umma_idesc(BN);
-    int it = 0, local = 0;
+    int s = 0, local = 0;
+    uint32_t phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
-      if (!mbar_wait(acc_empty + buf, acc_phase ^ 1)) { atomicExch(&g_gemm_error, 4); ok = false; break; }
+      if (!mbar_wait_warp(acc_empty + buf, acc_phase ^ 1)) { atomicExch(&g_gemm_error, 4); ok = false; break; }
       tcgen05_fence_after();
       const uint32_t tmem_d = tmem_base + buf * BN;
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t phase = (it / STAGES) & 1;
-        if (!mbar_wait(full + s, phase)) { atomicExch(&g_gemm_error, 2); ok = false; break; }
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait_warp(full + s, phase)) { atomicExch(&g_gemm_error, 2); ok = false; break; }
         tcgen05_fence_after();
         const uint32_t a_addr = smem_addr(smem + s * STAGE_BYTES), b_addr = a_addr + ROW_BYTES;
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)
-          umma_bf16(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, (kb | k) != 0);
-        umma_commit(empty + s);
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, (kb | k) != 0);
+          umma_commit(empty + s);
+        }
+        __syncwarp();
+        if (++s == STAGES) { s = 0; phase ^= 1; }
       }
-      umma_commit(acc_full + buf);
+      if (elect_one()) umma_commit(acc_full + buf);
+      __syncwarp();
     }
   } else if (warp >= 2) {
     // -------------------------------------------------------------------- epilogue
@@ -441,47 +457,54 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __g
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();                             // set-up above overlaps the kernel before; its results are read below
 
-  if (warp == 0 && lane == 0) {
+  if (warp == 0) {
     // ---------------------------------------------------------------- producer (both CTAs)
-    int it = 0;
+    int s = 0;
+    uint32_t phase = 0;
     bool ok = true;
     for (int tile = pair; tile < tiles && ok; tile += pairs) {
       const int row0 = (tile % m_tiles) * PAIR_M + static_cast<int>(rank) * BM;
       const int col0 = (tile / m_tiles) * BN + static_cast<int>(rank) * HALF_N;
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t phase = (it / STAGES) & 1;
-        if (!mbar_wait(empty + s, phase ^ 1)) { atomicExch(&g_gemm_error, 1); ok = false; break; }
-        if (leader) mbar_expect_tx(full + s, 2 * STAGE_BYTES);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait_warp(empty + s, phase ^ 1)) { atomicExch(&g_gemm_error, 1); ok = false; break; }
         const uint32_t leader_full = map_to_cta(smem_addr(full + s), 0);
         unsigned char* stage = smem + s * STAGE_BYTES;
-        tma_load_2d_pair(stage, &map_rows, leader_full, kb * BK, row0);
-        tma_load_2d_pair(stage + ROW_BYTES, &map_cols, leader_full, kb * BK, col0);
+        if (elect_one()) {
+          if (leader) mbar_expect_tx(full + s, 2 * STAGE_BYTES);
+          tma_load_2d_pair(stage, &map_rows, leader_full, kb * BK, row0);
+          tma_load_2d_pair(stage + ROW_BYTES, &map_cols, leader_full, kb * BK, col0);
+        }
+        __syncwarp();
+        if (++s == STAGES) { s = 0; phase ^= 1; }
       }
     }
-  } else if (warp == 1 && lane == 0 && leader) {
+  } else if (warp == 1 && leader) {
     // ---------------------------------------------------------------- tensor-core issue (leader)
     constexpr uint32_t idesc = umma_idesc_pair(BN);
-    int it = 0, local = 0;
+    int s = 0, local = 0;
+    uint32_t phase = 0;
     bool ok = true;
     for (int tile = pair; tile < tiles && ok; tile += pairs, ++local) {
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
-      if (!mbar_wait(acc_empty + buf, acc_phase ^ 1)) { atomicExch(&g_gemm_error, 4); ok = false; break; }
+      if (!mbar_wait_warp(acc_empty + buf, acc_phase ^ 1)) { atomicExch(&g_gemm_error, 4); ok = false; break; }
       tcgen05_fence_after();
       const uint32_t tmem_d = tmem_base + buf * BN;
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t phase = (it / STAGES) & 1;
-        if (!mbar_wait(full + s, phase)) { atomicExch(&g_gemm_error, 2); ok = false; break; }
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait_warp(full + s, phase)) { atomicExch(&g_gemm_error, 2); ok = false; break; }
         tcgen05_fence_after();
         const uint32_t a_addr = smem_addr(smem + s * STAGE_BYTES), b_addr = a_addr + ROW_BYTES;
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)
-          umma_bf16_pair(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, (kb | k) != 0);
-        umma_commit_pair(empty + s);
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16_pair(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, (kb | k) != 0);
+          umma_commit_pair(empty + s);
+        }
+        __syncwarp();
+        if (++s == STAGES) { s = 0; phase ^= 1; }
       }
-      umma_commit_pair(acc_full + buf);
+      if (elect_one()) umma_commit_pair(acc_full + buf);
+      __syncwarp();
     }
   } else if (warp >= 2) {
     // -------------------------------------------------------------------- epilogue (both CTAs)
@@ -629,47 +652,54 @@ gemm_tcgen05_streamk_kernel(const __grid_constant__ CUtensorMap map_rows, const 
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();                             // set-up above overlaps the kernel before; its results are read below
 
-  if (warp == 0 && lane == 0) {
+  if (warp == 0) {
     // ---------------------------------------------------------------- producer
-    int it = 0;
+    int s = 0;
+    uint32_t phase = 0;
     bool ok = true;
     plan.for_each_piece(cta, [&](int tile, int kb0, int kb1, int) {
       const int row0 = (tile % m_tiles) * BM, col0 = (tile / m_tiles) * BN;
-      for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t phase = (it / STAGES) & 1;
-        if (!mbar_wait(empty + s, phase ^ 1)) { atomicExch(&g_gemm_error, 1); ok = false; break; }
-        mbar_expect_tx(full + s, STAGE_BYTES);
+      for (int kb = kb0; kb < kb1 && ok; ++kb) {
+        if (!mbar_wait_warp(empty + s, phase ^ 1)) { atomicExch(&g_gemm_error, 1); ok = false; break; }
         unsigned char* stage = smem + s * STAGE_BYTES;
-        tma_load_2d(stage, &map_rows, full + s, kb * BK, row0);
-        tma_load_2d(stage + ROW_BYTES, &map_cols, full + s, kb * BK, col0);
+        if (elect_one()) {
+          mbar_expect_tx(full + s, STAGE_BYTES);
+          tma_load_2d(stage, &map_rows, full + s, kb * BK, row0);
+          tma_load_2d(stage + ROW_BYTES, &map_cols, full + s, kb * BK, col0);
+        }
+        __syncwarp();
+        if (++s == STAGES) { s = 0; phase ^= 1; }
       }
     });
-  } else if (warp == 1 && lane == 0) {
+  } else if (warp == 1) {
     // ---------------------------------------------------------------- tensor-core issue
     constexpr uint32_t idesc = umma_idesc(BN);
-    int it = 0, local = 0;
+    int s = 0, local = 0;
+    uint32_t phase = 0;
     bool ok = true;
     plan.for_each_piece(cta, [&](int, int kb0, int kb1, int) {
       if (!ok) return;
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       ++local;
-      if (!mbar_wait(acc_empty + buf, acc_phase ^ 1)) { atomicExch(&g_gemm_error, 4); ok = false; return; }
+      if (!mbar_wait_warp(acc_empty + buf, acc_phase ^ 1)) { atomicExch(&g_gemm_error, 4); ok = false; return; }
       tcgen05_fence_after();
       const uint32_t tmem_d = tmem_base + buf * BN;
-      for (int kb = kb0; kb < kb1; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t phase = (it / STAGES) & 1;
-        if (!mbar_wait(full + s, phase)) { atomicExch(&g_gemm_error, 2); ok = false; return; }
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait_warp(full + s, phase)) { atomicExch(&g_gemm_error, 2); ok = false; return; }
         tcgen05_fence_after();
         const uint32_t a_addr = smem_addr(smem + s * STAGE_BYTES), b_addr = a_addr + ROW_BYTES;
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)
-          umma_bf16(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, ((kb - kb0) | k) != 0);
-        umma_commit(empty + s);
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, ((kb - kb0) | k) != 0);
+          umma_commit(empty + s);
+        }
+        __syncwarp();
+        if (++s == STAGES) { s = 0; phase ^= 1; }
       }
-      umma_commit(acc_full + buf);
+      if (elect_one()) umma_commit(acc_full + buf);
+      __syncwarp();
     });
   } else if (warp >= 2) {
     // -------------------------------------------------------------------- epilogue
@@ -774,6 +804,210 @@ gemm_tcgen05_streamk_kernel(const __grid_constant__ CUtensorMap map_rows, const 
   }
 }
 
+// ------------------------------------------------------------------------ split-K
+// Products with so few tiles that one CTA per tile would leave most SMs without work (decoding
+// batches of 17 to 128 rows, short prompt portions).  A cluster of `splits` CTAs takes one
+// 128 x `bn` tile together, each a contiguous share of its K blocks, so that the weights stream
+// in through every SM.  Each CTA moves its accumulator from tensor memory into its own shared
+// memory (over the operand stages, which are done by then), the cluster meets at its barrier, and
+// every CTA finishes its share of the tile: 1/splits of the (row, 32-column) pieces, summed over
+// the CTAs' partial accumulators through distributed shared memory in the order of the K ranges.
+// The result depends on the shape of the product only.  The hardware starts the CTAs of a cluster
+// together, so no wait here depends on a CTA that has not started.  `bn` (a multiple of 32, at most
+// 256) and the number of stages are run-time values: the tile width is chosen so that tiles x splits
+// comes close to the number of SMs.
+__device__ __forceinline__ float4 load_cluster_float4(uint32_t cluster_address) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_address) : "memory");
+  return v;
+}
+
+template <bool SWIGLU, typename OutT>
+__global__ void __launch_bounds__(kThreads)
+gemm_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
+                           GemmParams p) {
+  constexpr uint32_t TMEM_COLS = 256;
+  const int bn = p.bn, stages = p.stages, splits = p.splits;
+  // The row operand's box holds a_rows <= 128 rows (a product with fewer rows brings in no more than it
+  // has); the MMA still reads 128 rows from the start of the stage, the rest of them being whatever
+  // follows in shared memory: those rows of the accumulator belong to no row of C and are never read.
+  const uint32_t ROW_BYTES = static_cast<uint32_t>(p.a_rows) * BK * 2;
+  const uint32_t stage_bytes = ROW_BYTES + static_cast<uint32_t>(bn) * BK * 2;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + stages * stage_bytes + BM * BK * 2);
+  uint64_t* empty = full + stages;
+  uint64_t* acc_full = empty + stages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (p.M + BM - 1) / BM;
+  const int tile = blockIdx.x / splits, part = static_cast<int>(cluster_rank());
+  const int row0 = (tile % m_tiles) * BM, col0 = (tile / m_tiles) * bn;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int kb0 = static_cast<int>(static_cast<long long>(num_kb) * part / splits);
+  const int kb1 = static_cast<int>(static_cast<long long>(num_kb) * (part + 1) / splits);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(acc_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int rows = min(BM, p.M - row0);
+  const int quarter = warp & 3;
+  const int row = quarter * 32 + lane;
+  bool ok = true;
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    // The weights do not depend on the kernel before this one: the first ring of weight tiles is asked
+    // for while that kernel is still finishing, the activations only after the wait.
+    const int ahead = min(stages, kb1 - kb0);
+    if (elect_one()) {
+      for (int i = 0; i < ahead; ++i) {
+        mbar_expect_tx(full + i, stage_bytes);
+        tma_load_2d(smem + i * stage_bytes + ROW_BYTES, &map_cols, full + i, (kb0 + i) * BK, col0);
+      }
+    }
+    __syncwarp();
+    pdl_wait();
+    if (elect_one()) {
+      for (int i = 0; i < ahead; ++i) tma_load_2d(smem + i * stage_bytes, &map_rows, full + i, (kb0 + i) * BK, row0);
+    }
+    __syncwarp();
+    uint32_t phase = ahead == stages ? 1 : 0;
+    for (int kb = kb0 + ahead, s = ahead == stages ? 0 : ahead; kb < kb1; ++kb) {
+      if (!mbar_wait_warp(empty + s, phase ^ 1)) { atomicExch(&g_gemm_error, 1); break; }
+      unsigned char* stage = smem + s * stage_bytes;
+      if (elect_one()) {
+        mbar_expect_tx(full + s, stage_bytes);
+        tma_load_2d(stage, &map_rows, full + s, kb * BK, row0);
+        tma_load_2d(stage + ROW_BYTES, &map_cols, full + s, kb * BK, col0);
+      }
+      __syncwarp();
+      if (++s == stages) { s = 0; phase ^= 1; }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- tensor-core issue
+    const uint32_t idesc = umma_idesc(bn);
+    uint32_t phase = 0;
+    for (int kb = kb0, s = 0; kb < kb1; ++kb) {
+      if (!mbar_wait_warp(full + s, phase)) { atomicExch(&g_gemm_error, 2); break; }
+      tcgen05_fence_after();
+      const uint32_t a_addr = smem_addr(smem + s * stage_bytes), b_addr = a_addr + ROW_BYTES;
+      if (elect_one()) {
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma_bf16(tmem_base, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc, ((kb - kb0) | k) != 0);
+        umma_commit(empty + s);
+      }
+      __syncwarp();
+      if (++s == stages) { s = 0; phase ^= 1; }
+    }
+    if (elect_one()) umma_commit(acc_full);
+    __syncwarp();
+  } else if (warp >= 2) {
+    // ---------------------------------------------- epilogue, first half: the accumulator leaves tensor memory
+    pdl_wait();                           // C and the bias may be the work of the kernel before
+    ok = kb1 > kb0 && mbar_wait(acc_full, 0);
+    if (!ok) atomicExch(&g_gemm_error, 3);
+    tcgen05_fence_after();
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    if (splits == 1) {
+      const int m = row0 + row;
+      OutT* crow = static_cast<OutT*>(p.c) + static_cast<size_t>(m) * p.ldc;
+      if (quarter * 32 < rows) {
+#pragma unroll 1
+        for (int c = 0; c < bn; c += 32) {
+          float v[32];
+          if (ok) {
+            tmem_load_32(taddr + c, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          }
+          if (m < p.M) finish_chunk<SWIGLU, OutT>(v, p, crow, col0 + c);
+        }
+      }
+    } else if (quarter * 32 < rows) {     // warps whose 32 rows all lie below the matrix have nothing to hand over
+      // 16-byte groups of four columns, the 128 rows of a group next to each other: no bank conflicts here,
+      // 512 contiguous bytes per warp for the CTA that reads them
+      float4* mine = reinterpret_cast<float4*>(smem);
+#pragma unroll 1
+      for (int c = 0; c < bn; c += 32) {
+        float v[32];
+        if (ok) {
+          tmem_load_32(taddr + c, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) mine[((c + j) >> 2) * BM + row] = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      }
+    }
+  }
+  if (splits > 1) {
+    __syncwarp();
+    cluster_sync_all();                   // every CTA's partial accumulator is in its shared memory
+    if (warp >= 2) {
+      const uint32_t base = smem_addr(smem);
+      const int pieces = rows * (bn / 32);
+      const int begin = static_cast<int>(static_cast<long long>(pieces) * part / splits);
+      const int end = static_cast<int>(static_cast<long long>(pieces) * (part + 1) / splits);
+#pragma unroll 1
+      for (int u = begin + static_cast<int>(threadIdx.x) - 64; u < end; u += 128) {
+        const int chunk = u / rows, r = u - chunk * rows;
+        const uint32_t offset = base + static_cast<uint32_t>((chunk * 8 * BM + r) * 16);
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0.f;
+#pragma unroll 1
+        for (int q = 0; q < splits; q += 4) {   // the loads of four CTAs' pieces are in flight together
+          float4 t[4][8];
+#pragma unroll
+          for (int h = 0; h < 4; ++h)
+            if (q + h < splits) {
+              const uint32_t remote = map_to_cta(offset, static_cast<uint32_t>(q + h));
+#pragma unroll
+              for (int j = 0; j < 8; ++j) t[h][j] = load_cluster_float4(remote + j * BM * 16);
+            }
+#pragma unroll
+          for (int h = 0; h < 4; ++h)
+            if (q + h < splits) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                v[4 * j] += t[h][j].x; v[4 * j + 1] += t[h][j].y; v[4 * j + 2] += t[h][j].z; v[4 * j + 3] += t[h][j].w;
+              }
+            }
+        }
+        const int m = row0 + r;
+        finish_chunk<SWIGLU, OutT>(v, p, static_cast<OutT*>(p.c) + static_cast<size_t>(m) * p.ldc, col0 + chunk * 32);
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();                   // nobody leaves while another CTA still reads its shared memory
+  }
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------------ host side
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -848,6 +1082,65 @@ static int launch_streamk(const CUtensorMap& rows, const CUtensorMap& cols, cons
   return static_cast<int>(cudaGetLastError());
 }
 
+// Split-K: `splits` = 0 and `bn` = 0 ask for the choice made here.  The width is the one whose tiles,
+// times the largest cluster that still fits, come closest to filling the SMs once (wider on a tie);
+// the choice depends on N and K only, so a row's result does not depend on how many rows came along.
+static int splitk_cluster(int tiles, int num_kb, int sm_count) {
+  int s = 1;                              // 1, 2 or 4: clusters of three or of eight such CTAs rarely find room (two to three times slower)
+  while (s < 4 && tiles * s * 2 <= sm_count && s * 2 <= num_kb) s *= 2;
+  return s;
+}
+static void splitk_shape(int m_tiles, int N, int num_kb, int sm_count, int* bn, int* splits) {
+  if (*bn <= 0) {
+    double best = -1.;
+    for (int width = 256; width >= 96; width -= 32) {
+      const int tiles = m_tiles * ((N + width - 1) / width);
+      const long ctas = static_cast<long>(tiles) * splitk_cluster(tiles, num_kb, sm_count);
+      const long waves = (ctas + sm_count - 1) / sm_count;
+      const double fill = static_cast<double>(ctas) / static_cast<double>(waves * sm_count);
+      if (fill > best + 1e-9) { best = fill; *bn = width; }
+    }
+  }
+  if (*splits <= 0) *splits = splitk_cluster(m_tiles * ((N + *bn - 1) / *bn), num_kb, sm_count);
+}
+
+template <bool SWIGLU, typename OutT>
+static int launch_splitk(const CUtensorMap& rows, const CUtensorMap& cols, GemmParams p, cudaStream_t stream) {
+  constexpr size_t kRing = 196 * 1024;                 // operand stages in flight per SM
+  constexpr size_t kTail = BM * BK * 2 + 1024 + 512;   // what an MMA may read past a short row operand; alignment; barriers
+  auto kernel = gemm_tcgen05_splitk_kernel<SWIGLU, OutT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRing + kTail));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const size_t stage = static_cast<size_t>(p.a_rows + p.bn) * BK * 2;
+  if (p.stages <= 0) p.stages = static_cast<int>(kRing / stage);
+  if (p.stages > 16) p.stages = 16;
+  // the partial accumulator (bn x 128 floats) lies over the stages
+  if (p.stages < 2 || static_cast<size_t>(p.stages) * stage > kRing ||
+      (p.splits > 1 && static_cast<size_t>(p.stages) * stage + BM * BK * 2 < static_cast<size_t>(p.bn) * BM * 4))
+    return B200_ERR_BAD_SIZE;
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + p.bn - 1) / p.bn);
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(tiles * p.splits);
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = static_cast<size_t>(p.stages) * stage + kTail;
+  config.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = p.splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = pdl_enabled() ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, rows, cols, p);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+}
+
 template <int STAGES, bool SWIGLU, typename OutT>
 static int launch_pair(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, cudaStream_t stream) {
   constexpr size_t smem = STAGES * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256;
@@ -903,7 +1196,10 @@ extern "C" int b200_gemm_tcgen05_error() {
 //               C = silu(gate) * up with N / 2 columns (ldc >= N / 2)
 //   accumulate  float output without swiglu: C += A W^T + bias (the residual sum done where the product is)
 //   kind        0: one CTA per 128 x tile_n tile, persistent; 1: pairs of CTAs on 256 x 256 tiles
-//               (cta_group::2); 2: stream-K (left-over tiles shared between CTAs)
+//               (cta_group::2); 2: stream-K (left-over tiles shared between CTAs); 3: split-K (every
+//               128 x tile_n tile shared by a cluster of `splits` <= 8 CTAs; tile_n a multiple of 32 up to
+//               256; 0 for either: chosen from N and K so that the SMs are filled once; `stages`: depth of
+//               the operand ring, 0 = as deep as shared memory allows)
 //   tile_n      128 or 256 columns per tile (kind 0; the others take 256): narrower tiles put a product
 //               with few rows on more SMs
 //   partials, flags  stream-K only: b200_gemm_tcgen05_streamk_partial_floats() floats and
@@ -917,6 +1213,7 @@ static int launch_kind(const CUtensorMap& rows, const CUtensorMap& cols, const G
   constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);      // 192 KB of stages in every case
   if constexpr (KIND == 0) return launch_persistent<BN, STAGES, SWIGLU, OutT>(rows, cols, p, stream);
   else if constexpr (KIND == 1) return launch_pair<6, SWIGLU, OutT>(rows, cols, p, stream);
+  else if constexpr (KIND == 3) return launch_splitk<SWIGLU, OutT>(rows, cols, p, stream);
   else return launch_streamk<BN, STAGES, SWIGLU, OutT>(rows, cols, p, stream);
 }
 template <int KIND, int BN>
@@ -930,20 +1227,33 @@ static int launch_variant(const CUtensorMap& rows, const CUtensorMap& cols, cons
 }
 
 extern "C" int b200_gemm_tcgen05(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int ldc,
-                                 int out_f32, int swiglu, int accumulate, int kind, int tile_n, float* partials, unsigned* flags,
-                                 cudaStream_t stream) {
+                                 int out_f32, int swiglu, int accumulate, int kind, int tile_n, int splits, int stages,
+                                 float* partials, unsigned* flags, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 != 0 || ldc < (swiglu ? N / 2 : N) || (swiglu && N % 16 != 0) || kind < 0 || kind > 2) return B200_ERR_BAD_SIZE;
+  if (K <= 0 || K % 8 != 0 || ldc < (swiglu ? N / 2 : N) || (swiglu && N % 16 != 0) || kind < 0 || kind > 3) return B200_ERR_BAD_SIZE;
   if (kind == 1) tile_n = 256;
-  if (tile_n != 128 && tile_n != 256) return B200_ERR_BAD_SIZE;
+  if (kind != 3 && tile_n != 128 && tile_n != 256) return B200_ERR_BAD_SIZE;
   if (accumulate && (!out_f32 || swiglu)) return B200_ERR_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return B200_ERR_BAD_SIZE;
   if (kind == 2 && (!partials || !flags || (reinterpret_cast<uintptr_t>(partials) & 15))) return 10004;
-  GemmParams p{C, bias, M, N, K, ldc, (ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0, accumulate, partials, flags};
+  GemmParams p{C, bias, M, N, K, ldc, (ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0, accumulate, partials, flags, splits, BM, tile_n, 0};
   CUtensorMap rows, cols;
   if (int e = make_map(&rows, A, M, K, BM)) return e;
-  if (int e = make_map(&cols, W, N, K, kind == 1 ? 128 : tile_n)) return e;
+  if (kind != 3)
+    if (int e = make_map(&cols, W, N, K, kind == 1 ? 128 : tile_n)) return e;
   if (kind == 1) return launch_variant<1, 256>(rows, cols, p, out_f32, swiglu, stream);
+  if (kind == 3) {
+    int device = 0, sm_count = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+    splitk_shape((M + BM - 1) / BM, N, (K + BK - 1) / BK, sm_count, &p.bn, &p.splits);
+    if (p.bn % 32 || p.bn < 32 || p.bn > 256 || p.splits < 1 || p.splits > 8 || p.splits > (K + BK - 1) / BK) return B200_ERR_BAD_SIZE;
+    p.a_rows = M >= BM ? BM : (M + 7) / 8 * 8;
+    p.stages = stages;
+    if (int e = make_map(&rows, A, M, K, p.a_rows)) return e;
+    if (int e = make_map(&cols, W, N, K, p.bn)) return e;
+    return launch_variant<3, 256>(rows, cols, p, out_f32, swiglu, stream);
+  }
   if (kind == 2) {                       // stream-K is built for 256 columns
     if (tile_n != 256) return B200_ERR_BAD_SIZE;
     return launch_variant<2, 256>(rows, cols, p, out_f32, swiglu, stream);

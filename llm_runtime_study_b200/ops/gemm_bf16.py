@@ -14,7 +14,7 @@ native.register_library(
     "b200_gemm_tcgen05", ("gemm_tcgen05.cu",),
     {
         "b200_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                              c_int, c_void_p, c_void_p, c_void_p],
+                              c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "b200_gemm_tcgen05_error": [],
         "b200_gemm_tcgen05_streamk_partial_floats": [],
         "b200_gemm_tcgen05_streamk_flags": [],
@@ -33,7 +33,7 @@ PAIR_MIN_ROWS = 256   # from here on pairs of SMs work on 256 x 256 tiles (tcgen
 PAIR_ENABLED = os.environ.get("LLM_RUNTIME_STUDY_B200_GEMM_PAIR", "1") != "0"
 SKINNY_M = 16         # up to here weights are streamed straight into mma.sync fragments
 _SM_COUNT = 148
-KERNELS = {"persistent": 0, "pair": 1, "streamk": 2}
+KERNELS = {"persistent": 0, "pair": 1, "streamk": 2, "splitk": 3}
 
 _STREAMK_WORKSPACE: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
 
@@ -62,16 +62,19 @@ def supported(m: int, n: int, k: int) -> bool:
 def pick_kernel(m: int, n: int, k: int) -> tuple[str, int]:
     """Which kernel and which tile width take a product of this shape (chosen from timings at the
     Qwen3-8B layer widths with 128 to 4,096 rows).  Pairs of SMs on 256 x 256 tiles when those fill
-    most of the 74 pairs; one CTA per 128 x 256 tile when those cover half the SMs or more; stream-K
-    when a third of the SMs or fewer would have a tile and the K range is long enough to share;
-    else one CTA per 128 x 128 tile.  What bounds a product with few tiles is how fast one SM can
-    pull its operands in (about 120 GB/s), so it pays to spread the bytes over more SMs."""
+    most of the 74 pairs; one CTA per 128 x 256 tile when those cover half the SMs or more; up to
+    256 rows and a third of the SMs: clusters that share a tile's K range (split-K, which chooses
+    its own width); stream-K when a third of the SMs or fewer would have a tile and the K range is
+    long enough to share; else one CTA per 128 x 128 tile.  A product with few tiles is as slow as
+    the SM that has most to pull in, so it pays to spread the bytes over more SMs."""
 
     if m >= PAIR_MIN_ROWS and PAIR_ENABLED and -(-m // 256) * -(-n // 256) >= 60:
         return "pair", 256
     tiles = -(-m // 128) * -(-n // 256)
     if 2 * tiles >= _SM_COUNT:
         return "persistent", 256
+    if m <= 256 and 3 * tiles <= _SM_COUNT:
+        return "splitk", 0
     if 3 * tiles <= _SM_COUNT + 2 and k >= 48 * 64:
         return "streamk", 256
     return "persistent", 128
@@ -79,15 +82,18 @@ def pick_kernel(m: int, n: int, k: int) -> tuple[str, int]:
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
            out_dtype: torch.dtype = torch.bfloat16, *, swiglu: bool = False, add_to: torch.Tensor | None = None,
-           kernel: str | None = None, tile_n: int | None = None) -> torch.Tensor:
+           kernel: str | None = None, tile_n: int | None = None, splits: int = 0, stages: int = 0) -> torch.Tensor:
     """``x @ weight.T (+ bias)`` on the tcgen05 tensor cores; float32 accumulation; bfloat16 or
     float32 output.
 
     ``swiglu``: the weight holds gate and up rows interleaved in blocks of eight and the result is
     ``silu(gate) * up``, half as wide.  ``add_to`` (float32 ``[M, N]``): the product is added to it
     in place and it is returned.  ``kernel``: "persistent" (one CTA per tile of 128 rows and
-    ``tile_n`` = 128 or 256 columns), "pair" (two CTAs per 256 x 256 tile) or "streamk" (few
-    tiles: up to three SMs share a tile's K range); both chosen by shape when not given."""
+    ``tile_n`` = 128 or 256 columns), "pair" (two CTAs per 256 x 256 tile), "streamk" (few
+    tiles: up to three SMs share a tile's K range) or "splitk" (few rows: a cluster of ``splits``
+    <= 8 CTAs shares the K range of every 128 x ``tile_n`` tile, ``tile_n`` a multiple of 32; 0 for either
+    lets the kernel choose so that the SMs are filled once; ``stages``: depth of its operand ring, 0 = as
+    deep as shared memory allows); chosen by shape when not given."""
 
     native.require(x, "x", dtype=torch.bfloat16, dims=2)
     native.require(weight, "weight", dtype=torch.bfloat16, dims=2)
@@ -110,14 +116,19 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
         out = torch.empty((m, n // 2 if swiglu else n), dtype=out_dtype, device=x.device)
     picked_kernel, picked_width = pick_kernel(m, n, k)
     kernel = kernel or picked_kernel
-    tile_n = tile_n or (picked_width if kernel == picked_kernel else 256)
-    if kernel not in KERNELS or tile_n not in (128, 256) or (tile_n == 128 and kernel != "persistent"):
-        raise KernelError(f"unknown projection kernel {kernel!r} or tile width {tile_n}: expected one of {sorted(KERNELS)}, "
-                          "256 columns, or 128 with the persistent kernel")
+    if kernel == "splitk":
+        tile_n = tile_n or 0                        # 0: the kernel chooses
+        if tile_n % 32 or not 0 <= tile_n <= 256 or not 0 <= splits <= 8:
+            raise KernelError(f"split-K takes tiles of 32 to 256 columns in steps of 32 and up to 8 CTAs per tile, got {tile_n}, {splits}")
+    else:
+        tile_n = tile_n or (picked_width if kernel == picked_kernel else 256)
+        if kernel not in KERNELS or tile_n not in (128, 256) or (tile_n == 128 and kernel != "persistent"):
+            raise KernelError(f"unknown projection kernel {kernel!r} or tile width {tile_n}: expected one of {sorted(KERNELS)}, "
+                              "256 columns, or 128 with the persistent kernel")
     partials, flags = _streamk_workspace(x.device) if kernel == "streamk" else (None, None)
     native.call("b200_gemm_tcgen05", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k,
                 out.shape[1], 1 if out_dtype == torch.float32 else 0, 1 if swiglu else 0, 0 if add_to is None else 1,
-                KERNELS[kernel], tile_n, native.ptr(partials), native.ptr(flags), native.stream_ptr())
+                KERNELS[kernel], tile_n, splits, stages, native.ptr(partials), native.ptr(flags), native.stream_ptr())
     return out
 
 
@@ -126,8 +137,10 @@ def check_error() -> None:
 
     code = native.query("b200_gemm_tcgen05_error")
     if code:
-        where = {1: "producer", 2: "tensor-core issue", 3: "epilogue", 4: "accumulator buffer", 5: "stream-K flag",
+        where = {1: "producer", 2: "tensor-core issue", 3: "epilogue", 4: "accumulator buffer", 5: "flag of a shared tile",
                  -1: "device error"}.get(code, str(code))
+        for _, flags in _STREAMK_WORKSPACE.values():     # a wait that ran out may have left flags behind
+            flags.zero_()
         raise KernelError(f"tcgen05 projection: a bounded wait ran out ({where})")
 
 

@@ -29,6 +29,7 @@ class Projection:
 
     GEMM_BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_GEMM", "tcgen05")
     TCGEN05_MIN_ROWS = 128
+    MID_ROWS = os.environ.get("LLM_RUNTIME_STUDY_B200_GEMM_MID", "library")     # 17 to 127 rows: "library" or "splitk"
     FUSE_RESIDUAL = os.environ.get("LLM_RUNTIME_STUDY_B200_FUSE_RESIDUAL", "1") != "0"
 
     def __init__(self, weights: list[torch.Tensor], biases: list[torch.Tensor] | None, runtime: Runtime) -> None:
@@ -53,6 +54,8 @@ class Projection:
                 return gemm_bf16.linear_skinny(x, self.weight, self.bias, torch.bfloat16, swiglu=True)
             if self.GEMM_BACKEND == "tcgen05" and m >= self.TCGEN05_MIN_ROWS:
                 return gemm_bf16.linear(x, self.weight, self.bias, torch.bfloat16, swiglu=True)
+            if self.GEMM_BACKEND == "tcgen05" and self.MID_ROWS == "splitk":
+                return gemm_bf16.linear(x, self.weight, self.bias, torch.bfloat16, swiglu=True, kernel="splitk")
         return F.silu_mul_interleaved(self(x))
 
     def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, *,
@@ -79,6 +82,11 @@ class Projection:
                     gemm_bf16.linear(x, self.weight, self.bias, torch.float32, add_to=add_to)
                     return None
                 return gemm_bf16.linear(x, self.weight, self.bias, out_dtype)
+            if self.GEMM_BACKEND == "tcgen05" and self.MID_ROWS == "splitk":
+                if add_to is not None and out_dtype == torch.float32 and self.FUSE_RESIDUAL:
+                    gemm_bf16.linear(x, self.weight, self.bias, torch.float32, add_to=add_to, kernel="splitk")
+                    return None
+                return gemm_bf16.linear(x, self.weight, self.bias, out_dtype, kernel="splitk")
         if out_dtype == torch.bfloat16:
             y = torch.mm(x, self.weight.t())
         else:

@@ -9,8 +9,8 @@ def test_projection_kernel_choice_is_always_something_the_library_builds():
     for m, n, k in itertools.product((1, 17, 128, 129, 255, 256, 300, 512, 1000, 2048, 8192),
                                      (8, 264, 4096, 6144, 24576, 151936), (8, 72, 4096, 12288)):
         kernel, width = gemm_bf16.pick_kernel(m, n, k)
-        assert kernel in gemm_bf16.KERNELS and width in (128, 256)
-        assert width == 256 or kernel == "persistent"          # 128-column tiles exist for the one-CTA kernel only
+        assert kernel in gemm_bf16.KERNELS and width in (0, 128, 256)
+        assert width == 256 or kernel == ("splitk" if width == 0 else "persistent")   # split-K chooses its own width
         if kernel == "pair":
             assert m >= gemm_bf16.PAIR_MIN_ROWS
         if kernel == "streamk":
@@ -21,7 +21,8 @@ def test_projection_kernel_choice_at_the_benchmark_shapes():
     layer = ((6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288))
     assert all(gemm_bf16.pick_kernel(2048, n, k) == ("pair", 256) for n, k in layer)
     assert gemm_bf16.pick_kernel(512, 4096, 4096) == ("persistent", 128)
-    assert gemm_bf16.pick_kernel(256, 4096, 12288) == ("streamk", 256)
+    assert gemm_bf16.pick_kernel(256, 4096, 12288) == ("splitk", 0)
+    assert gemm_bf16.pick_kernel(384, 4096, 12288) == ("streamk", 256)
 
 
 def test_decode_parts_are_bounded_and_use_the_gpu():

@@ -486,6 +486,53 @@ def test_tcgen05_stream_k_projection(m, n, k, bias, out):
 
 
 @pytest.mark.parametrize("m,n,k,bias", [
+    (17, 520, 328, True), (64, 4096, 4096, False), (100, 6144, 4096, True), (128, 4096, 12288, False), (24, 264, 72, True),
+    (300, 1000, 4096, True), (1, 8, 8, True), (127, 24576, 512, False), (256, 4096, 4096, False), (40, 151936, 64, False),
+])
+@pytest.mark.parametrize("out", [torch.float32, torch.bfloat16])
+def test_tcgen05_split_k_projection(m, n, k, bias, out):
+    """Clusters of CTAs that share a tile's K range and add their parts through distributed shared
+    memory: the shape the kernel chooses by itself, then every cluster size and several tile widths
+    and ring depths, row counts below a full tile (short row boxes) and above one."""
+
+    x, w, b, want = _gemm_case(m, n, k, bias)
+    args = (dev(x), dev(w), dev(b) if bias else None, out)
+    scale = float(want.abs().max())
+    blocks = -(-k // 64)
+    got = _gemm().linear(*args, kernel="splitk")
+    again = _gemm().linear(*args, kernel="splitk")
+    _gemm().check_error()
+    torch.testing.assert_close(got.cpu().double(), want, atol=(1e-2 if out == torch.bfloat16 else 2e-5) * scale, rtol=0)
+    assert torch.equal(got, again)                                     # parts are added in the order of the K ranges
+    for tile_n, splits, stages in ((256, 1, 0), (128, 2, 3), (96, 3, 0), (32, 4, 0), (160, 4, 3), (64, 8, 0)):
+        if splits > blocks or -(-m // 128) * -(-n // tile_n) * splits > 4096:
+            continue
+        other = _gemm().linear(*args, kernel="splitk", tile_n=tile_n, splits=splits, stages=stages)
+        _gemm().check_error()
+        torch.testing.assert_close(other.cpu().double(), want, atol=(1e-2 if out == torch.bfloat16 else 2e-5) * scale, rtol=0)
+
+
+def test_tcgen05_split_k_rows_do_not_depend_on_their_company():
+    """The tile shape is chosen from the widths only, so a row gives the same bits alone and among 127."""
+
+    x, w, _, _ = _gemm_case(128, 1000, 4096, False)
+    whole = _gemm().linear(dev(x), dev(w), None, torch.float32, kernel="splitk")
+    for rows in (1, 17, 64, 100):
+        part = _gemm().linear(dev(x[:rows].contiguous()), dev(w), None, torch.float32, kernel="splitk")
+        assert torch.equal(part, whole[:rows])
+    _gemm().check_error()
+
+
+def test_tcgen05_split_k_refuses_what_it_cannot_take():
+    from llm_runtime_study_b200.errors import KernelError
+
+    x, w = torch.zeros(32, 128, device="cuda").bfloat16(), torch.zeros(64, 128, device="cuda").bfloat16()
+    for kwargs in ({"tile_n": 48}, {"tile_n": 288}, {"splits": 9}, {"splits": 4}, {"tile_n": 256, "splits": 2, "stages": 1}):
+        with pytest.raises(KernelError):                              # 48, 288: no such width; 9: no such cluster; 4: only two K blocks; one stage
+            _gemm().linear(x, w, kernel="splitk", **kwargs)
+
+
+@pytest.mark.parametrize("m,n,k,bias", [
     (256, 256, 64, False), (130, 264, 72, True), (300, 1000, 520, True), (2048, 1024, 4096, False), (5000, 4096, 512, True),
     (257, 24, 12288, True), (640, 520, 8, False), (1, 8, 8, True), (2048, 4096, 12288, False), (4096, 6144, 4096, False),
 ])
@@ -517,14 +564,15 @@ def test_tcgen05_adds_to_the_residual(m, n, k, kernel):
     assert torch.equal(out, dev(resid) + delta)
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 1000, 520), (2048, 4096, 4096)])
-def test_tcgen05_stream_k_adds_to_the_residual(m, n, k):
+@pytest.mark.parametrize("kernel", ["streamk", "splitk"])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 1000, 520), (2048, 4096, 4096), (40, 520, 4096)])
+def test_tcgen05_shared_tiles_add_to_the_residual(m, n, k, kernel):
     x, w, b, want = _gemm_case(m, n, k, True)
     torch.manual_seed(3)
     resid = torch.randn(m, n)
     target = dev(resid.clone())
-    delta = _gemm().linear(dev(x), dev(w), dev(b), torch.float32, kernel="streamk")
-    out = _gemm().linear(dev(x), dev(w), dev(b), add_to=target, kernel="streamk")
+    delta = _gemm().linear(dev(x), dev(w), dev(b), torch.float32, kernel=kernel)
+    out = _gemm().linear(dev(x), dev(w), dev(b), add_to=target, kernel=kernel)
     _gemm().check_error()
     assert out.data_ptr() == target.data_ptr()
     assert torch.equal(out, dev(resid) + delta)                       # the same single float32 addition
@@ -609,7 +657,7 @@ def test_projection_with_swiglu_epilogue(m, inter, k):
     else:
         got = _gemm().linear(dev(x), w, None, torch.bfloat16, swiglu=True, kernel="persistent")
         _gemm().check_error()
-        for kernel in ("streamk", "pair"):
+        for kernel in ("streamk", "pair", "splitk"):
             other = _gemm().linear(dev(x), w, None, torch.bfloat16, swiglu=True, kernel=kernel)
             _gemm().check_error()
             torch.testing.assert_close(other.cpu().double(), want, atol=2e-2 * float(want.abs().max()), rtol=0)
