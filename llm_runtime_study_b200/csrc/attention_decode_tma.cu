@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
     const int slot = p.page_shift >= 0 ? t0 & (p.page_size - 1) : t0 % p.page_size;
     return page < 0 ? -1 : (page * p.nkv + kvh) * p.page_size + slot;
   };
-  auto issue = [&](int i, int page) {         // lane 0: ask for the K and V rows of this warp's i-th block
+  auto issue = [&](int i, int page) {         // one lane: ask for the K and V rows of this warp's i-th block
     const int row = row_of(i, page);
     unsigned char* stage = ring + (i % DEPTH) * STAGE_BYTES;
     uint64_t* bar = &full[i % DEPTH];
@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
   auto start = [&](int i) {                   // all lanes
     const int page = page_of(i);
     valid = (valid & ~(1u << (i % DEPTH))) | (page >= 0 ? 1u << (i % DEPTH) : 0u);
-    if (lane == 0) issue(i, page);
+    if (elect_one()) issue(i, page);          // one lane, but from a converged warp: operands stay in uniform registers
   };
   while (issued < my_count && issued < DEPTH && !(newest_here && warp + WARPS * issued == newest_block)) start(issued++);
   pdl_wait();
