@@ -19,10 +19,12 @@ class Projection:
     float32 runtime: our FFMA kernel.  bfloat16 runtime, float32 accumulation,
     bfloat16 or float32 output:
       * up to 16 rows (decoding): our weight-streaming mma.sync kernel;
-      * 128 rows and more (prompts): our persistent tcgen05/TMEM/TMA kernel;
+      * 128 rows and more (prompts): our tcgen05/TMEM/TMA kernels;
       * in between, and everywhere when ``LLM_RUNTIME_STUDY_B200_GEMM=library``: a
         library product (the reference's projections are ``nn.Linear``, i.e. library
-        products: mini_llm/nn/attention.py:102-111).
+        products: mini_llm/nn/attention.py:102-111), which is the faster one there;
+        ``LLM_RUNTIME_STUDY_B200_GEMM_MID=splitk`` sends these row counts to our cluster
+        split-K kernel instead.
     K must be a multiple of 8 for our bfloat16 kernels (16-byte rows); other
     widths go to the library product.
     """
