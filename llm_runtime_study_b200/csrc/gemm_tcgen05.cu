@@ -18,7 +18,6 @@
 // error code, stops issuing work, frees its TMEM and returns.
 #include <cuda.h>
 
-#include <cstdlib>
 #include "common.cuh"
 #include "mma.cuh"
 
