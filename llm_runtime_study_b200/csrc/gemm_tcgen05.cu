@@ -1082,8 +1082,10 @@ static int launch_streamk(const CUtensorMap& rows, const CUtensorMap& cols, cons
 }
 
 // Split-K: `splits` = 0 and `bn` = 0 ask for the choice made here.  The width is the one whose tiles,
-// times the largest cluster that still fits, come closest to filling the SMs once (wider on a tie);
-// the choice depends on N and K only, so a row's result does not depend on how many rows came along.
+// times the largest cluster that still fits, fill the SMs best, weighed by how much of a stage is weights
+// (every CTA brings the activations in again beside its weight tile, so narrow tiles cost more traffic
+// per weight byte).  The choice depends on N and K only, so a row's result does not depend on how many
+// rows came along.
 static int splitk_cluster(int tiles, int num_kb, int sm_count) {
   int s = 1;                              // 1, 2 or 4: clusters of three or of eight such CTAs rarely find room (two to three times slower)
   while (s < 4 && tiles * s * 2 <= sm_count && s * 2 <= num_kb) s *= 2;
@@ -1097,7 +1099,8 @@ static void splitk_shape(int m_tiles, int N, int num_kb, int sm_count, int* bn, 
       const long ctas = static_cast<long>(tiles) * splitk_cluster(tiles, num_kb, sm_count);
       const long waves = (ctas + sm_count - 1) / sm_count;
       const double fill = static_cast<double>(ctas) / static_cast<double>(waves * sm_count);
-      if (fill > best + 1e-9) { best = fill; *bn = width; }
+      const double score = fill * width / (width + 64.);
+      if (score > best + 1e-9) { best = score; *bn = width; }
     }
   }
   if (*splits <= 0) *splits = splitk_cluster(m_tiles * ((N + *bn - 1) / *bn), num_kb, sm_count);

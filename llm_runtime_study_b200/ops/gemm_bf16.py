@@ -80,6 +80,20 @@ def pick_kernel(m: int, n: int, k: int) -> tuple[str, int]:
     return "persistent", 128
 
 
+# weight elements from which 9 to 16 rows go to the tcgen05 split-K kernel
+SKINNY_LARGE = int(os.environ.get("LLM_RUNTIME_STUDY_B200_SKINNY_LARGE", 52_000_000))
+
+
+def few_rows_kernel(m: int, n: int, k: int) -> str:
+    """"skinny" or "splitk" for at most ``SKINNY_M`` rows.  The weight-streaming kernel handles 9 to 16
+    rows as two token tiles per weight fragment and then reaches about 5 TB/s; the split-K kernel
+    streams at 6 TB/s but costs about 4 us more per launch, so it takes the products whose weights
+    are larger than about 100 MB (Qwen3-32B at 16 rows: 178 against 205 us per layer; Qwen3-8B
+    gate/up: 37 against 43 us), and the weight-streaming kernel the rest and everything up to 8 rows."""
+
+    return "splitk" if m > 8 and n * k >= SKINNY_LARGE else "skinny"
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
            out_dtype: torch.dtype = torch.bfloat16, *, swiglu: bool = False, add_to: torch.Tensor | None = None,
            kernel: str | None = None, tile_n: int | None = None, splits: int = 0, stages: int = 0) -> torch.Tensor:

@@ -18,7 +18,9 @@ class Projection:
 
     float32 runtime: our FFMA kernel.  bfloat16 runtime, float32 accumulation,
     bfloat16 or float32 output:
-      * up to 16 rows (decoding): our weight-streaming mma.sync kernel;
+      * up to 16 rows (decoding): our weight-streaming mma.sync kernel, or, for 9 to 16 rows
+        and weights of more than about 100 MB, our tcgen05 split-K kernel
+        (``gemm_bf16.few_rows_kernel``);
       * 128 rows and more (prompts): our tcgen05/TMEM/TMA kernels;
       * in between, and everywhere when ``LLM_RUNTIME_STUDY_B200_GEMM=library``: a
         library product (the reference's projections are ``nn.Linear``, i.e. library
@@ -53,6 +55,8 @@ class Projection:
         if self.runtime.dtype == torch.bfloat16 and self.in_features % 8 == 0 and x.is_contiguous():
             m = x.shape[0]
             if m <= gemm_bf16.SKINNY_M:
+                if self.GEMM_BACKEND == "tcgen05" and gemm_bf16.few_rows_kernel(m, self.out_features, self.in_features) == "splitk":
+                    return gemm_bf16.linear(x, self.weight, self.bias, torch.bfloat16, swiglu=True, kernel="splitk")
                 return gemm_bf16.linear_skinny(x, self.weight, self.bias, torch.bfloat16, swiglu=True)
             if self.GEMM_BACKEND == "tcgen05" and m >= self.TCGEN05_MIN_ROWS:
                 return gemm_bf16.linear(x, self.weight, self.bias, torch.bfloat16, swiglu=True)
@@ -78,6 +82,11 @@ class Projection:
         m = x.shape[0]
         if self.in_features % 8 == 0 and x.is_contiguous():
             if m <= gemm_bf16.SKINNY_M:
+                if self.GEMM_BACKEND == "tcgen05" and gemm_bf16.few_rows_kernel(m, self.out_features, self.in_features) == "splitk":
+                    if add_to is not None and out_dtype == torch.float32 and self.FUSE_RESIDUAL:
+                        gemm_bf16.linear(x, self.weight, self.bias, torch.float32, add_to=add_to, kernel="splitk")
+                        return None
+                    return gemm_bf16.linear(x, self.weight, self.bias, out_dtype, kernel="splitk")
                 return gemm_bf16.linear_skinny(x, self.weight, self.bias, out_dtype)
             if self.GEMM_BACKEND == "tcgen05" and m >= self.TCGEN05_MIN_ROWS:
                 if add_to is not None and out_dtype == torch.float32 and self.FUSE_RESIDUAL:

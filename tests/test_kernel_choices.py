@@ -42,3 +42,9 @@ def test_tile_map_orders_tiles_longest_first():
     assert count == 5 and sorted(r[0] for r in rows) == [0, 1, 1, 1, 2]
     assert rows[0] == [2, 75, 1] and rows[1] == [0, 0, 5]        # 900 keys, then 300, then the 70-token prompt's tiles
     assert [r[2] for r in rows if r[0] == 1] == [6, 32, 32]      # its last tile (6 tokens, 70 keys) before the earlier ones
+
+
+def test_few_rows_go_to_the_streaming_kernel_unless_the_weights_are_large():
+    assert all(gemm_bf16.few_rows_kernel(m, 24576, 4096) == "skinny" for m in (1, 8))
+    assert gemm_bf16.few_rows_kernel(16, 24576, 4096) == "splitk" and gemm_bf16.few_rows_kernel(9, 51200, 5120) == "splitk"
+    assert gemm_bf16.few_rows_kernel(16, 4096, 12288) == "skinny" and gemm_bf16.few_rows_kernel(16, 4096, 4096) == "skinny"
