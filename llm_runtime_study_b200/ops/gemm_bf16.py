@@ -89,9 +89,13 @@ def few_rows_kernel(m: int, n: int, k: int) -> str:
     rows as two token tiles per weight fragment and then reaches about 5 TB/s; the split-K kernel
     streams at 6 TB/s but costs about 4 us more per launch, so it takes the products whose weights
     are larger than about 100 MB (Qwen3-32B at 16 rows: 178 against 205 us per layer; Qwen3-8B
-    gate/up: 37 against 43 us), and the weight-streaming kernel the rest and everything up to 8 rows."""
+    gate/up: 37 against 43 us), and the weight-streaming kernel the rest.  Up to 8 rows the
+    weight-streaming kernel is as fast or faster except where few output rows meet a very long K
+    (the down projections of Qwen3-14B and 32B: 33.6 against 36.9 us, 47.0 against 52.9 us)."""
 
-    return "splitk" if m > 8 and n * k >= SKINNY_LARGE else "skinny"
+    if m > 8:
+        return "splitk" if n * k >= SKINNY_LARGE else "skinny"
+    return "splitk" if k >= 16384 and n * k >= SKINNY_LARGE else "skinny"
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,

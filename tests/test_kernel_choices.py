@@ -46,5 +46,6 @@ def test_tile_map_orders_tiles_longest_first():
 
 def test_few_rows_go_to_the_streaming_kernel_unless_the_weights_are_large():
     assert all(gemm_bf16.few_rows_kernel(m, 24576, 4096) == "skinny" for m in (1, 8))
+    assert gemm_bf16.few_rows_kernel(1, 5120, 25600) == "splitk" and gemm_bf16.few_rows_kernel(8, 4096, 12288) == "skinny"
     assert gemm_bf16.few_rows_kernel(16, 24576, 4096) == "splitk" and gemm_bf16.few_rows_kernel(9, 51200, 5120) == "splitk"
     assert gemm_bf16.few_rows_kernel(16, 4096, 12288) == "skinny" and gemm_bf16.few_rows_kernel(16, 4096, 4096) == "skinny"
