@@ -100,3 +100,39 @@ def test_real_sizes_under_every_cut(material, dtype):
             for rid in requests:
                 for p in rows[rid]:
                     assert torch.equal(results[0][rid][p], other[rid][p]), (rid, p)
+
+
+def test_twelve_rows_decode_through_the_split_k_projections(material):
+    """Twelve requests decoded together: 9 to 16 rows send the products with large weights (gate/up, the
+    output head) to the tcgen05 split-K kernel instead of the weight-streaming one; the logits still are
+    those of the plain model, and those of the same requests decoded six at a time."""
+
+    from llm_runtime_study_b200.engine.replay import TraceReplayer
+    from llm_runtime_study_b200.ops import gemm_bf16
+
+    assert gemm_bf16.few_rows_kernel(12, 2 * 12288, 4096) == "splitk" and gemm_bf16.few_rows_kernel(6, 2 * 12288, 4096) == "skinny"
+    loaded = material["loaded"]
+    rng = random.Random(11)
+    requests = {f"d{i}": helpers.random_tokens(rng, 151936, 3 + i % 5) for i in range(12)}
+    weights = {n: t.float() for n, t in loaded.weights.items()}
+    want = {rid: helpers.plain_logits(weights, QWEN3_8B_TWO_LAYERS, toks, dtype=torch.float32)[-1].double()
+            for rid, toks in requests.items()}
+
+    def last_logits(groups):
+        out = {}
+        for group in groups:
+            replayer = TraceReplayer(loaded, max_tokens=64 * len(group), page_size=16)
+            head = {"step": 0, "entries": [{"id": r, "tokens": requests[r][:-1], "want": []} for r in group], "end": []}
+            tail = {"step": 1, "entries": [{"id": r, "tokens": requests[r][-1:], "want": [0]} for r in group], "end": list(group)}
+            replayer.run_step(head)
+            rows = torch.from_numpy(np.array(replayer.run_step(tail)))
+            out.update({r: rows[i] for i, r in enumerate(group)})
+            replayer.runner.manager.check()
+        return out
+
+    ids = list(requests)
+    together, by_six = last_logits([ids]), last_logits([ids[:6], ids[6:]])
+    for rid in ids:
+        scale = float(want[rid].abs().max())
+        torch.testing.assert_close(together[rid].double(), want[rid], atol=6e-2 * scale, rtol=5e-2)
+        torch.testing.assert_close(together[rid].double(), by_six[rid].double(), atol=3e-2 * scale, rtol=3e-2)
