@@ -1210,6 +1210,16 @@ extern "C" int b200_gemm_tcgen05_error() {
 extern "C" long b200_gemm_tcgen05_streamk_partial_floats() { return static_cast<long>(kStreamKMaxCtas) * BM * 256; }
 extern "C" int b200_gemm_tcgen05_streamk_flags() { return kStreamKMaxCtas; }
 
+// The tile width and cluster size the split-K kernel chooses for a product of M x N x K on a GPU with
+// `sm_count` SMs (host arithmetic only: callable without a GPU).
+extern "C" int b200_gemm_tcgen05_splitk_shape(int M, int N, int K, int sm_count, int* tile_n, int* splits) {
+  if (M <= 0 || N <= 0 || K <= 0 || sm_count <= 0 || !tile_n || !splits) return B200_ERR_BAD_SIZE;
+  *tile_n = 0;
+  *splits = 0;
+  splitk_shape((M + BM - 1) / BM, N, (K + BK - 1) / BK, sm_count, tile_n, splits);
+  return 0;
+}
+
 template <int KIND, int BN, bool SWIGLU, typename OutT>
 static int launch_kind(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, cudaStream_t stream) {
   constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);      // 192 KB of stages in every case

@@ -16,6 +16,7 @@ native.register_library(
         "b200_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "b200_gemm_tcgen05_error": [],
+        "b200_gemm_tcgen05_splitk_shape": [c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "b200_gemm_tcgen05_streamk_partial_floats": [],
         "b200_gemm_tcgen05_streamk_flags": [],
     },
@@ -82,6 +83,16 @@ def pick_kernel(m: int, n: int, k: int) -> tuple[str, int]:
 
 # weight elements from which 9 to 16 rows go to the tcgen05 split-K kernel
 SKINNY_LARGE = int(os.environ.get("LLM_RUNTIME_STUDY_B200_SKINNY_LARGE", 52_000_000))
+
+
+def splitk_shape(m: int, n: int, k: int, sm_count: int = _SM_COUNT) -> tuple[int, int]:
+    """(tile width, CTAs per tile) the split-K kernel chooses by itself for this product."""
+
+    import ctypes
+
+    width, splits = ctypes.c_int(0), ctypes.c_int(0)
+    native.call("b200_gemm_tcgen05_splitk_shape", m, n, k, sm_count, ctypes.addressof(width), ctypes.addressof(splits), launches=0)
+    return width.value, splits.value
 
 
 def few_rows_kernel(m: int, n: int, k: int) -> str:

@@ -49,3 +49,19 @@ def test_few_rows_go_to_the_streaming_kernel_unless_the_weights_are_large():
     assert gemm_bf16.few_rows_kernel(1, 5120, 25600) == "splitk" and gemm_bf16.few_rows_kernel(8, 4096, 12288) == "skinny"
     assert gemm_bf16.few_rows_kernel(16, 24576, 4096) == "splitk" and gemm_bf16.few_rows_kernel(9, 51200, 5120) == "splitk"
     assert gemm_bf16.few_rows_kernel(16, 4096, 12288) == "skinny" and gemm_bf16.few_rows_kernel(16, 4096, 4096) == "skinny"
+
+
+def test_split_k_shape_fills_the_sms_and_keeps_tiles_wide():
+    """The width and cluster size the split-K kernel picks by itself (host arithmetic in the library)."""
+
+    shape = gemm_bf16.splitk_shape
+    assert shape(64, 4096, 4096) == (128, 4)           # 32 tiles x 4 = 128 CTAs on 148 SMs
+    assert shape(16, 24576, 4096) == (192, 1)          # 128 tiles, nothing to share
+    assert shape(16, 151936, 4096) == (224, 1)         # 679 tiles: 4.6 rounds of wide tiles, not 10.7 of narrow ones
+    assert shape(200, 4096, 12288) == (256, 4)         # two row tiles: 32 wide tiles x 4 rather than 64 narrow ones x 2
+    assert shape(8, 24, 64) == (256, 1)                # one K block cannot be shared
+    for n, k in ((5120, 25600), (10240, 5120), (1000, 520), (7168, 5120)):
+        width, splits = shape(16, n, k)
+        assert width % 32 == 0 and 96 <= width <= 256 and splits in (1, 2, 4)
+        assert -(-n // width) * splits <= 148 or splits == 1
+        assert shape(128, n, k) == (width, splits)     # the choice does not depend on the rows that came along
