@@ -3,9 +3,10 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
 One JSON line: ``value`` is decoded tokens per second at batch 8 with 2,048
-cached tokens per request (device time, CUDA events around K steps of the step
-function plus sampling); ``e2e`` is the same through the scheduler the Python
-entry point uses, host token ids in and out, by the wall clock; ``prefill`` is one
+cached tokens per request (device time, CUDA events around K decode steps as
+generation runs them: slot records in, drawn tokens out, ids copied to the host);
+``e2e`` is the same through the scheduler the Python entry point uses, host token
+ids in and out, by the wall clock (batch 1 and 64 under its ``points``); ``prefill`` is one
 2,048-token prompt; ``points`` holds decode at batch 1 and 64; ``roofline`` is the
 bytes a decode step must read (every weight once plus the live requests' cache)
 over its time.  Weights are random (N(0, 0.02); norms 1 + N(0, 0.05)) and token
@@ -118,10 +119,10 @@ def prefill_flops(cfg: dict, layers: int, tokens: int) -> float:
 def run_ours(args) -> dict:
     import torch
 
+    from llm_runtime_study_b200.cache.slots import SlotRecord
     from llm_runtime_study_b200.engine.engine import Engine
     from llm_runtime_study_b200.engine.step import StepEntry
     from llm_runtime_study_b200.ops import native
-    from llm_runtime_study_b200.sampling import SamplingConfig
 
     cfg = dict(QWEN3_8B)
     full_layers = cfg["num_hidden_layers"]
@@ -141,11 +142,11 @@ def run_ours(args) -> dict:
     engine = Engine.from_random_weights(
         cfg, seed=0, device="cuda:0", dtype="bfloat16", max_seq_len=cfg["max_position_embeddings"],
         max_batch_size=max_batch, page_size=PAGE_SIZE,
-        max_cache_tokens=max_batch * (context + args.steps + max(args.warmup, 3) + 2 * PAGE_SIZE),
+        max_cache_tokens=max_batch * (context + args.steps + max_batch + max(args.warmup, 3) + 2 * PAGE_SIZE),
         max_tokens_per_step=PREFILL_TOKENS, use_cuda_graph=True)
     runner, manager = engine.runner, engine.cache_manager
     sampler = engine._sampler
-    greedy = SamplingConfig()
+    greedy = SlotRecord(position=0)          # temperature 0: the largest logit
 
     def timed(fn, repeat):
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -160,8 +161,8 @@ def run_ours(args) -> dict:
     # ------------------------------------------------------------- prefill
     def one_prefill():
         request = manager.admit()
-        logits = runner.step([StepEntry(request, prompt, [PREFILL_TOKENS - 1])])
-        sampler.sample(logits, [(greedy, 0, 0)])
+        handle = runner.step_sampled([StepEntry(request, prompt, [PREFILL_TOKENS - 1], greedy)], sampler)
+        handle.tokens()
         manager.release(request)
 
     prompt = ids(PREFILL_TOKENS)
@@ -177,26 +178,31 @@ def run_ours(args) -> dict:
 
     # -------------------------------------------------------------- decode
     def decode_point(batch, steps, warmup, sample_clocks=False):
+        """The decode step as generation runs it: slot records in, drawn tokens out, replayed from
+        a CUDA graph, the drawn ids copied to pinned host memory after every step."""
+
         requests = [manager.admit() for _ in range(batch)]
         for request in requests:
             for at in range(0, context, PREFILL_TOKENS):
-                runner.step([StepEntry(request, ids(min(PREFILL_TOKENS, context - at)), [])])
-        tokens = [ids(1) for _ in range(batch)]
+                n = min(PREFILL_TOKENS, context - at)
+                last = at + n == context
+                runner.step_sampled([StepEntry(request, ids(n), [n - 1] if last else [], greedy if last else None)], sampler)
+        handles = []
 
         def one_step():
-            logits = runner.step([StepEntry(r, t, [0]) for r, t in zip(requests, tokens)])
-            out = sampler.sample(logits, [(greedy, 0, 0)] * batch)
-            for t, o in zip(tokens, out):
-                t[0] = o
+            handles.append(runner.decode_sampled(requests, sampler))
 
         for _ in range(max(warmup, 3)):
             one_step()
+        handles.pop().tokens()
+        handles.clear()
         clocks = ClockSampler() if sample_clocks else None
         mark = clocks.mark() if clocks else 0
         before = native.launch_count()
         ms = timed(one_step, steps)
         launches = native.launch_count() - before
         info = clocks.stop(mark) if clocks else None
+        handles[-1].tokens()
         for request in requests:
             manager.release(request)
         return ms, launches, info
@@ -210,26 +216,36 @@ def run_ours(args) -> dict:
     ms_b64, _, _ = decode_point(64, args.steps, args.warmup)
 
     # ------------------------------------- end to end through the scheduler
-    engine.max_batch_size = args.batch
-    scheduler = engine.create_scheduler()
-    scheduler.max_batch_size = args.batch
-    for _ in range(args.batch):
-        scheduler.add_request(ids(CONTEXT), max_new_tokens=1024)
-    while scheduler.num_waiting or any(r.prefilling for r in scheduler._running):
-        scheduler.step()
-    for _ in range(max(args.warmup, 3)):
-        scheduler.step()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    produced = 0
-    for _ in range(args.steps):
-        produced += len(scheduler.step())
-    torch.cuda.synchronize()
-    e2e_seconds = time.perf_counter() - t0
-    scheduler.abort_all()
-    graph = runner._graphs._graphs.get(runner._graphs.bucket(args.batch)) if runner._graphs else None
-    h2d = (graph.dev.numel() * 4 if graph else 0) + args.batch * 6 * 4
-    d2h = args.batch * 4
+    def end_to_end(batch):
+        """Tokens per second by the wall clock through the scheduler that ``Engine.generate`` drives:
+        requests in as host token ids, events with token ids out.  Every step copies its slots and block
+        tables from pinned host memory to the device and the drawn ids back into pinned host memory."""
+
+        engine.max_batch_size = batch
+        scheduler = engine.create_scheduler()
+        for _ in range(batch):
+            scheduler.add_request(ids(CONTEXT), max_new_tokens=1024)
+        while scheduler.num_waiting or any(r.prefilling for r in scheduler._running):
+            scheduler.step()
+        for _ in range(max(args.warmup, 3)):
+            scheduler.step()
+        graph = runner._graphs.graph_for(batch) if runner._graphs else None
+        if graph is not None:
+            graph.always_send = True          # copy the step's inputs every step, changed or not
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        produced = 0
+        for _ in range(args.steps):
+            produced += len(scheduler.step())
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+        scheduler.abort_all()
+        torch.cuda.synchronize()
+        return produced / seconds, (graph.sent * 4 if graph else 0), batch * 4
+
+    e2e_b8, h2d, d2h = end_to_end(args.batch)
+    e2e_b1, _, _ = end_to_end(1)
+    e2e_b64, _, _ = end_to_end(64)
 
     pk = peaks()
     step_bytes = model_bytes(cfg, layers) + args.batch * CONTEXT * kv_bytes_per_token(cfg, layers)
@@ -246,11 +262,11 @@ def run_ours(args) -> dict:
             "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
             "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
             "seq_len": CONTEXT, "context_limit": cfg["max_position_embeddings"], "page_size": PAGE_SIZE,
-            "parallelism": "none (1 GPU)", "cuda_graph": True, "sampling": "greedy, in the timed step",
+            "parallelism": "none (1 GPU)", "cuda_graph": True, "sampling": "greedy, inside the captured step",
             "l2": "inputs larger than L2 (16 GB of weights per step)", "peaks": pk["source"],
         },
-        "e2e": {"value": round(produced / e2e_seconds, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h},
+        "e2e": {"value": round(e2e_b8, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "points": {"decode_b1": round(e2e_b1, 1), "decode_b64": round(e2e_b64, 1)}},
         "gpu_launches": launches,
         "prefill": {"value": round(PREFILL_TOKENS / (prefill_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
                     "ms": round(prefill_ms, 3), "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},

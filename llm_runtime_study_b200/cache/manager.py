@@ -21,6 +21,7 @@ import torch
 from ..errors import KVCacheError
 from ..parts.base import FixedState, PagedKV
 from .pages import PageAllocator
+from .slots import SlotTable
 
 
 @dataclass(frozen=True)
@@ -126,10 +127,14 @@ class CacheManager:
                 dtype=dtype, device=self.device,
             ))
             self.allocators.append(PageAllocator(self.num_pages))
+        # Fixed-size state: one row per request slot and one more that belongs to nobody, for the rows that
+        # pad a batch up to the size of its captured graph (what a mixer writes there is never read).
+        self.padding_slot = max_requests
         self.state_arrays: dict[int, torch.Tensor] = {
-            s.layer: torch.zeros((max_requests, *s.requirement.shape), dtype=s.requirement.dtype, device=self.device)
+            s.layer: torch.zeros((max_requests + 1, *s.requirement.shape), dtype=s.requirement.dtype, device=self.device)
             for s in layout.states
         }
+        self.slots = SlotTable(max_requests, self.device)
         self._layer_group = {layer: (g, i) for g, group in enumerate(layout.groups) for i, layer in enumerate(group.layers)}
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self._active: dict[int, RequestCache] = {}
@@ -206,6 +211,12 @@ class CacheManager:
         need_total = -(-new_length // self.page_size)
         return max((max(0, need_total - len(t)) for t in request.tables), default=0)
 
+    def pages_held(self, request: RequestCache) -> int:
+        """Pages' worth of positions the request's block tables cover (the same in every
+        group: groups grow together; a page that a window has given back still counts)."""
+
+        return min((len(t) for t in request.tables), default=0)
+
     def can_grow(self, request: RequestCache, new_length: int) -> bool:
         if new_length > self.max_seq_len:
             return False
@@ -280,6 +291,7 @@ class CacheManager:
             table.clear()
         self._active.pop(request.id, None)
         self._free_slots.append(request.slot)
+        self.slots.clear(request.slot)
         request.length = 0
 
     def check(self) -> None:

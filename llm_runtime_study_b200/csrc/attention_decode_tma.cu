@@ -466,7 +466,6 @@ extern "C" int b200_attention_decode_tma(const void* q, const void* k_pool, cons
   p.part_o = scratch;
   p.part_ml = scratch + static_cast<long>(requests) * nq * num_splits * D;
   p.tickets = tickets;
-  constexpr int kMaxDevices = 64;
   static int* error_address[kMaxDevices] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return 10007;
@@ -477,12 +476,8 @@ extern "C" int b200_attention_decode_tma(const void* q, const void* k_pool, cons
   CUtensorMap kmap, vmap;
   if (int e = pool_map(k_pool, rows, &kmap)) return e;
   if (int e = pool_map(v_pool, rows, &vmap)) return e;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static DeviceOnce once;
+  if (int e = configure_once(once, decode_attention_tma_kernel, SMEM_BYTES)) return e;
   dim3 grid(num_splits, nkv * p.slices, requests);
   launch(decode_attention_tma_kernel, grid, dim3(128), SMEM_BYTES, stream, kmap, vmap, p);
   return launch_status();

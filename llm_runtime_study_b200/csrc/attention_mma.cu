@@ -673,12 +673,8 @@ extern "C" int b200_attention_prefill_bf16(const void* q, const void* k_pool, co
   p.tile_entry = tile_entry;
   p.tile_start = tile_start;
   p.tile_count = tile_count;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static DeviceOnce once;
+  if (int e = configure_once(once, prefill_attention_kernel<4>, kSmemBytes)) return e;
   dim3 grid(nkv * p.slices, num_tiles);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
   launch(prefill_attention_kernel<4>, dim3(grid), dim3(128), kSmemBytes, stream, p);
@@ -713,23 +709,15 @@ extern "C" int b200_attention_decode_bf16(const void* q, const void* k_pool, con
   if (!use_rows) {
     p.gs = p.group < kTGs ? p.group : kTGs;
     p.slices = (p.group + p.gs - 1) / p.gs;
-    static bool configured_t = false;
-    if (!configured_t) {
-      cudaError_t e = cudaFuncSetAttribute(decode_attention_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmemBytes);
-      if (e != cudaSuccess) return static_cast<int>(e);
-      configured_t = true;
-    }
+    static DeviceOnce once_t;
+    if (int e = configure_once(once_t, decode_attention_t_kernel, kTSmemBytes)) return e;
     dim3 tgrid(num_splits, nkv * p.slices, requests);
     launch(decode_attention_t_kernel, tgrid, dim3(128), kTSmemBytes, stream, p);
   } else
 #endif
   {
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-      if (e != cudaSuccess) return static_cast<int>(e);
-      configured = true;
-    }
+    static DeviceOnce once;
+    if (int e = configure_once(once, decode_attention_kernel, kSmemBytes)) return e;
     dim3 grid(num_splits, nkv * p.slices, requests);
     launch(decode_attention_kernel, dim3(grid), dim3(128), kSmemBytes, stream, p);
   }

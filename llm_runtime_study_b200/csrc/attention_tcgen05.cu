@@ -417,13 +417,8 @@ extern "C" int b200_attention_prefill_tcgen05(const void* q, const void* k_pool,
   if (int e = make_map_2d(&map_v, v_pool, pool_rows, D, page_size)) return e;
 
   constexpr size_t smem = SMEM_TILES + 256;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static DeviceOnce once;
+  if (int e = configure_once(once, prefill_attention_tcgen05_kernel, smem)) return e;
   dim3 grid(nkv * p.slices, num_tiles);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
   launch(prefill_attention_tcgen05_kernel, grid, dim3(kTcThreads), smem, stream, map_q, map_k, map_v, p);

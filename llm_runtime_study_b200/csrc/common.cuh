@@ -142,6 +142,31 @@ inline void launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem
   cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 
+// The opt-in to more than 48 KB of dynamic shared memory is an attribute of (kernel, device), and the
+// number of SMs is the device's: a launcher keeps one of these per kernel and sets a device up the
+// first time it launches there, whichever device is current.
+constexpr int kMaxDevices = 64;
+struct DeviceOnce {
+  bool done[kMaxDevices] = {};
+  int sm_count[kMaxDevices] = {};
+};
+// 0, or a cudaError_t / 10007 (device index out of range); *sm_count receives the current device's SM count.
+template <typename Kernel>
+inline int configure_once(DeviceOnce& once, Kernel kernel, size_t smem_bytes, int* sm_count = nullptr) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return 10007;
+  if (!once.done[device]) {
+    if (smem_bytes > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    if (cudaDeviceGetAttribute(&once.sm_count[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 10007;
+    once.done[device] = true;
+  }
+  if (sm_count) *sm_count = once.sm_count[device];
+  return 0;
+}
+
 }  // namespace b200
 
 // Error codes of our own, above the CUDA range, for refused sizes.

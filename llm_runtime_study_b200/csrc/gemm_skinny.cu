@@ -167,7 +167,10 @@ extern "C" int b200_gemm_skinny_variant(const void* X, const void* W, const floa
     // instead of two: that pays when it lets all CTAs be resident at once (measured on the
     // 6144 x 4096 projection: 13.2 -> 10.4 us), and costs otherwise.
     const int ctas = (N + 15) / 16;
-    if (ctas > 2 * 148 && ctas <= 3 * 148) variant = 2;
+    static DeviceOnce once;
+    int sms = 0;
+    if (int e = configure_once(once, gemm_skinny_kernel<1, 8, 8, false, float>, 0, &sms)) return e;
+    if (ctas > 2 * sms && ctas <= 3 * sms) variant = 2;
   }
   if (M <= 8) {
     switch (variant) {

@@ -1042,16 +1042,9 @@ template <int BN, int STAGES, bool SWIGLU, typename OutT>
 static int launch_persistent(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, cudaStream_t stream) {
   constexpr size_t smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
   auto kernel = gemm_tcgen05_persistent_kernel<BN, STAGES, SWIGLU, OutT>;
-  static bool configured = false;
-  static int sm_count = 0;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    int device = 0;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-    configured = true;
-  }
+  static b200::DeviceOnce once;
+  int sm_count = 0;
+  if (int e = b200::configure_once(once, kernel, smem, &sm_count)) return e;
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count ? tiles : sm_count;
   b200::launch(kernel, dim3(grid), dim3(kThreads), smem, stream, rows, cols, p);
@@ -1062,16 +1055,9 @@ template <int BN, int STAGES, bool SWIGLU, typename OutT>
 static int launch_streamk(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, cudaStream_t stream) {
   constexpr size_t smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
   auto kernel = gemm_tcgen05_streamk_kernel<BN, STAGES, SWIGLU, OutT>;
-  static bool configured = false;
-  static int sm_count = 0;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    int device = 0;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-    configured = true;
-  }
+  static b200::DeviceOnce once;
+  int sm_count = 0;
+  if (int e = b200::configure_once(once, kernel, smem, &sm_count)) return e;
   const long long units = static_cast<long long>((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * ((p.K + BK - 1) / BK);
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   int grid = sm_count < kStreamKMaxCtas ? sm_count : kStreamKMaxCtas;
@@ -1111,12 +1097,8 @@ static int launch_splitk(const CUtensorMap& rows, const CUtensorMap& cols, GemmP
   constexpr size_t kRing = 196 * 1024;                 // operand stages in flight per SM
   constexpr size_t kTail = BM * BK * 2 + 1024 + 512;   // what an MMA may read past a short row operand; alignment; barriers
   auto kernel = gemm_tcgen05_splitk_kernel<SWIGLU, OutT>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRing + kTail));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static b200::DeviceOnce once;
+  if (int e = b200::configure_once(once, kernel, kRing + kTail)) return e;
   const size_t stage = static_cast<size_t>(p.a_rows + p.bn) * BK * 2;
   if (p.stages <= 0) p.stages = static_cast<int>(kRing / stage);
   if (p.stages > 16) p.stages = 16;
@@ -1147,16 +1129,9 @@ template <int STAGES, bool SWIGLU, typename OutT>
 static int launch_pair(const CUtensorMap& rows, const CUtensorMap& cols, const GemmParams& p, cudaStream_t stream) {
   constexpr size_t smem = STAGES * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256;
   auto kernel = gemm_tcgen05_pair_kernel<STAGES, SWIGLU, OutT>;
-  static bool configured = false;
-  static int sm_count = 0;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    int device = 0;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-    configured = true;
-  }
+  static b200::DeviceOnce once;
+  int sm_count = 0;
+  if (int e = b200::configure_once(once, kernel, smem, &sm_count)) return e;
   const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
   int pairs = sm_count / 2;
   if (tiles < pairs) pairs = tiles;

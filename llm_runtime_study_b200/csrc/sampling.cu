@@ -13,9 +13,34 @@
 // bits a pass (fifteen candidate thresholds are counted at once), which needs no sort and
 // no scratch memory; the passes over the row use 16-byte loads, two in flight per thread.
 // Every sum is taken in an order fixed by the launch shape: the same bits every run.
+//
+// The per-row parameters are six words [temperature bits, top_k, top_p bits, seed low, seed high,
+// counter].  They come either as an array [rows][6], or out of the per-request slot records on the
+// device (slots.cu): then `row_slots[row]` names the record, and the kernel that settles a row also
+// writes the chosen token and the advanced counter back into it, so that the next decode step and
+// the next draw need nothing from the host.
 #include "common.cuh"
+#include "slots.h"
 
 namespace b200 {
+
+constexpr int kParamWords = 6;   // per row: [temperature bits, top_k, top_p bits, seed low, seed high, counter]
+
+// Where a row's six parameter words are, and (slot records only) where its result goes.
+struct RowParams {
+  int* base;              // [rows][6], or the slot table
+  const int* row_slots;   // nullptr: row i uses base + 6 i; else base + kSlotWords * row_slots[i] + kSlotSampling
+  __device__ __forceinline__ const int* of(int row) const {
+    return row_slots ? base + static_cast<size_t>(row_slots[row]) * kSlotWords + kSlotSampling : base + row * kParamWords;
+  }
+  // The draw for this row is settled: remember it in the request's record and advance its counter.
+  __device__ __forceinline__ void settle(int row, int token, int counter) const {
+    if (!row_slots) return;
+    int* rec = base + static_cast<size_t>(row_slots[row]) * kSlotWords;
+    rec[kSlotLastToken] = token;
+    rec[kSlotCounter] = counter + 1;
+  }
+};
 
 __device__ __forceinline__ uint32_t ordered_key(float x) {
   const uint32_t b = __float_as_uint(x);
@@ -216,13 +241,10 @@ __device__ ArgMax block_argmax(ArgMax v, ArgMax* scratch) {
   return t;  // every thread holds the result
 }
 
-// params per row: [temperature bits, top_k, top_p bits, seed lo, seed hi, counter]
-constexpr int kParamWords = 6;
-
 // One cluster of CTAs per row (gridDim.x = rows * cluster size): each CTA scans its slice of the row and
 // the CTAs combine their results through distributed shared memory.
 __global__ void __launch_bounds__(1024)
-sample_kernel(const float* __restrict__ logits, int ld, int vocab, const int* __restrict__ params,
+sample_kernel(const float* __restrict__ logits, int ld, int vocab, RowParams params,
               int* __restrict__ out, int filtered_only) {
   __shared__ ArgMax arg_scratch[32];
   __shared__ float sum_scratch[32];
@@ -233,7 +255,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const int* __
   pdl_wait();
   const uint32_t ranks = cluster_size(), rank = cluster_rank();
   const int row = blockIdx.x / ranks;
-  const int* p = params + row * kParamWords;
+  const int* p = params.of(row);
   // the whole cluster leaves together: no CTA may wait at a cluster barrier for one that has returned
   if (filtered_only && !(__int_as_float(p[0]) != 0.f && ((p[1] > 0 && p[1] < vocab) || __int_as_float(p[2]) < 1.f))) return;
   const float temperature = __int_as_float(p[0]);
@@ -302,7 +324,11 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const int* __
     });
     result = cluster_argmax(best).index;
   }
-  if (rank == 0 && threadIdx.x == 0) out[row] = result;
+  // every CTA of the cluster has read the row's parameters by now (the reductions above are barriers)
+  if (rank == 0 && threadIdx.x == 0) {
+    out[row] = result;
+    params.settle(row, result, static_cast<int>(counter));
+  }
   if (ranks > 1) cluster_barrier();        // nobody leaves while its slots may still be read
 }
 
@@ -317,14 +343,14 @@ __device__ __forceinline__ bool row_is_filtered(const int* p, int vocab) {
 }
 
 __global__ void __launch_bounds__(256)
-sample_partial_kernel(const float* __restrict__ logits, int ld, int vocab, const int* __restrict__ params,
+sample_partial_kernel(const float* __restrict__ logits, int ld, int vocab, RowParams params,
                       float* __restrict__ part_value, int* __restrict__ part_index, int chunks) {
   __shared__ ArgMax arg_scratch[32];
   __shared__ float sum_scratch[32];
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.y, chunk = blockIdx.x;
-  const int* p = params + row * kParamWords;
+  const int* p = params.of(row);
   if (row_is_filtered(p, vocab)) return;
   const float* x = logits + static_cast<size_t>(row) * ld;
   const float temperature = __int_as_float(p[0]);
@@ -350,11 +376,13 @@ sample_partial_kernel(const float* __restrict__ logits, int ld, int vocab, const
 }
 
 __global__ void sample_final_kernel(const float* __restrict__ part_value, const int* __restrict__ part_index,
-                                    const int* __restrict__ params, int vocab, int* __restrict__ out, int chunks) {
+                                    RowParams params, int vocab, int* __restrict__ out, int chunks) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;
-  if (row_is_filtered(params + row * kParamWords, vocab)) return;   // written by sample_kernel
+  const int* p = params.of(row);
+  if (row_is_filtered(p, vocab)) return;   // written by sample_kernel
+  const int counter = p[5];
   ArgMax best{-INFINITY, 0x7fffffff};
   bool bad = false;
   for (int c = threadIdx.x; c < chunks; c += 32) {
@@ -368,14 +396,17 @@ __global__ void sample_final_kernel(const float* __restrict__ part_value, const 
     best = better(best, other);
   }
   bad = __any_sync(0xffffffffu, bad);
-  if (threadIdx.x == 0) out[row] = bad ? -1 : best.index;
+  if (threadIdx.x == 0) {
+    out[row] = bad ? -1 : best.index;
+    params.settle(row, bad ? -1 : best.index, counter);
+  }
 }
 
 }  // namespace b200
 
 // The single-kernel path: a cluster of up to eight CTAs per row for vocabularies of 32,768 entries and
 // more, one CTA otherwise.
-static int launch_sample(const float* logits, int ld, int vocab, const int* params, int* out, int rows, int filtered_only,
+static int launch_sample(const float* logits, int ld, int vocab, b200::RowParams params, int* out, int rows, int filtered_only,
                          cudaStream_t stream) {
   const int threads = vocab >= 8192 ? 1024 : (vocab >= 1024 ? 256 : 128);
   // a cluster of CTAs per row for large vocabularies, as long as all clusters fit on the GPU at once
@@ -402,14 +433,14 @@ extern "C" int b200_sample(const float* logits, int ld, int vocab, const int* pa
                            int rows, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0 || ld < vocab) return B200_ERR_BAD_SIZE;
-  return launch_sample(logits, ld, vocab, params, out, rows, 0, stream);
+  return launch_sample(logits, ld, vocab, b200::RowParams{const_cast<int*>(params), nullptr}, out, rows, 0, stream);
 }
 
 // Two-stage variant.  `scratch` holds rows * chunks floats followed by rows * chunks ints;
 // `any_filtered` tells whether some row uses top_k / top_p (then the single-CTA kernel also
 // runs, for those rows only).
-extern "C" int b200_sample_chunked(const float* logits, int ld, int vocab, const int* params, int* out, int rows,
-                                   int chunks, void* scratch, int any_filtered, cudaStream_t stream) {
+static int sample_chunked(const float* logits, int ld, int vocab, b200::RowParams params, int* out, int rows,
+                          int chunks, void* scratch, int any_filtered, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0 || ld < vocab || chunks <= 0 || rows > 65535) return B200_ERR_BAD_SIZE;
   float* part_value = static_cast<float*>(scratch);
@@ -420,4 +451,19 @@ extern "C" int b200_sample_chunked(const float* logits, int ld, int vocab, const
   if (int e = b200::launch_status()) return e;
   if (any_filtered) return launch_sample(logits, ld, vocab, params, out, rows, 1, stream);
   return 0;
+}
+
+extern "C" int b200_sample_chunked(const float* logits, int ld, int vocab, const int* params, int* out, int rows,
+                                   int chunks, void* scratch, int any_filtered, cudaStream_t stream) {
+  return sample_chunked(logits, ld, vocab, b200::RowParams{const_cast<int*>(params), nullptr}, out, rows, chunks, scratch,
+                        any_filtered, stream);
+}
+
+// The same selection with the rows' parameters taken from the slot records (`records`: the table,
+// `row_slots[i]`: the record of row i): the chosen token and the advanced counter are written back
+// into the record as well as into `out`.
+extern "C" int b200_sample_slots(const float* logits, int ld, int vocab, int* records, const int* row_slots, int* out,
+                                 int rows, int chunks, void* scratch, int any_filtered, cudaStream_t stream) {
+  if (records == nullptr || row_slots == nullptr) return B200_ERR_BAD_SIZE;
+  return sample_chunked(logits, ld, vocab, b200::RowParams{records, row_slots}, out, rows, chunks, scratch, any_filtered, stream);
 }

@@ -38,6 +38,8 @@ class Engine:
     max_tokens_per_step: int = 2048
     max_cache_tokens: int | None = None
     page_policy: str = "on_demand"
+    strict_dtype: bool = True
+    device_sampling: bool = True
     tokenizer: Any = None
     source: Any = None   # how the weights were obtained: ("dir", path) or ("random", config, seed, on_device)
     _runner: StepRunner | None = field(default=None, init=False, repr=False)
@@ -59,10 +61,14 @@ class Engine:
     ) -> "Engine":
         """Load a folder with ``config.json`` and safetensors weights.  Further
         options: ``page_size``, ``max_tokens_per_step``, ``max_cache_tokens``,
-        ``page_policy`` ("on_demand" or "reserve")."""
+        ``page_policy`` ("on_demand" or "reserve"), ``strict_dtype`` (on by default:
+        every floating tensor must be stored in config.json's ``torch_dtype``),
+        ``device_sampling`` (on by default: tokens are drawn on the device and a
+        request's position, pending token and random counter live in its slot record
+        there; off: logits come back to the host for every step)."""
 
         started = time.perf_counter()
-        loaded = load(model_dir, device=device, dtype=dtype)
+        loaded = load(model_dir, device=device, dtype=dtype, strict_dtype=options.get("strict_dtype", True))
         tokenizer = None
         if (Path(model_dir) / "tokenizer.json").is_file():
             from ..tokenizer import load_tokenizer
@@ -179,7 +185,7 @@ class Engine:
         if self.source is None:
             raise EngineError("this engine does not know where its weights came from and cannot be moved")
         if self.source[0] == "dir":
-            self.loaded = load(self.source[1], device=new_device, dtype=new_dtype)
+            self.loaded = load(self.source[1], device=new_device, dtype=new_dtype, strict_dtype=self.strict_dtype)
         else:
             _, config, seed, on_device = self.source
             self.loaded = load_random(config, seed, device=new_device, dtype=new_dtype, on_device=on_device)
@@ -190,6 +196,8 @@ class Engine:
 
     # ------------------------------------------------------------ generation
     def create_scheduler(self) -> Scheduler:
+        from ..ops import native
+
         runner = self._ensure_runner()
         description = self.model.description
         return Scheduler(
@@ -198,6 +206,7 @@ class Engine:
             max_tokens_per_step=self.max_tokens_per_step, policy=self.page_policy,
             synchronize=self.synchronize, seed_source=fresh_seed,
             detokenize=self.tokenizer.decode if self.tokenizer is not None else None,
+            device_sampling=self.device_sampling, check_kernels=native.check_kernel_errors,
         )
 
     def encode_prompt(self, prompt: Any, *, enable_thinking: bool = False) -> list[int]:
@@ -222,10 +231,13 @@ class Engine:
                                   max_new_tokens=max_new_tokens, sampling=sampling)
 
         def iterate() -> Iterator[tuple[int, GenerationEvent]]:
+            from ..ops import native
+
             try:
                 with torch.cuda.device(self.device):
                     while scheduler.has_unfinished:
                         yield from scheduler.step()
+                    native.check_kernel_errors()
             finally:
                 scheduler.abort_all()
 

@@ -101,7 +101,8 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--device", default="cuda:0")
     args = parser.parse_args(argv)
     print("[trace_run] loading model and kernels ...", file=sys.stderr, flush=True)
-    loaded = load(args.model, device=args.device, dtype=args.dtype)
+    # a trace is about arithmetic, not about where the weights came from: any floating storage type is taken
+    loaded = load(args.model, device=args.device, dtype=args.dtype, strict_dtype=False)
     replayer = TraceReplayer(loaded, max_tokens=args.max_tokens, page_size=args.page_size, out_dir=args.out)
     replay_stream(replayer, sys.stdin)
     return 0

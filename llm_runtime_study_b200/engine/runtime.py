@@ -80,13 +80,13 @@ class LoadedModel:
         )
 
 
-def load(model_dir: str | Path, *, device="auto", dtype="auto") -> LoadedModel:
+def load(model_dir: str | Path, *, device="auto", dtype="auto", strict_dtype: bool = True) -> LoadedModel:
     from ..config.registry import load_config
 
     load_config(model_dir)  # a bad folder or config.json is reported before anything about the device
     runtime = Runtime(resolve_device(device), resolve_dtype(dtype))
     with torch.cuda.device(runtime.device):
-        model, config, _ = load_model_dir(model_dir, runtime)
+        model, config, _ = load_model_dir(model_dir, runtime, strict_dtype=strict_dtype)
     return LoadedModel(model, config, runtime)
 
 

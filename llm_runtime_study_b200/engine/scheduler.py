@@ -19,6 +19,21 @@ first; if the decoded tokens alone still do not fit, the request admitted last
 is *preempted*: its pages and slot are given back and it returns to the front of
 the queue with its prompt extended by what it has generated, to be recomputed.
 Its events are not repeated and its random stream continues where it was.
+
+Two ways of running a step.  With a runner that can draw tokens on the device
+(``step_sampled`` / ``decode_sampled``, see ``engine/step.py``) a request's pending
+token, position, sampling options and random counter live in its slot record on the
+device, and the drawn ids come back through a pinned buffer: the scheduler *launches*
+a step and reads its tokens one call later.  While nothing but decoding goes on, the
+next decode step is launched before the tokens of the one in flight are read, so the
+device never waits for the host; ``step()`` then returns the events of the step
+before.  A request that turns out to have ended (an EOS token) has by then been
+given one token too many on the device; that token is dropped, and what it wrote
+lies in pages and a slot that only later launches on the same stream can reuse.
+Whenever anything else is due (an admission, a prompt portion, a preemption) the step in flight is
+read first and the host's picture is exact.  With any other runner (the scripted
+one of the CPU tests) logits come back to the host and ``sampler.sample`` picks:
+the plain path, kept as the oracle of the first.
 """
 
 from __future__ import annotations
@@ -30,6 +45,7 @@ from dataclasses import dataclass, field
 from typing import Any, Callable, Literal, Sequence
 
 from ..cache.manager import CacheManager, RequestCache
+from ..cache.slots import SlotRecord
 from ..errors import GenerationError, SamplingError
 from ..sampling.config import SamplingConfig
 from .step import StepEntry
@@ -66,6 +82,7 @@ class _Request:
     pending: int | None = None      # sampled token not yet in the cache
     admitted_at: int = 0
     text: str = ""
+    finished: bool = False
 
     @property
     def prefilling(self) -> bool:
@@ -78,7 +95,8 @@ class Scheduler:
         eos_token_ids: Sequence[int], vocab_size: int, max_tokens_per_step: int = 2048,
         policy: Literal["on_demand", "reserve"] = "on_demand",
         synchronize: Callable[[], None] | None = None, seed_source: Callable[[], int] | None = None,
-        detokenize: Callable[[list[int]], str] | None = None,
+        detokenize: Callable[[list[int]], str] | None = None, device_sampling: bool | None = None,
+        check_kernels: Callable[[], None] | None = None,
     ) -> None:
         if max_batch_size <= 0:
             raise GenerationError("max_batch_size must be positive")
@@ -104,7 +122,15 @@ class Scheduler:
         self._admissions = itertools.count()
         self._waiting: deque[_Request] = deque()
         self._running: list[_Request] = []
-        self.stats = {"steps": 0, "preemptions": 0, "tokens": 0}
+        self.stats = {"steps": 0, "preemptions": 0, "tokens": 0, "chained_steps": 0}
+        # tokens are drawn on the device and read one call later when the runner can do that
+        can = hasattr(runner, "decode_sampled") and hasattr(runner, "step_sampled") and hasattr(sampler, "sample_slots")
+        self.device_sampling = can if device_sampling is None else bool(device_sampling)
+        if self.device_sampling and not can:
+            raise GenerationError("this runner or sampler cannot draw tokens on the device")
+        self._check_kernels = check_kernels
+        self._inflight: tuple[Any, list[_Request], float] | None = None   # (token handle, its requests, launch time)
+        self._last_read = 0.0
 
     # ------------------------------------------------------------- requests
     def add_request(
@@ -145,7 +171,7 @@ class Scheduler:
 
     @property
     def has_unfinished(self) -> bool:
-        return bool(self._waiting or self._running)
+        return bool(self._waiting or self._running or self._inflight)
 
     @property
     def num_waiting(self) -> int:
@@ -160,6 +186,7 @@ class Scheduler:
 
         running, self._running = self._running, []
         self._waiting.clear()
+        self._inflight = None
         for request in running:
             if request.cache is not None:
                 self.manager.release(request.cache)
@@ -167,10 +194,23 @@ class Scheduler:
     # ----------------------------------------------------------------- step
     def step(self) -> list[tuple[int, GenerationEvent]]:
         """Advance every running request by one token (or one prompt portion)
-        and return the events produced.  Any failure aborts every request."""
+        and return the events that are known now: with tokens drawn on the device,
+        those of the step launched by the call before.  Any failure aborts every
+        request."""
 
         events: list[tuple[int, GenerationEvent]] = []
         try:
+            if self.device_sampling:
+                chain = self._chainable()
+                if chain:
+                    # nothing but decoding: launch the next step, then read the one before
+                    started = time.perf_counter()
+                    handle = self.runner.decode_sampled([r.cache for r in chain], self.sampler)
+                    self._count(len(chain), chained=True)
+                    self._read_inflight(events)
+                    self._inflight = (handle, chain, started)
+                    return events
+                self._read_inflight(events)
             plan = self._plan(events)
             # Requests that all wait for pages held by one another make no plan:
             # take the pages of the one admitted last and plan again.
@@ -178,11 +218,86 @@ class Scheduler:
                 self._preempt_last()
                 plan = self._plan(events)
             if plan:
-                self._run(plan, events)
+                (self._launch if self.device_sampling else self._run)(plan, events)
+            elif self._waiting and not self._running:
+                head = self._waiting[0]
+                raise GenerationError(
+                    f"no progress is possible: nothing is running, and the request at the head of the queue cannot "
+                    f"be admitted ({self.manager.free_pages} pages of {self.manager.page_size} tokens and "
+                    f"{self.manager.free_slots} request slots are free; it has {len(head.prompt)} prompt tokens). "
+                    "Pages or slots are held outside this scheduler."
+                )
         except Exception:
             self.abort_all()
             raise
         return events
+
+    def _count(self, tokens: int, chained: bool = False) -> None:
+        self.stats["steps"] += 1
+        self.stats["tokens"] += tokens
+        self.stats["chained_steps"] += chained
+
+    # ------------------------------------------- tokens drawn on the device
+    def _chainable(self) -> list[_Request] | None:
+        """The requests of the next decode step, if it can be launched before the tokens
+        of the step in flight are known: every running request awaits a token of that
+        step, nobody can be admitted, and the pages suffice.  A request whose last token
+        is the one in flight is left out (it ends whatever that token is); one that ends
+        with an EOS token is found out a step late."""
+
+        if self._inflight is None or not self._running:
+            return None
+        if self._waiting and (self._waiting[0].output_limit == 0
+                              or (len(self._running) < self.max_batch_size and self.manager.free_slots)):
+            return None
+        awaited = {id(r) for r in self._inflight[1]}
+        if any(r.prefilling or id(r) not in awaited for r in self._running):
+            return None
+        going = [r for r in self._running if len(r.generated) + 1 < r.output_limit]
+        if not going or sum(self._pages_for(r, r.cache.length + 1) for r in going) > self.manager.free_pages:
+            return None
+        return going
+
+    def _read_inflight(self, events: list) -> None:
+        """Wait for the step in flight, if any, and turn its tokens into events."""
+
+        if self._inflight is None:
+            return
+        handle, requests, started = self._inflight
+        self._inflight = None
+        tokens = handle.tokens()
+        now = time.perf_counter()
+        seconds = now - max(started, self._last_read)
+        self._last_read = now
+        for request, token in zip(requests, tokens):
+            if not request.finished:        # else: the token after its last, drawn before the end was known
+                self._emit(request, int(token), seconds, events)
+
+    def _launch(self, plan: list[tuple[_Request, list[int], bool]], events: list) -> None:
+        """Start the planned step with its tokens drawn on the device; do not wait for them."""
+
+        started = time.perf_counter()
+        drawing = [r for r, _, wants in plan if wants]
+        if not any(r.prefilling for r, _, _ in plan):
+            # single decoded tokens only (no request is still feeding its prompt): they are in the slot records already
+            handle = self.runner.decode_sampled([r.cache for r in drawing], self.sampler)
+        else:
+            entries = []
+            for request, tokens, wants in plan:
+                record = None
+                if wants:
+                    config = request.sampling
+                    record = SlotRecord(position=0, temperature=config.temperature, top_k=config.top_k or 0,
+                                        top_p=config.top_p, seed=request.seed, counter=len(request.generated))
+                entries.append(StepEntry(request.cache, tokens, [len(tokens) - 1] if wants else [], record))
+            handle = self.runner.step_sampled(entries, self.sampler)
+        self._count(sum(len(t) for _, t, _ in plan))
+        for request, fed_tokens, _ in plan:
+            if request.prefilling:
+                request.fed += len(fed_tokens)
+            request.pending = None
+        if handle is not None:
+            self._inflight = (handle, drawing, started)
 
     # ----------------------------------------------------- building a batch
     def _pages_for(self, request: _Request, new_length: int) -> int:
@@ -227,7 +342,7 @@ class Scheduler:
         for request in sorted((r for r in self._running if r.prefilling), key=lambda r: r.admitted_at):
             if budget <= 0:
                 break
-            held = len(request.cache.tables[0]) if request.cache.tables else 0
+            held = manager.pages_held(request.cache)
             n = portion_for(request, request.cache.length, held)
             if n <= 0:
                 continue
@@ -262,7 +377,7 @@ class Scheduler:
             waiting.admitted_at = next(self._admissions)
             if self.policy == "reserve":
                 manager.grow(waiting.cache, lifetime)
-                free_pages -= len(waiting.cache.tables[0]) if waiting.cache.tables else 0
+                free_pages -= manager.pages_held(waiting.cache)
             else:
                 free_pages -= -(-n // manager.page_size)
             self._running.append(waiting)
@@ -285,8 +400,7 @@ class Scheduler:
         if self._synchronize:
             self._synchronize()
         seconds = time.perf_counter() - started
-        self.stats["steps"] += 1
-        self.stats["tokens"] += sum(len(t) for _, t, _ in plan)
+        self._count(sum(len(t) for _, t, _ in plan))
         for request, fed_tokens, _ in plan:
             if request.prefilling:
                 request.fed += len(fed_tokens)
@@ -313,6 +427,11 @@ class Scheduler:
         if reason is None:
             request.pending = token
         else:
+            request.finished = True
             self.manager.release(request.cache)
             request.cache = None
             self._running.remove(request)
+            if self._check_kernels is not None:
+                # a kernel whose bounded wait ran out finishes on incomplete data: before this
+                # request's tokens count as final, ask whether that ever happened
+                self._check_kernels()

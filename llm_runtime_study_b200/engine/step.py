@@ -15,14 +15,15 @@ mini_llm/model/base.py:175, 188-190: the same contract seen from outside).
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 from typing import Any, Sequence
 
 import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, RequestCache
-from ..errors import GenerationError, KVCacheError
+from ..cache.slots import SLOT_WORDS, SlotRecord
+from ..errors import GenerationError, KVCacheError, SamplingError
 from ..ops import attention as attention_ops
 from ..parts.base import Runtime
 
@@ -30,11 +31,32 @@ from ..parts.base import Runtime
 @dataclass
 class StepEntry:
     """The next tokens of one request.  ``want`` lists the places among these
-    tokens (0-based) whose logits are asked for; it may be empty."""
+    tokens (0-based) whose logits are asked for; it may be empty.  ``sample``
+    (``step_sampled`` only): draw the request's next token on the device from the
+    logits at the entry's last token, with these options, and keep it in the
+    request's slot record; ``want`` is then that one place."""
 
     request: RequestCache
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    sample: SlotRecord | None = None
+
+
+class TokenHandle:
+    """Token ids drawn on the device by a step, on their way to the host.  The
+    step that produced them may still be running; ``tokens()`` waits for it."""
+
+    def __init__(self, host: torch.Tensor, event: "torch.cuda.Event | None", count: int) -> None:
+        self._host, self._event, self.count = host, event, count
+
+    def tokens(self) -> list[int]:
+        if self._event is not None:
+            self._event.synchronize()
+            self._event = None
+        ids = self._host[: self.count].tolist()
+        if any(t < 0 for t in ids):
+            raise SamplingError("logits must contain only finite values")
+        return ids
 
 
 class StepContext:
@@ -62,6 +84,8 @@ class StepContext:
         self.max_kv_len = 0
         self.all_decode = False
         self.captured = False   # True while a CUDA graph holds this batch's launches
+        self.row_slots: torch.Tensor = None      # [M] int32 slot of each sampled row (step_sampled / decode_sampled)
+        self.staged_records: torch.Tensor = None # [M, SLOT_WORDS] int32 records the host writes for the sampled rows
 
     def block_table(self, group: int) -> torch.Tensor:
         return self.tables[group]
@@ -132,6 +156,13 @@ class StepRunner:
         self.last_context: StepContext | None = None
         self.use_cuda_graph = False
         self._graphs = None
+        self.last_logits: torch.Tensor | None = None   # logits of the last sampled step (valid until the next step)
+        cuda = runtime.device.type == "cuda"
+        rows = max(manager.max_requests, 1)
+        self._ids_device = torch.zeros(rows, dtype=torch.int32, device=runtime.device)
+        self._ids_host = [torch.zeros(rows, dtype=torch.int32, pin_memory=cuda) for _ in range(4)]
+        self._ids_events: list[torch.cuda.Event | None] = [None] * 4
+        self._ids_turn = 0
 
     # ---------------------------------------------------------------- build
     def build_context(self, entries: Sequence[StepEntry], *, table_width: int | None = None) -> StepContext:
@@ -142,14 +173,17 @@ class StepRunner:
         manager = self.manager
         return self._pack_context(entries, q_lens, starts, table_width)
 
-    def validate_and_grow(self, entries: Sequence[StepEntry]) -> tuple[list[int], list[int]]:
+    def validate_and_grow(self, entries: Sequence[StepEntry], *, tokens_on_device: bool = False) -> tuple[list[int], list[int]]:
+        """``tokens_on_device``: every entry is one decoded token that the device holds in
+        the request's slot record (it came out of the sampler, so it is in the vocabulary)."""
+
         if not entries:
             raise GenerationError("a step needs at least one entry")
         manager = self.manager
         seen: set[int] = set()
         q_lens, starts = [], []
         for entry in entries:
-            n = len(entry.tokens)
+            n = 1 if tokens_on_device else len(entry.tokens)
             if n == 0:
                 raise GenerationError("an entry needs at least one token")
             if entry.request.released:
@@ -157,7 +191,7 @@ class StepRunner:
             if entry.request.id in seen:
                 raise GenerationError("a request may appear once in a step")
             seen.add(entry.request.id)
-            for t in entry.tokens:
+            for t in (() if tokens_on_device else entry.tokens):
                 if not 0 <= int(t) < self.vocab_size:
                     raise GenerationError(f"token id {t} is outside the vocabulary [0, {self.vocab_size})")
             start = entry.request.length
@@ -168,6 +202,10 @@ class StepRunner:
             for w in entry.want:
                 if not 0 <= int(w) < n:
                     raise GenerationError(f"wanted place {w} is outside the entry's {n} tokens")
+            if entry.sample is not None and list(entry.want) != [n - 1]:
+                raise GenerationError("an entry whose next token is drawn on the device wants the logits of its last token only")
+            if tokens_on_device and start == 0:
+                raise GenerationError("a request with nothing in the cache has no decoded token to continue from")
             q_lens.append(n)
             starts.append(start)
         # pages for every entry, or for none: check the total first
@@ -207,8 +245,16 @@ class StepRunner:
                 table[i, : len(row)] = row
             tables.append(table)
 
+        sampled = [e for e in entries if e.sample is not None]
+        row_slots = np.asarray([e.request.slot for e in sampled], dtype=np.int32)
+        staged = np.zeros((len(sampled), SLOT_WORDS), dtype=np.int32)
+        for e, length in zip(entries, kv_lens):
+            if e.sample is not None:    # the record's position is where the drawn token will go: the length after this step
+                e.sample = replace(e.sample, position=length)
+        for i, e in enumerate(sampled):
+            staged[i] = manager.slots.note(e.request.slot, e.sample)
         pieces = [token_ids, positions, token_entry, q_start, np.asarray(kv_lens, dtype=np.int32), slots,
-                  logit_rows, *[t.reshape(-1) for t in tables]]
+                  logit_rows, *[t.reshape(-1) for t in tables], row_slots, staged.reshape(-1)]
         # every piece starts on a 16-byte boundary
         offsets, total = [], 0
         for piece in pieces:
@@ -227,6 +273,8 @@ class StepRunner:
         ctx.token_ids, ctx.positions, ctx.token_entry = view(0), view(1), view(2)
         ctx.q_start, ctx.kv_len, ctx.slots, ctx.logit_rows = view(3), view(4), view(5), view(6)
         ctx.tables = [view(7 + g).view(num_entries, tables[g].shape[1]) for g in range(len(tables))]
+        ctx.row_slots = view(7 + len(tables))
+        ctx.staged_records = view(8 + len(tables)).view(len(sampled), SLOT_WORDS)
         ctx.q_lens, ctx.kv_lens = q_lens, kv_lens
         ctx.entry_slots = [e.request.slot for e in entries]
         ctx.max_q_len, ctx.max_kv_len = max(q_lens), max(kv_lens)
@@ -237,15 +285,8 @@ class StepRunner:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
         """Run one batch.  Returns float32 logits ``[wanted, vocab]`` on the
         device, rows in the order of the entries and of each entry's ``want``
-        (``None`` if nothing was wanted)."""
+        (``None`` if nothing was wanted).  The tensor is the caller's."""
 
-        if self.use_cuda_graph and self.runtime.device.type == "cuda":
-            if self._graphs is None:
-                from .graph import DecodeGraphs
-
-                self._graphs = DecodeGraphs(self)
-            if self._graphs.eligible(entries):
-                return self._step_captured(entries)
         ctx = self.build_context(entries)
         with torch.inference_mode():
             logits = self.model.forward(ctx)
@@ -254,12 +295,119 @@ class StepRunner:
         self.last_context = ctx
         return logits
 
-    def _step_captured(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """A batch of single decoded tokens, replayed from a CUDA graph.  The
-        same host-side checks and page-taking as the eager path come first."""
+    # ------------------------------------------- steps that draw on the device
+    def _send_home(self, ids: torch.Tensor, count: int) -> TokenHandle:
+        """Start the copy of ``count`` drawn ids into pinned host memory; do not wait."""
 
-        self.validate_and_grow(entries)
-        logits, kv_lens = self._graphs.run(entries)
-        for entry, length in zip(entries, kv_lens):
+        self._ids_turn = (self._ids_turn + 1) % len(self._ids_host)
+        event = self._ids_events[self._ids_turn]
+        if event is not None:
+            event.synchronize()          # the host has long read what this buffer held four steps ago
+        host = self._ids_host[self._ids_turn]
+        host[:count].copy_(ids[:count], non_blocking=True)
+        if self.runtime.device.type != "cuda":
+            return TokenHandle(host, None, count)
+        event = event or torch.cuda.Event()
+        event.record()
+        self._ids_events[self._ids_turn] = event
+        return TokenHandle(host, event, count)
+
+    def step_sampled(self, entries: Sequence[StepEntry], sampler: Any) -> TokenHandle | None:
+        """Run one batch packed by the host (prompt portions, decoded tokens whose ids the
+        host knows) and draw, on the device, the next token of every entry that carries a
+        ``sample`` record.  The records are written into the requests' slots before the
+        draw; afterwards each slot holds the drawn token and the advanced counter, so the
+        request can go on with ``decode_sampled`` without the host.  Returns the handle of
+        the drawn ids (in the order of the sampled entries), or ``None`` if none is drawn."""
+
+        from ..ops import slots as slot_ops
+
+        ctx = self.build_context(entries)
+        sampled = [e for e in entries if e.sample is not None]
+        with torch.inference_mode():
+            if sampled:
+                slot_ops.slot_store(self.manager.slots.records, ctx.staged_records, ctx.row_slots)
+            logits = self.model.forward(ctx)
+            if sampled:
+                sampler.sample_slots(logits, self.manager.slots.records, ctx.row_slots, self._ids_device,
+                                     filtered=any(e.sample.filtered for e in sampled))
+        for entry, length in zip(entries, ctx.kv_lens):
             self.manager.commit(entry.request, length)
-        return logits
+        for entry in sampled:
+            self.manager.slots.advanced(entry.request.slot, tokens=0, draws=1)
+        self.last_context, self.last_logits = ctx, logits
+        return self._send_home(self._ids_device, len(sampled)) if sampled else None
+
+    def decode_sampled(self, requests: Sequence[RequestCache], sampler: Any) -> TokenHandle:
+        """One decode step for requests whose pending token is in their slot records: feed
+        it, draw the next one, keep it in the record.  Nothing but the list of slots and the
+        block tables goes to the device, and nothing but the drawn ids comes back.  With
+        ``use_cuda_graph`` the step (embedding to sampling) is replayed from a CUDA graph
+        whenever every part of the model allows it."""
+
+        entries = [StepEntry(r, (), [0]) for r in requests]
+        self.validate_and_grow(entries, tokens_on_device=True)
+        filtered = any(self.manager.slots.filtered(r.slot) for r in requests)
+        use_graph = (self.use_cuda_graph and self.runtime.device.type == "cuda"
+                     and getattr(self.model, "graph_safe", lambda: False)())
+        if use_graph:
+            if self._graphs is None:
+                from .graph import DecodeGraphs
+
+                self._graphs = DecodeGraphs(self)
+            ids, self.last_logits = self._graphs.run(requests, sampler, filtered)
+        else:
+            ids, self.last_logits = self._decode_eager(requests, sampler, filtered)
+        for request in requests:
+            self.manager.commit(request, request.length + 1)
+            self.manager.slots.advanced(request.slot, tokens=1, draws=1)
+        return self._send_home(ids, len(requests))
+
+    def _decode_eager(self, requests: Sequence[RequestCache], sampler: Any, filtered: bool):
+        """The launches a captured decode step holds, issued one by one."""
+
+        from ..ops import slots as slot_ops
+
+        manager = self.manager
+        n = len(requests)
+        starts = [r.length for r in requests]
+        tables = []
+        for g in range(len(manager.layout.groups)):
+            width = _round_up(max(max(len(r.tables[g]) for r in requests), 1), 4)
+            table = np.full((n, width), -1, dtype=np.int32)
+            for i, r in enumerate(requests):
+                table[i, : len(r.tables[g])] = r.tables[g]
+            tables.append(table)
+        ramp = np.arange(n + 1, dtype=np.int32)
+        slots = np.asarray([r.slot for r in requests], dtype=np.int32)
+        blank = np.zeros(n, dtype=np.int32)
+        # token ids, positions and lengths are filled in on the device from the slot records
+        pieces = [blank, blank, ramp[:n], ramp, blank, slots, ramp[:n], *[t.reshape(-1) for t in tables]]
+        offsets, total = [], 0
+        for piece in pieces:
+            offsets.append(total)
+            total += _round_up(piece.shape[0], 4)
+        packed = np.zeros(total, dtype=np.int32)
+        for piece, off in zip(pieces, offsets):
+            packed[off : off + piece.shape[0]] = piece
+        dev = self._buffers.upload(packed)
+
+        def view(i: int) -> torch.Tensor:
+            return dev[offsets[i] : offsets[i] + pieces[i].shape[0]]
+
+        ctx = StepContext(self.runtime, manager)
+        ctx.num_tokens = ctx.num_entries = ctx.num_logit_rows = n
+        ctx.token_ids, ctx.positions, ctx.token_entry = view(0), view(1), view(2)
+        ctx.q_start, ctx.kv_len, ctx.slots, ctx.logit_rows = view(3), view(4), view(5), view(6)
+        ctx.tables = [view(7 + g).view(n, tables[g].shape[1]) for g in range(len(tables))]
+        ctx.row_slots = ctx.slots
+        ctx.q_lens, ctx.kv_lens = [1] * n, [s + 1 for s in starts]
+        ctx.entry_slots = [r.slot for r in requests]
+        ctx.max_q_len, ctx.max_kv_len = 1, max(ctx.kv_lens)
+        ctx.all_decode = True
+        with torch.inference_mode():
+            slot_ops.slot_load(manager.slots.records, ctx.slots, ctx.token_ids, ctx.positions, ctx.kv_len)
+            logits = self.model.forward(ctx)
+            sampler.sample_slots(logits, manager.slots.records, ctx.row_slots, self._ids_device, filtered=filtered)
+        self.last_context = ctx
+        return self._ids_device, logits

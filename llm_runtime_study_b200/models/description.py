@@ -13,9 +13,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Mapping
 
-from ..parts.base import BLOCKS
-from ..parts.base import NORMS
-from ..parts.embedding import OutputHead, TokenEmbedding
+from ..parts import embedding as _embedding_kinds  # noqa: F401  (registers the embedding and head kinds of this package)
+from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS
 from ..weights.checkpoint import TensorSpec
 
 
@@ -36,11 +35,11 @@ class ModelDescription:
     hidden_size: int
     max_positions: int
     eos_token_ids: tuple[int, ...]
-    embedding: Mapping[str, Any]          # parameters of TokenEmbedding + "prefix"
+    embedding: Mapping[str, Any]          # embedding description ("kind", default "token_embedding") + "prefix"
     layers: tuple[LayerDescription, ...]
     order: tuple[int, ...]                # indices into ``layers``, in execution order
     final_norm: Mapping[str, Any]         # norm description + "prefix"
-    head: Mapping[str, Any]               # parameters of OutputHead + "prefix"
+    head: Mapping[str, Any]               # output head description ("kind", default "linear_head") + "prefix"
     cache_of: tuple[int | None, ...] = () # per run: the earlier run whose cache it uses (None: its own)
     extra: Mapping[str, Any] = field(default_factory=dict)
 
@@ -69,10 +68,10 @@ def build_parts(description: ModelDescription):
     norm_prefix, norm_params = _split(description.final_norm)
     head_prefix, head_params = _split(description.head)
     return {
-        "embedding": (emb_prefix, TokenEmbedding(**emb_params)),
+        "embedding": (emb_prefix, EMBEDDINGS.build({"kind": "token_embedding", **emb_params})),
         "blocks": [(layer.prefix, BLOCKS.build(layer.block)) for layer in description.layers],
         "final_norm": (norm_prefix, NORMS.build(norm_params)),
-        "head": (head_prefix, OutputHead(**head_params)),
+        "head": (head_prefix, HEADS.build({"kind": "linear_head", **head_params})),
     }
 
 

@@ -15,15 +15,22 @@ from ..weights.view import TensorView
 from .model import DecoderModel
 
 
-def load_model_dir(model_dir: str | Path, runtime: Runtime) -> tuple[DecoderModel, Any, Architecture]:
+def load_model_dir(model_dir: str | Path, runtime: Runtime, *, strict_dtype: bool = True) -> tuple[DecoderModel, Any, Architecture]:
     """config.json picks the architecture; headers are validated against the
-    model's schema before any payload is read (mini_llm/model/base.py:276-294)."""
+    model's schema before any payload is read (mini_llm/model/base.py:276-294).
+    Then every part takes its tensors one by one from the mapped files and places
+    them on the device: no host copy of the checkpoint is ever made.
+
+    ``strict_dtype``: every floating tensor must be stored in config.json's
+    ``torch_dtype`` (the reference's rule, mini_llm/checkpoint.py:290, 478-481);
+    off, any floating storage type is taken and converted."""
 
     arch, config = load_config(model_dir)
     model = DecoderModel(arch.describe(config))
     checkpoint = Checkpoint.from_model_dir(model_dir)
-    validate_manifest(checkpoint, model.tensor_schema(), architecture=arch.model_type)
-    model.load(checkpoint.get_tensors(), runtime)
+    validate_manifest(checkpoint, model.tensor_schema(), architecture=arch.model_type,
+                      torch_dtype=getattr(config, "torch_dtype", None) if strict_dtype else None)
+    model.load(checkpoint.view(), runtime)
     return model, config, arch
 
 

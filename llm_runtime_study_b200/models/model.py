@@ -65,6 +65,12 @@ class DecoderModel:
             for run, source in enumerate(self.description.cache_of)
         ]
 
+    def graph_safe(self) -> bool:
+        """Whether every part allows its launches to be replayed from a CUDA graph."""
+
+        parts = [self.embedding, *(block for _, block in self.blocks), self.final_norm, self.head]
+        return all(part.capture_safe() for part in parts)
+
     # ------------------------------------------------------------ forward
     def forward(self, ctx: Any) -> torch.Tensor | None:
         """Run the batch in ``ctx``; return float32 logits ``[wanted, vocab]``

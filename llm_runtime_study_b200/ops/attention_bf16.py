@@ -15,7 +15,7 @@ from .native import c_float, c_int, c_void_p
 
 c_long = native.ctypes.c_long
 MAX_HEAD_DIM = 256
-_CTA_SLOTS = 4 * 148     # resident CTAs of the decode kernel (registers allow four per SM)
+_CTAS_PER_SM = 4         # resident CTAs of the cp.async decode kernel on one SM (registers allow four)
 _MIN_KEYS_PER_SPLIT = 128
 
 _TABLE = {
@@ -60,6 +60,7 @@ def tc_library_name(head_dim: int) -> str:
     name = f"b200_attention_tcgen05_d{head_dim}"
     if name not in native.library_specs():
         native.register_library(name, ("attention_tcgen05.cu",), _TC_TABLE, defines=(f"HEAD_DIM={head_dim}",))
+        native.register_error_probe(name, "b200_attention_tcgen05_error", f"tcgen05 attention (head size {head_dim})")
     return name
 
 
@@ -74,6 +75,7 @@ def tma_library_name(head_dim: int, depth: int = 3) -> str:
     if name not in native.library_specs():
         native.register_library(name, ("attention_decode_tma.cu",), _TMA_TABLE,
                                 defines=(f"HEAD_DIM={head_dim}", f"DECODE_DEPTH={depth}"))
+        native.register_error_probe(name, "b200_attention_decode_tma_error", f"TMA decode attention (head size {head_dim})")
     return name
 
 
@@ -125,7 +127,7 @@ def decode_splits(requests: int, kv_heads: int, slices: int, longest: int, slots
     bandwidth, whichever is less; every further part costs the merge a fraction of a microsecond.
     A part is not shorter than two tiles of keys, and there are at most 64."""
 
-    slots = slots or _CTA_SLOTS
+    slots = slots or _CTAS_PER_SM * native.sm_count()
     ctas = max(1, requests * kv_heads * slices)
     most = max(1, -(-longest // _MIN_KEYS_PER_SPLIT))
     bytes_per_key = 4 * head_dim                     # K and V rows of one KV head, bfloat16
@@ -269,8 +271,9 @@ def decode_slots(head_dim: int, page_size: int, window: int, ctas: int = 1) -> i
     """CTAs of the decode kernel that fit on the GPU at once."""
 
     if DECODE_BACKEND == "tma" and tma_supported(head_dim, page_size, window):
-        return 148 * native.query("b200_attention_decode_tma_ctas_per_sm", library=tma_library_name(head_dim, tma_depth(ctas)))
-    return _CTA_SLOTS
+        return native.sm_count() * native.query("b200_attention_decode_tma_ctas_per_sm",
+                                                library=tma_library_name(head_dim, tma_depth(ctas)))
+    return _CTAS_PER_SM * native.sm_count()
 
 
 def _decode_attention_tma(q, keys, values, kv_len, block_table, scale, splits) -> torch.Tensor:

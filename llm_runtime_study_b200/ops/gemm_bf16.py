@@ -33,7 +33,6 @@ native.register_library(
 PAIR_MIN_ROWS = 256   # from here on pairs of SMs work on 256 x 256 tiles (tcgen05 cta_group::2)
 PAIR_ENABLED = os.environ.get("LLM_RUNTIME_STUDY_B200_GEMM_PAIR", "1") != "0"
 SKINNY_M = 16         # up to here weights are streamed straight into mma.sync fragments
-_SM_COUNT = 148
 KERNELS = {"persistent": 0, "pair": 1, "streamk": 2, "splitk": 3}
 
 _STREAMK_WORKSPACE: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
@@ -69,14 +68,15 @@ def pick_kernel(m: int, n: int, k: int) -> tuple[str, int]:
     long enough to share; else one CTA per 128 x 128 tile.  A product with few tiles is as slow as
     the SM that has most to pull in, so it pays to spread the bytes over more SMs."""
 
-    if m >= PAIR_MIN_ROWS and PAIR_ENABLED and -(-m // 256) * -(-n // 256) >= 60:
+    sms = native.sm_count()
+    if m >= PAIR_MIN_ROWS and PAIR_ENABLED and 5 * -(-m // 256) * -(-n // 256) >= 2 * sms:   # 60 of a B200's 74 pairs
         return "pair", 256
     tiles = -(-m // 128) * -(-n // 256)
-    if 2 * tiles >= _SM_COUNT:
+    if 2 * tiles >= sms:
         return "persistent", 256
-    if m <= 256 and 3 * tiles <= _SM_COUNT:
+    if m <= 256 and 3 * tiles <= sms:
         return "splitk", 0
-    if 3 * tiles <= _SM_COUNT + 2 and k >= 48 * 64:
+    if 3 * tiles <= sms + 2 and k >= 48 * 64:
         return "streamk", 256
     return "persistent", 128
 
@@ -85,13 +85,13 @@ def pick_kernel(m: int, n: int, k: int) -> tuple[str, int]:
 SKINNY_LARGE = int(os.environ.get("LLM_RUNTIME_STUDY_B200_SKINNY_LARGE", 52_000_000))
 
 
-def splitk_shape(m: int, n: int, k: int, sm_count: int = _SM_COUNT) -> tuple[int, int]:
+def splitk_shape(m: int, n: int, k: int, sm_count: int = 0) -> tuple[int, int]:
     """(tile width, CTAs per tile) the split-K kernel chooses by itself for this product."""
 
     import ctypes
 
     width, splits = ctypes.c_int(0), ctypes.c_int(0)
-    native.call("b200_gemm_tcgen05_splitk_shape", m, n, k, sm_count, ctypes.addressof(width), ctypes.addressof(splits), launches=0)
+    native.call("b200_gemm_tcgen05_splitk_shape", m, n, k, sm_count or native.sm_count(), ctypes.addressof(width), ctypes.addressof(splits), launches=0)
     return width.value, splits.value
 
 
@@ -159,6 +159,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
                 out.shape[1], 1 if out_dtype == torch.float32 else 0, 1 if swiglu else 0, 0 if add_to is None else 1,
                 KERNELS[kernel], tile_n, splits, stages, native.ptr(partials), native.ptr(flags), native.stream_ptr())
     return out
+
+
+native.register_error_probe("b200_gemm_tcgen05", "b200_gemm_tcgen05_error", "tcgen05 projection")
 
 
 def check_error() -> None:

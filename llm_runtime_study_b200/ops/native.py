@@ -150,6 +150,47 @@ def query(name: str, *args, library: str | None = None) -> int:
     return _function(name, library)(*args)
 
 
+B200_SM_COUNT = 148
+_sm_counts: dict[int, int] = {}
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current CUDA device (a B200's 148 where no device is visible,
+    so that the host-side rules that choose kernels can be exercised without one)."""
+
+    if not torch.cuda.is_available():
+        return B200_SM_COUNT
+    device = torch.cuda.current_device()
+    count = _sm_counts.get(device)
+    if count is None:
+        count = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return count
+
+
+# (library, C function returning a status word, what a non-zero word means)
+_ERROR_PROBES: list[tuple[str, str, str]] = []
+
+
+def register_error_probe(library: str, function: str, what: str) -> None:
+    """A library whose kernels bound their waits keeps a status word on the device; ``function``
+    (no arguments, synchronises) returns it."""
+
+    if (library, function, what) not in _ERROR_PROBES:
+        _ERROR_PROBES.append((library, function, what))
+
+
+def check_kernel_errors() -> None:
+    """Raise ``KernelError`` if a bounded wait inside any loaded kernel library ever ran out.  A kernel
+    whose wait ran out finishes on incomplete data, so what it wrote must not be used."""
+
+    for library, function, what in list(_ERROR_PROBES):
+        if not library_loaded(library):
+            continue
+        code = query(function, library=library)
+        if code:
+            raise KernelError(f"{what}: a bounded wait ran out inside the kernel (status {code}); its results are invalid")
+
+
 def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 

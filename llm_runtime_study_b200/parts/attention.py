@@ -12,6 +12,7 @@ from ..weights.checkpoint import TensorSpec
 from ..weights.view import TensorView
 from .base import MIXERS, NORMS, POSITION_ENCODINGS, Mixer, PagedKV, Runtime
 from .linear import Projection
+from .norm import RMSNorm
 
 
 @MIXERS.register("gqa_attention")
@@ -46,7 +47,15 @@ class GroupedQueryAttention(Mixer):
         self.shares_kv = bool(shares_kv)
         self.q_norm = NORMS.build(qk_norm) if qk_norm else None
         self.k_norm = NORMS.build(qk_norm) if qk_norm else None
+        if qk_norm and not isinstance(self.q_norm, RMSNorm):
+            # the kernel that normalises, rotates and writes the cache in one pass computes an RMS norm
+            raise ValueError(f"gqa_attention normalises q and k with an rms_norm only; got the norm kind {qk_norm.get('kind')!r}")
         self.position = POSITION_ENCODINGS.build(position) if position else None
+
+    graph_safe = True
+
+    def children(self):
+        return tuple(p for p in (self.q_norm, self.k_norm, self.position) if p is not None)
 
     # ------------------------------------------------------------- weights
     def tensor_specs(self) -> dict[str, TensorSpec]:

@@ -23,6 +23,9 @@ Interfaces (all tensors live on the CUDA device; ``x`` is ``[tokens, width]``):
 ``FeedForward``     ``forward(x, ctx) -> float32 [tokens, hidden]``.
 ``Block``           ``forward(stream, ctx, cache)`` where ``stream`` carries the
                     residual rows and the not-yet-added output of the previous part.
+Embeddings (``forward(token_ids) -> float32 [tokens, hidden]``) and output heads
+(``forward(x) -> float32 [rows, vocab]``; ``load`` also gets ``embedding=`` for tied
+weights) are registered kinds too.
 """
 
 from __future__ import annotations
@@ -47,12 +50,14 @@ class Runtime:
     dtype: torch.dtype
 
     def place_matrix(self, t: torch.Tensor) -> torch.Tensor:
-        return t.to(device=self.device, dtype=self.dtype).contiguous()
+        """To the device as stored (for a mapped file: straight from its pages), then to the run type there."""
+
+        return t.to(device=self.device).to(dtype=self.dtype).contiguous()
 
     def place_vector_f32(self, t: torch.Tensor) -> torch.Tensor:
         """Norm weights and other small vectors are kept in float32 in both modes."""
 
-        return t.to(device=self.device, dtype=torch.float32).contiguous()
+        return t.to(device=self.device).to(dtype=torch.float32).contiguous()
 
 
 # ------------------------------------------------------- cache requirements
@@ -79,6 +84,23 @@ class FixedState:
 # ------------------------------------------------------------------ parts
 class Part:
     """Anything that owns weights."""
+
+    # Whether the part's launches may be recorded into a CUDA graph and replayed for other batches
+    # of the same size.  Such a part takes everything that changes from step to step out of device
+    # tensors of the context (``ctx.slots``, ``ctx.positions``, ``ctx.kv_len``, the block tables),
+    # never out of its host-side lists (under capture ``ctx.entry_slots`` is ``None`` and
+    # ``ctx.kv_lens`` holds upper bounds), launches the same kernels whatever the data, and lets rows
+    # that pad the batch (slot ``manager.padding_slot``, length 0) write only into that slot's row of
+    # its state.  The kinds of this package do; a kind registered from outside must say so itself.
+    graph_safe = False
+
+    def children(self) -> tuple["Part", ...]:
+        """The parts this part is made of (their weights live under its prefix)."""
+
+        return ()
+
+    def capture_safe(self) -> bool:
+        return bool(self.graph_safe) and all(child.capture_safe() for child in self.children())
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         return {}
@@ -170,6 +192,8 @@ class Registry:
         return tuple(sorted(self._kinds))
 
 
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("output head")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 MIXERS = Registry("mixer")

@@ -35,6 +35,11 @@ class PreNormBlock(Block):
         self.mixer_norm = NORMS.build(mixer_norm)
         self.ffn_norm = NORMS.build(ffn_norm)
 
+    graph_safe = True
+
+    def children(self):
+        return (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+
     def _parts(self):
         return (
             (self.names["mixer_norm"], self.mixer_norm),

@@ -8,12 +8,15 @@ import torch
 
 from ..ops import functional as F
 from ..weights.checkpoint import TensorSpec
-from .base import Part, Runtime
+from .base import EMBEDDINGS, HEADS, Part, Runtime
 from .linear import Projection
 
 
+@EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Part):
     """``h = E[token] * scale`` (mini_llm/model/base.py:72-74; Qwen3 uses scale 1)."""
+
+    graph_safe = True
 
     def __init__(self, *, vocab_size: int, hidden_size: int, scale: float = 1.0) -> None:
         self.vocab_size, self.hidden_size, self.scale = vocab_size, hidden_size, float(scale)
@@ -30,10 +33,13 @@ class TokenEmbedding(Part):
         return F.embedding(token_ids, self.weight, self.scale)
 
 
+@HEADS.register("linear_head")
 class OutputHead(Part):
     """``logits = h W^T`` in float32, no bias (mini_llm/model/qwen.py:112).  With
     ``tied`` the weight may be absent from the checkpoint; the embedding matrix
     is used then.  A stored ``lm_head.weight`` is always used when present."""
+
+    graph_safe = True
 
     def __init__(self, *, vocab_size: int, hidden_size: int, tied: bool = False) -> None:
         self.vocab_size, self.hidden_size, self.tied = vocab_size, hidden_size, bool(tied)

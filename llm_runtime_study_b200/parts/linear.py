@@ -38,13 +38,15 @@ class Projection:
 
     def __init__(self, weights: list[torch.Tensor], biases: list[torch.Tensor] | None, runtime: Runtime) -> None:
         self.runtime = runtime
-        stacked = weights[0] if len(weights) == 1 else torch.cat(list(weights), dim=0)
-        self.weight = runtime.place_matrix(stacked)
+        # each tensor goes to the device as it is (possibly straight from a mapped file); stacking happens there
+        placed = [runtime.place_matrix(w) for w in weights]
+        self.weight = placed[0] if len(placed) == 1 else torch.cat(placed, dim=0)
+        del placed
         self.out_features, self.in_features = self.weight.shape
         self.bias = None
         if biases:
-            b = biases[0] if len(biases) == 1 else torch.cat(list(biases), dim=0)
-            self.bias = b.to(device=runtime.device, dtype=torch.float32).contiguous()
+            placed = [runtime.place_vector_f32(b) for b in biases]
+            self.bias = placed[0] if len(placed) == 1 else torch.cat(placed, dim=0)
 
     def swiglu(self, x: torch.Tensor) -> torch.Tensor:
         """For a projection whose rows are gate and up features interleaved in blocks of

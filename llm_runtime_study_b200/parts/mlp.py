@@ -18,6 +18,8 @@ class SwiGLU(FeedForward):
     gate and up are one stacked product; the activation and the product with
     ``up`` are computed in float32 and rounded once."""
 
+    graph_safe = True
+
     def __init__(self, *, hidden_size: int, intermediate_size: int) -> None:
         if hidden_size <= 0 or intermediate_size <= 0:
             raise ValueError("swiglu sizes must be positive")
@@ -33,7 +35,7 @@ class SwiGLU(FeedForward):
 
     def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         self.runtime = runtime
-        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        gate, up = runtime.place_matrix(tensors["gate_proj.weight"]), runtime.place_matrix(tensors["up_proj.weight"])
         # When the width allows, gate and up rows are interleaved in blocks of eight
         # ([g0..g7, u0..u7, g8..g15, ...]): a projection kernel then holds matching gate and
         # up features in one tile and can apply SiLU * up before it writes anything.
@@ -41,7 +43,9 @@ class SwiGLU(FeedForward):
         if self.interleaved:
             blocks = self.intermediate_size // 8
             stacked = torch.stack((gate.view(blocks, 8, -1), up.view(blocks, 8, -1)), dim=1).reshape(2 * self.intermediate_size, -1)
+            del gate, up
             self.gate_up_proj = Projection([stacked], None, runtime)
+            del stacked
         else:
             self.gate_up_proj = Projection([gate, up], None, runtime)
         self.down_proj = Projection([tensors["down_proj.weight"]], None, runtime)

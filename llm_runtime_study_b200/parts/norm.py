@@ -17,6 +17,8 @@ class RMSNorm(Norm):
     applied as ``w`` (mini_llm/nn/norm.py:42-46).  Random weights are
     ``1 + N(0, 0.05)``."""
 
+    graph_safe = True
+
     def __init__(self, dim: int, eps: float) -> None:
         if dim <= 0 or eps <= 0:
             raise ValueError(f"rms_norm needs dim > 0 and eps > 0, got {dim}, {eps}")

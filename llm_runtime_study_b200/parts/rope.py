@@ -18,6 +18,8 @@ class RotaryEmbedding(PositionEncoding):
     ``(i, i + rotary_dim/2)`` (mini_llm/nn/rope.py:110-114).  ``rotary_dim``
     smaller than the head size leaves the remaining columns unrotated."""
 
+    graph_safe = True
+
     def __init__(self, head_dim: int, theta: float, rotary_dim: int | None = None) -> None:
         rotary_dim = head_dim if rotary_dim is None else rotary_dim
         if head_dim <= 0 or rotary_dim <= 0 or rotary_dim % 2 or rotary_dim > head_dim:

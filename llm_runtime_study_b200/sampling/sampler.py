@@ -20,6 +20,8 @@ native.register_library(
                         native.c_int, native.c_void_p],
         "b200_sample_chunked": [native.c_void_p, native.c_int, native.c_int, native.c_void_p, native.c_void_p,
                                 native.c_int, native.c_int, native.c_void_p, native.c_int, native.c_void_p],
+        "b200_sample_slots": [native.c_void_p, native.c_int, native.c_int, native.c_void_p, native.c_void_p, native.c_void_p,
+                              native.c_int, native.c_int, native.c_void_p, native.c_int, native.c_void_p],
     },
 )
 
@@ -94,3 +96,23 @@ class Sampler:
         if any(t < 0 for t in tokens):
             raise SamplingError("logits must contain only finite values")
         return tokens
+
+    def sample_slots(self, logits: torch.Tensor, records: torch.Tensor, row_slots: torch.Tensor, out: torch.Tensor, *,
+                     filtered: bool) -> None:
+        """Draw one token per row of ``logits`` with the options, seed and counter found in
+        the slot record ``records[row_slots[i]]``, write it into ``out[i]`` and, with the
+        advanced counter, back into the record.  Nothing is copied to the host and nothing
+        waits: the call may sit inside a CUDA-graph capture.  ``filtered``: some row uses
+        top-k or top-p (then the kernel for those rows runs too)."""
+
+        native.require(logits, "logits", dtype=torch.float32, dims=2)
+        n, vocab = logits.shape
+        native.require(records, "records", dtype=torch.int32, dims=2)
+        native.require(row_slots, "row_slots", dtype=torch.int32, shape=(n,))
+        native.require(out, "out", dtype=torch.int32, dims=1)
+        if n > self.max_rows or out.shape[0] < n:
+            raise SamplingError(f"at most {min(self.max_rows, out.shape[0])} rows can be sampled at once")
+        chunks = CHUNKS if vocab >= 4096 else 1
+        native.call("b200_sample_slots", logits.data_ptr(), logits.stride(0), vocab, records.data_ptr(), row_slots.data_ptr(),
+                    out.data_ptr(), n, chunks, self._scratch.data_ptr(), 1 if filtered else 0, native.stream_ptr(),
+                    launches=3 if filtered else 2)

@@ -2,9 +2,9 @@
 
 Locating rules follow mini_llm/checkpoint.py:83-137 (``model.safetensors`` if
 present, else ``model.safetensors.index.json`` whose ``weight_map`` names the
-shards).  Validation follows mini_llm/checkpoint.py:453-487: every name and shape
-is checked before any payload is read, and *all* problems are reported in one
-error.  The schema itself is not written here: each part of the model declares
+shards).  Validation follows mini_llm/checkpoint.py:453-487: every name, shape and
+storage type is checked before any payload is read, and *all* problems are reported
+in one error.  The schema itself is not written here: each part of the model declares
 the tensors it owns (``Part.tensor_specs``), and the model description joins them.
 """
 
@@ -18,15 +18,19 @@ from typing import Iterable, Mapping
 import torch
 
 from ..errors import CheckpointError, CheckpointValidationError
-from .safetensors_io import FLOAT_DTYPES, INT_DTYPES, TensorInfo, read_header, read_tensors
+from .safetensors_io import FLOAT_DTYPES, INT_DTYPES, TensorInfo, map_tensor, read_header, read_tensors
+from .view import TensorView
+
+# config.json's torch_dtype -> the safetensors type every floating tensor must then be stored in
+STORAGE_NAME = {"float32": "F32", "bfloat16": "BF16", "float16": "F16"}
 
 
 @dataclass(frozen=True, slots=True)
 class TensorSpec:
     """What the model expects of one stored tensor.
 
-    ``kind`` is ``"float"`` (any floating storage type is accepted and converted
-    at placement) or ``"int"`` (index tables; placed as int32).  ``init`` tells
+    ``kind`` is ``"float"`` (converted to the run type at placement) or ``"int"``
+    (index tables; placed as int32).  ``init`` tells
     the random-weights mode how to fill it: ``"normal"`` N(0, std),
     ``"one_plus_normal"`` 1 + N(0, std), ``"zeros"``.  ``optional`` tensors may
     be absent (a tied output head).
@@ -99,15 +103,29 @@ class Checkpoint:
         return name in self._by_name
 
     def get_tensors(self, names: Iterable[str] | None = None) -> dict[str, torch.Tensor]:
+        """Copies of the named tensors (all of them by default), in host memory."""
+
         wanted = self.names() if names is None else tuple(names)
         return read_tensors(self.info(name) for name in wanted)
 
+    def view(self) -> TensorView:
+        """The tensors by name, each mapped from its file when it is asked for and
+        dropped when the caller lets go of it (mini_llm/checkpoint.py:62-68: payloads
+        stay unmapped until needed).  This is what the model is loaded from."""
+
+        return TensorView(self.names(), lambda name: map_tensor(self.info(name)))
+
 
 def validate_manifest(
-    checkpoint: Checkpoint, expected: Mapping[str, TensorSpec], *, architecture: str
+    checkpoint: Checkpoint, expected: Mapping[str, TensorSpec], *, architecture: str, torch_dtype: str | None = None,
 ) -> None:
     """Raise one ``CheckpointValidationError`` listing every missing tensor,
-    every unexpected tensor, every wrong shape and every wrong storage class."""
+    every unexpected tensor, every wrong shape and every wrong storage type.
+
+    ``torch_dtype`` (config.json's): every floating tensor must be stored in exactly
+    that type, as the reference demands (mini_llm/checkpoint.py:290, 478-481), so a
+    mislabelled or mixed-precision checkpoint does not load silently.  ``None`` accepts
+    any floating storage type (it is converted at placement)."""
 
     actual = {info.name: info for info in checkpoint.manifest}
     errors: list[str] = []
@@ -124,6 +142,8 @@ def validate_manifest(
                 f"shape mismatch for {name}: expected {tuple(spec.shape)}, got {info.shape}"
             )
         allowed = FLOAT_DTYPES if spec.kind == "float" else INT_DTYPES
+        if spec.kind == "float" and torch_dtype is not None:
+            allowed = (STORAGE_NAME[torch_dtype],)
         if info.dtype not in allowed:
             errors.append(
                 f"dtype mismatch for {name}: expected one of {'/'.join(allowed)}, got {info.dtype}"

@@ -4,7 +4,8 @@ A safetensors file is an 8-byte little-endian header length, a JSON header that
 maps tensor names to ``{"dtype", "shape", "data_offsets"}``, and the raw tensor
 bytes.  The reference inspects headers first and leaves payloads unmapped until
 a tensor is asked for (mini_llm/checkpoint.py:62-68, :139-164); so does this
-module: ``read_header`` touches only the header, ``open_tensors`` memory-maps.
+module: ``read_header`` touches only the header, ``map_tensor`` maps the bytes of one
+tensor, and ``read_tensors`` returns copies that outlive the files.
 """
 
 from __future__ import annotations
@@ -98,30 +99,28 @@ def read_header(path: str | Path) -> list[TensorInfo]:
     return infos
 
 
-def read_tensors(infos: Iterable[TensorInfo]) -> dict[str, torch.Tensor]:
-    """Materialise tensors (CPU, stored dtype).  Each file is mapped once; the
-    returned tensors own copies, so the maps are closed before returning."""
+def map_tensor(info: TensorInfo) -> torch.Tensor:
+    """One stored tensor as a CPU tensor over a private mapping of just its bytes
+    (nothing is copied; pages come in as they are read).  The mapping lives as long
+    as the tensor does, so a loader that places one tensor after the other on the
+    device never holds more of the file in memory than the tensors it still uses."""
 
-    by_path: dict[Path, list[TensorInfo]] = {}
-    for info in infos:
-        by_path.setdefault(info.path, []).append(info)
-    out: dict[str, torch.Tensor] = {}
-    for path, group in by_path.items():
-        with open(path, "rb") as handle:
-            mapped = mmap.mmap(handle.fileno(), 0, access=mmap.ACCESS_READ)
-            try:
-                for info in group:
-                    dtype = _DTYPES[info.dtype][0]
-                    if info.num_elements == 0:
-                        out[info.name] = torch.empty(info.shape, dtype=dtype)
-                        continue
-                    view = memoryview(mapped)[info.begin : info.begin + info.num_bytes]
-                    flat = torch.frombuffer(bytearray(view), dtype=dtype)
-                    view.release()
-                    out[info.name] = flat.reshape(info.shape)
-            finally:
-                mapped.close()
-    return out
+    dtype = _DTYPES[info.dtype][0]
+    if info.num_elements == 0:
+        return torch.empty(info.shape, dtype=dtype)
+    start = info.begin - info.begin % mmap.ALLOCATIONGRANULARITY
+    with open(info.path, "rb") as handle:
+        # a private (copy-on-write) mapping is writable as far as torch is concerned, and never written
+        mapped = mmap.mmap(handle.fileno(), info.begin - start + info.num_bytes, access=mmap.ACCESS_COPY, offset=start)
+    flat = torch.frombuffer(mapped, dtype=dtype, count=info.num_elements, offset=info.begin - start)
+    return flat.reshape(info.shape)
+
+
+def read_tensors(infos: Iterable[TensorInfo]) -> dict[str, torch.Tensor]:
+    """Materialise tensors (CPU, stored dtype) as copies of their own, which stay
+    valid when the files change or disappear."""
+
+    return {info.name: map_tensor(info).clone() for info in infos}
 
 
 def write_file(path: str | Path, tensors: Mapping[str, torch.Tensor]) -> None:

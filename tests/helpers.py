@@ -55,8 +55,35 @@ def make_model_dir(path: Path, config: dict, seed: int, *, torch_dtype: str | No
     return path, Checkpoint.from_model_dir(path).get_tensors()
 
 
-def plain_logits(weights: dict, config: dict, token_ids, dtype=torch.float64) -> torch.Tensor:
-    return qwen3_plain.forward(weights, config, token_ids, dtype=dtype)
+def plain_logits(weights: dict, config: dict, token_ids, dtype=torch.float64, *, rows=None, rounded: bool = False) -> torch.Tensor:
+    """``rounded``: the plain model keeps its activations as a bfloat16 engine stores them."""
+
+    store = qwen3_plain.round_bfloat16 if rounded else qwen3_plain._keep
+    return qwen3_plain.forward(weights, config, token_ids, dtype=dtype, rows=rows, store=store)
+
+
+# Largest allowed |engine - plain| in a row of logits, as a fraction of the row's root mean square.
+# float32: the engine in 32-bit against the plain model in 64-bit: only the order of the sums differs.
+# bfloat16: the plain model (64-bit arithmetic) rounds its activations to bfloat16 where the engine
+# stores them, so what is left is the order of the sums, the rounding of the attention weights, and
+# roundings that fall the other way here and there.
+REPLAY_TOL = {"float32": 3e-4, "bfloat16": 3e-2}
+
+
+def plain_for(dtype: str, weights: dict, config: dict, token_ids, **kw) -> torch.Tensor:
+    """The plain logits an engine of run type ``dtype`` is compared with."""
+
+    return plain_logits(weights, config, token_ids, rounded=dtype == "bfloat16", **kw)
+
+
+def first_wrong_row(got: torch.Tensor, want: torch.Tensor, tol: float):
+    """(index of the first row whose error exceeds ``tol`` x its rms, or None; the worst error / rms).
+    A NaN anywhere in a row makes it wrong."""
+
+    rms = want.pow(2).mean(dim=1, keepdim=True).sqrt().clamp_min(1e-30)
+    err = ((got - want).abs() / rms).max(dim=1).values
+    bad = (~(err <= tol)).nonzero()
+    return (int(bad[0]) if bad.numel() else None), float(err.max())
 
 
 def random_tokens(rng: random.Random, vocab: int, length: int) -> list[int]:

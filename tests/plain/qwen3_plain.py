@@ -5,6 +5,13 @@ restates.  It shares no code with the engine: it takes a ``config.json`` dict
 and a ``{tensor name: tensor}`` dict with the checkpoint's own names, and uses
 only elementary torch operations (matmul, exp, sum, ...).  ``dtype`` is the
 arithmetic type (float32, or float64 to separate rounding from faults).
+
+``store`` (optional) is applied wherever a serving engine with 16-bit activations
+keeps a tensor in memory between two operations: the normalised rows, the q/k/v
+rows, q and k after the rotation, the attention output, and silu(gate) * up.  With
+``store=round_bfloat16`` the plain model carries the same roundings as such an
+engine and what is left between the two is the order of the sums; the residual
+stream, the statistics and the logits stay in ``dtype`` either way.
 """
 
 from __future__ import annotations
@@ -13,6 +20,16 @@ import math
 from typing import Mapping
 
 import torch
+
+
+def _keep(x: torch.Tensor) -> torch.Tensor:
+    return x
+
+
+def round_bfloat16(x: torch.Tensor) -> torch.Tensor:
+    """Round to the nearest bfloat16 and widen again."""
+
+    return x.to(torch.bfloat16).to(x.dtype)
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -28,7 +45,7 @@ def rotary_tables(positions: torch.Tensor, head_dim: int, theta: float, dtype: t
     share the angles (mini_llm/nn/rope.py:37-40, 74-80).  Angles are formed in
     float32 exactly as the reference does, then widened to ``dtype``."""
 
-    dims = torch.arange(0, head_dim, 2, dtype=torch.float32)
+    dims = torch.arange(0, head_dim, 2, dtype=torch.float32, device=positions.device)
     inv_freq = 1.0 / (theta ** (dims / head_dim))
     angles = positions.to(torch.float32).unsqueeze(-1) * inv_freq  # [T, d/2]
     angles = torch.cat((angles, angles), dim=-1).to(torch.float64)
@@ -54,7 +71,7 @@ def causal_attention(q, k, v, scale: float, window: int | None = None) -> torch.
     nkv = k.shape[1]
     group = nq // nkv
     out = torch.empty_like(q)
-    idx = torch.arange(T)
+    idx = torch.arange(T, device=q.device)
     visible = idx.view(1, T) <= idx.view(T, 1)
     if window is not None:
         visible &= idx.view(1, T) > idx.view(T, 1) - window
@@ -69,7 +86,7 @@ def causal_attention(q, k, v, scale: float, window: int | None = None) -> torch.
     return out
 
 
-def attention_block(x, w: Mapping[str, torch.Tensor], prefix: str, cfg, cos, sin) -> torch.Tensor:
+def attention_block(x, w: Mapping[str, torch.Tensor], prefix: str, cfg, cos, sin, store=_keep) -> torch.Tensor:
     """q/k/v projections, head split, per-head q/k RMSNorm before rotary, rotation,
     causal GQA attention, merge heads, output projection without bias
     (mini_llm/nn/attention.py:161-181, 250-254, 291-302)."""
@@ -83,47 +100,51 @@ def attention_block(x, w: Mapping[str, torch.Tensor], prefix: str, cfg, cos, sin
         q = q + w[f"{prefix}.q_proj.bias"]
         k = k + w[f"{prefix}.k_proj.bias"]
         v = v + w[f"{prefix}.v_proj.bias"]
-    q, k, v = q.view(T, nq, d), k.view(T, nkv, d), v.view(T, nkv, d)
+    q, k, v = store(q).view(T, nq, d), store(k).view(T, nkv, d), store(v).view(T, nkv, d)
     q = rms_norm(q, w[f"{prefix}.q_norm.weight"], cfg["rms_norm_eps"])
     k = rms_norm(k, w[f"{prefix}.k_norm.weight"], cfg["rms_norm_eps"])
-    q, k = rotate(q, cos, sin), rotate(k, cos, sin)
-    o = causal_attention(q, k, v, 1.0 / math.sqrt(d))
+    q, k = store(rotate(q, cos, sin)), store(rotate(k, cos, sin))
+    o = store(causal_attention(q, k, v, 1.0 / math.sqrt(d)))
     return o.reshape(T, nq * d) @ w[f"{prefix}.o_proj.weight"].T
 
 
-def swiglu(x, w: Mapping[str, torch.Tensor], prefix: str) -> torch.Tensor:
+def swiglu(x, w: Mapping[str, torch.Tensor], prefix: str, store=_keep) -> torch.Tensor:
     """down(silu(gate(x)) * up(x)), silu(z) = z * sigmoid(z), no biases
     (mini_llm/nn/mlp.py:80-87)."""
 
     gate = x @ w[f"{prefix}.gate_proj.weight"].T
     up = x @ w[f"{prefix}.up_proj.weight"].T
-    return ((gate / (1.0 + torch.exp(-gate))) * up) @ w[f"{prefix}.down_proj.weight"].T
+    return store((gate / (1.0 + torch.exp(-gate))) * up) @ w[f"{prefix}.down_proj.weight"].T
 
 
-def decoder_layer(h, w, layer: int, cfg, cos, sin) -> torch.Tensor:
+def decoder_layer(h, w, layer: int, cfg, cos, sin, store=_keep) -> torch.Tensor:
     """Pre-norm block: h = h + Attn(norm_in(h)); h = h + MLP(norm_post(h))
     (mini_llm/model/qwen.py:58-72)."""
 
     p = f"model.layers.{layer}"
     eps = cfg["rms_norm_eps"]
-    h = h + attention_block(rms_norm(h, w[f"{p}.input_layernorm.weight"], eps), w, f"{p}.self_attn", cfg, cos, sin)
-    h = h + swiglu(rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], eps), w, f"{p}.mlp")
+    h = h + attention_block(store(rms_norm(h, w[f"{p}.input_layernorm.weight"], eps)), w, f"{p}.self_attn", cfg, cos, sin, store)
+    h = h + swiglu(store(rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], eps)), w, f"{p}.mlp", store)
     return h
 
 
-def forward(weights: Mapping[str, torch.Tensor], cfg: Mapping, token_ids, dtype=torch.float32) -> torch.Tensor:
-    """Logits [T, vocab] for one whole sequence starting at position 0: embedding
+def forward(weights: Mapping[str, torch.Tensor], cfg: Mapping, token_ids, dtype=torch.float32, *, rows=None,
+            store=_keep) -> torch.Tensor:
+    """Logits [T, vocab] (or only at the positions ``rows``) for one whole sequence starting at position 0: embedding
     without scaling, rotary tables once, the layers in order, the final norm on every
     row, the output head without bias (mini_llm/model/base.py:72-89,
     mini_llm/model/qwen.py:112).  A tied head (no ``lm_head.weight`` stored) uses the
     embedding matrix."""
 
     w = {name: t.to(dtype) for name, t in weights.items()}
-    ids = torch.as_tensor(token_ids, dtype=torch.long)
+    device = w["model.embed_tokens.weight"].device
+    ids = torch.as_tensor(token_ids, dtype=torch.long, device=device)
     h = w["model.embed_tokens.weight"][ids]
-    cos, sin = rotary_tables(torch.arange(ids.shape[0]), cfg["head_dim"], float(cfg["rope_theta"]), dtype)
+    cos, sin = rotary_tables(torch.arange(ids.shape[0], device=device), cfg["head_dim"], float(cfg["rope_theta"]), dtype)
     for layer in range(cfg["num_hidden_layers"]):
-        h = decoder_layer(h, w, layer, cfg, cos, sin)
-    h = rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
+        h = decoder_layer(h, w, layer, cfg, cos, sin, store)
+    if rows is not None:
+        h = h[torch.as_tensor(rows, dtype=torch.long, device=device)]
+    h = store(rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"]))
     head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
     return h @ head.T

@@ -87,7 +87,8 @@ def test_slots_run_out_and_state_is_zeroed():
     with pytest.raises(KVCacheError, match="slots"):
         m.admit()
     state = m.layer_cache(2).state
-    assert state.shape == (2, 3)
+    assert state.shape == (2 + 1, 3)          # one row per request slot and the row of the padding slot
+    assert m.padding_slot == 2 and m.slots.records.shape == (3, 12)
     state[a.slot] = 7.0
     m.release(a)
     c = m.admit()

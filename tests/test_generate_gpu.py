@@ -89,6 +89,52 @@ def test_seeded_temperature_generation_matches_plain(tmp_path):
         assert_same_until_a_tie(runs[0][i], want, gaps, 1e-4)
 
 
+@pytest.mark.parametrize("sampled", [False, True], ids=["greedy", "temperature"])
+@pytest.mark.parametrize("policy", ["on_demand", "reserve"])
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("B", "bfloat16")])
+def test_pool_too_small_for_all_requests(tmp_path, name, dtype, policy, sampled):
+    """Five requests against a pool that holds about half of what they need together.  Taking pages
+    on demand, the request admitted last is preempted when the pages run out and is recomputed
+    later; its tokens, greedy or drawn with a seed, are those of the plain loop all the same (the
+    seeded stream continues where it was).  Reserving whole lifetimes at admission (the reference's
+    rule), nobody is preempted and requests wait instead.  Nothing is left in the pool afterwards."""
+
+    from llm_runtime_study_b200.engine.engine import Engine
+    from llm_runtime_study_b200.sampling import SamplingConfig
+
+    raw, seed, page = helpers.TINY[name]
+    path, weights = helpers.make_model_dir(tmp_path / "m", raw, seed, torch_dtype=dtype)
+    eos = raw["eos_token_id"] if isinstance(raw["eos_token_id"], list) else [raw["eos_token_id"]]
+    rng = random.Random(17)
+    prompts = [helpers.random_tokens(rng, raw["vocab_size"], n) for n in (9, 20, 14, 30, 5)]
+    new_tokens = 24
+    engine = Engine.from_model_dir(path, device="cuda:0", dtype=dtype, max_seq_len=128, max_batch_size=4,
+                                   page_size=page, max_tokens_per_step=16, max_cache_tokens=96, page_policy=policy)
+    sampling = SamplingConfig(temperature=0.7, seed=1234) if sampled else SamplingConfig()
+    scheduler = engine.create_scheduler()
+    index_of = {scheduler.add_request(p, max_new_tokens=new_tokens, sampling=sampling): i for i, p in enumerate(prompts)}
+    out = {i: [] for i in range(len(prompts))}
+    while scheduler.has_unfinished:
+        for index, event in scheduler.step():
+            out[index_of[index]].append(event)
+        engine.cache_manager.check()
+    if policy == "on_demand":
+        assert scheduler.stats["preemptions"] > 0
+    else:
+        assert scheduler.stats["preemptions"] == 0
+    tie = (1e-5 if dtype == "float32" else 3e-2) * (4 if sampled else 1)
+    for i, prompt in enumerate(prompts):
+        kw = dict(temperature=0.7, seed=1234) if sampled else {}
+        want, gaps = plain_generate(weights, raw, prompt, new_tokens, eos=eos, **kw)
+        got = [e.token_id for e in out[i]]
+        assert [e.token_index for e in out[i]] == list(range(len(got)))         # no event twice, none missing
+        assert_same_until_a_tie(got, want, gaps, tie)
+        assert out[i][-1].finish_reason in ("max_new_tokens", "eos")
+    manager = engine.cache_manager
+    manager.check()
+    assert manager.active_sequences == 0 and manager.free_pages == manager.num_pages and manager.free_slots == 4
+
+
 def test_command_line(tmp_path):
     from llm_runtime_study_b200.cli import main
 
@@ -115,35 +161,56 @@ def test_command_line(tmp_path):
     assert main(["--model", str(tmp_path / "none"), "--prompt-ids", "1"], output=out, error=err) == 2
 
 
+def _decode_both_ways(loaded, prompts, live_by_step, *, page, max_seq_len, sampling):
+    """Prefill the prompts, then decode with tokens drawn on the device, eagerly and from CUDA
+    graphs; returns for each way the drawn ids and the logits of every step."""
+
+    from llm_runtime_study_b200.cache.slots import SlotRecord
+    from llm_runtime_study_b200.engine.step import StepEntry
+    from llm_runtime_study_b200.sampling import Sampler
+
+    results = []
+    for use_graph in (False, True):
+        runner = loaded.make_runner(max_tokens=len(prompts) * max_seq_len, page_size=page, max_requests=len(prompts),
+                                    max_seq_len=max_seq_len)
+        runner.use_cuda_graph = use_graph
+        sampler = Sampler(loaded.runtime.device, max_rows=len(prompts))
+        requests = [runner.manager.admit() for _ in prompts]
+        records = [SlotRecord(position=0, temperature=sampling.temperature, top_k=sampling.top_k or 0, top_p=sampling.top_p,
+                              seed=sampling.seed or 0, counter=0) for _ in prompts]
+        first = runner.step_sampled([StepEntry(r, p, [len(p) - 1], rec) for r, p, rec in zip(requests, prompts, records)], sampler)
+        ids, logits = [first.tokens()], [runner.last_logits.clone()]
+        for live in live_by_step:
+            handle = runner.decode_sampled([requests[i] for i in live], sampler)
+            ids.append(handle.tokens())
+            logits.append(runner.last_logits.clone())
+        assert (runner._graphs is not None) is use_graph
+        runner.manager.check()
+        results.append((ids, logits))
+    return results
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_cuda_graph_decode_equals_eager(tmp_path, dtype):
-    """The captured decode step gives the same logits as the eager step, for
-    several batch sizes, ragged lengths and a block table that changes."""
+    """The captured decode step (slot records in, drawn tokens out) gives the same logits and the
+    same tokens as the same launches issued one by one, for several batch sizes (one padded up to
+    its bucket), ragged lengths, block tables that change, greedy and seeded draws."""
 
     from llm_runtime_study_b200.engine.runtime import load
-    from llm_runtime_study_b200.engine.step import StepEntry
+    from llm_runtime_study_b200.sampling import SamplingConfig
 
     raw, seed, page = helpers.TINY["B"]
     path, _ = helpers.make_model_dir(tmp_path / "m", raw, seed, torch_dtype=dtype)
     loaded = load(path, device="cuda:0", dtype=dtype)
     rng = random.Random(6)
     prompts = [helpers.random_tokens(rng, raw["vocab_size"], n) for n in (3, 30, 9, 17)]
-    follow = [helpers.random_tokens(rng, raw["vocab_size"], 12) for _ in prompts]
-
-    def run(use_graph):
-        runner = loaded.make_runner(max_tokens=512, page_size=page, max_requests=4, max_seq_len=128)
-        runner.use_cuda_graph = use_graph
-        requests = [runner.manager.admit() for _ in prompts]
-        runner.step([StepEntry(r, p, []) for r, p in zip(requests, prompts)])
-        rows = []
-        for t in range(12):
-            live = requests if t < 6 else (requests[:3] if t < 9 else requests[:2])   # 4, then 3 (padded to 4), then 2
-            logits = runner.step([StepEntry(r, [f[t]], [0]) for r, f in zip(live, follow)])
-            rows.append(logits.clone())
-        return torch.cat(rows)
-
-    eager, captured = run(False), run(True)
-    assert torch.equal(eager, captured)
+    live = [[0, 1, 2, 3]] * 6 + [[0, 1, 2]] * 3 + [[0, 1]] * 3          # 4, then 3 (padded to 4), then 2
+    for sampling in (SamplingConfig(), SamplingConfig(temperature=0.8, seed=99), SamplingConfig(temperature=0.8, top_k=20, top_p=0.9, seed=5)):
+        (eager_ids, eager_logits), (graph_ids, graph_logits) = _decode_both_ways(
+            loaded, prompts, live, page=page, max_seq_len=128, sampling=sampling)
+        assert eager_ids == graph_ids
+        for a, b in zip(eager_logits, graph_logits):
+            assert torch.equal(a, b)
 
 
 def test_graph_buckets_pad_with_empty_rows(tmp_path):
@@ -155,8 +222,13 @@ def test_graph_buckets_pad_with_empty_rows(tmp_path):
     class Runner:
         manager = Manager()
 
+    from llm_runtime_study_b200.engine.graph import length_class
+
     graphs = DecodeGraphs(Runner())
     assert [graphs.bucket(n) for n in (1, 2, 3, 5, 8, 9, 33, 48)] == [1, 2, 4, 8, 8, 16, 48, 48]
+    # lengths are captured under bounds a quarter of a power of two apart (at least 512), never above the limit
+    assert [length_class(n, 4096) for n in (1, 512, 513, 2049, 2560, 2561, 4000)] == [512, 512, 1024, 2560, 2560, 3072, 4096]
+    assert length_class(9000, 40960) == 10240 and length_class(300, 384) == 384
 
 
 def test_engine_to_and_cache_handles(tmp_path):

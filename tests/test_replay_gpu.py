@@ -19,10 +19,7 @@ pytestmark = pytest.mark.gpu
 
 ROOT = Path(__file__).resolve().parent.parent
 LENGTHS = {"A": [1, 2, 7, 19, 64, 65, 130, 200], "B": [2, 9, 16, 33, 70, 257, 129, 48], "C": [3, 40, 100, 31, 17]}
-# float32: only summation order differs from the float64 plain model.
-# bfloat16: the plain model runs on the same bfloat16 weights in float64; what is
-# left is the rounding of activations (2^-9 relative each) through the layers.
-TOL = {"float32": dict(atol=2e-5, rtol=1e-4), "bfloat16": dict(atol=2.5e-2, rtol=2e-2)}
+TOL = helpers.REPLAY_TOL      # error of a row of logits as a fraction of its root mean square
 
 
 def _requests(name):
@@ -40,7 +37,7 @@ def setup(request, tmp_path_factory):
     raw, seed, page = helpers.TINY[name]
     path, weights = helpers.make_model_dir(tmp_path_factory.mktemp(f"model{name}{dtype}"), raw, seed, torch_dtype=dtype)
     requests = _requests(name)
-    plain = {rid: helpers.plain_logits(weights, raw, toks) for rid, toks in requests.items()}
+    plain = {rid: helpers.plain_for(dtype, weights, raw, toks) for rid, toks in requests.items()}
     loaded = load(path, device="cuda:0", dtype=dtype)
     return dict(name=name, dtype=dtype, raw=raw, page=page, path=path, requests=requests, plain=plain, loaded=loaded)
 
@@ -65,13 +62,11 @@ def _compare(setup, got):
     for rid, tokens in setup["requests"].items():
         assert sorted(got[rid]) == list(range(len(tokens))), rid
         rows = torch.stack([got[rid][p] for p in range(len(tokens))]).double()
-        want = setup["plain"][rid]
-        diff = (rows - want).abs()
-        worst = max(worst, float(diff.max()))
-        bad = (diff > TOL[setup["dtype"]]["atol"] + TOL[setup["dtype"]]["rtol"] * want.abs()).any(dim=1).nonzero()
-        assert bad.numel() == 0, (
-            f"request {rid}: first wrong position {int(bad[0])} of {len(tokens)} "
-            f"(page size {setup['page']}), max |diff| {float(diff.max()):.3e}"
+        bad, err = helpers.first_wrong_row(rows, setup["plain"][rid], TOL[setup["dtype"]])
+        worst = max(worst, err)
+        assert bad is None, (
+            f"request {rid}: first wrong position {bad} of {len(tokens)} "
+            f"(page size {setup['page']}), worst |diff| / rms {err:.3e}"
         )
     return worst
 
@@ -91,10 +86,21 @@ def test_chunked(setup):
     _compare(setup, got)
 
 
+def fed_before(steps, step, rid) -> int:
+    """Tokens of request ``rid`` fed in the steps before ``step``."""
+
+    return sum(len(e["tokens"]) for s in steps if s["step"] < step["step"] for e in s["entries"] if e["id"] == rid)
+
+
 def test_mixed_with_page_reuse(setup):
     steps = helpers.trace_mixed(setup["requests"], random.Random(5))
     assert max(len(s["entries"]) for s in steps) >= 3
-    assert any(len(e["tokens"]) > 1 for s in steps if len(s["entries"]) > 1 for e in s["entries"])
+    # a single decoded token of one request beside a portion of another, in one step
+    assert any(
+        any(len(e["tokens"]) == 1 and fed_before(steps, s, e["id"]) > 0 for e in s["entries"])
+        and any(len(e["tokens"]) > 1 for e in s["entries"])
+        for s in steps
+    )
     budget = helpers.pool_tokens(steps)
     assert budget < sum(-(-len(t) // 64) * 64 for t in setup["requests"].values())   # pages must come back
     got, manager = _replay(setup, steps, max_tokens=budget)
@@ -128,12 +134,11 @@ def test_long_decoding(setup):
     from llm_runtime_study_b200.weights import Checkpoint
 
     weights = Checkpoint.from_model_dir(setup["path"]).get_tensors()
-    want = helpers.plain_logits(weights, raw, tokens)
+    want = helpers.plain_for(setup["dtype"], weights, raw, tokens)
     replayer = TraceReplayer(setup["loaded"], max_tokens=256, page_size=setup["page"])
     rows = torch.stack([torch.from_numpy(np.array(replayer.run_step(s)))[0] for s in steps]).double()
-    diff = (rows - want).abs()
-    bad = (diff > TOL[setup["dtype"]]["atol"] + TOL[setup["dtype"]]["rtol"] * want.abs()).any(dim=1).nonzero()
-    assert bad.numel() == 0, f"first wrong position {int(bad[0])}, max |diff| {float(diff.max()):.3e}"
+    bad, err = helpers.first_wrong_row(rows, want, TOL[setup["dtype"]])
+    assert bad is None, f"first wrong position {bad}, worst |diff| / rms {err:.3e}"
 
 
 def test_trace_run_program(setup, tmp_path):

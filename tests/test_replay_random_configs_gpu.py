@@ -13,7 +13,7 @@ from tests import helpers
 
 pytestmark = pytest.mark.gpu
 
-TOL = {"float32": (2e-5, 1e-4), "bfloat16": (2.5e-2, 2e-2)}
+TOL = helpers.REPLAY_TOL
 
 
 def _configuration(case: int):
@@ -47,14 +47,13 @@ def test_random_configuration(case, dtype, tmp_path):
     raw, lengths, rng = _configuration(case)
     path, weights = helpers.make_model_dir(tmp_path / "model", raw, case, torch_dtype=dtype)
     requests = {f"r{i}": helpers.random_tokens(rng, raw["vocab_size"], n) for i, n in enumerate(lengths)}
-    plain = {rid: helpers.plain_logits(weights, raw, tokens) for rid, tokens in requests.items()}
+    plain = {rid: helpers.plain_for(dtype, weights, raw, tokens) for rid, tokens in requests.items()}
     loaded = load(path, device="cuda:0", dtype=dtype)
     traces = {
         "whole": helpers.trace_whole(requests),
         "mixed": helpers.trace_mixed(requests, random.Random(case), sizes=(2, 3, 8, 40, 130, 260)),
         "portions": helpers.trace_chunked(requests, random.Random(case), sizes=(2, 17, 64, 128, 129, 250)),
     }
-    atol, rtol = TOL[dtype]
     for kind, steps in traces.items():
         replayer = TraceReplayer(loaded, max_tokens=helpers.pool_tokens(steps))
         outputs = {}
@@ -66,9 +65,8 @@ def test_random_configuration(case, dtype, tmp_path):
         got = helpers.collect_logits(steps, outputs)
         for rid, tokens in requests.items():
             rows = torch.stack([got[rid][p] for p in range(len(tokens))]).double()
-            diff = (rows - plain[rid]).abs()
-            bad = (~(diff <= atol + rtol * plain[rid].abs())).any(dim=1).nonzero()
-            assert bad.numel() == 0, (
-                f"{kind}, request {rid}: first wrong position {int(bad[0])} of {len(tokens)}, "
-                f"max |diff| {float(diff.max()):.3e}; configuration {raw}"
+            bad, err = helpers.first_wrong_row(rows, plain[rid], TOL[dtype])
+            assert bad is None, (
+                f"{kind}, request {rid}: first wrong position {bad} of {len(tokens)}, "
+                f"worst |diff| / rms {err:.3e}; configuration {raw}"
             )

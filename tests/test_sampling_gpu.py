@@ -94,3 +94,60 @@ def test_non_finite_logits_are_an_error(sampler):
         sampler.sample(logits.cuda(), [(cfg(), 0, 0)] * 2)
     with pytest.raises(SamplingError, match="top_k"):
         sampler.sample(torch.zeros(1, 10).cuda(), [(cfg(temperature=1.0, top_k=11), 0, 0)])
+
+
+@pytest.mark.parametrize("vocab", [503, 151936])
+def test_drawing_out_of_slot_records_equals_drawing_out_of_rows_and_writes_back(sampler, vocab):
+    """The same kernels with their per-row options taken from the requests' slot records: the same tokens,
+    and each record afterwards holds the drawn token and a counter advanced by one; other records and the
+    other words of the drawn ones are untouched."""
+
+    from llm_runtime_study_b200.cache.slots import COUNTER, LAST_TOKEN, SLOT_WORDS, SlotRecord, SlotTable
+
+    torch.manual_seed(3)
+    options = [dict(), dict(temperature=0.7), dict(temperature=1.1, top_k=7), dict(temperature=0.9, top_p=0.7), dict(),
+               dict(temperature=1.0, top_k=30, top_p=0.9)]
+    rows = len(options)
+    logits = (torch.randn(rows, vocab) * 3).cuda()
+    specs = [(cfg(**o), (1 << 40) + 17 * r, 5 + r) for r, o in enumerate(options)]
+    want = sampler.sample(logits, specs)
+    table = SlotTable(16, torch.device("cuda:0"))
+    slots = [9, 2, 15, 0, 7, 4]                                   # rows and slots are in different orders
+    for slot, (c, seed, counter) in zip(slots, specs):
+        table.note(slot, SlotRecord(position=100 + slot, temperature=c.temperature, top_k=c.top_k or 0, top_p=c.top_p,
+                                    seed=seed, counter=counter, last_token=-7))
+    table.records.copy_(torch.from_numpy(table.mirror))
+    before = table.records.clone()
+    out = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    sampler.sample_slots(logits, table.records, torch.tensor(slots, dtype=torch.int32, device="cuda"), out, filtered=True)
+    assert out.tolist() == want
+    after = table.records.cpu()
+    expect = before.cpu().clone()
+    for slot, token, (_, _, counter) in zip(slots, want, specs):
+        expect[slot, LAST_TOKEN] = token
+        expect[slot, COUNTER] = counter + 1
+    assert torch.equal(after, expect) and after.shape == (17, SLOT_WORDS)
+
+
+def test_slot_records_feed_a_decode_step():
+    """``slot_store`` writes records by slot; ``slot_load`` turns the records of a batch's slots into token
+    ids, positions and lengths, advances the positions of live records and leaves the padding record alone."""
+
+    from llm_runtime_study_b200.cache.slots import POSITION, SlotRecord, SlotTable
+    from llm_runtime_study_b200.ops import slots as slot_ops
+
+    table = SlotTable(6, torch.device("cuda:0"))
+    chosen = [4, 1, 3]
+    staged = torch.tensor([SlotRecord(position=10 * s, last_token=100 + s, temperature=0.5, counter=s).words() for s in chosen],
+                          dtype=torch.int32, device="cuda")
+    slot_ops.slot_store(table.records, staged, torch.tensor(chosen, dtype=torch.int32, device="cuda"))
+    got = table.records.cpu()
+    assert torch.equal(got[chosen], staged.cpu()) and int(got[[0, 2, 5, 6]].abs().sum()) == 0
+    batch = torch.tensor([3, table.padding_slot, 4, 1], dtype=torch.int32, device="cuda")
+    ids, pos, lens = (torch.full((4,), -9, dtype=torch.int32, device="cuda") for _ in range(3))
+    slot_ops.slot_load(table.records, batch, ids, pos, lens)
+    assert ids.tolist() == [103, 0, 104, 101] and pos.tolist() == [30, 0, 40, 10] and lens.tolist() == [31, 0, 41, 11]
+    after = table.records.cpu()
+    assert after[:, POSITION].tolist() == [0, 11, 0, 31, 41, 0, 0]
+    slot_ops.slot_load(table.records, batch, ids, pos, lens)                    # the next step continues from there
+    assert pos.tolist() == [31, 0, 41, 11]

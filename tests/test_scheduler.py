@@ -221,3 +221,139 @@ def test_seeds_and_counters_reach_the_sampler():
     first = [row for rows in sampler.rows for row in rows if row[1] == 1234]
     assert [c for _, _, c in first] == [0, 1, 2] and all(t == 0.7 for t, _, _ in first)
     assert {row[1] for rows in sampler.rows for row in rows} == {1234, 77}
+
+
+# ------------------------------------------------------------------------------------------------
+# Tokens drawn "on the device": the scheduler launches a step and reads its tokens one call later.
+# The device side is emulated on the CPU (slot records in a dict, the draw is an argmax), so that
+# the scheduler's decisions on this path can be checked without a GPU against the host path above.
+
+class _Handle:
+    def __init__(self, ids):
+        self._ids = ids
+
+    def tokens(self):
+        return list(self._ids)
+
+
+class EmulatedDeviceRunner(StepRunner):
+    """``step_sampled`` / ``decode_sampled`` with the records kept in a dict: token and counter per slot."""
+
+    def __init__(self, *args, **kw):
+        super().__init__(*args, **kw)
+        self.records = {}
+        self.calls = []
+
+    def _draw(self, ctx, entries, drawn):
+        logits = self.model.forward(ctx)
+        for entry, length in zip(entries, ctx.kv_lens):
+            self.manager.commit(entry.request, length)
+        ids = logits.argmax(dim=-1).tolist() if logits is not None else []
+        for (entry, counter), token in zip(drawn, ids):
+            self.records[entry.request.slot] = {"token": token, "counter": counter + 1}
+        return _Handle(ids) if drawn else None
+
+    def step_sampled(self, entries, sampler):
+        self.calls.append("step")
+        ctx = self.build_context(entries)
+        return self._draw(ctx, entries, [(e, e.sample.counter) for e in entries if e.sample is not None])
+
+    def decode_sampled(self, requests, sampler):
+        from llm_runtime_study_b200.engine.step import StepEntry
+
+        self.calls.append("decode")
+        entries = [StepEntry(r, [self.records[r.slot]["token"]], [0]) for r in requests]
+        ctx = self.build_context(entries)
+        return self._draw(ctx, entries, [(e, self.records[e.request.slot]["counter"]) for e in entries])
+
+
+class SlotSampler(ArgmaxSampler):
+    def sample_slots(self, *args, **kw):        # its presence is what the scheduler looks for
+        raise AssertionError("the emulated runner draws by itself")
+
+
+def make_device(pool_tokens=64, page=4, batch=4, budget=16, seq=32, policy="on_demand", check=None):
+    layout = CacheLayout.from_requirements([PagedKV(1, 16)])
+    manager = CacheManager(layout, max_tokens=pool_tokens, page_size=page, max_requests=batch,
+                           dtype=torch.float32, device="cpu", max_seq_len=seq)
+    model = ScriptedModel()
+    runner = EmulatedDeviceRunner(model, manager, Runtime(torch.device("cpu"), torch.float32), vocab_size=VOCAB, max_positions=seq)
+    scheduler = Scheduler(runner, SlotSampler(), max_batch_size=batch, max_seq_len=seq, eos_token_ids=[EOS],
+                          vocab_size=VOCAB, max_tokens_per_step=budget, policy=policy, seed_source=lambda: 77,
+                          check_kernels=check)
+    assert scheduler.device_sampling
+    return scheduler, model, manager, runner
+
+
+WORKLOAD = [([3, 4, 5], 6), ([46], 10), (list(range(10, 23)), 5), ([7], 1), ([20, 21], 9), ([44, 45, 46], 8)]
+
+
+@pytest.mark.parametrize("pool,budget,batch", [(64, 16, 4), (24, 5, 3), (40, 7, 2)])
+def test_device_path_emits_what_the_host_path_emits(pool, budget, batch):
+    outs = []
+    for factory in (make, make_device):
+        s, model, manager, _ = factory(pool_tokens=pool, budget=budget, batch=batch)
+        for prompt, n in WORKLOAD:
+            s.add_request(prompt, max_new_tokens=n)
+        out = drain(s)
+        manager.check()
+        assert manager.active_sequences == 0 and manager.free_pages == manager.num_pages
+        outs.append({i: [(e.token_id, e.token_index, e.finish_reason, e.prompt_token_count) for e in ev] for i, ev in out.items()})
+    assert outs[0] == outs[1]
+
+
+def test_decode_steps_are_launched_before_the_tokens_of_the_step_before_are_read():
+    s, model, manager, runner = make_device()
+    s.add_request([3, 4, 5], max_new_tokens=5)
+    assert s.step() == []                          # the prompt is launched; its token is not read yet
+    first = s.step()                               # nothing but decoding: step 2 is launched, then step 1 read
+    assert [e.token_id for _, e in first] == [6] and runner.calls == ["step", "decode"]
+    out = drain(s)
+    assert tokens(out[0]) == [7, 8, 9, 10] and out[0][-1].finish_reason == "max_new_tokens"
+    # five tokens cost one prompt step and four decode steps: the last token never pays a decode, chained or not
+    assert runner.calls == ["step"] + ["decode"] * 4 and s.stats["chained_steps"] >= 3
+
+
+def test_an_eos_found_out_a_step_late_costs_one_dropped_token():
+    s, model, manager, runner = make_device()
+    s.add_request([46], max_new_tokens=10)         # 47, 48, 49 = EOS
+    out = drain(s)
+    assert tokens(out[0]) == [47, 48, 49] and out[0][-1].finish_reason == "eos"
+    assert runner.calls == ["step", "decode", "decode", "decode"]     # the third decode fed the EOS token: dropped
+    assert manager.active_sequences == 0 and manager.free_pages == manager.num_pages
+    manager.check()
+
+
+def test_an_arrival_breaks_the_chain_and_joins():
+    s, model, manager, runner = make_device(budget=8)
+    s.add_request([1, 2], max_new_tokens=8)
+    early = [e.token_id for _ in range(3) for _, e in s.step()]
+    s.add_request([30, 31, 32], max_new_tokens=3)
+    out = drain(s)
+    assert early + tokens(out[0]) == list(range(3, 11)) and tokens(out[1]) == [33, 34, 35]
+    assert [1, 3] in [b[0] for b in model.batches]      # the new prompt rode beside a decoded token
+
+
+def test_a_kernel_that_gave_up_aborts_everything():
+    from llm_runtime_study_b200.errors import KernelError
+
+    def check():
+        raise KernelError("a bounded wait ran out")
+
+    s, model, manager, _ = make_device(check=check)
+    s.add_request([3, 4], max_new_tokens=2)
+    s.add_request([9], max_new_tokens=6)
+    with pytest.raises(KernelError):
+        drain(s)
+    assert not s.has_unfinished and manager.active_sequences == 0 and manager.free_pages == manager.num_pages
+
+
+@pytest.mark.parametrize("factory", [make, make_device])
+def test_pages_held_outside_the_scheduler_do_not_make_it_spin(factory):
+    s, model, manager, _ = factory(pool_tokens=16, page=4)
+    outside = manager.admit()
+    manager.grow(outside, 16)                      # the whole pool
+    s.add_request([1, 2, 3], max_new_tokens=2)
+    with pytest.raises(GenerationError, match="no progress is possible"):
+        s.step()
+    assert not s.has_unfinished

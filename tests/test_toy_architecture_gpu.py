@@ -55,7 +55,23 @@ def register_toy():
                 at += n
             return self.out(sums.to(x.dtype), torch.float32)
 
+    class DecaySumOnDevice(DecaySum):
+        """The same mixer, written so that a decode step may be replayed from a CUDA graph: for a
+        batch of single tokens it finds its rows of the state through the device-side ``ctx.slots``
+        (rows that pad the batch point at the padding slot's row) and never looks at the host lists."""
+
+        graph_safe = True
+
+        def forward(self, x, ctx, cache):
+            if not ctx.all_decode:
+                return super().forward(x, ctx, cache)
+            slots = ctx.slots.long()
+            s = self.decay * cache.state.index_select(0, slots) + x.float()
+            cache.state.index_copy_(0, slots, s)
+            return self.out(s.to(x.dtype), torch.float32)
+
     MIXERS.register("toy_decay_sum", DecaySum, replace=True)
+    MIXERS.register("toy_decay_sum_on_device", DecaySumOnDevice, replace=True)
 
     def describe(cfg):
         norm = {"kind": "rms_norm", "dim": H, "eps": EPS}
@@ -70,7 +86,7 @@ def register_toy():
 
         layers = (
             LayerDescription(block(attention), "toy.layers.0"),
-            LayerDescription(block({"kind": "toy_decay_sum", "hidden_size": H}), "toy.layers.1"),
+            LayerDescription(block({"kind": cfg.state_mixer, "hidden_size": H}), "toy.layers.1"),
             LayerDescription(block({**attention, "shares_kv": True}), "toy.layers.2"),
         )
         return ModelDescription(
@@ -82,10 +98,13 @@ def register_toy():
         )
 
     class ToyConfig:
+        def __init__(self, raw):
+            self.state_mixer = raw.get("state_mixer", "toy_decay_sum")
+
         def validate_context_length(self, n):
             assert n <= 128
 
-    register_architecture(Architecture("ToyHybrid", "toy_hybrid", lambda raw: ToyConfig(), describe), replace=True)
+    register_architecture(Architecture("ToyHybrid", "toy_hybrid", ToyConfig, describe), replace=True)
 
 
 def plain_toy(w, tokens):
@@ -157,3 +176,46 @@ def test_toy_architecture_is_built_and_stepped(tmp_path, dtype):
             rows = torch.stack([got[rid][p] for p in range(len(toks))]).double()
             torch.testing.assert_close(rows, want[rid], **tol)
         replayer.runner.manager.check()
+
+
+@pytest.mark.parametrize("state_mixer,captured", [("toy_decay_sum", False), ("toy_decay_sum_on_device", True)])
+def test_toy_architecture_generates_through_the_engine(tmp_path, state_mixer, captured):
+    """The same toy model through ``Engine.generate`` with CUDA graphs asked for.  A mixer from outside the
+    package that reads the host-side lists of the batch is not replayed from a graph (it does not say it
+    may be), one that says so and keeps to the device-side slots is; both give the plain model's tokens,
+    with requests joining and leaving the batch so that slots change hands between replays."""
+
+    from llm_runtime_study_b200.engine.engine import Engine
+    from llm_runtime_study_b200.weights import Checkpoint, write_random_model
+
+    register_toy()
+    raw = {"model_type": "toy_hybrid", "architectures": ["ToyHybrid"], "torch_dtype": "float32", "state_mixer": state_mixer}
+    write_random_model(tmp_path / "toy", raw, seed=5)
+    weights = Checkpoint.from_model_dir(tmp_path / "toy").get_tensors()
+    engine = Engine.from_model_dir(tmp_path / "toy", device="cuda:0", dtype="float32", max_seq_len=64, max_batch_size=3,
+                                   page_size=8, max_tokens_per_step=16, use_cuda_graph=True)
+    assert engine.model.graph_safe() is captured
+    rng = random.Random(12)
+    prompts = [helpers.random_tokens(rng, V - 1, n) for n in (4, 11, 7, 19, 2)]
+    new_tokens = [9, 5, 12, 6, 10]
+    scheduler = engine.create_scheduler()
+    for prompt, n in zip(prompts, new_tokens):
+        scheduler.add_request([t + 1 for t in prompt], max_new_tokens=n)       # token 0 is the EOS
+    got = {i: [] for i in range(len(prompts))}
+    while scheduler.has_unfinished:
+        for index, event in scheduler.step():
+            got[index].append(event.token_id)
+    assert (engine.runner._graphs is not None and len(engine.runner._graphs._graphs) > 0) is captured
+    for i, (prompt, n) in enumerate(zip(prompts, new_tokens)):
+        tokens = [t + 1 for t in prompt]
+        for k in range(n):
+            logits = plain_toy(weights, tokens)[-1]
+            top = torch.topk(logits, 2).values
+            if got[i][k] != int(logits.argmax()):
+                assert float(top[0] - top[1]) < 1e-5, (i, k)
+                break
+            tokens.append(got[i][k])
+            if got[i][k] == 0:
+                break
+    engine.cache_manager.check()
+    assert engine.cache_manager.active_sequences == 0

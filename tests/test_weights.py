@@ -87,11 +87,34 @@ def test_one_error_lists_everything(tmp_path):
     assert "dtype mismatch for model.layers.0.self_attn.k_norm.weight" in text
 
 
-def test_storage_type_may_differ_from_config(tmp_path):
-    # a float tensor stored in another floating type is accepted and converted at placement
+def test_storage_type_must_be_the_configurations_unless_relaxed(tmp_path):
+    """Every floating tensor stored in config.json's torch_dtype (mini_llm/checkpoint.py:290, 478-481);
+    all offenders in the one error; without a torch_dtype any floating storage is taken."""
+
     state = random_state(_schema(TINY_A), 0, dtype=torch.bfloat16, include_optional=False)
+    state["model.norm.weight"] = state["model.norm.weight"].float()
     write_file(tmp_path / "model.safetensors", state)
-    validate_manifest(Checkpoint.from_model_dir(tmp_path), _schema(TINY_A), architecture="qwen3")
+    checkpoint = Checkpoint.from_model_dir(tmp_path)
+    validate_manifest(checkpoint, _schema(TINY_A), architecture="qwen3")
+    with pytest.raises(CheckpointValidationError) as err:
+        validate_manifest(checkpoint, _schema(TINY_A), architecture="qwen3", torch_dtype="bfloat16")
+    assert str(err.value).count("dtype mismatch") == 1 and "model.norm.weight: expected one of BF16, got F32" in str(err.value)
+    with pytest.raises(CheckpointValidationError) as err:
+        validate_manifest(checkpoint, _schema(TINY_A), architecture="qwen3", torch_dtype="float32")
+    assert str(err.value).count("dtype mismatch") == len(state) - 1
+
+
+def test_mapped_tensors_equal_copies_and_outlive_the_checkpoint_object(tmp_path):
+    write_random_model(tmp_path, TINY_B, 1, shards=2)
+    checkpoint = Checkpoint.from_model_dir(tmp_path)
+    copies = checkpoint.get_tensors()
+    view = checkpoint.view()
+    assert sorted(view.keys()) == sorted(copies)
+    kept = {name: view[name] for name in copies}
+    del checkpoint, view
+    assert all(torch.equal(kept[name], copies[name]) and kept[name].dtype == copies[name].dtype for name in copies)
+    sub = Checkpoint.from_model_dir(tmp_path).view().sub("model.layers.1.mlp")
+    assert torch.equal(sub["up_proj.weight"], copies["model.layers.1.mlp.up_proj.weight"])
 
 
 def test_file_errors(tmp_path):

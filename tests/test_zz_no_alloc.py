@@ -67,6 +67,28 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point():
         assert torch.equal(got, want)      # same kernels, same order of sums
 
 
+def test_a_warmed_call_takes_no_device_memory():
+    """What the entry point is for: after its first call on the device (which looks up the address of the
+    scratch array) a call neither takes nor gives back device memory.  Seen from outside: the driver's count
+    of free memory is the same before and after, and so is the count of torch's allocator, which the test's
+    own tensors come from."""
+
+    fn = _library()
+    q, keys, values, kv_len, table = _case(4, [500, 130, 64])
+    out = torch.empty_like(q)
+    args = (q.data_ptr(), keys.data_ptr(), values.data_ptr(), out.data_ptr(), kv_len.data_ptr(), table.data_ptr(),
+            table.shape[1], PAGE, q.shape[0], NQ, NKV, 1 / math.sqrt(HEAD_DIM), 0, 4, torch.cuda.current_stream().cuda_stream)
+    assert fn(*args) == 0                                      # the first call on this device sets up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before = torch.cuda.memory_reserved()
+    for _ in range(3):
+        assert fn(*args) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before and torch.cuda.memory_reserved() == reserved_before
+
+
 def test_refuses_what_does_not_fit_and_launches_nothing():
     fn = _library()
     q, keys, values, kv_len, table = _case(3, [64] * 4)
