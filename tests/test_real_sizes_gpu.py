@@ -36,7 +36,7 @@ TAIL = 32
 # bfloat16 engine against the plain model that rounds its activations to bfloat16 at the same places:
 # what is left is the order of the sums, the rounding of the attention weights, and roundings that
 # fall the other way; as a fraction of the row's root mean square.
-TOL = {"float32": 2e-3, "bfloat16": 2.5e-2}
+TOL = {"float32": 2e-3, "bfloat16": 5e-2}
 
 
 def _checked_rows(index: int, length: int) -> list[int]:
