@@ -61,6 +61,32 @@ __global__ void embedding_vec_kernel(const int* __restrict__ ids, const T* __res
   }
 }
 
+// The same gather for the first layer of a decode step of at most 16 tokens, which has no norm kernel of its
+// own: besides the float32 row it writes the row multiplied by the first norm's weight, rounded to the
+// activation type, and the row's sum of squares (partials[row]); the projection that follows applies
+// rsqrt(sum / hidden + eps) to its accumulators (see gemm_skinny.cu).
+template <typename T>
+__global__ void embedding_weighted_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
+                                          const float* __restrict__ norm_weight, __nv_bfloat16* __restrict__ weighted,
+                                          float* __restrict__ partials, int hidden, int vocab, float scale) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const int id = ids[row];
+  const bool ok = id >= 0 && id < vocab;
+  const T* src = table + static_cast<size_t>(ok ? id : 0) * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = ok ? to_float(src[i]) * scale : 0.f;
+    out[static_cast<size_t>(row) * hidden + i] = v;
+    weighted[static_cast<size_t>(row) * hidden + i] = __float2bfloat16_rn(v * norm_weight[i]);
+    ss += v * v;
+  }
+  const float total = block_sum(ss, scratch);
+  if (threadIdx.x == 0) partials[row] = total;
+}
+
 // ------------------------------------------------- residual add + RMS norm
 // x = resid[src] (+ delta[src]);  if write_resid: resid[src] = x
 // out[row] = x * rsqrt(mean(x^2) + eps) * weight
@@ -515,6 +541,18 @@ extern "C" int b200_embedding(const int* ids, const void* table, float* out, int
     else
       launch(embedding_kernel<T>, dim3(n), dim3(threads), 0, stream, ids, static_cast<const T*>(table), out, hidden, vocab, scale);
   });
+  return launch_status();
+}
+
+// n <= 16 rows; partials receives n floats (the layout of one CTA's partial sums in gemm_skinny.cu)
+extern "C" int b200_embedding_weighted(const int* ids, const void* table, float* out, const float* norm_weight, void* weighted,
+                                       float* partials, int n, int hidden, int vocab, float scale, int dtype,
+                                       cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n > 16 || hidden <= 0 || vocab <= 0) return B200_ERR_BAD_SIZE;
+  B200_DISPATCH_DTYPE(dtype, T,
+      launch(embedding_weighted_kernel<T>, dim3(n), dim3(256), 0, stream, ids, static_cast<const T*>(table), out, norm_weight,
+             static_cast<__nv_bfloat16*>(weighted), partials, hidden, vocab, scale));
   return launch_status();
 }
 

@@ -96,7 +96,7 @@ class DecodeGraph:
         # kernels launched under capture may only size their grids from limits that never change
         ctx.kv_lens = [self.bound] * b
         ctx.max_q_len, ctx.max_kv_len = 1, self.bound
-        ctx.all_decode = True
+        ctx.all_decode = ctx.logits_at_every_row = True
         ctx.captured = True
         ctx.entry_slots = None     # the slots of a replay are on the device only (``ctx.slots``)
         return ctx

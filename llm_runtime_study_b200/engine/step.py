@@ -84,6 +84,7 @@ class StepContext:
         self.max_kv_len = 0
         self.all_decode = False
         self.captured = False   # True while a CUDA graph holds this batch's launches
+        self.logits_at_every_row = False         # the wanted rows are all rows, in order
         self.row_slots: torch.Tensor = None      # [M] int32 slot of each sampled row (step_sampled / decode_sampled)
         self.staged_records: torch.Tensor = None # [M, SLOT_WORDS] int32 records the host writes for the sampled rows
 
@@ -279,6 +280,7 @@ class StepRunner:
         ctx.entry_slots = [e.request.slot for e in entries]
         ctx.max_q_len, ctx.max_kv_len = max(q_lens), max(kv_lens)
         ctx.all_decode = ctx.max_q_len == 1
+        ctx.logits_at_every_row = logit_rows.shape[0] == num_tokens and bool((logit_rows == np.arange(num_tokens)).all())
         return ctx
 
     # ------------------------------------------------------------------ run
@@ -404,7 +406,7 @@ class StepRunner:
         ctx.q_lens, ctx.kv_lens = [1] * n, [s + 1 for s in starts]
         ctx.entry_slots = [r.slot for r in requests]
         ctx.max_q_len, ctx.max_kv_len = 1, max(ctx.kv_lens)
-        ctx.all_decode = True
+        ctx.all_decode = ctx.logits_at_every_row = True
         with torch.inference_mode():
             slot_ops.slot_load(manager.slots.records, ctx.slots, ctx.token_ids, ctx.positions, ctx.kv_len)
             logits = self.model.forward(ctx)

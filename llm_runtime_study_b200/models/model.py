@@ -76,10 +76,26 @@ class DecoderModel:
         """Run the batch in ``ctx``; return float32 logits ``[wanted, vocab]``
         (``None`` when no row is wanted: the cache is written all the same)."""
 
-        stream = ResidualStream(self.embedding.forward(ctx.token_ids))
-        for run, index in enumerate(self.order):
-            self.blocks[index][1].forward(stream, ctx, self._layer_caches[run])
+        blocks = [self.blocks[index][1] for index in self.order]
+        # the norm that reads the stream after each block: the next block's first norm, at last the final norm
+        readers = [block.first_norm() for block in blocks[1:]] + [self.final_norm]
+        if getattr(self.embedding, "fuses_norms", False):
+            first = self.embedding.forward(ctx.token_ids, next_norm=blocks[0].first_norm())
+        else:
+            first = self.embedding.forward(ctx.token_ids)
+        if isinstance(first, tuple):     # (rows, the same rows prepared for the first norm)
+            stream = ResidualStream(first[0], weighted=first[1], weighted_for=blocks[0].first_norm())
+        else:
+            stream = ResidualStream(first)
+        for run, (block, reader) in enumerate(zip(blocks, readers)):
+            if block.fuses_norms:
+                block.forward(stream, ctx, self._layer_caches[run], next_norm=reader)
+            else:
+                block.forward(stream, ctx, self._layer_caches[run])
         if ctx.num_logit_rows == 0:
             return None
-        x = self.final_norm.norm_rows(stream.resid, stream.delta, ctx.logit_rows)
+        if stream.weighted is not None and stream.weighted_for is self.final_norm and getattr(ctx, "logits_at_every_row", False):
+            x = stream.take_rows(self.final_norm, self.head)       # every row is wanted, in order: no gather
+        else:
+            x = self.final_norm.norm_rows(stream.resid, stream.delta, ctx.logit_rows)
         return self.head.forward(x)

@@ -25,6 +25,22 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> tor
     return out
 
 
+def embedding_weighted(ids: torch.Tensor, table: torch.Tensor, scale: float, norm_weight: torch.Tensor):
+    """For at most 16 tokens: the embedding rows as float32, the same rows times ``norm_weight`` in bfloat16,
+    and each row's sum of squares (``[1, 16]``, the layout ``gemm_bf16.linear_skinny`` takes as ``partials``)."""
+
+    require(ids, "ids", dtype=torch.int32, dims=1)
+    require(table, "table", dims=2)
+    n, (vocab, hidden) = ids.shape[0], table.shape
+    require(norm_weight, "norm_weight", dtype=torch.float32, shape=(hidden,))
+    out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    weighted = torch.empty((n, hidden), dtype=torch.bfloat16, device=table.device)
+    partials = torch.empty((1, 16), dtype=torch.float32, device=table.device)
+    call("b200_embedding_weighted", ptr(ids), ptr(table), ptr(out), ptr(norm_weight), ptr(weighted), ptr(partials), n, hidden,
+         vocab, float(scale), tag(table.dtype), stream_ptr())
+    return out, weighted, partials
+
+
 def add_rmsnorm(
     resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
     out_dtype: torch.dtype, *, rows: torch.Tensor | None = None,

@@ -26,7 +26,11 @@ native.register_library(
     "b200_gemm_skinny", ("gemm_skinny.cu",),
     {
         "b200_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
-        "b200_gemm_skinny_variant": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "b200_gemm_skinny_variant": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                     c_void_p, c_int, native.c_float, c_void_p],
+        "b200_gemm_skinny_residual": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                      c_void_p, c_void_p],
+        "b200_gemm_skinny_max_partials": [],
     },
 )
 
@@ -176,10 +180,16 @@ def check_error() -> None:
         raise KernelError(f"tcgen05 projection: a bounded wait ran out ({where})")
 
 
+MAX_PARTIALS = 512     # CTAs whose partial sums of squares the weight-streaming kernel can add up (csrc/gemm_skinny.cu)
+
+
 def linear_skinny(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
-                  out_dtype: torch.dtype = torch.bfloat16, *, variant: int = 0, swiglu: bool = False) -> torch.Tensor:
+                  out_dtype: torch.dtype = torch.bfloat16, *, variant: int = 0, swiglu: bool = False,
+                  partials: torch.Tensor | None = None, eps: float = 0.0) -> torch.Tensor:
     """``x @ weight.T (+ bias)`` for at most 16 rows of ``x``: the weight-streaming kernel.
-    ``swiglu``: see ``linear``."""
+    ``swiglu``: see ``linear``.  ``partials`` (float32 ``[P, 16]``): the rows of ``x`` still lack their
+    RMS-norm factor ``rsqrt(sum of squares / K + eps)``; row ``m``'s sum of squares is ``partials[:, m].sum()``
+    and the factor is applied to the product (before the bias)."""
 
     native.require(x, "x", dtype=torch.bfloat16, dims=2)
     native.require(weight, "weight", dtype=torch.bfloat16, dims=2)
@@ -193,8 +203,38 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
         native.require(bias, "bias", dtype=torch.float32, shape=(n,))
     if swiglu and n % 16:
         raise KernelError("the SwiGLU epilogue needs an even number of 8-feature blocks")
+    count = 0
+    if partials is not None:
+        native.require(partials, "partials", dtype=torch.float32, dims=2)
+        count = partials.shape[0]
+        if partials.shape[1] != 16 or not 0 < count <= MAX_PARTIALS:
+            raise KernelError(f"partials must be [1..{MAX_PARTIALS}, 16], got {tuple(partials.shape)}")
     width = n // 2 if swiglu else n
     out = torch.empty((m, width), dtype=out_dtype, device=x.device)
     native.call("b200_gemm_skinny_variant", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k, width,
-                1 if out_dtype == torch.float32 else 0, variant, 1 if swiglu else 0, native.stream_ptr())
+                1 if out_dtype == torch.float32 else 0, variant, 1 if swiglu else 0, native.ptr(partials), count, float(eps),
+                native.stream_ptr())
     return out
+
+
+def linear_skinny_residual(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, resid: torch.Tensor,
+                           next_weight: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``resid += x @ weight.T (+ bias)`` in place (float32 ``[M, N]``, at most 16 rows), and on the way out
+    what the norm after it needs: ``resid * next_weight`` rounded to bfloat16, and per CTA of the kernel the
+    sum of squares of its 16 columns of every row (``[ceil(N / 16), 16]``).  Returns (weighted, partials)."""
+
+    native.require(x, "x", dtype=torch.bfloat16, dims=2)
+    native.require(weight, "weight", dtype=torch.bfloat16, dims=2)
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k or m > SKINNY_M or k % 8:
+        raise KernelError(f"the weight-streaming kernel takes at most {SKINNY_M} rows and K a multiple of 8; got {m}, {k}")
+    native.require(resid, "resid", dtype=torch.float32, shape=(m, n))
+    native.require(next_weight, "next_weight", dtype=torch.float32, shape=(n,))
+    if bias is not None:
+        native.require(bias, "bias", dtype=torch.float32, shape=(n,))
+    weighted = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    partials = torch.empty((-(-n // 16), 16), dtype=torch.float32, device=x.device)
+    native.call("b200_gemm_skinny_residual", x.data_ptr(), weight.data_ptr(), native.ptr(bias), resid.data_ptr(), m, n, k, n,
+                next_weight.data_ptr(), weighted.data_ptr(), partials.data_ptr(), native.stream_ptr())
+    return weighted, partials

@@ -102,8 +102,9 @@ class GroupedQueryAttention(Mixer):
 
     # ------------------------------------------------------------- forward
     adds_to_residual = True
+    fuses_norms = True
 
-    def forward(self, x: torch.Tensor, ctx: Any, cache: Any, residual: torch.Tensor | None = None) -> torch.Tensor | None:
+    def forward(self, x: Any, ctx: Any, cache: Any, residual: torch.Tensor | None = None, next_norm: Any = None):
         qkv = self.qkv_proj(x)
         rotary = self.position.rotary_parameters() if self.position is not None else None
         table = ctx.block_table(cache.group)
@@ -124,4 +125,4 @@ class GroupedQueryAttention(Mixer):
             k_pool=None if self.shares_kv else cache.keys, v_pool=None if self.shares_kv else cache.values,
         )
         out = ctx.attention(q, cache, scale=self.scale, window=self.window or 0)
-        return self.o_proj(out.view(out.shape[0], -1), torch.float32, add_to=residual)
+        return self.o_proj(out.view(out.shape[0], -1), torch.float32, add_to=residual, next_norm=next_norm)

@@ -110,6 +110,12 @@ class Part:
 
 
 class Norm(Part):
+    def fusable(self) -> tuple[torch.Tensor, float] | None:
+        """(weight, eps) if the norm is ``weight * x * rsqrt(mean(x^2) + eps)``, which a projection before it
+        and one after it can carry out between them (see ``WeightedRows``); ``None`` for any other norm."""
+
+        return None
+
     def add_norm(self, resid: torch.Tensor, delta: torch.Tensor | None) -> torch.Tensor:
         raise NotImplementedError
 
@@ -131,6 +137,10 @@ class Mixer(Part):
     # holding everything before this part) and may add its output to them in place, returning
     # ``None`` instead of the output; the block then has nothing left to add.
     adds_to_residual = False
+    # A part that sets this as well takes ``WeightedRows`` as its input where it would take normalised
+    # rows, and a keyword ``next_norm`` (the norm that follows it, or ``None``): when it adds into the
+    # residual rows it may return ``WeightedRows`` prepared for that norm instead of ``None``.
+    fuses_norms = False
 
     def cache_requirement(self) -> PagedKV | FixedState | None:
         return None
@@ -141,6 +151,7 @@ class Mixer(Part):
 
 class FeedForward(Part):
     adds_to_residual = False    # as for Mixer
+    fuses_norms = False         # as for Mixer
 
     def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
         raise NotImplementedError
@@ -148,19 +159,72 @@ class FeedForward(Part):
 
 class Block(Part):
     mixer: Mixer
+    # A block that sets this takes a keyword ``next_norm``: the norm that will read the stream after
+    # this block (the next block's first norm, or the model's final norm), so that its last part may
+    # prepare the rows for it.
+    fuses_norms = False
+
+    def first_norm(self) -> "Norm | None":
+        """The norm that reads the stream first when this block runs, if it has one."""
+
+        return None
 
     def forward(self, stream: "ResidualStream", ctx: Any, cache: Any) -> None:
         raise NotImplementedError
 
 
 @dataclass
+class WeightedRows:
+    """Rows of the residual stream multiplied by a norm's weight and rounded to the activation type,
+    still lacking the norm's factor ``rsqrt(mean of squares + eps)``.  That factor is one number per
+    row and commutes with a matrix product, so a projection that is handed such rows applies it to its
+    results instead (``Projection`` does, where its kernel can).  ``partials[:, m].sum()`` is row
+    ``m``'s sum of squares.  This is how a part that adds its output into the residual rows can do the
+    work of the norm that follows while it has the rows in its hands, and a batch of a few decoded
+    tokens runs without norm kernels."""
+
+    values: torch.Tensor        # [rows, width], activation type
+    partials: torch.Tensor      # [P, 16] float32
+    eps: float
+
+    def normalised(self) -> torch.Tensor:
+        """The normalised rows themselves, for a consumer that cannot apply the factor (plain tensor operations)."""
+
+        rows, width = self.values.shape
+        factor = torch.rsqrt(self.partials[:, :rows].sum(dim=0) / width + self.eps)
+        return (self.values.float() * factor[:, None]).to(self.values.dtype)
+
+
+@dataclass
 class ResidualStream:
     """The float32 residual rows and the output of the last part that has not
     been added yet: the next norm adds it while it normalises (one pass over
-    memory instead of two)."""
+    memory instead of two).  ``weighted`` holds, when the last part has added its
+    output itself and prepared the rows for the norm ``weighted_for``, those rows."""
 
     resid: torch.Tensor
     delta: torch.Tensor | None = None
+    weighted: WeightedRows | None = None
+    weighted_for: Any = None
+
+    def take_rows(self, norm: "Norm", consumer: Any) -> "torch.Tensor | WeightedRows":
+        """What ``consumer`` gets as the rows normalised by ``norm``."""
+
+        rows, made_for = self.weighted, self.weighted_for
+        self.weighted = self.weighted_for = None
+        if rows is not None and made_for is norm:
+            return rows if getattr(consumer, "fuses_norms", False) else rows.normalised()
+        return norm.add_norm(self.resid, self.delta)
+
+    def put(self, out: "torch.Tensor | WeightedRows | None", norm: "Norm | None") -> None:
+        """Record what a part returned: its output (to be added by the next norm), ``None`` (it added its
+        output itself), or the rows it prepared for ``norm`` (added, and that norm half done)."""
+
+        self.delta = self.weighted = self.weighted_for = None
+        if isinstance(out, WeightedRows):
+            self.weighted, self.weighted_for = out, norm
+        else:
+            self.delta = out
 
 
 # --------------------------------------------------------------- registries

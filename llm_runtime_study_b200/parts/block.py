@@ -57,14 +57,23 @@ class PreNormBlock(Block):
         for prefix, part in self._parts():
             part.load(view.sub(prefix), runtime)
 
-    def forward(self, stream: ResidualStream, ctx: Any, cache: Any) -> None:
-        x = self.mixer_norm.add_norm(stream.resid, stream.delta)
-        if self.mixer.adds_to_residual:
-            stream.delta = self.mixer.forward(x, ctx, cache, residual=stream.resid)
-        else:
-            stream.delta = self.mixer.forward(x, ctx, cache)
-        x = self.ffn_norm.add_norm(stream.resid, stream.delta)
-        if self.feed_forward.adds_to_residual:
-            stream.delta = self.feed_forward.forward(x, ctx, residual=stream.resid)
-        else:
-            stream.delta = self.feed_forward.forward(x, ctx)
+    fuses_norms = True
+
+    def first_norm(self):
+        return self.mixer_norm
+
+    def forward(self, stream: ResidualStream, ctx: Any, cache: Any, next_norm: Any = None) -> None:
+        x = stream.take_rows(self.mixer_norm, self.mixer)
+        stream.put(self._run(self.mixer, (x, ctx, cache), stream.resid, self.ffn_norm), self.ffn_norm)
+        x = stream.take_rows(self.ffn_norm, self.feed_forward)
+        stream.put(self._run(self.feed_forward, (x, ctx), stream.resid, next_norm), next_norm)
+
+    @staticmethod
+    def _run(part: Any, args: tuple, resid: torch.Tensor, next_norm: Any):
+        """Call a mixer or feed-forward with as much as it says it can take."""
+
+        if not part.adds_to_residual:
+            return part.forward(*args)
+        if part.fuses_norms:
+            return part.forward(*args, residual=resid, next_norm=next_norm)
+        return part.forward(*args, residual=resid)

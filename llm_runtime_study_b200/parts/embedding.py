@@ -2,13 +2,13 @@
 
 from __future__ import annotations
 
-from typing import Mapping
+from typing import Any, Mapping
 
 import torch
 
 from ..ops import functional as F
 from ..weights.checkpoint import TensorSpec
-from .base import EMBEDDINGS, HEADS, Part, Runtime
+from .base import EMBEDDINGS, HEADS, Part, Runtime, WeightedRows
 from .linear import Projection
 
 
@@ -29,7 +29,14 @@ class TokenEmbedding(Part):
         self.runtime = runtime
         self.weight = runtime.place_matrix(tensors["weight"])
 
-    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+    fuses_norms = True    # takes a keyword ``next_norm`` and may return (rows, WeightedRows for that norm)
+
+    def forward(self, token_ids: torch.Tensor, next_norm: Any = None):
+        fusable = next_norm.fusable() if next_norm is not None and Projection.FUSE_NORMS else None
+        if (fusable is not None and self.runtime.dtype == torch.bfloat16 and token_ids.shape[0] <= 16
+                and fusable[0].shape[0] == self.hidden_size):
+            rows, weighted, partials = F.embedding_weighted(token_ids, self.weight, self.scale, fusable[0])
+            return rows, WeightedRows(weighted, partials, fusable[1])
         return F.embedding(token_ids, self.weight, self.scale)
 
 
@@ -58,5 +65,7 @@ class OutputHead(Part):
         else:
             raise KeyError("output head has no weight and is not tied to the embedding")
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    fuses_norms = True    # takes ``WeightedRows`` prepared for the final norm
+
+    def forward(self, x: "torch.Tensor | WeightedRows") -> torch.Tensor:
         return self.proj(x, torch.float32)

@@ -51,7 +51,8 @@ class SwiGLU(FeedForward):
         self.down_proj = Projection([tensors["down_proj.weight"]], None, runtime)
 
     adds_to_residual = True
+    fuses_norms = True
 
-    def forward(self, x: torch.Tensor, ctx: Any, residual: torch.Tensor | None = None) -> torch.Tensor | None:
+    def forward(self, x: Any, ctx: Any, residual: torch.Tensor | None = None, next_norm: Any = None):
         hidden = self.gate_up_proj.swiglu(x) if self.interleaved else F.silu_mul(self.gate_up_proj(x))
-        return self.down_proj(hidden, torch.float32, add_to=residual)
+        return self.down_proj(hidden, torch.float32, add_to=residual, next_norm=next_norm)

@@ -32,6 +32,9 @@ class RMSNorm(Norm):
         self.runtime = runtime
         self.weight = runtime.place_vector_f32(tensors["weight"])
 
+    def fusable(self) -> tuple[torch.Tensor, float]:
+        return self.weight, self.eps
+
     def add_norm(self, resid: torch.Tensor, delta: torch.Tensor | None) -> torch.Tensor:
         return F.add_rmsnorm(resid, delta, self.weight, self.eps, self.runtime.dtype)
 

@@ -663,3 +663,107 @@ def test_projection_with_swiglu_epilogue(m, inter, k):
             torch.testing.assert_close(other.cpu().double(), want, atol=2e-2 * float(want.abs().max()), rtol=0)
     assert got.shape == (m, inter)
     torch.testing.assert_close(got.cpu().double(), want, atol=2e-2 * float(want.abs().max()), rtol=0)
+
+
+# ------------------------------------------------ RMS norms carried by the weight-streaming projections
+@pytest.mark.parametrize("m,n,k,bias", [(1, 4096, 4096, False), (8, 4096, 12288, False), (3, 1000, 520, True),
+                                        (16, 264, 96, True), (9, 100, 72, False)])
+def test_projection_adds_into_the_residual_and_prepares_the_next_norm(m, n, k, bias):
+    """resid += x W^T (+ b); on the way out the rows times the next norm's weight in bfloat16, and per CTA of
+    the kernel the sum of squares of its 16 columns: the column sums of `partials` are the rows' sums of squares."""
+
+    x, w, b, product = _gemm_case(m, n, k, bias)
+    torch.manual_seed(n)
+    resid = torch.randn(m, n)
+    next_weight = 1 + 0.05 * torch.randn(n)
+    want = resid.double() + product
+    resid_dev = dev(resid)
+    weighted, partials = _gemm().linear_skinny_residual(dev(x), dev(w), dev(b) if bias else None, resid_dev, dev(next_weight))
+    scale = float(want.abs().max())
+    torch.testing.assert_close(resid_dev.cpu().double(), want, atol=1e-5 * scale, rtol=0)
+    torch.testing.assert_close(weighted.cpu().double(), want * next_weight.double(), atol=1e-2 * scale, rtol=0)
+    assert partials.shape == (-(-n // 16), 16)
+    torch.testing.assert_close(partials[:, :m].sum(dim=0).cpu().double(), (want * want).sum(dim=1), rtol=1e-5, atol=0)
+    # the same bits whatever the other rows are
+    resid_one = dev(resid[:1])
+    weighted_one, partials_one = _gemm().linear_skinny_residual(dev(x[:1]), dev(w), dev(b) if bias else None, resid_one, dev(next_weight))
+    assert torch.equal(resid_one[0], resid_dev[0]) and torch.equal(weighted_one[0], weighted[0])
+    assert torch.equal(partials_one[:, 0], partials[:, 0])
+
+
+@pytest.mark.parametrize("m,n,k,bias,parts", [(1, 6144, 4096, False, 256), (8, 136, 4096, True, 256), (3, 1000, 520, True, 33),
+                                              (16, 272, 96, False, 6), (12, 503, 72, False, 1), (5, 17, 8, True, 512)])
+@pytest.mark.parametrize("out", [torch.float32, torch.bfloat16])
+def test_projection_finishes_a_norm_that_was_left_half_done(m, n, k, bias, parts, out):
+    """Rows that lack their factor rsqrt(sum of squares / K + eps), the sums of squares given as partial sums:
+    the kernel adds the partial sums up and applies the factor to its results, before the bias."""
+
+    x, w, b, product = _gemm_case(m, n, k, bias)
+    torch.manual_seed(k)
+    partials = torch.rand(parts, 16) * (k / parts)
+    eps = 1e-5
+    factor = torch.rsqrt(partials[:, :m].double().sum(dim=0) / k + eps)
+    want = (product - (b.double() if bias else 0)) * factor[:, None] + (b.double() if bias else 0)
+    got = _gemm().linear_skinny(dev(x), dev(w), dev(b) if bias else None, out, partials=dev(partials), eps=eps)
+    again = _gemm().linear_skinny(dev(x), dev(w), dev(b) if bias else None, out, partials=dev(partials), eps=eps)
+    assert torch.equal(got, again)
+    scale = float(want.abs().max())
+    torch.testing.assert_close(got.cpu().double(), want, atol=(1e-2 if out == torch.bfloat16 else 2e-5) * scale, rtol=0)
+
+
+def test_swiglu_projection_finishes_a_norm():
+    torch.manual_seed(21)
+    m, inter, k = 7, 272, 96
+    x = torch.randn(m, k).bfloat16()
+    gate, up = (torch.randn(inter, k) * 0.08).bfloat16(), (torch.randn(inter, k) * 0.08).bfloat16()
+    partials = torch.rand(6, 16) * 20
+    factor = torch.rsqrt(partials[:, :m].double().sum(dim=0) / k + 1e-6)[:, None]
+    g, u = (x.double() @ gate.double().T) * factor, (x.double() @ up.double().T) * factor
+    want = g / (1 + torch.exp(-g)) * u
+    got = _gemm().linear_skinny(dev(x), dev(_interleave(gate, up)), None, torch.bfloat16, swiglu=True, partials=dev(partials), eps=1e-6)
+    torch.testing.assert_close(got.cpu().double(), want, atol=2e-2 * float(want.abs().max()), rtol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,hidden,vocab", [(1, 4096, 1000), (16, 100, 37), (5, 264, 503)])
+def test_embedding_prepares_the_first_norm(dtype, n, hidden, vocab):
+    torch.manual_seed(2)
+    table = torch.randn(vocab, hidden).to(dtype)
+    ids = torch.randint(0, vocab, (n,), dtype=torch.int32)
+    norm_weight = 1 + 0.05 * torch.randn(hidden)
+    rows, weighted, partials = F().embedding_weighted(dev(ids), dev(table), 1.5, dev(norm_weight))
+    want = table[ids.long()].double() * 1.5
+    torch.testing.assert_close(rows.cpu().double(), want, atol=1e-6, rtol=1e-6)
+    torch.testing.assert_close(weighted.cpu().double(), want * norm_weight.double(), atol=1e-2 * float(want.abs().max()), rtol=1e-2)
+    torch.testing.assert_close(partials[0, :n].cpu().double(), (want * want).sum(dim=1), rtol=1e-5, atol=0)
+
+
+def test_weighted_rows_through_projections_equal_the_norm_kernel():
+    """The two halves together against the norm kernel followed by the plain product, on one layer's worth of
+    shapes: rows prepared by a projection into the residual, finished by the projection after it."""
+
+    from llm_runtime_study_b200.parts import Projection, Runtime
+    from llm_runtime_study_b200.parts.norm import RMSNorm
+
+    torch.manual_seed(5)
+    runtime = Runtime(torch.device("cuda:0"), torch.bfloat16)
+    hidden, inner, m = 264, 520, 6
+    down = Projection([(torch.randn(hidden, inner) * 0.05).bfloat16()], None, runtime)
+    up = Projection([(torch.randn(inner, hidden) * 0.05).bfloat16()], [torch.randn(inner)], runtime)
+    norm = RMSNorm(hidden, 1e-5)
+    norm.load({"weight": 1 + 0.05 * torch.randn(hidden)}, runtime)
+    x = dev(torch.randn(m, inner).bfloat16())
+    resid = dev(torch.randn(m, hidden))
+    # the fused way
+    resid_a = resid.clone()
+    rows = down(x, torch.float32, add_to=resid_a, next_norm=norm)
+    assert type(rows).__name__ == "WeightedRows"
+    got = up(rows, torch.float32)
+    # the plain way: product, add, norm kernel, product
+    resid_b = resid.clone()
+    delta = down(x, torch.float32)
+    normed = norm.add_norm(resid_b, delta)
+    want = up(normed, torch.float32)
+    torch.testing.assert_close(resid_a, resid_b, atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(got, want, atol=2e-2 * float(want.abs().max()), rtol=0)
+    torch.testing.assert_close(rows.normalised().float(), normed.float(), atol=2e-2 * float(normed.float().abs().max()), rtol=0)
