@@ -12,6 +12,16 @@
 // in their fixed order, so no second launch is needed and the result does not depend on which CTA
 // came last.
 //
+// The kernel can also do what otherwise a kernel before it does for the one new token of every
+// request (mini_llm/nn/attention.py:174-187: per-head RMS norm of q and k before the rotation,
+// mini_llm/nn/norm.py:90; rotation of the pairs (i, i + d/2) by position * inv_freq[i],
+// mini_llm/nn/rope.py:110-146; write of k and v at the token's position,
+// mini_llm/cache/paged/store.py:51-60): given the raw rows of the stacked q/k/v projection, every CTA
+// normalises and rotates its own query heads in registers, and the warp whose block of keys holds the
+// new position computes the new key, patches it (and the new value) into the block in shared memory once
+// the block has arrived, and stores both rows into the cache pages for the steps to come.  No block then
+// depends on the kernel before, so all of a part's first blocks are asked for before the dependency wait.
+//
 // Sizes: head sizes that are multiples of 64 (HEAD_DIM at compile time), pages of a multiple of 16
 // tokens, any number of heads and groups, no window.  Other shapes use the kernels of
 // attention_mma.cu.
@@ -64,6 +74,15 @@ struct DecodeParams {
   float* part_ml;       // [requests][nq][num_splits][2]
   unsigned* tickets;    // [requests][nkv][slices], zero between launches
   int* error;
+  // the new token's raw projections, when this kernel also prepares them (else nullptr and q is ready-made)
+  const bf16* qkv;      // [requests][qkv_stride]: query heads, then key heads, then value heads, D columns each
+  int qkv_stride;
+  const float* q_weight;   // [D] or nullptr: RMS-norm weight of the query heads
+  const float* k_weight;   // [D] or nullptr
+  float eps;
+  const float* inv_freq;   // [D / 2] or nullptr: no rotation
+  bf16* k_pool;            // [pages][nkv][page_size][D], written at the new position
+  bf16* v_pool;
 };
 
 __device__ int g_decode_error = 0;
@@ -167,19 +186,125 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
     valid = (valid & ~(1u << (i % DEPTH))) | (page >= 0 ? 1u << (i % DEPTH) : 0u);
     if (elect_one()) issue(i, page);          // one lane, but from a converged warp: operands stay in uniform registers
   };
-  while (issued < my_count && issued < DEPTH && !(newest_here && warp + WARPS * issued == newest_block)) start(issued++);
+  const bool fused = p.qkv != nullptr;   // the newest key is made here, not read: no block waits for the kernel before
+  while (issued < my_count && issued < DEPTH && (fused || !(newest_here && warp + WARPS * issued == newest_block))) start(issued++);
   pdl_wait();
   while (issued < my_count && issued < DEPTH) start(issued++);
 
+  // cosines and sines of the new position, one copy per warp (no CTA-wide meeting before the main loop)
+  __shared__ float sm_cos[WARPS][D / 2], sm_sin[WARPS][D / 2];
+  const bool rotate = fused && p.inv_freq != nullptr;
+  if (rotate) {
+    for (int j = lane; j < D / 2; j += 32) sincosf(static_cast<float>(len - 1) * p.inv_freq[j], &sm_sin[warp][j], &sm_cos[warp][j]);
+    __syncwarp();
+  }
+  // The new key and value, held by the warp whose block they fall into: lane l has the pairs (j, j + D/2), j = l, l + 32, ...
+  constexpr int PAIRS = D / 64;
+  const bool patcher = fused && newest_here && len > 0 && warp == newest_block % WARPS;
+  float knew_lo[PAIRS], knew_hi[PAIRS];
+  uint32_t vnew[PAIRS];       // bf16 pair: v[j], v[j + D/2]
+  if (patcher) {
+    const bf16* krow = p.qkv + static_cast<size_t>(b) * p.qkv_stride + static_cast<size_t>(p.nq + kvh) * D;
+    const bf16* vrow = p.qkv + static_cast<size_t>(b) * p.qkv_stride + static_cast<size_t>(p.nq + p.nkv + kvh) * D;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < PAIRS; ++i) {
+      const int j = lane + 32 * i;
+      knew_lo[i] = __bfloat162float(krow[j]);
+      knew_hi[i] = __bfloat162float(krow[j + D / 2]);
+      ss += knew_lo[i] * knew_lo[i] + knew_hi[i] * knew_hi[i];
+      const uint16_t a = *reinterpret_cast<const uint16_t*>(vrow + j), c = *reinterpret_cast<const uint16_t*>(vrow + j + D / 2);
+      vnew[i] = static_cast<uint32_t>(a) | (static_cast<uint32_t>(c) << 16);
+    }
+    const float r = p.k_weight ? rsqrtf(warp_sum(ss) / static_cast<float>(D) + p.eps) : 1.f;
+#pragma unroll
+    for (int i = 0; i < PAIRS; ++i) {
+      const int j = lane + 32 * i;
+      float a = knew_lo[i], c = knew_hi[i];
+      if (p.k_weight) {
+        a *= r * p.k_weight[j];
+        c *= r * p.k_weight[j + D / 2];
+      }
+      if (rotate) {
+        const float co = sm_cos[warp][j], si = sm_sin[warp][j];
+        knew_lo[i] = a * co - c * si;
+        knew_hi[i] = c * co + a * si;
+      } else {
+        knew_lo[i] = a;
+        knew_hi[i] = c;
+      }
+    }
+    if (slice == 0) {   // one CTA per (request, KV head) stores the rows for the steps to come
+      const int pos = len - 1;
+      const int page = table[p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size];
+      if (page >= 0) {
+        const size_t row = (static_cast<size_t>(page) * p.nkv + kvh) * p.page_size + (p.page_shift >= 0 ? pos & (p.page_size - 1) : pos % p.page_size);
+        bf16* kdst = p.k_pool + row * D;
+        bf16* vdst = p.v_pool + row * D;
+#pragma unroll
+        for (int i = 0; i < PAIRS; ++i) {
+          const int j = lane + 32 * i;
+          kdst[j] = __float2bfloat16_rn(knew_lo[i]);
+          kdst[j + D / 2] = __float2bfloat16_rn(knew_hi[i]);
+          *reinterpret_cast<uint16_t*>(vdst + j) = static_cast<uint16_t>(vnew[i] & 0xffffu);
+          *reinterpret_cast<uint16_t*>(vdst + j + D / 2) = static_cast<uint16_t>(vnew[i] >> 16);
+        }
+      }
+    }
+  }
+
   // Q^T as B fragments: lane (g, t) holds Q[head g][16 ks + 2t, +1] and Q[head g][16 ks + 8 + 2t, +1]
   uint32_t qb[KS][2];
+  {
+    const bf16* qrow = fused ? p.qkv + static_cast<size_t>(b) * p.qkv_stride + static_cast<size_t>(head0 + g) * D
+                             : p.q + (static_cast<size_t>(b) * p.nq + head0 + g) * D;
 #pragma unroll
-  for (int ks = 0; ks < KS; ++ks) {
-    qb[ks][0] = qb[ks][1] = 0u;
-    if (g < heads_here) {
-      const bf16* src = p.q + (static_cast<size_t>(b) * p.nq + head0 + g) * D + 16 * ks + 2 * t;
-      qb[ks][0] = *reinterpret_cast<const uint32_t*>(src);
-      qb[ks][1] = *reinterpret_cast<const uint32_t*>(src + 8);
+    for (int ks = 0; ks < KS; ++ks) {
+      qb[ks][0] = qb[ks][1] = 0u;
+      if (g < heads_here) {
+        qb[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * t);
+        qb[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * t + 8);
+      }
+    }
+  }
+  if (fused && (p.q_weight != nullptr || rotate)) {
+    // this lane's 4 KS elements of head g: columns 16 ks + 2t, +1, +8, +9; the other half of a rotation pair
+    // (column + D/2) is in the same lane, KS/2 steps on.  The sum of squares of a head is spread over the
+    // four lanes of a quad.
+    float v[KS][4];
+    float ss = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qb[ks][0]));
+      const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qb[ks][1]));
+      v[ks][0] = a.x; v[ks][1] = a.y; v[ks][2] = c.x; v[ks][3] = c.y;
+      ss += a.x * a.x + a.y * a.y + c.x * c.x + c.y * c.y;
+    }
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    if (p.q_weight) {
+      const float r = rsqrtf(ss / static_cast<float>(D) + p.eps);
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[ks][e] *= r * p.q_weight[16 * ks + 2 * t + (e & 1) + (e >> 1) * 8];
+    }
+    if (rotate) {
+#pragma unroll
+      for (int ks = 0; ks < KS / 2; ++ks)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = 16 * ks + 2 * t + (e & 1) + (e >> 1) * 8;        // < D / 2
+          const float co = sm_cos[warp][j], si = sm_sin[warp][j];
+          const float a = v[ks][e], c = v[ks + KS / 2][e];
+          v[ks][e] = a * co - c * si;
+          v[ks + KS / 2][e] = c * co + a * si;
+        }
+    }
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      qb[ks][0] = g < heads_here ? pack_bf16(v[ks][0], v[ks][1]) : 0u;
+      qb[ks][1] = g < heads_here ? pack_bf16(v[ks][2], v[ks][3]) : 0u;
     }
   }
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};   // heads 2t and 2t + 1
@@ -202,6 +327,23 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
     }
     if ((valid >> (i % DEPTH)) & 1u) {        // else: no page, nothing was copied into the stage
       const uint32_t kbase = smem_addr(ring + (i % DEPTH) * STAGE_BYTES), vbase = kbase + TENSOR_BYTES;
+      if (patcher && warp + WARPS * i == newest_block) {
+        // the block that holds the new position: put the new key and value where the cache's (not yet written,
+        // or being written right now) rows were copied to
+        unsigned char* kst = ring + (i % DEPTH) * STAGE_BYTES;
+        const int r = len - 1 - t0;
+#pragma unroll
+        for (int q = 0; q < PAIRS; ++q) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int col = lane + 32 * q + half * (D / 2);
+            const int off = (col >> 6) * BOX_BYTES + r * 128 + ((((col & 63) >> 3) ^ (r & 7)) << 4) + (col & 7) * 2;
+            *reinterpret_cast<bf16*>(kst + off) = __float2bfloat16_rn(half ? knew_hi[q] : knew_lo[q]);
+            *reinterpret_cast<uint16_t*>(kst + TENSOR_BYTES + off) = static_cast<uint16_t>(half ? vnew[q] >> 16 : vnew[q] & 0xffffu);
+          }
+        }
+        __syncwarp();
+      }
       if (t0 + KEYS - 1 > c1) {
         // rows past the end of the sequence hold whatever the page held before: their scores are
         // masked below, their values are cleared here so that 0 x (stale) cannot become NaN
@@ -412,7 +554,7 @@ extern "C" int b200_attention_decode_tma_head_dim() { return HEAD_DIM; }
 // CTAs of the kernel that fit on an SM: shared memory (ring, static arrays, 1 KB the system keeps per
 // CTA) or registers (128 threads of up to 128 registers: four CTAs), whichever is less.
 extern "C" int b200_attention_decode_tma_ctas_per_sm() {
-  const int by_smem = (227 * 1024) / (SMEM_BYTES + 1024 + 2 * HEADS * MAX_SPLITS * 4);
+  const int by_smem = (227 * 1024) / (SMEM_BYTES + 1024 + 2 * HEADS * MAX_SPLITS * 4 + 2 * WARPS * (D / 2) * 4);
   return by_smem < 4 ? by_smem : 4;
 }
 
@@ -433,10 +575,20 @@ extern "C" int b200_attention_decode_tma_error() {
   return value;
 }
 
-extern "C" int b200_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, void* out, const int* kv_len,
-                                         const int* block_table, int table_stride, int page_size, int num_pages, int requests,
-                                         int nq, int nkv, float scale, int num_splits, float* scratch, long scratch_floats,
-                                         unsigned* tickets, long ticket_count, cudaStream_t stream) {
+// What the fused form adds to a launch: the raw q/k/v rows and the constants of the norm and the rotation.
+struct FusedInputs {
+  const void* qkv = nullptr;
+  int qkv_stride = 0;
+  const float* q_weight = nullptr;
+  const float* k_weight = nullptr;
+  float eps = 0.f;
+  const float* inv_freq = nullptr;
+};
+
+static int decode_tma(const void* q, const FusedInputs& fused, const void* k_pool, const void* v_pool, void* out, const int* kv_len,
+                      const int* block_table, int table_stride, int page_size, int num_pages, int requests,
+                      int nq, int nkv, float scale, int num_splits, float* scratch, long scratch_floats,
+                      unsigned* tickets, long ticket_count, cudaStream_t stream) {
   if (requests <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || page_size % KEYS != 0 || table_stride <= 0 || num_pages <= 0)
     return B200_ERR_BAD_SIZE;
@@ -445,8 +597,18 @@ extern "C" int b200_attention_decode_tma(const void* q, const void* k_pool, cons
   if (rows >= (1ull << 31)) return B200_ERR_TOO_LARGE;
   if (scratch_floats < b200_attention_decode_tma_scratch_floats(requests, nq, num_splits)) return 10004;
   if (num_splits > 1 && (tickets == nullptr || ticket_count < b200_attention_decode_tma_tickets(requests, nq, nkv))) return 10004;
+  if (fused.qkv != nullptr && (fused.qkv_stride < (nq + 2 * nkv) * D || (reinterpret_cast<uintptr_t>(fused.qkv) & 3) || (fused.qkv_stride & 1)))
+    return B200_ERR_BAD_SIZE;
   DecodeParams p{};
   p.q = static_cast<const bf16*>(q);
+  p.qkv = static_cast<const bf16*>(fused.qkv);
+  p.qkv_stride = fused.qkv_stride;
+  p.q_weight = fused.q_weight;
+  p.k_weight = fused.k_weight;
+  p.eps = fused.eps;
+  p.inv_freq = fused.inv_freq;
+  p.k_pool = static_cast<bf16*>(const_cast<void*>(k_pool));
+  p.v_pool = static_cast<bf16*>(const_cast<void*>(v_pool));
   p.out = static_cast<bf16*>(out);
   p.kv_len = kv_len;
   p.block_table = block_table;
@@ -481,4 +643,34 @@ extern "C" int b200_attention_decode_tma(const void* q, const void* k_pool, cons
   dim3 grid(num_splits, nkv * p.slices, requests);
   launch(decode_attention_tma_kernel, grid, dim3(128), SMEM_BYTES, stream, kmap, vmap, p);
   return launch_status();
+}
+
+extern "C" int b200_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, void* out, const int* kv_len,
+                                         const int* block_table, int table_stride, int page_size, int num_pages, int requests,
+                                         int nq, int nkv, float scale, int num_splits, float* scratch, long scratch_floats,
+                                         unsigned* tickets, long ticket_count, cudaStream_t stream) {
+  return decode_tma(q, FusedInputs{}, k_pool, v_pool, out, kv_len, block_table, table_stride, page_size, num_pages, requests, nq,
+                    nkv, scale, num_splits, scratch, scratch_floats, tickets, ticket_count, stream);
+}
+
+// The same attention for the one new token of every request, starting from the raw rows of the stacked q/k/v
+// projection (`qkv`: [requests][qkv_stride], query heads, key heads, value heads): the kernel normalises
+// (weights optional) and rotates (inv_freq optional, whole head) q and the new k itself, writes the new k and v
+// into the pools at position kv_len - 1, and attends over all kv_len keys.
+extern "C" int b200_attention_decode_tma_fused(const void* qkv, int qkv_stride, const float* q_weight, const float* k_weight,
+                                               float eps, const float* inv_freq, void* k_pool, void* v_pool, void* out,
+                                               const int* kv_len, const int* block_table, int table_stride, int page_size,
+                                               int num_pages, int requests, int nq, int nkv, float scale, int num_splits,
+                                               float* scratch, long scratch_floats, unsigned* tickets, long ticket_count,
+                                               cudaStream_t stream) {
+  if (qkv == nullptr) return B200_ERR_BAD_SIZE;
+  FusedInputs fused;
+  fused.qkv = qkv;
+  fused.qkv_stride = qkv_stride;
+  fused.q_weight = q_weight;
+  fused.k_weight = k_weight;
+  fused.eps = eps;
+  fused.inv_freq = inv_freq;
+  return decode_tma(nullptr, fused, k_pool, v_pool, out, kv_len, block_table, table_stride, page_size, num_pages, requests, nq,
+                    nkv, scale, num_splits, scratch, scratch_floats, tickets, ticket_count, stream);
 }

@@ -26,11 +26,12 @@ from ..errors import GenerationError
 from .runtime import LoadedModel, load
 from .step import StepEntry, StepRunner
 
-MAX_LIVE_REQUESTS = 16
+DEFAULT_LIVE_REQUESTS = 16
 
 
 class TraceReplayer:
-    def __init__(self, loaded: LoadedModel, *, max_tokens: int, page_size: int = 16, out_dir: str | Path | None = None) -> None:
+    def __init__(self, loaded: LoadedModel, *, max_tokens: int, page_size: int = 16, out_dir: str | Path | None = None,
+                 max_requests: int = DEFAULT_LIVE_REQUESTS) -> None:
         if max_tokens <= 0:
             raise GenerationError("--max-tokens must be positive")
         # The caller counts each request rounded up to a multiple of 64 tokens; a
@@ -39,7 +40,7 @@ class TraceReplayer:
             raise GenerationError(f"page size {page_size} must divide 64 or be a multiple of it")
         self.loaded = loaded
         self.runner: StepRunner = loaded.make_runner(
-            max_tokens=max_tokens, page_size=page_size, max_requests=MAX_LIVE_REQUESTS
+            max_tokens=max_tokens, page_size=page_size, max_requests=max_requests
         )
         self.live: dict[str, RequestCache] = {}
         self.out_dir = None if out_dir is None else Path(out_dir)
@@ -98,11 +99,13 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at once (each rounded up to 64)")
     parser.add_argument("--page-size", type=int, default=16)
+    parser.add_argument("--max-requests", type=int, default=DEFAULT_LIVE_REQUESTS, help="most requests live at a time")
     parser.add_argument("--device", default="cuda:0")
     args = parser.parse_args(argv)
     print("[trace_run] loading model and kernels ...", file=sys.stderr, flush=True)
     # a trace is about arithmetic, not about where the weights came from: any floating storage type is taken
     loaded = load(args.model, device=args.device, dtype=args.dtype, strict_dtype=False)
-    replayer = TraceReplayer(loaded, max_tokens=args.max_tokens, page_size=args.page_size, out_dir=args.out)
+    replayer = TraceReplayer(loaded, max_tokens=args.max_tokens, page_size=args.page_size, out_dir=args.out,
+                             max_requests=args.max_requests)
     replay_stream(replayer, sys.stdin)
     return 0

@@ -34,7 +34,10 @@ _TMA_TABLE = {
     "b200_attention_decode_tma_tickets": [c_int, c_int, c_int],
     "b200_attention_decode_tma_error": [],
     "b200_attention_decode_tma": [c_void_p] * 6 + [c_int] * 6 + [c_float, c_int, c_void_p, c_long, c_void_p, c_long, c_void_p],
+    "b200_attention_decode_tma_fused": [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p] + [c_void_p] * 5 + [c_int] * 6
+                                       + [c_float, c_int, c_void_p, c_long, c_void_p, c_long, c_void_p],
 }
+FUSE_DECODE = os.environ.get("LLM_RUNTIME_STUDY_B200_FUSE_DECODE", "1") != "0"
 # "tma": pages streamed by TMA, parts merged in the same launch; "mma": the cp.async kernels of attention_mma.cu
 DECODE_BACKEND = os.environ.get("LLM_RUNTIME_STUDY_B200_DECODE_ATTENTION", "tma")
 # Stages of each warp's ring: 3 keeps most bytes in flight when few CTAs share the machine; with one
@@ -291,6 +294,60 @@ def _decode_attention_tma(q, keys, values, kv_len, block_table, scale, splits) -
     return out
 
 
+def fused_decode_supported(head_dim: int, page_size: int, window: int, rotary_dim: int) -> bool:
+    """Whether the TMA decode kernel can itself normalise, rotate and store the new token's q, k and v: wherever
+    it runs at all, provided the whole head is rotated or none of it."""
+
+    return (FUSE_DECODE and DECODE_BACKEND == "tma" and tma_supported(head_dim, page_size, window)
+            and rotary_dim in (0, head_dim))
+
+
+def decode_attention_fused(
+    qkv: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, *, num_q_heads: int, q_weight: torch.Tensor | None,
+    k_weight: torch.Tensor | None, eps: float, inv_freq: torch.Tensor | None, kv_len: torch.Tensor, block_table: torch.Tensor,
+    scale: float, splits: int = 1,
+) -> torch.Tensor:
+    """Decode attention straight from the rows of the stacked q/k/v projection (``[requests, (nq + 2 nkv) d]``, one new
+    token per request): per-head RMS norm of q and k (weights optional), rotation by the token's position
+    ``kv_len - 1`` (``inv_freq`` optional), write of the new k and v into the pools, attention over all ``kv_len`` keys."""
+
+    for t, name in ((qkv, "qkv"), (keys, "keys"), (values, "values")):
+        native.require(t, name, dtype=torch.bfloat16)
+    n = qkv.shape[0]
+    nkv, page_size, d = keys.shape[1], keys.shape[2], keys.shape[3]
+    nq = num_q_heads
+    if qkv.dim() != 2 or qkv.shape[1] != (nq + 2 * nkv) * d or nq % nkv:
+        raise KernelError(f"qkv rows of width {tuple(qkv.shape)} do not hold {nq} + 2 x {nkv} heads of {d}")
+    if not tma_supported(d, page_size, 0) or splits > TMA_MAX_SPLITS:
+        raise KernelError(f"the TMA decode kernel does not take head size {d} with pages of {page_size} in {splits} parts")
+    for w, name in ((q_weight, "q_weight"), (k_weight, "k_weight")):
+        if w is not None:
+            native.require(w, name, dtype=torch.float32, shape=(d,))
+    if inv_freq is not None:
+        native.require(inv_freq, "inv_freq", dtype=torch.float32, shape=(d // 2,))
+    count = native.query("b200_attention_decode_tma_tickets", n, nq, nkv, library=tma_library_name(d))
+    lib = tma_library_name(d, tma_depth(count))
+    floats = native.query("b200_attention_decode_tma_scratch_floats", n, nq, splits, library=lib)
+    scratch = torch.empty(max(floats, 1), dtype=torch.float32, device=qkv.device)
+    tickets = _tickets(qkv.device, count)
+    out = torch.empty((n, nq, d), dtype=torch.bfloat16, device=qkv.device)
+    native.call(
+        "b200_attention_decode_tma_fused", qkv.data_ptr(), qkv.stride(0), native.ptr(q_weight), native.ptr(k_weight), float(eps),
+        native.ptr(inv_freq), keys.data_ptr(), values.data_ptr(), out.data_ptr(), kv_len.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], page_size, keys.shape[0], n, nq, nkv, float(scale), splits, scratch.data_ptr(), floats,
+        tickets.data_ptr(), tickets.numel(), native.stream_ptr(), library=lib)
+    return out
+
+
+def decode_parts(ctx: Any, n: int, nq: int, nkv: int, d: int, page_size: int, window: int) -> int:
+    """The number of parts the decode kernels cut each sequence of this batch into."""
+
+    slices = -(-(nq // nkv) // 16)
+    if DECODE_BACKEND == "tma" and tma_supported(d, page_size, window):
+        slices = -(-(nq // nkv) // 8)        # that kernel takes eight query heads of a group per CTA
+    return decode_splits(n, nkv, slices, ctx.max_kv_len, decode_slots(d, page_size, window, n * nkv * slices), d)
+
+
 def check_decode_tma_error(head_dim: int) -> None:
     """Raise if a wait inside the TMA decode kernel ever gave up (synchronises the device)."""
 
@@ -312,12 +369,8 @@ def try_paged_attention(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Tens
         return None
     _, _, _, nkv, _, gs, slices = _geometry(q, cache.keys)
     if ctx.all_decode and n == ctx.num_entries:
-        if DECODE_BACKEND == "tma" and tma_supported(d, cache.keys.shape[2], window):
-            slices = -(-(nq // nkv) // 8)        # that kernel takes eight query heads of a group per CTA
         return decode_attention(q, cache.keys, cache.values, kv_len=ctx.kv_len, block_table=table, scale=scale,
-                                window=window,
-                                splits=decode_splits(n, nkv, slices, ctx.max_kv_len,
-                                                     decode_slots(d, cache.keys.shape[2], window, n * nkv * slices), d))
+                                window=window, splits=decode_parts(ctx, n, nq, nkv, d, cache.keys.shape[2], window))
     maps = ctx.__dict__.setdefault("_tile_maps", {})
     page_size = cache.keys.shape[2]
     if PREFILL_BACKEND == "tcgen05" and tc_supported(d, page_size, window) and ctx.max_q_len >= TC_MIN_PORTION:

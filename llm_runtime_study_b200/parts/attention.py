@@ -7,6 +7,7 @@ from typing import Any, Mapping
 
 import torch
 
+from ..ops import attention_bf16
 from ..ops import functional as F
 from ..weights.checkpoint import TensorSpec
 from ..weights.view import TensorView
@@ -109,6 +110,20 @@ class GroupedQueryAttention(Mixer):
         rotary = self.position.rotary_parameters() if self.position is not None else None
         table = ctx.block_table(cache.group)
         written_kv_heads = 0 if self.shares_kv else self.num_kv_heads
+        if (ctx.all_decode and qkv.dtype == torch.bfloat16 and qkv.shape[0] == ctx.num_entries and not self.shares_kv
+                and (self.position is None or rotary is not None)
+                and attention_bf16.fused_decode_supported(self.head_dim, cache.page_size, self.window or 0, rotary[1] if rotary else 0)):
+            # one new token per request: the decode kernel normalises, rotates and stores q, k and v itself
+            splits = attention_bf16.decode_parts(ctx, qkv.shape[0], self.num_heads, self.num_kv_heads, self.head_dim,
+                                                 cache.page_size, 0)
+            if splits <= attention_bf16.TMA_MAX_SPLITS:
+                out = attention_bf16.decode_attention_fused(
+                    qkv, cache.keys, cache.values, num_q_heads=self.num_heads,
+                    q_weight=self.q_norm.weight if self.q_norm is not None else None,
+                    k_weight=self.k_norm.weight if self.k_norm is not None else None,
+                    eps=self.q_norm.eps if self.q_norm is not None else 1.0,
+                    inv_freq=rotary[0] if rotary else None, kv_len=ctx.kv_len, block_table=table, scale=self.scale, splits=splits)
+                return self.o_proj(out.view(out.shape[0], -1), torch.float32, add_to=residual, next_norm=next_norm)
         if self.position is not None and rotary is None:
             nq, nkv, d = self.num_heads, written_kv_heads, self.head_dim
             q_view = qkv[:, : nq * d].unflatten(1, (nq, d))

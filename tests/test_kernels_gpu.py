@@ -419,6 +419,66 @@ def test_decode_attention_tma_finds_a_far_key(boost):
     torch.testing.assert_close(out.cpu().double(), want, atol=3e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (32, 8, 128, 16), (5, 1, 64, 16), (24, 2, 64, 32), (3, 3, 192, 16),
+                                           (2, 1, 256, 64)])
+@pytest.mark.parametrize("splits,norm,rot", [(1, True, True), (4, True, True), (16, False, True), (3, True, False), (2, False, False)])
+def test_decode_attention_tma_prepares_the_new_token_itself(nq, nkv, d, page, splits, norm, rot):
+    """From the raw rows of the q/k/v projection: per-head RMS norm and rotation of q and of the new k, the new k
+    and v stored at the new position, attention over everything.  The cache rows of the new position hold
+    poison before the launch; afterwards they hold the plain model's new key and value."""
+
+    mma = _mma()
+    torch.manual_seed(9)
+    eps, theta = 1e-5, 1e4
+    lens = [1, 16, 17, 33, 64, 65, 200, 700]
+    wq, wk = 1 + 0.1 * torch.randn(d), 1 + 0.1 * torch.randn(d)
+    dims = torch.arange(0, d, 2, dtype=torch.float32)
+    inv_freq = 1.0 / (theta ** (dims / d))
+    rows, tables, pools_k, pools_v, wants, new_k, new_v, base = [], [], [], [], [], [], [], 0
+    for e, L in enumerate(lens):
+        k, v = torch.randn(L, nkv, d).bfloat16(), torch.randn(L, nkv, d).bfloat16()
+        raw = torch.randn((nq + 2 * nkv) * d).bfloat16()
+        q_raw, k_raw, v_raw = raw[: nq * d].view(1, nq, d).double(), raw[nq * d : (nq + nkv) * d].view(1, nkv, d).double(), raw[(nq + nkv) * d :].view(nkv, d)
+        if norm:
+            q_raw, k_raw = plain.rms_norm(q_raw, wq.double(), eps), plain.rms_norm(k_raw, wk.double(), eps)
+        if rot:
+            cos, sin = plain.rotary_tables(torch.tensor([L - 1]), d, theta, torch.float64)
+            q_raw, k_raw = plain.rotate(q_raw, cos, sin), plain.rotate(k_raw, cos, sin)
+        keys = torch.cat([k[: L - 1].double(), k_raw.bfloat16().double()])
+        vals = torch.cat([v[: L - 1].double(), v_raw.double().view(1, nkv, d)])
+        out = torch.empty(nq, d, dtype=torch.float64)
+        for h in range(nq):
+            kv = h // (nq // nkv)
+            w = torch.softmax((keys[:, kv] @ q_raw[0, h]) / math.sqrt(d), dim=0)
+            out[h] = w @ vals[:, kv]
+        wants.append(out)
+        new_k.append(k_raw[0])
+        new_v.append(v_raw.double())
+        k[L - 1], v[L - 1] = 3e4, -3e4                         # what the cache holds there before: poison
+        kp, vp, ids = _scatter_to_pages(k, v, page, nkv, d, torch.bfloat16, seed=40 + e)
+        pools_k.append(kp)
+        pools_v.append(vp)
+        tables.append(ids + base)
+        base += kp.shape[0]
+        rows.append(raw)
+    table = torch.full((len(lens), max(t.shape[0] for t in tables)), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        table[i, : t.shape[0]] = t
+    kp, vp = dev(torch.cat(pools_k)), dev(torch.cat(pools_v))
+    kw = dict(num_q_heads=nq, q_weight=dev(wq) if norm else None, k_weight=dev(wk) if norm else None, eps=eps,
+              inv_freq=dev(inv_freq) if rot else None, kv_len=dev(torch.tensor(lens, dtype=torch.int32)),
+              block_table=dev(table), scale=1 / math.sqrt(d), splits=splits)
+    first = mma.decode_attention_fused(dev(torch.stack(rows)), kp, vp, **kw)
+    second = mma.decode_attention_fused(dev(torch.stack(rows)), kp, vp, **kw)      # the rows it stored are the rows it makes
+    torch.testing.assert_close(first.cpu().double(), torch.stack(wants), **BF16_TOL)
+    assert torch.equal(first, second)
+    for e, L in enumerate(lens):
+        page_id, slot = int(table[e, (L - 1) // page]), (L - 1) % page
+        torch.testing.assert_close(kp[page_id, :, slot].cpu().double(), new_k[e], atol=2e-2, rtol=2e-2)
+        assert torch.equal(vp[page_id, :, slot].cpu().double(), new_v[e])
+    mma.check_decode_tma_error(d)
+
+
 # ------------------------------------------------------------ bfloat16 projections
 def _gemm():
     from llm_runtime_study_b200.ops import gemm_bf16
