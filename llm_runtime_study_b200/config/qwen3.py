@@ -3,12 +3,16 @@
 Keys, defaults and checks follow the reference (mini_llm/config.py:137-188 for
 the fields, :226-296 for the checks, :357-383 for the Qwen3 class).  Every size
 and constant the model uses comes from here; nothing is hard-coded elsewhere.
+
+The class itself only holds the values.  What is read and what is checked is
+written down as three tables at the end of this file (``KEYS``, ``REFUSED``,
+``RULES``), which ``from_dict`` and ``validate`` walk through.
 """
 
 from __future__ import annotations
 
 from dataclasses import asdict, dataclass
-from typing import Any, Mapping
+from typing import Any, Callable, Mapping
 
 from ..errors import ConfigError
 from .fields import optional, required, token_id_tuple
@@ -46,110 +50,21 @@ class Qwen3Config:
     # ------------------------------------------------------------------ reading
     @classmethod
     def from_dict(cls, raw: Mapping[str, Any]) -> "Qwen3Config":
-        architectures = raw.get("architectures", [])
-        if not isinstance(architectures, list) or not all(
-            isinstance(item, str) for item in architectures
-        ):
-            raise ConfigError("architectures must be a list of strings")
-        if raw.get("quantization_config") is not None:
-            raise ConfigError(
-                "quantization_config is present: quantized checkpoints are not supported"
-            )
-        # The reference never reads these keys (its attention is always full and its rotary
-        # angles are never rescaled, mini_llm/config.py:137-188), so honouring them is not
-        # possible and ignoring them would compute something else than the file asks for:
-        # a null or disabled value is accepted, anything else is refused.
-        if raw.get("use_sliding_window") is True and raw.get("sliding_window") is not None:
-            raise ConfigError(
-                "use_sliding_window is enabled: Qwen3 dense attends to the full context in this "
-                "engine, as in the reference runtime; sliding-window checkpoints are not supported"
-            )
-        if raw.get("rope_scaling") is not None:
-            raise ConfigError(
-                "rope_scaling is set: rotary angles are position * theta^(-2i/d) in this engine, as in "
-                "the reference runtime; scaled rotary embeddings are not supported"
-            )
-        config = cls(
-            architectures=tuple(architectures),
-            model_type=required(raw, "model_type", str),
-            vocab_size=required(raw, "vocab_size", int),
-            hidden_size=required(raw, "hidden_size", int),
-            intermediate_size=required(raw, "intermediate_size", int),
-            num_hidden_layers=required(raw, "num_hidden_layers", int),
-            num_attention_heads=required(raw, "num_attention_heads", int),
-            num_key_value_heads=required(raw, "num_key_value_heads", int),
-            head_dim=required(raw, "head_dim", int),
-            max_position_embeddings=required(raw, "max_position_embeddings", int),
-            rms_norm_eps=float(required(raw, "rms_norm_eps", (int, float))),
-            rope_theta=float(required(raw, "rope_theta", (int, float))),
-            hidden_act=required(raw, "hidden_act", str),
-            attention_bias=raw.get("attention_bias", False),
-            attention_dropout=float(optional(raw, "attention_dropout", (int, float), 0.0)),
-            tie_word_embeddings=raw.get("tie_word_embeddings", False),
-            torch_dtype=required(raw, "torch_dtype", str),
-            bos_token_id=required(raw, "bos_token_id", int),
-            eos_token_ids=token_id_tuple(raw, "eos_token_id"),
-        )
+        """Read the keys listed in ``KEYS`` (presence and JSON type), refuse what ``REFUSED`` names,
+        then apply ``RULES`` in their order; the first rule that fails raises ``ConfigError``."""
+
+        for refuses, complaint in REFUSED:
+            if refuses(raw):
+                raise ConfigError(complaint)
+        values = {key.field: key.read(raw) for key in KEYS}
+        config = cls(**values)
         config.validate()
         return config
 
     def validate(self) -> None:
-        if self.model_type != self.MODEL_TYPE:
-            raise ConfigError(
-                f"unsupported model_type {self.model_type!r}; expected {self.MODEL_TYPE!r}"
-            )
-        if self.architectures != (self.ARCHITECTURE,):
-            raise ConfigError(
-                f"architecture must be {self.ARCHITECTURE}, got {self.architectures}"
-            )
-        for name in (
-            "vocab_size",
-            "hidden_size",
-            "intermediate_size",
-            "num_hidden_layers",
-            "num_attention_heads",
-            "num_key_value_heads",
-            "head_dim",
-            "max_position_embeddings",
-        ):
-            value = getattr(self, name)
-            if value <= 0:
-                raise ConfigError(f"{name} must be positive, got {value}")
-        if self.num_attention_heads % self.num_key_value_heads != 0:
-            raise ConfigError(
-                "num_attention_heads must be divisible by num_key_value_heads "
-                f"for grouped-query attention, got {self.num_attention_heads} and "
-                f"{self.num_key_value_heads}"
-            )
-        if self.head_dim % 2 != 0:
-            raise ConfigError(
-                f"head_dim must be even for rotary embeddings, got {self.head_dim}"
-            )
-        if self.rms_norm_eps <= 0:
-            raise ConfigError(f"rms_norm_eps must be positive, got {self.rms_norm_eps}")
-        if self.rope_theta <= 0:
-            raise ConfigError(f"rope_theta must be positive, got {self.rope_theta}")
-        if self.hidden_act != "silu":
-            raise ConfigError(f"unsupported hidden_act {self.hidden_act!r}; expected 'silu'")
-        if not isinstance(self.attention_bias, bool):
-            raise ConfigError("attention_bias must be boolean")
-        if self.attention_dropout < 0 or self.attention_dropout >= 1:
-            raise ConfigError("attention_dropout must satisfy 0 <= value < 1")
-        if not isinstance(self.tie_word_embeddings, bool):
-            raise ConfigError("tie_word_embeddings must be boolean")
-        if self.torch_dtype not in DTYPE_BYTES:
-            supported = ", ".join(sorted(DTYPE_BYTES))
-            raise ConfigError(
-                f"unsupported torch_dtype {self.torch_dtype!r}; expected one of: {supported}"
-            )
-        for name, token_id in (
-            ("bos_token_id", self.bos_token_id),
-            *(("eos_token_id", item) for item in self.eos_token_ids),
-        ):
-            if not 0 <= token_id < self.vocab_size:
-                raise ConfigError(
-                    f"{name} must be within vocabulary [0, {self.vocab_size}), got {token_id}"
-                )
+        for holds, complaint in RULES:
+            if not holds(self):
+                raise ConfigError(complaint(self))
 
     # ------------------------------------------------------------------ derived
     @property
@@ -196,3 +111,108 @@ class Qwen3Config:
         eos = raw.pop("eos_token_ids")
         raw["eos_token_id"] = eos[0] if len(eos) == 1 else list(eos)
         return raw
+
+
+# ------------------------------------------------------------------------------- the key table
+# One row per config.json key the model reads (the reference's fields: mini_llm/config.py:137-188 and
+# :361-367 for the key that Qwen3 adds, head_dim).  ``kinds`` is the JSON type (a bool never passes
+# for an int), ``default`` is ``REQUIRED`` for keys that must be present.
+REQUIRED = object()
+SIZE_KEYS = ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
+             "num_key_value_heads", "head_dim", "max_position_embeddings")
+
+
+@dataclass(frozen=True)
+class Key:
+    name: str
+    kinds: Any
+    default: Any = REQUIRED
+    field: str = ""                      # attribute of Qwen3Config, when it is not the key's name
+    convert: Callable[[Any], Any] = staticmethod(lambda value: value)
+
+    def __post_init__(self) -> None:
+        if not self.field:
+            object.__setattr__(self, "field", self.name)
+
+    def read(self, raw: Mapping[str, Any]) -> Any:
+        if self.kinds is None:                       # the key has a reader of its own
+            return self.convert(raw)
+        if self.default is REQUIRED:
+            return self.convert(required(raw, self.name, self.kinds))
+        return self.convert(optional(raw, self.name, self.kinds, self.default))
+
+
+def _architectures(raw: Mapping[str, Any]) -> tuple[str, ...]:
+    listed = raw.get("architectures", [])
+    if not isinstance(listed, list) or not all(isinstance(item, str) for item in listed):
+        raise ConfigError("architectures must be a list of strings")
+    return tuple(listed)
+
+
+KEYS: tuple[Key, ...] = (
+    Key("architectures", None, convert=_architectures),
+    Key("model_type", str),
+    *(Key(name, int) for name in SIZE_KEYS),
+    Key("rms_norm_eps", (int, float), convert=float),
+    Key("rope_theta", (int, float), convert=float),
+    Key("hidden_act", str),
+    # the two switches are type-checked by the rules below, so that their complaint names them
+    Key("attention_bias", None, convert=lambda raw: raw.get("attention_bias", False)),
+    Key("attention_dropout", (int, float), default=0.0, convert=float),
+    Key("tie_word_embeddings", None, convert=lambda raw: raw.get("tie_word_embeddings", False)),
+    Key("torch_dtype", str),
+    Key("bos_token_id", int),
+    Key("eos_token_id", None, field="eos_token_ids", convert=lambda raw: token_id_tuple(raw, "eos_token_id")),
+)
+
+# Keys that the reference never reads (its attention is always full and its rotary angles are never
+# rescaled, mini_llm/config.py:137-188).  Honouring them is not possible and ignoring them would compute
+# something else than the file asks for: a null or disabled value passes, anything else is refused.
+REFUSED: tuple[tuple[Callable[[Mapping[str, Any]], bool], str], ...] = (
+    (lambda raw: raw.get("quantization_config") is not None,
+     "quantization_config is present: quantized checkpoints are not supported"),
+    (lambda raw: raw.get("use_sliding_window") is True and raw.get("sliding_window") is not None,
+     "use_sliding_window is enabled: Qwen3 dense attends to the full context in this engine, as in the "
+     "reference runtime; sliding-window checkpoints are not supported"),
+    (lambda raw: raw.get("rope_scaling") is not None,
+     "rope_scaling is set: rotary angles are position * theta^(-2i/d) in this engine, as in the reference "
+     "runtime; scaled rotary embeddings are not supported"),
+)
+
+
+def _positive(name: str):
+    return (lambda c: getattr(c, name) > 0, lambda c: f"{name} must be positive, got {getattr(c, name)}")
+
+
+def _in_vocabulary(c: "Qwen3Config") -> tuple[str, int] | None:
+    """The first special token id outside ``[0, vocab_size)``, if any."""
+
+    for name, token in (("bos_token_id", c.bos_token_id), *(("eos_token_id", t) for t in c.eos_token_ids)):
+        if not 0 <= token < c.vocab_size:
+            return name, token
+    return None
+
+
+# What must hold between the values (the reference's checks, mini_llm/config.py:235-296, one row each):
+# (condition that must hold, complaint when it does not).
+RULES: tuple[tuple[Callable[["Qwen3Config"], bool], Callable[["Qwen3Config"], str]], ...] = (
+    (lambda c: c.model_type == c.MODEL_TYPE,
+     lambda c: f"unsupported model_type {c.model_type!r}; expected {c.MODEL_TYPE!r}"),
+    (lambda c: c.architectures == (c.ARCHITECTURE,),
+     lambda c: f"architecture must be {c.ARCHITECTURE}, got {c.architectures}"),
+    *(_positive(name) for name in SIZE_KEYS),
+    (lambda c: c.num_attention_heads % c.num_key_value_heads == 0,
+     lambda c: "num_attention_heads must be divisible by num_key_value_heads for grouped-query attention, "
+               f"got {c.num_attention_heads} and {c.num_key_value_heads}"),
+    (lambda c: c.head_dim % 2 == 0, lambda c: f"head_dim must be even for rotary embeddings, got {c.head_dim}"),
+    _positive("rms_norm_eps"),
+    _positive("rope_theta"),
+    (lambda c: c.hidden_act == "silu", lambda c: f"unsupported hidden_act {c.hidden_act!r}; expected 'silu'"),
+    (lambda c: isinstance(c.attention_bias, bool), lambda c: "attention_bias must be boolean"),
+    (lambda c: 0 <= c.attention_dropout < 1, lambda c: "attention_dropout must satisfy 0 <= value < 1"),
+    (lambda c: isinstance(c.tie_word_embeddings, bool), lambda c: "tie_word_embeddings must be boolean"),
+    (lambda c: c.torch_dtype in DTYPE_BYTES,
+     lambda c: f"unsupported torch_dtype {c.torch_dtype!r}; expected one of: {', '.join(sorted(DTYPE_BYTES))}"),
+    (lambda c: _in_vocabulary(c) is None,
+     lambda c: "{} must be within vocabulary [0, {}), got {}".format(_in_vocabulary(c)[0], c.vocab_size, _in_vocabulary(c)[1])),
+)
