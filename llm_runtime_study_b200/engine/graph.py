@@ -27,6 +27,7 @@ Steps that hold prompt portions run eagerly.
 
 from __future__ import annotations
 
+import gc
 from typing import Any, Sequence
 
 import numpy as np
@@ -164,8 +165,17 @@ class DecodeGraph:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = native.launch_count()
-        with torch.inference_mode(), torch.cuda.graph(graph, pool=pool):
-            self.logits = self._launches(sampler, ids)
+        # Nothing may be destroyed on the device while the stream is capturing: unreachable objects of earlier
+        # engines (their graphs, their tensors) go now, and the collector stays off until the capture has ended.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.inference_mode(), torch.cuda.graph(graph, pool=pool):
+                self.logits = self._launches(sampler, ids)
+        finally:
+            if collecting:
+                gc.enable()
         self.kernel_launches = native.launch_count() - before
         native.add_launches(-self.kernel_launches)   # capturing launched nothing
         self.graph = graph
