@@ -220,3 +220,44 @@ def test_captured_decode_step_at_real_sizes(material, dtype, lengths):
                 assert float(top[row, 0] - top[row, 1]) <= 2 * TOL[dtype] * float(rms[row]), (step, row)
                 return
             sequences[row].append(ib[row])
+
+
+def test_a_real_size_folder_through_the_command_line(tmp_path):
+    """A model folder of Qwen3-8B width (two layers, two shards, 3.3 GB) written by the random-weights mode, loaded
+    by the command line in a process of its own, and the same folder replayed step by step: the same greedy tokens.
+    The loader maps one tensor at a time: the host memory the load adds stays below twice the largest tensor."""
+
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from llm_runtime_study_b200.engine.replay import TraceReplayer
+    from llm_runtime_study_b200.engine.runtime import load
+    from llm_runtime_study_b200.weights import write_random_model
+
+    folder = tmp_path / "model"
+    write_random_model(folder, QWEN3_8B_TWO_LAYERS, 3, shards=2)
+    assert (folder / "model.safetensors.index.json").is_file()
+    prompt = helpers.random_tokens(random.Random(2), 151936, 40)
+    root = Path(__file__).resolve().parent.parent
+    done = subprocess.run(
+        [sys.executable, "-m", "llm_runtime_study_b200", "--model", str(folder), "--prompt-ids", " ".join(map(str, prompt)),
+         "--max-new-tokens", "6", "--max-seq-len", "256", "--no-stream"],
+        capture_output=True, text=True, timeout=600, cwd=root, env={**os.environ, "PYTHONDONTWRITEBYTECODE": "1"})
+    assert done.returncode == 0, done.stderr[-2000:]
+    lines = done.stdout.splitlines()
+    generated = [int(t) for t in lines[0].split()]
+    assert len(generated) == 6 and "stop reason:         max_new_tokens" in done.stdout
+    host_mib = float(next(l for l in lines if "load host memory:" in l).split()[-2])
+    largest_mib = 151936 * 4096 * 2 / 2**20
+    assert host_mib < 2 * largest_mib, f"loading added {host_mib:.0f} MiB of host memory; the largest tensor is {largest_mib:.0f} MiB"
+    # the same folder, replayed: feed the prompt, then the command line's tokens one by one; each must be the argmax
+    loaded = load(folder, device="cuda:0", dtype="bfloat16")
+    replayer = TraceReplayer(loaded, max_tokens=64, page_size=16)
+    rows = replayer.run_step({"step": 0, "entries": [{"id": "a", "tokens": prompt, "want": [len(prompt) - 1]}], "end": []})
+    for i, token in enumerate(generated):
+        top = torch.topk(torch.from_numpy(np.array(rows[0])), 2)
+        assert int(top.indices[0]) == token or float(top.values[0] - top.values[1]) < 5e-2, (i, token, top)
+        rows = replayer.run_step({"step": i + 1, "entries": [{"id": "a", "tokens": [token], "want": [0]}], "end": []})
