@@ -124,7 +124,7 @@ class Engine:
             with torch.cuda.device(self.device):
                 self._runner = self.loaded.make_runner(
                     max_tokens=tokens, page_size=self.page_size, max_requests=self.max_batch_size,
-                    max_seq_len=self.max_seq_len,
+                    max_seq_len=self.max_seq_len, max_step_tokens=self.max_tokens_per_step,
                 )
                 self._runner.use_cuda_graph = self.use_cuda_graph
                 self._sampler = Sampler(self.device, max_rows=max(self.max_batch_size, 1))

@@ -54,11 +54,12 @@ class DecodeGraph:
         runner = owner.runner
         self.runner, self.batch, self.bound, self.filtered = runner, batch, bound, filtered
         manager = runner.manager
-        self.table_width = _round_up(-(-manager.max_seq_len // manager.page_size), 4)
+        # a block table wide enough for the longest sequence, per group (groups may differ in page size)
+        self.table_widths = [_round_up(-(-manager.max_seq_len // pool.page_size), 4) for pool in manager.groups]
         self.groups = len(manager.layout.groups)
-        b, w = batch, self.table_width
+        b = batch
         # what the host sends every step (slots, tables), then what never changes, then what the device fills in
-        sizes = [b] + [b * w] * self.groups + [b, b + 1, b] + [b, b, b]
+        sizes = [b] + [b * w for w in self.table_widths] + [b, b + 1, b] + [b, b, b]
         self.offsets, total = [], 0
         for size in sizes:
             self.offsets.append(total)
@@ -90,7 +91,7 @@ class DecodeGraph:
         ctx = StepContext(runner.runtime, runner.manager)
         ctx.num_tokens = ctx.num_entries = ctx.num_logit_rows = b
         ctx.slots = ctx.row_slots = self._view(0)
-        ctx.tables = [self._view(1 + i).view(b, self.table_width) for i in range(g)]
+        ctx.tables = [self._view(1 + i).view(b, self.table_widths[i]) for i in range(g)]
         ctx.token_entry, ctx.q_start, ctx.logit_rows = self._view(1 + g), self._view(2 + g), self._view(3 + g)
         ctx.token_ids, ctx.positions, ctx.kv_len = self._view(4 + g), self._view(5 + g), self._view(6 + g)
         ctx.q_lens = [1] * b
@@ -106,14 +107,14 @@ class DecodeGraph:
         """This step's slots and block tables.  Rows beyond the requests are padding: the
         slot that is never live and an empty block table."""
 
-        b, w = self.batch, self.table_width
+        b = self.batch
         manager = self.runner.manager
         sent = np.full(self.sent, -1, dtype=np.int32)
         sent[:b] = manager.padding_slot
         sent[: len(requests)] = [r.slot for r in requests]
         sent[b : self.offsets[1]] = 0
         for g in range(self.groups):
-            o = self.offsets[1 + g]
+            o, w = self.offsets[1 + g], self.table_widths[g]
             table = sent[o : o + b * w].reshape(b, w)
             for i, r in enumerate(requests):
                 row = r.tables[g]

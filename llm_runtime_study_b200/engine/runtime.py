@@ -66,13 +66,17 @@ class LoadedModel:
     weights: Mapping[str, torch.Tensor] | None = None  # CPU copies, random mode only
 
     def make_runner(
-        self, *, max_tokens: int, page_size: int, max_requests: int, max_seq_len: int | None = None
+        self, *, max_tokens: int, page_size: int, max_requests: int, max_seq_len: int | None = None,
+        max_step_tokens: int | None = None,
     ) -> StepRunner:
+        """``max_step_tokens``: the most tokens one step will ever carry, if the caller knows it (a scheduler's
+        token budget); groups of layers that read a window only are then given pools for the window."""
+
         description = self.model.description
         manager = CacheManager(
             self.model.cache_layout(), max_tokens=max_tokens, page_size=page_size,
             max_requests=max_requests, dtype=self.runtime.dtype, device=self.runtime.device,
-            max_seq_len=max_seq_len or description.max_positions,
+            max_seq_len=max_seq_len or description.max_positions, max_step_tokens=max_step_tokens,
         )
         return StepRunner(
             self.model, manager, self.runtime, vocab_size=description.vocab_size,

@@ -155,9 +155,9 @@ class Scheduler:
             )
         output_limit = min(max_new_tokens, self.context_limit - len(prompt))
         required = len(prompt) + output_limit
-        if output_limit > 0 and required > self.manager.num_pages * self.manager.page_size:
+        if output_limit > 0 and required > self.manager.max_request_tokens:
             raise GenerationError(
-                f"request needs {required} cache tokens but the KV cache holds {self.manager.capacity}"
+                f"request needs {required} cache tokens but the KV cache holds {self.manager.max_request_tokens}"
             )
         seed = sampling.seed
         if seed is None:
@@ -254,7 +254,8 @@ class Scheduler:
         if any(r.prefilling or id(r) not in awaited for r in self._running):
             return None
         going = [r for r in self._running if len(r.generated) + 1 < r.output_limit]
-        if not going or sum(self._pages_for(r, r.cache.length + 1) for r in going) > self.manager.free_pages:
+        budget = self.manager.budget()
+        if not going or not all(budget.take(self.manager.held(r.cache), r.cache.length + 1) for r in going):
             return None
         return going
 
@@ -300,9 +301,6 @@ class Scheduler:
             self._inflight = (handle, drawing, started)
 
     # ----------------------------------------------------- building a batch
-    def _pages_for(self, request: _Request, new_length: int) -> int:
-        return self.manager.pages_needed(request.cache, new_length)
-
     def _preempt_last(self) -> None:
         victim = max(self._running, key=lambda r: r.admitted_at)
         self._running.remove(victim)
@@ -321,38 +319,36 @@ class Scheduler:
         # 1. decoded tokens of running requests: they must fit; preempt if they do not
         while True:
             decoding = [r for r in self._running if not r.prefilling and r.pending is not None]
-            need = sum(self._pages_for(r, r.cache.length + 1) for r in decoding)
-            if need <= manager.free_pages or len(self._running) <= 1:
+            budget = manager.budget()
+            if all(budget.take(manager.held(r.cache), r.cache.length + 1) for r in decoding) or len(self._running) <= 1:
                 break
             self._preempt_last()
         plan: list[tuple[_Request, list[int], bool]] = [(r, [r.pending], True) for r in decoding]
-        free_pages = manager.free_pages - need
-        budget = self.max_tokens_per_step - len(plan)
+        tokens_left = self.max_tokens_per_step - len(plan)
 
-        def portion_for(request: _Request, cache_length: int, held_pages: int) -> int:
+        def portion_for(request: _Request, cache_length: int, held: list[int]) -> int:
             """Largest portion of the request's remaining prompt that fits the
             token budget and the free pages."""
 
-            nonlocal free_pages
             remaining = len(request.prompt) - request.fed
-            room = (held_pages + free_pages) * manager.page_size - cache_length
-            return max(0, min(remaining, budget, room))
+            return max(0, min(remaining, tokens_left, budget.room(held) - cache_length))
 
         # 2. requests already admitted that are still feeding their prompt, oldest first
         for request in sorted((r for r in self._running if r.prefilling), key=lambda r: r.admitted_at):
-            if budget <= 0:
+            if tokens_left <= 0:
                 break
-            held = manager.pages_held(request.cache)
+            held = manager.held(request.cache)
             n = portion_for(request, request.cache.length, held)
             if n <= 0:
                 continue
-            free_pages -= self._pages_for(request, request.cache.length + n)
-            budget -= n
+            budget.take(held, request.cache.length + n)
+            tokens_left -= n
             tokens = request.prompt[request.fed : request.fed + n]
             plan.append((request, tokens, request.fed + n == len(request.prompt)))
 
         # 3. admissions, strictly first come first served
-        while self._waiting and budget > 0:
+        nothing = [0] * len(manager.groups)
+        while self._waiting and tokens_left > 0:
             waiting = self._waiting[0]
             if waiting.output_limit == 0:
                 # the prompt fills the context: finish without a slot or a forward pass
@@ -365,23 +361,21 @@ class Scheduler:
                 break
             lifetime = waiting.prompt_token_count + waiting.output_limit
             if self.policy == "reserve":
-                if -(-lifetime // manager.page_size) > free_pages:
+                if not budget.take(nothing, lifetime):
                     break
-                n = min(len(waiting.prompt), budget)
+                n = min(len(waiting.prompt), tokens_left)
             else:
-                n = portion_for(waiting, 0, 0)
+                n = portion_for(waiting, 0, nothing)
                 if n <= 0:
                     break
+                budget.take(nothing, n)
             self._waiting.popleft()
             waiting.cache = manager.admit()
             waiting.admitted_at = next(self._admissions)
             if self.policy == "reserve":
                 manager.grow(waiting.cache, lifetime)
-                free_pages -= manager.pages_held(waiting.cache)
-            else:
-                free_pages -= -(-n // manager.page_size)
             self._running.append(waiting)
-            budget -= n
+            tokens_left -= n
             plan.append((waiting, waiting.prompt[:n], n == len(waiting.prompt)))
         return plan
 

@@ -210,15 +210,12 @@ class StepRunner:
             q_lens.append(n)
             starts.append(start)
         # pages for every entry, or for none: check the total first
-        for g, allocator in enumerate(manager.allocators):
-            need = sum(
-                max(0, -(-(s + n) // manager.page_size) - len(e.request.tables[g]))
-                for e, s, n in zip(entries, starts, q_lens)
-            )
-            if need > allocator.num_free:
-                raise KVCacheError(
-                    f"KV page pool exhausted: need {need} pages but only {allocator.num_free} are free"
-                )
+        budget = manager.budget()
+        for entry, start, n in zip(entries, starts, q_lens):
+            held = manager.held(entry.request)
+            if not budget.take(held, start + n):
+                need, free = budget.short_by(held, start + n)
+                raise KVCacheError(f"KV page pool exhausted: need {need} pages but only {free} are free")
         for entry, start, n in zip(entries, starts, q_lens):
             manager.grow(entry.request, start + n)
         return q_lens, starts

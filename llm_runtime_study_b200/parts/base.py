@@ -62,14 +62,33 @@ class Runtime:
 
 # ------------------------------------------------------- cache requirements
 @dataclass(frozen=True)
-class PagedKV:
-    """Keys and values that grow with the sequence, kept in pages.  ``window``
-    (tokens) bounds how far back the mixer reads; pages wholly behind it are
-    given back early.  Layers with equal requirements share a group of pages."""
+class PagedTensors:
+    """Per-token memory that grows with the sequence, kept in pages: what a mixer asks the cache for.
+    ``tensors`` names each tensor and gives its shape per token; a tensor of per-token shape ``(a, b, ...)``
+    is held as ``[pages, a, page_size, b, ...]`` (one (page, a) tile is contiguous), one of shape ``(a,)`` as
+    ``[pages, page_size, a]``.  ``window`` (tokens) bounds how far back the mixer reads; pages wholly behind
+    it are given back early and the group's pool is sized for the window rather than for whole sequences.
+    ``page_size`` is the group's own (``None``: the cache manager's default).  Layers with equal
+    requirements share a group of pages: one page id addresses the same positions in each of them."""
 
-    num_kv_heads: int
-    head_dim: int
+    tensors: tuple[tuple[str, tuple[int, ...]], ...]
     window: int | None = None
+    page_size: int | None = None
+
+
+@dataclass(frozen=True)
+class PagedKV(PagedTensors):
+    """Keys and values of ``num_kv_heads`` heads of ``head_dim`` each: the request of an attention mixer."""
+
+    num_kv_heads: int = 0
+    head_dim: int = 0
+
+    def __init__(self, num_kv_heads: int, head_dim: int, window: int | None = None, page_size: int | None = None) -> None:
+        object.__setattr__(self, "tensors", (("keys", (num_kv_heads, head_dim)), ("values", (num_kv_heads, head_dim))))
+        object.__setattr__(self, "window", window)
+        object.__setattr__(self, "page_size", page_size)
+        object.__setattr__(self, "num_kv_heads", num_kv_heads)
+        object.__setattr__(self, "head_dim", head_dim)
 
 
 @dataclass(frozen=True)

@@ -62,13 +62,15 @@ def plain_logits(weights: dict, config: dict, token_ids, dtype=torch.float64, *,
     return qwen3_plain.forward(weights, config, token_ids, dtype=dtype, rows=rows, store=store)
 
 
-# Largest allowed |engine - plain| in a row of logits, as a fraction of the row's root mean square.
+# How far a row of logits may be from the plain model's, as fractions of the row's root mean square:
+# (the root mean square of the differences, the largest difference).
 # float32: the engine in 32-bit against the plain model in 64-bit: only the order of the sums differs.
 # bfloat16: the plain model (64-bit arithmetic) rounds its activations to bfloat16 where the engine
 # stores them, so what is left is the order of the sums, the rounding of the attention weights, and
-# roundings that fall the other way here and there (one bfloat16 step is 2^-8 of a value); the worst
-# seen over the configurations of these tests, tiny and of real size alike, is 3.2e-2.
-REPLAY_TOL = {"float32": 3e-4, "bfloat16": 5e-2}
+# roundings that fall the other way here and there (one bfloat16 step is 2^-8 of a value).  The root
+# mean square over a row is a steady figure (a wrong key, position or page moves it by tens of per
+# cent); the largest of up to 151,936 differences is a tail value of the same noise and gets more room.
+REPLAY_TOL = {"float32": (1e-4, 3e-4), "bfloat16": (1.5e-2, 8e-2)}
 
 
 def plain_for(dtype: str, weights: dict, config: dict, token_ids, **kw) -> torch.Tensor:
@@ -77,14 +79,19 @@ def plain_for(dtype: str, weights: dict, config: dict, token_ids, **kw) -> torch
     return plain_logits(weights, config, token_ids, rounded=dtype == "bfloat16", **kw)
 
 
-def first_wrong_row(got: torch.Tensor, want: torch.Tensor, tol: float):
-    """(index of the first row whose error exceeds ``tol`` x its rms, or None; the worst error / rms).
+def first_wrong_row(got: torch.Tensor, want: torch.Tensor, tol: tuple[float, float]):
+    """(index of the first row that is too far off, or None; the worst rms error / rms; the worst error / rms).
     A NaN anywhere in a row makes it wrong."""
 
     rms = want.pow(2).mean(dim=1, keepdim=True).sqrt().clamp_min(1e-30)
-    err = ((got - want).abs() / rms).max(dim=1).values
-    bad = (~(err <= tol)).nonzero()
-    return (int(bad[0]) if bad.numel() else None), float(err.max())
+    diff = (got - want).abs() / rms
+    worst, mean = diff.max(dim=1).values, diff.pow(2).mean(dim=1).sqrt()
+    bad = (~((mean <= tol[0]) & (worst <= tol[1]))).nonzero()
+    import os
+    if os.environ.get("B200_TEST_REPORT"):
+        with open(os.environ["B200_TEST_REPORT"], "a") as f:
+            f.write(f"{got.shape[1]} {float(mean.max()):.4e} {float(worst.max()):.4e}\n")
+    return (int(bad[0]) if bad.numel() else None), float(mean.max()), float(worst.max())
 
 
 def random_tokens(rng: random.Random, vocab: int, length: int) -> list[int]:

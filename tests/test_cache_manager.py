@@ -143,3 +143,57 @@ def test_random_orders_keep_the_books(seed):
         m.release(r)
     m.check()
     assert all(a.num_free == m.num_pages for a in m.allocators) and m.free_slots == 5
+
+
+def test_groups_with_their_own_tensors_page_size_and_window_pool():
+    """A group states its tensors per token and may bring a page size of its own; a group that reads a window
+    only gets a pool for the window (and one step's tokens), not for whole sequences."""
+
+    from llm_runtime_study_b200.cache.manager import pool_shape
+    from llm_runtime_study_b200.parts.base import PagedTensors
+
+    latent = PagedTensors(tensors=(("latent", (24,)), ("rope_key", (1, 8))), page_size=8)
+    windowed = PagedKV(2, 16, window=12)
+    layout = CacheLayout.from_requirements([PagedKV(2, 16), latent, windowed, latent])
+    m = CacheManager(layout, max_tokens=256, page_size=4, max_requests=3, dtype=torch.float32, device="cpu",
+                     max_seq_len=128, max_step_tokens=16)
+    full, lat, win = m.groups
+    assert (full.page_size, full.num_pages) == (4, 64) and (lat.page_size, lat.num_pages) == (8, 32)
+    assert win.num_pages == 3 * (3 + 3) + 4 < full.num_pages          # window of 12 = 3 pages, +3 per request, +16 tokens
+    assert lat.tensors["latent"].shape == (2, 32, 8, 24) and lat.tensors["rope_key"].shape == (2, 32, 1, 8, 8)
+    assert pool_shape((2, 16), 5, 4) == (5, 2, 4, 16) and pool_shape((24,), 5, 8) == (5, 8, 24)
+    view = m.layer_cache(3)
+    assert view.page_size == 8 and set(view.tensors) == {"latent", "rope_key"} and view.keys is None
+    assert m.layer_cache(0).keys.shape == (64, 2, 4, 16) and m.max_request_tokens == 256
+    # a request grows in every group by that group's own pages
+    r = m.admit()
+    m.grow(r, 21)
+    assert [len(t) for t in r.tables] == [6, 3, 6]
+    m.commit(r, 21)
+    assert r.tables[2][:2] == [-1, -1] and r.tables[2][2] >= 0         # positions 0..7 lie behind the window of 12
+    budget = m.budget()
+    assert budget.free == [58, 29, win.num_pages - 4]
+    assert budget.room(m.held(r)) == min(64 * 4, 32 * 8, (6 + win.num_pages - 4) * 4)
+    assert budget.take(m.held(r), 40) and budget.free == [54, 27, win.num_pages - 8]
+    assert not budget.take(m.held(None) or [0, 0, 0], 10_000)
+    m.release(r)
+    m.check()
+    assert m.all_free
+
+
+def test_a_long_request_lives_in_a_window_pool_that_is_much_smaller_than_it():
+    layout = CacheLayout.from_requirements([PagedKV(1, 16, window=8)])
+    m = CacheManager(layout, max_tokens=4096, page_size=4, max_requests=2, dtype=torch.float32, device="cpu",
+                     max_seq_len=4096, max_step_tokens=8)
+    assert m.groups[0].num_pages == 2 * (2 + 3) + 2 and m.max_request_tokens == 4096
+    r = m.admit()
+    length = 0
+    while length < 4000:
+        step = min(8, 4000 - length)
+        m.grow(r, length + step)
+        length += step
+        m.commit(r, length)
+        m.check()
+    assert m.groups[0].allocator.num_held <= 4
+    m.release(r)
+    assert m.all_free

@@ -32,11 +32,10 @@ QWEN3_8B_TWO_LAYERS = {
 LENGTHS = [2400, 300, 150, 40]
 CHECK_ROWS = 24          # positions per request whose full logit rows are compared
 TAIL = 32
+# (rms of the differences, largest difference) of a row of logits as fractions of the row's rms.
 # float32 engine against the float32 plain model: both carry summation-order noise over K = 12288.
-# bfloat16 engine against the plain model that rounds its activations to bfloat16 at the same places:
-# what is left is the order of the sums, the rounding of the attention weights, and roundings that
-# fall the other way; as a fraction of the row's root mean square.
-TOL = {"float32": 2e-3, "bfloat16": 5e-2}
+# bfloat16: see helpers.REPLAY_TOL.
+TOL = {"float32": (5e-4, 2e-3), "bfloat16": helpers.REPLAY_TOL["bfloat16"]}
 
 
 def _checked_rows(index: int, length: int) -> list[int]:
@@ -130,12 +129,10 @@ def test_real_sizes_under_every_cut(material, dtype):
         for rid in requests:
             out = torch.stack([got[rid][p] for p in rows[rid]]).double()
             want = material["plain"][dtype][rid]
-            rms = want.pow(2).mean(dim=1, keepdim=True).sqrt()
-            err = ((out - want).abs() / rms).max(dim=1).values
-            bad = (err > TOL[dtype]).nonzero()
-            assert bad.numel() == 0, (
-                f"{dtype} {name} request {rid}: first wrong checked position {rows[rid][int(bad[0])]}, "
-                f"worst |diff| / rms {float(err.max()):.3e} (allowed {TOL[dtype]:.1e})")
+            bad, err, top = helpers.first_wrong_row(out, want, TOL[dtype])
+            assert bad is None, (
+                f"{dtype} {name} request {rid}: first wrong checked position {rows[rid][bad]}, "
+                f"rms and largest |diff| / rms {err:.3e}, {top:.3e} (allowed {TOL[dtype]})")
     if dtype == "float32":       # and the bits do not depend on the cut
         for name, other in results.items():
             for rid in requests:
@@ -175,9 +172,9 @@ def test_twelve_rows_decode_through_the_split_k_projections(material):
     ids = list(requests)
     together, by_six = last_logits([ids]), last_logits([ids[:6], ids[6:]])
     for rid in ids:
-        rms = float(want[rid].pow(2).mean().sqrt())
-        torch.testing.assert_close(together[rid].double(), want[rid], atol=TOL["bfloat16"] * rms, rtol=0)
-        torch.testing.assert_close(together[rid].double(), by_six[rid].double(), atol=TOL["bfloat16"] * rms, rtol=0)
+        for other in (want[rid], by_six[rid].double()):
+            bad, err, top = helpers.first_wrong_row(together[rid].double()[None], other[None], TOL["bfloat16"])
+            assert bad is None, (rid, err, top)
 
 
 @pytest.mark.parametrize("dtype,lengths", [("bfloat16", (40, 300, 700)), ("bfloat16", tuple(5 + 17 * i for i in range(12))),
@@ -205,19 +202,19 @@ def test_captured_decode_step_at_real_sizes(material, dtype, lengths):
         if dtype == "float32":
             assert torch.equal(a, b), step
         rms = a.double().pow(2).mean(dim=1, keepdim=True).sqrt()
-        worst = float(((a.double() - b.double()).abs() / rms).max())
-        assert worst <= TOL[dtype], (step, worst)
+        bad, err, top = helpers.first_wrong_row(b.double().cpu(), a.double().cpu(), TOL[dtype])
+        assert bad is None, (step, err, top)
         # against the plain model on everything fed so far (the last step only: a whole forward pass per request)
         if step == len(eager_logits) - 1:
             for row, tokens in enumerate(sequences):
                 want = helpers.plain_logits(on_gpu, QWEN3_8B_TWO_LAYERS, tokens, dtype=torch.float32, rows=[len(tokens) - 1],
                                             rounded=dtype == "bfloat16")[0].double().cpu()
-                err = float((b[row].double().cpu() - want).abs().max() / want.pow(2).mean().sqrt())
-                assert err <= TOL[dtype], (row, err)
+                bad, err, top = helpers.first_wrong_row(b[row].double().cpu()[None], want[None], TOL[dtype])
+                assert bad is None, (row, err, top)
         top = torch.topk(a, 2, dim=1).values
         for row in range(len(prompts)):
             if ia[row] != ib[row]:      # only a near-tie may be drawn differently; the sequences then part
-                assert float(top[row, 0] - top[row, 1]) <= 2 * TOL[dtype] * float(rms[row]), (step, row)
+                assert float(top[row, 0] - top[row, 1]) <= 2 * TOL[dtype][1] * float(rms[row]), (step, row)
                 return
             sequences[row].append(ib[row])
 

@@ -65,8 +65,8 @@ def test_random_configuration(case, dtype, tmp_path):
         got = helpers.collect_logits(steps, outputs)
         for rid, tokens in requests.items():
             rows = torch.stack([got[rid][p] for p in range(len(tokens))]).double()
-            bad, err = helpers.first_wrong_row(rows, plain[rid], TOL[dtype])
+            bad, err, top = helpers.first_wrong_row(rows, plain[rid], TOL[dtype])
             assert bad is None, (
                 f"{kind}, request {rid}: first wrong position {bad} of {len(tokens)}, "
-                f"worst |diff| / rms {err:.3e}; configuration {raw}"
+                f"rms and largest |diff| / rms {err:.3e}, {top:.3e}; configuration {raw}"
             )
