@@ -70,7 +70,9 @@ def plain_logits(weights: dict, config: dict, token_ids, dtype=torch.float64, *,
 # roundings that fall the other way here and there (one bfloat16 step is 2^-8 of a value).  The root
 # mean square over a row is a steady figure (a wrong key, position or page moves it by tens of per
 # cent); the largest of up to 151,936 differences is a tail value of the same noise and gets more room.
-REPLAY_TOL = {"float32": (1e-4, 3e-4), "bfloat16": (1.5e-2, 8e-2)}
+# Seen over all rows these tests compare, tiny models and real sizes alike: rms up to 1.35e-2 (median
+# 0.6e-2 to 0.9e-2), largest up to 6.2e-2; the bounds are one and a half times that.
+REPLAY_TOL = {"float32": (1e-4, 3e-4), "bfloat16": (2e-2, 1e-1)}
 
 
 def plain_for(dtype: str, weights: dict, config: dict, token_ids, **kw) -> torch.Tensor:
@@ -87,10 +89,6 @@ def first_wrong_row(got: torch.Tensor, want: torch.Tensor, tol: tuple[float, flo
     diff = (got - want).abs() / rms
     worst, mean = diff.max(dim=1).values, diff.pow(2).mean(dim=1).sqrt()
     bad = (~((mean <= tol[0]) & (worst <= tol[1]))).nonzero()
-    import os
-    if os.environ.get("B200_TEST_REPORT"):
-        with open(os.environ["B200_TEST_REPORT"], "a") as f:
-            f.write(f"{got.shape[1]} {float(mean.max()):.4e} {float(worst.max()):.4e}\n")
     return (int(bad[0]) if bad.numel() else None), float(mean.max()), float(worst.max())
 
 
