@@ -62,13 +62,15 @@ __global__ void embedding_vec_kernel(const int* __restrict__ ids, const T* __res
 }
 
 // The same gather for the first layer of a decode step of at most 16 tokens, which has no norm kernel of its
-// own: besides the float32 row it writes the row multiplied by the first norm's weight, rounded to the
-// activation type, and the row's sum of squares (partials[row]); the projection that follows applies
-// rsqrt(sum / hidden + eps) to its accumulators (see gemm_skinny.cu).
-template <typename T>
+// own: besides the float32 row it writes the row multiplied by the first norm's weight, rounded to bfloat16,
+// and the row's factor rsqrt(mean of squares + eps) (row_scale[row]), which the projection that follows
+// applies to its accumulators (see gemm_skinny.cu).  16-byte loads of the table row, the row kept in registers.
+template <typename T, int VPT>
 __global__ void embedding_weighted_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
                                           const float* __restrict__ norm_weight, __nv_bfloat16* __restrict__ weighted,
-                                          float* __restrict__ partials, int hidden, int vocab, float scale) {
+                                          float* __restrict__ row_scale, int hidden, int vocab, float scale, float eps) {
+  constexpr int VN = Vec<T>::n;
+  using V = typename Vec<T>::type;
   __shared__ float scratch[32];
   pdl_trigger();
   pdl_wait();
@@ -76,15 +78,32 @@ __global__ void embedding_weighted_kernel(const int* __restrict__ ids, const T* 
   const int id = ids[row];
   const bool ok = id >= 0 && id < vocab;
   const T* src = table + static_cast<size_t>(ok ? id : 0) * hidden;
+  float x[VPT][VN];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float v = ok ? to_float(src[i]) * scale : 0.f;
-    out[static_cast<size_t>(row) * hidden + i] = v;
-    weighted[static_cast<size_t>(row) * hidden + i] = __float2bfloat16_rn(v * norm_weight[i]);
-    ss += v * v;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = (threadIdx.x + v * blockDim.x) * VN;
+#pragma unroll
+    for (int e = 0; e < VN; ++e) x[v][e] = 0.f;
+    if (i < hidden && ok) Vec<T>::unpack(*reinterpret_cast<const V*>(src + i), x[v]);
+#pragma unroll
+    for (int e = 0; e < VN; ++e) {
+      x[v][e] *= scale;
+      ss += x[v][e] * x[v][e];
+    }
   }
   const float total = block_sum(ss, scratch);
-  if (threadIdx.x == 0) partials[row] = total;
+  if (threadIdx.x == 0) row_scale[row] = rsqrtf(total / static_cast<float>(hidden) + eps);
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int i = (threadIdx.x + v * blockDim.x) * VN;
+    if (i >= hidden) continue;
+#pragma unroll
+    for (int e = 0; e < VN; ++e) {
+      out[static_cast<size_t>(row) * hidden + i + e] = x[v][e];
+      weighted[static_cast<size_t>(row) * hidden + i + e] = __float2bfloat16_rn(x[v][e] * norm_weight[i + e]);
+    }
+  }
 }
 
 // ------------------------------------------------- residual add + RMS norm
@@ -544,15 +563,31 @@ extern "C" int b200_embedding(const int* ids, const void* table, float* out, int
   return launch_status();
 }
 
-// n <= 16 rows; partials receives n floats (the layout of one CTA's partial sums in gemm_skinny.cu)
+// n <= 16 rows, hidden a multiple of the 16-byte vector of the table's type and at most 8 x 256 vectors;
+// row_scale receives n floats.
 extern "C" int b200_embedding_weighted(const int* ids, const void* table, float* out, const float* norm_weight, void* weighted,
-                                       float* partials, int n, int hidden, int vocab, float scale, int dtype,
+                                       float* row_scale, int n, int hidden, int vocab, float scale, float eps, int dtype,
                                        cudaStream_t stream) {
   if (n <= 0) return 0;
   if (n > 16 || hidden <= 0 || vocab <= 0) return B200_ERR_BAD_SIZE;
-  B200_DISPATCH_DTYPE(dtype, T,
-      launch(embedding_weighted_kernel<T>, dim3(n), dim3(256), 0, stream, ids, static_cast<const T*>(table), out, norm_weight,
-             static_cast<__nv_bfloat16*>(weighted), partials, hidden, vocab, scale));
+  if (reinterpret_cast<uintptr_t>(table) & 15) return B200_ERR_BAD_SIZE;
+  B200_DISPATCH_DTYPE(dtype, T, {
+    constexpr int VN = Vec<T>::n;
+    if (hidden % VN != 0) return B200_ERR_BAD_SIZE;
+    const int vectors = hidden / VN;
+    auto* tab = static_cast<const T*>(table);
+    auto* wt = static_cast<__nv_bfloat16*>(weighted);
+    if (vectors <= 256)
+      launch(embedding_weighted_kernel<T, 1>, dim3(n), dim3(256), 0, stream, ids, tab, out, norm_weight, wt, row_scale, hidden, vocab, scale, eps);
+    else if (vectors <= 512)
+      launch(embedding_weighted_kernel<T, 2>, dim3(n), dim3(256), 0, stream, ids, tab, out, norm_weight, wt, row_scale, hidden, vocab, scale, eps);
+    else if (vectors <= 1024)
+      launch(embedding_weighted_kernel<T, 4>, dim3(n), dim3(256), 0, stream, ids, tab, out, norm_weight, wt, row_scale, hidden, vocab, scale, eps);
+    else if (vectors <= 2048)
+      launch(embedding_weighted_kernel<T, 8>, dim3(n), dim3(256), 0, stream, ids, tab, out, norm_weight, wt, row_scale, hidden, vocab, scale, eps);
+    else
+      return B200_ERR_TOO_LARGE;
+  });
   return launch_status();
 }
 

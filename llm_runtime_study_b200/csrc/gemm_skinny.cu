@@ -15,11 +15,11 @@
 // (y = w * x * rsqrt(mean(x^2) + eps), mini_llm/nn/norm.py:42-46; h = r + f(x), mini_llm/model/qwen.py:67, 72):
 //   * EPI_RESIDUAL: the product is added into the float32 residual rows in place; the same pass writes
 //     the rows multiplied by the *next* norm's weight, rounded to bfloat16, and every CTA leaves the sum
-//     of squares of its 16 columns of every row (`partials`, [CTAs][16 rows]).
+//     of squares of its 16 columns of every row in scratch memory ([CTAs][16 rows]).  The CTA that
+//     finishes last (a ticket counter) adds those up in CTA order, whoever it is, and writes the rows'
+//     factors rsqrt(mean of squares + eps).
 //   * SCALED: the rows this kernel multiplies are such weighted, not yet normalised rows.  The factor
-//     rsqrt(mean + eps) is one number per row and commutes with the product, so it is applied to the
-//     accumulators instead: each CTA adds up the partial sums (fetched into shared memory by cp.async
-//     behind the main loop, added in a fixed order) and scales its results.
+//     is one number per row and commutes with the product, so it is applied to the accumulators.
 // Rounding r * w to bfloat16 before the scale instead of after changes nothing in relative terms.
 #include "common.cuh"
 #include "mma.cuh"
@@ -35,16 +35,16 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 }
 
 enum Epilogue : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESIDUAL = 2 };
-constexpr int kMaxPartials = 512;   // CTAs of the kernel that left the partial sums of squares (its N / 16)
 
 // What the two fusions need beyond the product itself.
 struct NormFusion {
-  const float* partials;      // SCALED: [num_partials][16] sums of squares of the rows being multiplied
-  int num_partials;
-  float eps;                  // SCALED: rows are scaled by rsqrt(sum / K + eps)
+  const float* row_scale;     // SCALED: [16] factors the rows being multiplied still lack
   const float* next_weight;   // EPI_RESIDUAL: weight of the norm that follows, [N]
+  float eps;                  // EPI_RESIDUAL: its eps
   __nv_bfloat16* weighted;    // EPI_RESIDUAL: out, [M][N] = (residual + product) * next_weight
-  float* partials_out;        // EPI_RESIDUAL: out, [gridDim.x][16]
+  float* row_scale_out;       // EPI_RESIDUAL: out, [16] = rsqrt(mean of squares of the new residual row + eps)
+  float* partials;            // EPI_RESIDUAL: scratch, [gridDim.x][16]
+  unsigned* ticket;           // EPI_RESIDUAL: zero before the launch, zero again after it
 };
 
 template <int NT, int UNROLL, int kSkinnyWarps, int EPI, bool SCALED, typename OutT>
@@ -53,9 +53,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
                    const float* __restrict__ bias, OutT* __restrict__ C, int M, int N, int K, int ldc, NormFusion fuse) {
   constexpr bool SWIGLU = EPI == EPI_SWIGLU;
   __shared__ float red[kSkinnyWarps][16][NT * 8 + 1];
-  __shared__ __align__(16) float part[SCALED ? kMaxPartials : 1][16];
-  __shared__ float slice_sum[SCALED ? kSkinnyWarps * 2 : 1][16];
-  __shared__ float row_scale[16];
+  __shared__ float slice_sum[EPI == EPI_RESIDUAL ? kSkinnyWarps * 2 : 1][16];
+  __shared__ int is_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
   const __nv_bfloat16* wa = W + static_cast<size_t>(min(n0 + g, N - 1)) * K + t * 8;
@@ -85,12 +84,6 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
     }
   }
   pdl_wait();
-  if constexpr (SCALED) {
-    // the partial sums of squares are needed only after the main loop: let them trickle into shared memory meanwhile
-    for (int i = threadIdx.x; i < fuse.num_partials * 4; i += kSkinnyWarps * 32)
-      cp_async_16(&part[0][0] + 4 * i, fuse.partials + 4 * i, 16);
-    cp_async_commit();
-  }
   for (int k0 = warp * kChunk; k0 < K; k0 += kSkinnyWarps * kChunk) {
 #pragma unroll
     for (int h = 0; h < kChunk / 32; h += UNROLL) {
@@ -125,25 +118,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
     red[warp][g + 8][j * 8 + 2 * t] = c[j][2];
     red[warp][g + 8][j * 8 + 2 * t + 1] = c[j][3];
   }
-  if constexpr (SCALED) cp_async_wait<0>();
   __syncthreads();
-  if constexpr (SCALED) {
-    // rsqrt(mean of squares + eps) of every row: thread (row = t % 16, slice = t / 16) adds every
-    // (threads / 16)-th partial sum, then one thread per row adds the slices; the order is fixed by the launch shape
-    constexpr int kSlices = kSkinnyWarps * 2;
-    const int r = threadIdx.x & 15, slice = threadIdx.x >> 4;
-    float s = 0.f;
-    for (int i = slice; i < fuse.num_partials; i += kSlices) s += part[i][r];
-    slice_sum[slice][r] = s;
-    __syncthreads();
-    if (threadIdx.x < 16) {
-      float total = 0.f;
-#pragma unroll
-      for (int i = 0; i < kSlices; ++i) total += slice_sum[i][threadIdx.x];
-      row_scale[threadIdx.x] = rsqrtf(total / static_cast<float>(K) + fuse.eps);
-    }
-    __syncthreads();
-  }
   if constexpr (EPI == EPI_RESIDUAL) {
     // C is the float32 residual stream: add the product in place, write the rows weighted for the next norm,
     // and leave this CTA's share of every row's sum of squares.  All lanes stay in the loop for the shuffles.
@@ -165,7 +140,28 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
       float sq = r * r;
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-      if (row == 0) fuse.partials_out[static_cast<size_t>(blockIdx.x) * 16 + m] = sq;
+      if (row == 0) fuse.partials[static_cast<size_t>(blockIdx.x) * 16 + m] = sq;
+    }
+    // The CTA that comes last adds the partial sums of all CTAs, in their order: thread (row = t % 16,
+    // slice = t / 16) takes every (threads / 16)-th CTA's, then one thread per row adds the slices.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicInc(fuse.ticket, gridDim.x - 1) == gridDim.x - 1;   // wraps to zero
+    __syncthreads();
+    if (is_last) {
+      __threadfence();
+      constexpr int kSlices = kSkinnyWarps * 2;
+      const int r = threadIdx.x & 15, slice = threadIdx.x >> 4;
+      float s = 0.f;
+      for (int i = slice; i < static_cast<int>(gridDim.x); i += kSlices) s += __ldcg(fuse.partials + static_cast<size_t>(i) * 16 + r);
+      slice_sum[slice][r] = s;
+      __syncthreads();
+      if (threadIdx.x < 16) {
+        float total = 0.f;
+#pragma unroll
+        for (int i = 0; i < kSlices; ++i) total += slice_sum[i][threadIdx.x];
+        fuse.row_scale_out[threadIdx.x] = threadIdx.x < NT * 8 ? rsqrtf(total / static_cast<float>(N) + fuse.eps) : 0.f;
+      }
     }
   } else if constexpr (SWIGLU) {
     // rows 0..7 of the tile are gate features, rows 8..15 the matching up features
@@ -180,8 +176,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
         up += red[w][f + 8][m];
       }
       if constexpr (SCALED) {
-        gate *= row_scale[m];
-        up *= row_scale[m];
+        gate *= fuse.row_scale[m];
+        up *= fuse.row_scale[m];
       }
       if (bias) {
         gate += bias[n];
@@ -197,7 +193,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
       float acc = 0.f;
 #pragma unroll
       for (int w = 0; w < kSkinnyWarps; ++w) acc += red[w][row][m];
-      if constexpr (SCALED) acc *= row_scale[m];
+      if constexpr (SCALED) acc *= fuse.row_scale[m];
       acc += bias ? bias[n] : 0.f;
       C[static_cast<size_t>(m) * ldc + n] = from_float<OutT>(acc);
     }
@@ -219,7 +215,7 @@ static void launch_one(const __nv_bfloat16* w, const __nv_bfloat16* x, const flo
 template <int NT, int UNROLL, int WARPS>
 static void launch_skinny(const __nv_bfloat16* w, const __nv_bfloat16* x, const float* bias, void* C, int M, int N, int K,
                           int ldc, int out_f32, int epi, const NormFusion& fuse, cudaStream_t stream) {
-  const bool scaled = fuse.partials != nullptr;
+  const bool scaled = fuse.row_scale != nullptr;
   if (epi == EPI_RESIDUAL) {
     launch_one<NT, UNROLL, WARPS, EPI_RESIDUAL, false, float>(w, x, bias, C, M, N, K, ldc, fuse, stream);
   } else if (epi == EPI_SWIGLU) {
@@ -247,9 +243,6 @@ static int skinny(const void* X, const void* W, const float* bias, void* C, int 
   if (M > 16 || K <= 0 || K % 8 != 0 || ldc < (epi == EPI_SWIGLU ? N / 2 : N)) return B200_ERR_BAD_SIZE;
   if (epi == EPI_SWIGLU && N % 16 != 0) return B200_ERR_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W)) & 15) return B200_ERR_BAD_SIZE;
-  if (fuse.partials && (fuse.num_partials <= 0 || fuse.num_partials > kMaxPartials ||
-                        (reinterpret_cast<uintptr_t>(fuse.partials) & 15)))
-    return B200_ERR_BAD_SIZE;
   const auto* w = static_cast<const __nv_bfloat16*>(W);
   const auto* x = static_cast<const __nv_bfloat16*>(X);
   if (variant == 0) {
@@ -276,36 +269,48 @@ static int skinny(const void* X, const void* W, const float* bias, void* C, int 
 // `variant` picks the shape of a CTA (0: the default for the size; 2: fewer loads in flight, more CTAs per SM).
 // `swiglu` = 1: W holds gate and up rows interleaved in blocks of eight (N a multiple of 16);
 // the output is silu(gate) * up, N / 2 columns wide (ldc >= N / 2).
-// `partials` (optional, [num_partials][16] floats): X holds rows that still lack their factor
-// rsqrt(sum of squares / K + eps), the sums of squares being the column sums of `partials`; the factor is
-// applied to the product (before the bias).
+// `row_scale` (optional, 16 floats): X holds rows that still lack these factors (an RMS norm left half
+// done); they are applied to the product, before the bias.
 extern "C" int b200_gemm_skinny_variant(const void* X, const void* W, const float* bias, void* C, int M, int N, int K,
-                                        int ldc, int out_f32, int variant, int swiglu, const float* partials,
-                                        int num_partials, float eps, cudaStream_t stream) {
+                                        int ldc, int out_f32, int variant, int swiglu, const float* row_scale,
+                                        cudaStream_t stream) {
   NormFusion fuse{};
-  fuse.partials = partials;
-  fuse.num_partials = num_partials;
-  fuse.eps = eps;
+  fuse.row_scale = row_scale;
   return skinny(X, W, bias, C, M, N, K, ldc, out_f32, variant, swiglu ? EPI_SWIGLU : EPI_STORE, fuse, stream);
 }
 
 extern "C" int b200_gemm_skinny(const void* X, const void* W, const float* bias, void* C, int M, int N, int K,
                                 int ldc, int out_f32, cudaStream_t stream) {
-  return b200_gemm_skinny_variant(X, W, bias, C, M, N, K, ldc, out_f32, 0, 0, nullptr, 0, 0.f, stream);
+  return b200_gemm_skinny_variant(X, W, bias, C, M, N, K, ldc, out_f32, 0, 0, nullptr, stream);
 }
 
+// Tickets of the residual form: one counter per launch, taken in turn out of a zeroed array on the device.  A
+// launch leaves its counter at zero and launches follow each other on one stream, so a counter is free again
+// long before its turn comes round.
+constexpr int kTickets = 4096;
+__device__ unsigned g_skinny_tickets[kTickets];
+
 // resid[M][N] (float32, row stride ldc) += X W^T (+ bias); weighted[M][N] (bfloat16) = resid * next_weight;
-// partials_out[(N + 15) / 16][16] = per CTA, the sum of squares of its 16 columns of every row of the new resid.
-// N / 16 (rounded up) may not exceed b200_gemm_skinny_max_partials() if a SCALED product is to consume them.
+// row_scale_out[16] = rsqrt(mean of squares of each new row of resid + eps) (rows from M on: 0).
+// `partials` is scratch of b200_gemm_skinny_partial_floats(N) floats.
 extern "C" int b200_gemm_skinny_residual(const void* X, const void* W, const float* bias, float* resid, int M, int N, int K,
-                                         int ldc, const float* next_weight, void* weighted, float* partials_out,
-                                         cudaStream_t stream) {
-  if (!resid || !next_weight || !weighted || !partials_out) return B200_ERR_BAD_SIZE;
+                                         int ldc, const float* next_weight, float eps, void* weighted, float* row_scale_out,
+                                         float* partials, cudaStream_t stream) {
+  if (!resid || !next_weight || !weighted || !row_scale_out || !partials) return B200_ERR_BAD_SIZE;
+  static unsigned* tickets[kMaxDevices] = {};
+  static unsigned turn = 0;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return 10007;
+  if (!tickets[device] && cudaGetSymbolAddress(reinterpret_cast<void**>(&tickets[device]), g_skinny_tickets) != cudaSuccess)
+    return 10007;
   NormFusion fuse{};
   fuse.next_weight = next_weight;
+  fuse.eps = eps;
   fuse.weighted = static_cast<__nv_bfloat16*>(weighted);
-  fuse.partials_out = partials_out;
+  fuse.row_scale_out = row_scale_out;
+  fuse.partials = partials;
+  fuse.ticket = tickets[device] + (turn++ % kTickets);
   return skinny(X, W, bias, resid, M, N, K, ldc, 1, 0, EPI_RESIDUAL, fuse, stream);
 }
 
-extern "C" int b200_gemm_skinny_max_partials() { return kMaxPartials; }
+extern "C" long b200_gemm_skinny_partial_floats(int N) { return static_cast<long>((N + 15) / 16) * 16; }

@@ -25,9 +25,10 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> tor
     return out
 
 
-def embedding_weighted(ids: torch.Tensor, table: torch.Tensor, scale: float, norm_weight: torch.Tensor):
+def embedding_weighted(ids: torch.Tensor, table: torch.Tensor, scale: float, norm_weight: torch.Tensor, eps: float):
     """For at most 16 tokens: the embedding rows as float32, the same rows times ``norm_weight`` in bfloat16,
-    and each row's sum of squares (``[1, 16]``, the layout ``gemm_bf16.linear_skinny`` takes as ``partials``)."""
+    and each row's factor ``rsqrt(mean of squares + eps)`` (``[16]`` floats, what ``gemm_bf16.linear_skinny``
+    takes as ``row_scale``).  The row width must be a multiple of a 16-byte vector of the table's type."""
 
     require(ids, "ids", dtype=torch.int32, dims=1)
     require(table, "table", dims=2)
@@ -35,10 +36,10 @@ def embedding_weighted(ids: torch.Tensor, table: torch.Tensor, scale: float, nor
     require(norm_weight, "norm_weight", dtype=torch.float32, shape=(hidden,))
     out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
     weighted = torch.empty((n, hidden), dtype=torch.bfloat16, device=table.device)
-    partials = torch.empty((1, 16), dtype=torch.float32, device=table.device)
-    call("b200_embedding_weighted", ptr(ids), ptr(table), ptr(out), ptr(norm_weight), ptr(weighted), ptr(partials), n, hidden,
-         vocab, float(scale), tag(table.dtype), stream_ptr())
-    return out, weighted, partials
+    row_scale = torch.empty(16, dtype=torch.float32, device=table.device)
+    call("b200_embedding_weighted", ptr(ids), ptr(table), ptr(out), ptr(norm_weight), ptr(weighted), ptr(row_scale), n, hidden,
+         vocab, float(scale), float(eps), tag(table.dtype), stream_ptr())
+    return out, weighted, row_scale
 
 
 def add_rmsnorm(

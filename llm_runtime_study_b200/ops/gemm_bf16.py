@@ -27,10 +27,10 @@ native.register_library(
     {
         "b200_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "b200_gemm_skinny_variant": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                     c_void_p, c_int, native.c_float, c_void_p],
-        "b200_gemm_skinny_residual": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                      c_void_p, c_void_p],
-        "b200_gemm_skinny_max_partials": [],
+                                     c_void_p, c_void_p],
+        "b200_gemm_skinny_residual": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                      native.c_float, c_void_p, c_void_p, c_void_p, c_void_p],
+        "b200_gemm_skinny_partial_floats": [c_int],
     },
 )
 
@@ -180,16 +180,12 @@ def check_error() -> None:
         raise KernelError(f"tcgen05 projection: a bounded wait ran out ({where})")
 
 
-MAX_PARTIALS = 512     # CTAs whose partial sums of squares the weight-streaming kernel can add up (csrc/gemm_skinny.cu)
-
-
 def linear_skinny(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
                   out_dtype: torch.dtype = torch.bfloat16, *, variant: int = 0, swiglu: bool = False,
-                  partials: torch.Tensor | None = None, eps: float = 0.0) -> torch.Tensor:
+                  row_scale: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ weight.T (+ bias)`` for at most 16 rows of ``x``: the weight-streaming kernel.
-    ``swiglu``: see ``linear``.  ``partials`` (float32 ``[P, 16]``): the rows of ``x`` still lack their
-    RMS-norm factor ``rsqrt(sum of squares / K + eps)``; row ``m``'s sum of squares is ``partials[:, m].sum()``
-    and the factor is applied to the product (before the bias)."""
+    ``swiglu``: see ``linear``.  ``row_scale`` (float32 ``[16]``): the rows of ``x`` still lack these factors
+    (an RMS norm left half done, see ``linear_skinny_residual``); they are applied to the product, before the bias."""
 
     native.require(x, "x", dtype=torch.bfloat16, dims=2)
     native.require(weight, "weight", dtype=torch.bfloat16, dims=2)
@@ -203,25 +199,20 @@ def linear_skinny(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
         native.require(bias, "bias", dtype=torch.float32, shape=(n,))
     if swiglu and n % 16:
         raise KernelError("the SwiGLU epilogue needs an even number of 8-feature blocks")
-    count = 0
-    if partials is not None:
-        native.require(partials, "partials", dtype=torch.float32, dims=2)
-        count = partials.shape[0]
-        if partials.shape[1] != 16 or not 0 < count <= MAX_PARTIALS:
-            raise KernelError(f"partials must be [1..{MAX_PARTIALS}, 16], got {tuple(partials.shape)}")
+    if row_scale is not None:
+        native.require(row_scale, "row_scale", dtype=torch.float32, shape=(16,))
     width = n // 2 if swiglu else n
     out = torch.empty((m, width), dtype=out_dtype, device=x.device)
     native.call("b200_gemm_skinny_variant", x.data_ptr(), weight.data_ptr(), native.ptr(bias), out.data_ptr(), m, n, k, width,
-                1 if out_dtype == torch.float32 else 0, variant, 1 if swiglu else 0, native.ptr(partials), count, float(eps),
-                native.stream_ptr())
+                1 if out_dtype == torch.float32 else 0, variant, 1 if swiglu else 0, native.ptr(row_scale), native.stream_ptr())
     return out
 
 
 def linear_skinny_residual(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, resid: torch.Tensor,
-                           next_weight: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+                           next_weight: torch.Tensor, eps: float) -> tuple[torch.Tensor, torch.Tensor]:
     """``resid += x @ weight.T (+ bias)`` in place (float32 ``[M, N]``, at most 16 rows), and on the way out
-    what the norm after it needs: ``resid * next_weight`` rounded to bfloat16, and per CTA of the kernel the
-    sum of squares of its 16 columns of every row (``[ceil(N / 16), 16]``).  Returns (weighted, partials)."""
+    what the RMS norm after it needs: ``resid * next_weight`` rounded to bfloat16, and every row's factor
+    ``rsqrt(mean of squares + eps)`` (``[16]`` floats; rows from ``M`` on hold 0).  Returns (weighted, row_scale)."""
 
     native.require(x, "x", dtype=torch.bfloat16, dims=2)
     native.require(weight, "weight", dtype=torch.bfloat16, dims=2)
@@ -234,7 +225,9 @@ def linear_skinny_residual(x: torch.Tensor, weight: torch.Tensor, bias: torch.Te
     if bias is not None:
         native.require(bias, "bias", dtype=torch.float32, shape=(n,))
     weighted = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
-    partials = torch.empty((-(-n // 16), 16), dtype=torch.float32, device=x.device)
+    row_scale = torch.empty(16, dtype=torch.float32, device=x.device)
+    partials = torch.empty(native.query("b200_gemm_skinny_partial_floats", n), dtype=torch.float32, device=x.device)
     native.call("b200_gemm_skinny_residual", x.data_ptr(), weight.data_ptr(), native.ptr(bias), resid.data_ptr(), m, n, k, n,
-                next_weight.data_ptr(), weighted.data_ptr(), partials.data_ptr(), native.stream_ptr())
-    return weighted, partials
+                next_weight.data_ptr(), float(eps), weighted.data_ptr(), row_scale.data_ptr(), partials.data_ptr(),
+                native.stream_ptr())
+    return weighted, row_scale

@@ -36,7 +36,7 @@ _LIBRARIES = {
         {
             "b200_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
             "b200_embedding_weighted": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
-                                        c_int, c_void_p],
+                                        c_float, c_int, c_void_p],
             "b200_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
             "b200_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
             "b200_silu_mul_interleaved": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],

@@ -196,22 +196,19 @@ class Block(Part):
 class WeightedRows:
     """Rows of the residual stream multiplied by a norm's weight and rounded to the activation type,
     still lacking the norm's factor ``rsqrt(mean of squares + eps)``.  That factor is one number per
-    row and commutes with a matrix product, so a projection that is handed such rows applies it to its
-    results instead (``Projection`` does, where its kernel can).  ``partials[:, m].sum()`` is row
-    ``m``'s sum of squares.  This is how a part that adds its output into the residual rows can do the
-    work of the norm that follows while it has the rows in its hands, and a batch of a few decoded
-    tokens runs without norm kernels."""
+    row (``scale``) and commutes with a matrix product, so a projection that is handed such rows applies
+    it to its results instead (``Projection`` does, where its kernel can).  This is how a part that adds
+    its output into the residual rows can do the work of the norm that follows while it has the rows in
+    its hands, and a batch of a few decoded tokens runs without norm kernels."""
 
     values: torch.Tensor        # [rows, width], activation type
-    partials: torch.Tensor      # [P, 16] float32
-    eps: float
+    scale: torch.Tensor         # [16] float32; the first ``rows`` entries count
 
     def normalised(self) -> torch.Tensor:
         """The normalised rows themselves, for a consumer that cannot apply the factor (plain tensor operations)."""
 
-        rows, width = self.values.shape
-        factor = torch.rsqrt(self.partials[:, :rows].sum(dim=0) / width + self.eps)
-        return (self.values.float() * factor[:, None]).to(self.values.dtype)
+        rows = self.values.shape[0]
+        return (self.values.float() * self.scale[:rows, None]).to(self.values.dtype)
 
 
 @dataclass

@@ -34,9 +34,9 @@ class TokenEmbedding(Part):
     def forward(self, token_ids: torch.Tensor, next_norm: Any = None):
         fusable = next_norm.fusable() if next_norm is not None and Projection.FUSE_NORMS else None
         if (fusable is not None and self.runtime.dtype == torch.bfloat16 and token_ids.shape[0] <= 16
-                and fusable[0].shape[0] == self.hidden_size):
-            rows, weighted, partials = F.embedding_weighted(token_ids, self.weight, self.scale, fusable[0])
-            return rows, WeightedRows(weighted, partials, fusable[1])
+                and fusable[0].shape[0] == self.hidden_size and self.hidden_size % 8 == 0 and self.hidden_size <= 8 * 2048):
+            rows, weighted, row_scale = F.embedding_weighted(token_ids, self.weight, self.scale, *fusable)
+            return rows, WeightedRows(weighted, row_scale)
         return F.embedding(token_ids, self.weight, self.scale)
 
 

@@ -69,8 +69,8 @@ class Projection:
 
         if not isinstance(x, WeightedRows):
             return x, {}
-        if self._streams(x.values.shape[0]) and x.partials.shape[0] <= gemm_bf16.MAX_PARTIALS and x.values.is_contiguous():
-            return x.values, {"partials": x.partials, "eps": x.eps}
+        if self._streams(x.values.shape[0]) and x.values.is_contiguous():
+            return x.values, {"row_scale": x.scale}
         return x.normalised(), {}
 
     def swiglu(self, x: "torch.Tensor | WeightedRows") -> torch.Tensor:
@@ -118,9 +118,8 @@ class Projection:
         if self.in_features % 8 == 0 and x.is_contiguous():
             fusable = next_norm.fusable() if (next_norm is not None and self.FUSE_NORMS) else None
             if (fusable is not None and add_to is not None and out_dtype == torch.float32 and self._streams(m)
-                    and fusable[0].shape[0] == self.out_features and -(-self.out_features // 16) <= gemm_bf16.MAX_PARTIALS):
-                weighted, partials = gemm_bf16.linear_skinny_residual(x, self.weight, self.bias, add_to, fusable[0])
-                return WeightedRows(weighted, partials, fusable[1])
+                    and fusable[0].shape[0] == self.out_features):
+                return WeightedRows(*gemm_bf16.linear_skinny_residual(x, self.weight, self.bias, add_to, *fusable))
             if m <= gemm_bf16.SKINNY_M:
                 if self.GEMM_BACKEND == "tcgen05" and gemm_bf16.few_rows_kernel(m, self.out_features, self.in_features) == "splitk":
                     if add_to is not None and out_dtype == torch.float32 and self.FUSE_RESIDUAL:

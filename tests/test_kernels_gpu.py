@@ -727,48 +727,48 @@ def test_projection_with_swiglu_epilogue(m, inter, k):
 
 # ------------------------------------------------ RMS norms carried by the weight-streaming projections
 @pytest.mark.parametrize("m,n,k,bias", [(1, 4096, 4096, False), (8, 4096, 12288, False), (3, 1000, 520, True),
-                                        (16, 264, 96, True), (9, 100, 72, False)])
+                                        (16, 264, 96, True), (9, 100, 72, False), (2, 12288, 64, False)])
 def test_projection_adds_into_the_residual_and_prepares_the_next_norm(m, n, k, bias):
-    """resid += x W^T (+ b); on the way out the rows times the next norm's weight in bfloat16, and per CTA of
-    the kernel the sum of squares of its 16 columns: the column sums of `partials` are the rows' sums of squares."""
+    """resid += x W^T (+ b); on the way out the rows times the next norm's weight in bfloat16, and every row's
+    factor rsqrt(mean of squares + eps), added up over the kernel's CTAs by whichever of them finishes last."""
 
     x, w, b, product = _gemm_case(m, n, k, bias)
     torch.manual_seed(n)
     resid = torch.randn(m, n)
     next_weight = 1 + 0.05 * torch.randn(n)
+    eps = 1e-5
     want = resid.double() + product
     resid_dev = dev(resid)
-    weighted, partials = _gemm().linear_skinny_residual(dev(x), dev(w), dev(b) if bias else None, resid_dev, dev(next_weight))
-    scale = float(want.abs().max())
-    torch.testing.assert_close(resid_dev.cpu().double(), want, atol=1e-5 * scale, rtol=0)
-    torch.testing.assert_close(weighted.cpu().double(), want * next_weight.double(), atol=1e-2 * scale, rtol=0)
-    assert partials.shape == (-(-n // 16), 16)
-    torch.testing.assert_close(partials[:, :m].sum(dim=0).cpu().double(), (want * want).sum(dim=1), rtol=1e-5, atol=0)
-    # the same bits whatever the other rows are
+    args = (dev(x), dev(w), dev(b) if bias else None)
+    weighted, scale = _gemm().linear_skinny_residual(*args, resid_dev, dev(next_weight), eps)
+    size = float(want.abs().max())
+    torch.testing.assert_close(resid_dev.cpu().double(), want, atol=1e-5 * size, rtol=0)
+    torch.testing.assert_close(weighted.cpu().double(), want * next_weight.double(), atol=1e-2 * size, rtol=0)
+    torch.testing.assert_close(scale[:m].cpu().double(), torch.rsqrt((want * want).mean(dim=1) + eps), rtol=1e-5, atol=0)
+    # again on fresh rows: the ticket of the first launch has come back to zero, and the sums are added in a fixed order
+    resid_again = dev(resid)
+    weighted_again, scale_again = _gemm().linear_skinny_residual(*args, resid_again, dev(next_weight), eps)
+    assert torch.equal(resid_again, resid_dev) and torch.equal(weighted_again, weighted) and torch.equal(scale_again[:m], scale[:m])
+    # and the same bits whatever the other rows are
     resid_one = dev(resid[:1])
-    weighted_one, partials_one = _gemm().linear_skinny_residual(dev(x[:1]), dev(w), dev(b) if bias else None, resid_one, dev(next_weight))
-    assert torch.equal(resid_one[0], resid_dev[0]) and torch.equal(weighted_one[0], weighted[0])
-    assert torch.equal(partials_one[:, 0], partials[:, 0])
+    weighted_one, scale_one = _gemm().linear_skinny_residual(dev(x[:1]), dev(w), dev(b) if bias else None, resid_one, dev(next_weight), eps)
+    assert torch.equal(resid_one[0], resid_dev[0]) and torch.equal(weighted_one[0], weighted[0]) and torch.equal(scale_one[0], scale[0])
 
 
-@pytest.mark.parametrize("m,n,k,bias,parts", [(1, 6144, 4096, False, 256), (8, 136, 4096, True, 256), (3, 1000, 520, True, 33),
-                                              (16, 272, 96, False, 6), (12, 503, 72, False, 1), (5, 17, 8, True, 512)])
+@pytest.mark.parametrize("m,n,k,bias", [(1, 6144, 4096, False), (8, 136, 4096, True), (3, 1000, 520, True),
+                                        (16, 272, 96, False), (12, 503, 72, False), (5, 17, 8, True)])
 @pytest.mark.parametrize("out", [torch.float32, torch.bfloat16])
-def test_projection_finishes_a_norm_that_was_left_half_done(m, n, k, bias, parts, out):
-    """Rows that lack their factor rsqrt(sum of squares / K + eps), the sums of squares given as partial sums:
-    the kernel adds the partial sums up and applies the factor to its results, before the bias."""
+def test_projection_finishes_a_norm_that_was_left_half_done(m, n, k, bias, out):
+    """Rows that lack a factor each: the kernel applies the factors to its results, before the bias."""
 
     x, w, b, product = _gemm_case(m, n, k, bias)
     torch.manual_seed(k)
-    partials = torch.rand(parts, 16) * (k / parts)
-    eps = 1e-5
-    factor = torch.rsqrt(partials[:, :m].double().sum(dim=0) / k + eps)
-    want = (product - (b.double() if bias else 0)) * factor[:, None] + (b.double() if bias else 0)
-    got = _gemm().linear_skinny(dev(x), dev(w), dev(b) if bias else None, out, partials=dev(partials), eps=eps)
-    again = _gemm().linear_skinny(dev(x), dev(w), dev(b) if bias else None, out, partials=dev(partials), eps=eps)
-    assert torch.equal(got, again)
-    scale = float(want.abs().max())
-    torch.testing.assert_close(got.cpu().double(), want, atol=(1e-2 if out == torch.bfloat16 else 2e-5) * scale, rtol=0)
+    factor = torch.zeros(16)
+    factor[:m] = 0.2 + torch.rand(m)
+    want = (product - (b.double() if bias else 0)) * factor[:m, None].double() + (b.double() if bias else 0)
+    got = _gemm().linear_skinny(dev(x), dev(w), dev(b) if bias else None, out, row_scale=dev(factor))
+    size = float(want.abs().max())
+    torch.testing.assert_close(got.cpu().double(), want, atol=(1e-2 if out == torch.bfloat16 else 2e-5) * size, rtol=0)
 
 
 def test_swiglu_projection_finishes_a_norm():
@@ -776,26 +776,26 @@ def test_swiglu_projection_finishes_a_norm():
     m, inter, k = 7, 272, 96
     x = torch.randn(m, k).bfloat16()
     gate, up = (torch.randn(inter, k) * 0.08).bfloat16(), (torch.randn(inter, k) * 0.08).bfloat16()
-    partials = torch.rand(6, 16) * 20
-    factor = torch.rsqrt(partials[:, :m].double().sum(dim=0) / k + 1e-6)[:, None]
-    g, u = (x.double() @ gate.double().T) * factor, (x.double() @ up.double().T) * factor
+    factor = torch.zeros(16)
+    factor[:m] = 0.5 + torch.rand(m)
+    g, u = (x.double() @ gate.double().T) * factor[:m, None].double(), (x.double() @ up.double().T) * factor[:m, None].double()
     want = g / (1 + torch.exp(-g)) * u
-    got = _gemm().linear_skinny(dev(x), dev(_interleave(gate, up)), None, torch.bfloat16, swiglu=True, partials=dev(partials), eps=1e-6)
+    got = _gemm().linear_skinny(dev(x), dev(_interleave(gate, up)), None, torch.bfloat16, swiglu=True, row_scale=dev(factor))
     torch.testing.assert_close(got.cpu().double(), want, atol=2e-2 * float(want.abs().max()), rtol=0)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n,hidden,vocab", [(1, 4096, 1000), (16, 100, 37), (5, 264, 503)])
+@pytest.mark.parametrize("n,hidden,vocab", [(1, 4096, 1000), (16, 104, 37), (5, 264, 503), (3, 16384, 50)])
 def test_embedding_prepares_the_first_norm(dtype, n, hidden, vocab):
     torch.manual_seed(2)
     table = torch.randn(vocab, hidden).to(dtype)
     ids = torch.randint(0, vocab, (n,), dtype=torch.int32)
     norm_weight = 1 + 0.05 * torch.randn(hidden)
-    rows, weighted, partials = F().embedding_weighted(dev(ids), dev(table), 1.5, dev(norm_weight))
+    rows, weighted, scale = F().embedding_weighted(dev(ids), dev(table), 1.5, dev(norm_weight), 1e-5)
     want = table[ids.long()].double() * 1.5
     torch.testing.assert_close(rows.cpu().double(), want, atol=1e-6, rtol=1e-6)
     torch.testing.assert_close(weighted.cpu().double(), want * norm_weight.double(), atol=1e-2 * float(want.abs().max()), rtol=1e-2)
-    torch.testing.assert_close(partials[0, :n].cpu().double(), (want * want).sum(dim=1), rtol=1e-5, atol=0)
+    torch.testing.assert_close(scale[:n].cpu().double(), torch.rsqrt((want * want).mean(dim=1) + 1e-5), rtol=1e-5, atol=0)
 
 
 def test_weighted_rows_through_projections_equal_the_norm_kernel():
