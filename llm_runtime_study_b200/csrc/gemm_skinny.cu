@@ -15,9 +15,11 @@
 // (y = w * x * rsqrt(mean(x^2) + eps), mini_llm/nn/norm.py:42-46; h = r + f(x), mini_llm/model/qwen.py:67, 72):
 //   * EPI_RESIDUAL: the product is added into the float32 residual rows in place; the same pass writes
 //     the rows multiplied by the *next* norm's weight, rounded to bfloat16, and every CTA leaves the sum
-//     of squares of its 16 columns of every row in scratch memory ([CTAs][16 rows]).  The CTA that
-//     finishes last (a ticket counter) adds those up in CTA order, whoever it is, and writes the rows'
-//     factors rsqrt(mean of squares + eps).
+//     of squares of its 16 columns of every row in scratch memory ([CTAs][16 rows]).  A one-CTA kernel
+//     behind it adds those up in CTA order and writes the rows' factors rsqrt(mean of squares + eps); it
+//     releases the kernel after it at its first instruction, so the next projection fetches its first
+//     weights meanwhile.  (Adding them up in every CTA of the consuming kernel, or in the producing
+//     kernel's last CTA behind a ticket, cost 4 to 6 us per layer more: measured.)
 //   * SCALED: the rows this kernel multiplies are such weighted, not yet normalised rows.  The factor
 //     is one number per row and commutes with the product, so it is applied to the accumulators.
 // Rounding r * w to bfloat16 before the scale instead of after changes nothing in relative terms.
@@ -42,9 +44,7 @@ struct NormFusion {
   const float* next_weight;   // EPI_RESIDUAL: weight of the norm that follows, [N]
   float eps;                  // EPI_RESIDUAL: its eps
   __nv_bfloat16* weighted;    // EPI_RESIDUAL: out, [M][N] = (residual + product) * next_weight
-  float* row_scale_out;       // EPI_RESIDUAL: out, [16] = rsqrt(mean of squares of the new residual row + eps)
-  float* partials;            // EPI_RESIDUAL: scratch, [gridDim.x][16]
-  unsigned* ticket;           // EPI_RESIDUAL: zero before the launch, zero again after it
+  float* partials;            // EPI_RESIDUAL: out, [gridDim.x][16] sums of squares of the new residual rows, per CTA
 };
 
 template <int NT, int UNROLL, int kSkinnyWarps, int EPI, bool SCALED, typename OutT>
@@ -53,8 +53,6 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
                    const float* __restrict__ bias, OutT* __restrict__ C, int M, int N, int K, int ldc, NormFusion fuse) {
   constexpr bool SWIGLU = EPI == EPI_SWIGLU;
   __shared__ float red[kSkinnyWarps][16][NT * 8 + 1];
-  __shared__ float slice_sum[EPI == EPI_RESIDUAL ? kSkinnyWarps * 2 : 1][16];
-  __shared__ int is_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
   const __nv_bfloat16* wa = W + static_cast<size_t>(min(n0 + g, N - 1)) * K + t * 8;
@@ -142,27 +140,6 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
       for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
       if (row == 0) fuse.partials[static_cast<size_t>(blockIdx.x) * 16 + m] = sq;
     }
-    // The CTA that comes last adds the partial sums of all CTAs, in their order: thread (row = t % 16,
-    // slice = t / 16) takes every (threads / 16)-th CTA's, then one thread per row adds the slices.
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) is_last = atomicInc(fuse.ticket, gridDim.x - 1) == gridDim.x - 1;   // wraps to zero
-    __syncthreads();
-    if (is_last) {
-      __threadfence();
-      constexpr int kSlices = kSkinnyWarps * 2;
-      const int r = threadIdx.x & 15, slice = threadIdx.x >> 4;
-      float s = 0.f;
-      for (int i = slice; i < static_cast<int>(gridDim.x); i += kSlices) s += __ldcg(fuse.partials + static_cast<size_t>(i) * 16 + r);
-      slice_sum[slice][r] = s;
-      __syncthreads();
-      if (threadIdx.x < 16) {
-        float total = 0.f;
-#pragma unroll
-        for (int i = 0; i < kSlices; ++i) total += slice_sum[i][threadIdx.x];
-        fuse.row_scale_out[threadIdx.x] = threadIdx.x < NT * 8 ? rsqrtf(total / static_cast<float>(N) + fuse.eps) : 0.f;
-      }
-    }
   } else if constexpr (SWIGLU) {
     // rows 0..7 of the tile are gate features, rows 8..15 the matching up features
     for (int idx = threadIdx.x; idx < 8 * NT * 8; idx += kSkinnyWarps * 32) {
@@ -197,6 +174,26 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
       acc += bias ? bias[n] : 0.f;
       C[static_cast<size_t>(m) * ldc + n] = from_float<OutT>(acc);
     }
+  }
+}
+
+// row_scale[r] = rsqrt(sum over CTAs of partials[cta][r] / width + eps) for the 16 rows: thread (row = t % 16,
+// slice = t / 16) adds every 16th CTA's share, one thread per row adds the slices.  One CTA of 256 threads.
+__global__ void __launch_bounds__(256) rms_finish_kernel(const float* __restrict__ partials, int ctas, int rows, float width,
+                                                          float eps, float* __restrict__ row_scale) {
+  __shared__ float slice_sum[16][16];
+  pdl_launch_dependents();     // what follows is a projection: it may fetch its first weights while this runs
+  pdl_wait();
+  const int r = threadIdx.x & 15, slice = threadIdx.x >> 4;
+  float s = 0.f;
+  for (int i = slice; i < ctas; i += 16) s += partials[static_cast<size_t>(i) * 16 + r];
+  slice_sum[slice][r] = s;
+  __syncthreads();
+  if (threadIdx.x < 16) {
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) total += slice_sum[i][threadIdx.x];
+    row_scale[threadIdx.x] = static_cast<int>(threadIdx.x) < rows ? rsqrtf(total / width + eps) : 0.f;
   }
 }
 
@@ -284,33 +281,23 @@ extern "C" int b200_gemm_skinny(const void* X, const void* W, const float* bias,
   return b200_gemm_skinny_variant(X, W, bias, C, M, N, K, ldc, out_f32, 0, 0, nullptr, stream);
 }
 
-// Tickets of the residual form: one counter per launch, taken in turn out of a zeroed array on the device.  A
-// launch leaves its counter at zero and launches follow each other on one stream, so a counter is free again
-// long before its turn comes round.
-constexpr int kTickets = 4096;
-__device__ unsigned g_skinny_tickets[kTickets];
-
 // resid[M][N] (float32, row stride ldc) += X W^T (+ bias); weighted[M][N] (bfloat16) = resid * next_weight;
 // row_scale_out[16] = rsqrt(mean of squares of each new row of resid + eps) (rows from M on: 0).
-// `partials` is scratch of b200_gemm_skinny_partial_floats(N) floats.
+// `partials` is scratch of b200_gemm_skinny_partial_floats(N) floats.  Two launches.
 extern "C" int b200_gemm_skinny_residual(const void* X, const void* W, const float* bias, float* resid, int M, int N, int K,
                                          int ldc, const float* next_weight, float eps, void* weighted, float* row_scale_out,
                                          float* partials, cudaStream_t stream) {
   if (!resid || !next_weight || !weighted || !row_scale_out || !partials) return B200_ERR_BAD_SIZE;
-  static unsigned* tickets[kMaxDevices] = {};
-  static unsigned turn = 0;
-  int device = 0;
-  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return 10007;
-  if (!tickets[device] && cudaGetSymbolAddress(reinterpret_cast<void**>(&tickets[device]), g_skinny_tickets) != cudaSuccess)
-    return 10007;
   NormFusion fuse{};
   fuse.next_weight = next_weight;
   fuse.eps = eps;
   fuse.weighted = static_cast<__nv_bfloat16*>(weighted);
-  fuse.row_scale_out = row_scale_out;
   fuse.partials = partials;
-  fuse.ticket = tickets[device] + (turn++ % kTickets);
-  return skinny(X, W, bias, resid, M, N, K, ldc, 1, 0, EPI_RESIDUAL, fuse, stream);
+  if (int e = skinny(X, W, bias, resid, M, N, K, ldc, 1, 0, EPI_RESIDUAL, fuse, stream)) return e;
+  if (M <= 0 || N <= 0) return 0;
+  launch(rms_finish_kernel, dim3(1), dim3(256), 0, stream, static_cast<const float*>(partials), (N + 15) / 16, M,
+         static_cast<float>(N), eps, row_scale_out);
+  return launch_status();
 }
 
 extern "C" long b200_gemm_skinny_partial_floats(int N) { return static_cast<long>((N + 15) / 16) * 16; }

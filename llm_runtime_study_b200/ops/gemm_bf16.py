@@ -229,5 +229,5 @@ def linear_skinny_residual(x: torch.Tensor, weight: torch.Tensor, bias: torch.Te
     partials = torch.empty(native.query("b200_gemm_skinny_partial_floats", n), dtype=torch.float32, device=x.device)
     native.call("b200_gemm_skinny_residual", x.data_ptr(), weight.data_ptr(), native.ptr(bias), resid.data_ptr(), m, n, k, n,
                 next_weight.data_ptr(), float(eps), weighted.data_ptr(), row_scale.data_ptr(), partials.data_ptr(),
-                native.stream_ptr())
+                native.stream_ptr(), launches=2)
     return weighted, row_scale

@@ -730,7 +730,7 @@ def test_projection_with_swiglu_epilogue(m, inter, k):
                                         (16, 264, 96, True), (9, 100, 72, False), (2, 12288, 64, False)])
 def test_projection_adds_into_the_residual_and_prepares_the_next_norm(m, n, k, bias):
     """resid += x W^T (+ b); on the way out the rows times the next norm's weight in bfloat16, and every row's
-    factor rsqrt(mean of squares + eps), added up over the kernel's CTAs by whichever of them finishes last."""
+    factor rsqrt(mean of squares + eps), added up over the kernel's CTAs in their order by a small kernel behind it."""
 
     x, w, b, product = _gemm_case(m, n, k, bias)
     torch.manual_seed(n)
@@ -745,7 +745,7 @@ def test_projection_adds_into_the_residual_and_prepares_the_next_norm(m, n, k, b
     torch.testing.assert_close(resid_dev.cpu().double(), want, atol=1e-5 * size, rtol=0)
     torch.testing.assert_close(weighted.cpu().double(), want * next_weight.double(), atol=1e-2 * size, rtol=0)
     torch.testing.assert_close(scale[:m].cpu().double(), torch.rsqrt((want * want).mean(dim=1) + eps), rtol=1e-5, atol=0)
-    # again on fresh rows: the ticket of the first launch has come back to zero, and the sums are added in a fixed order
+    # again on fresh rows: the sums are added in a fixed order
     resid_again = dev(resid)
     weighted_again, scale_again = _gemm().linear_skinny_residual(*args, resid_again, dev(next_weight), eps)
     assert torch.equal(resid_again, resid_dev) and torch.equal(weighted_again, weighted) and torch.equal(scale_again[:m], scale[:m])
@@ -785,7 +785,7 @@ def test_swiglu_projection_finishes_a_norm():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n,hidden,vocab", [(1, 4096, 1000), (16, 104, 37), (5, 264, 503), (3, 16384, 50)])
+@pytest.mark.parametrize("n,hidden,vocab", [(1, 4096, 1000), (16, 104, 37), (5, 264, 503), (3, 8192, 50)])
 def test_embedding_prepares_the_first_norm(dtype, n, hidden, vocab):
     torch.manual_seed(2)
     table = torch.randn(vocab, hidden).to(dtype)
