@@ -83,6 +83,13 @@ struct DecodeParams {
   const float* inv_freq;   // [D / 2] or nullptr: no rotation
   bf16* k_pool;            // [pages][nkv][page_size][D], written at the new position
   bf16* v_pool;
+  // A launch recorded into a CUDA graph has its grid fixed for good, sized (num_splits) for the longest sequence
+  // the engine may ever hold.  How many of those parts a replay uses is looked up on the device: the host writes
+  // the longest length of the batch into *live_longest before every replay, and parts_table[length >> table_shift]
+  // is what the host would choose for that length.  CTAs of the parts beyond it leave at once.
+  const int* live_longest; // nullptr: every launch uses num_splits parts
+  const int* parts_table;
+  int table_shift, table_len;
 };
 
 __device__ int g_decode_error = 0;
@@ -130,7 +137,13 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
   // the newest were written by earlier steps.  Only q, the newest key and the outputs depend on the
   // kernel before this one, so the first blocks can be asked for before the dependency wait.
   const int len = p.kv_len[b];
-  int chunk = (len + p.num_splits - 1) / p.num_splits;
+  int splits = p.num_splits;     // parts in use: all of the grid's, or what the table says for the batch's longest sequence
+  if (p.live_longest != nullptr) {
+    const int at = min(max(*p.live_longest, 0) >> p.table_shift, p.table_len - 1);
+    splits = max(1, min(p.parts_table[at], p.num_splits));
+  }
+  if (split >= splits) return;   // the whole CTA: nothing of it has touched a barrier or a ticket
+  int chunk = (len + splits - 1) / splits;
   chunk = ((chunk + 63) / 64) * 64;
   const int c0 = split * chunk;
   const int c1 = min(c0 + chunk, len) - 1;    // last key of this CTA's part (c1 < c0: nothing to do)
@@ -449,7 +462,7 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
       L += sm_l[w * HEADS + h] * f;
     }
     const int head = head0 + h;
-    if (p.num_splits == 1) {
+    if (splits == 1) {
       p.out[(static_cast<long>(b) * p.nq + head) * D + col] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     } else {
       const long slot = (static_cast<long>(b) * p.nq + head) * p.num_splits + split;
@@ -460,20 +473,20 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
       }
     }
   }
-  if (p.num_splits == 1) return;
+  if (splits == 1) return;
 
   // ticket: the CTA that finishes last among the parts of this (request, KV head, slice) adds them up
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
-    const unsigned old = atomicInc(&p.tickets[(static_cast<size_t>(b) * p.nkv + kvh) * p.slices + slice], p.num_splits - 1);
-    sm_last = old == static_cast<unsigned>(p.num_splits - 1);   // atomicInc wraps to zero: ready for the next launch
+    const unsigned old = atomicInc(&p.tickets[(static_cast<size_t>(b) * p.nkv + kvh) * p.slices + slice], splits - 1);
+    sm_last = old == static_cast<unsigned>(splits - 1);   // atomicInc wraps to zero: ready for the next launch
   }
   __syncthreads();
   if (!sm_last) return;
   __threadfence();
-  for (int idx = threadIdx.x; idx < heads_here * p.num_splits; idx += 128) {
-    const int h = idx / p.num_splits, s = idx - h * p.num_splits;
+  for (int idx = threadIdx.x; idx < heads_here * splits; idx += 128) {
+    const int h = idx / splits, s = idx - h * splits;
     const long slot = (static_cast<long>(b) * p.nq + head0 + h) * p.num_splits + s;
     sm_pm[h][s] = __ldcg(p.part_ml + slot * 2);
     sm_pl[h][s] = __ldcg(p.part_ml + slot * 2 + 1);
@@ -483,19 +496,19 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
   for (int idx = threadIdx.x; idx < heads_here * (D / 4); idx += 128) {
     const int h = idx / (D / 4), col = (idx - h * (D / 4)) * 4;
     float M = -INFINITY;
-    for (int s = 0; s < p.num_splits; ++s) M = fmaxf(M, sm_pm[h][s]);
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, sm_pm[h][s]);
     const float ref = M == -INFINITY ? 0.f : M;
     const float* part = p.part_o + (static_cast<long>(b) * p.nq + head0 + h) * p.num_splits * D + col;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     float L = 0.f;
-    for (int s0 = 0; s0 < p.num_splits; s0 += 8) {
+    for (int s0 = 0; s0 < splits; s0 += 8) {
       float4 v[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u)
-        if (s0 + u < p.num_splits) v[u] = __ldcg(reinterpret_cast<const float4*>(part + static_cast<long>(s0 + u) * D));
+        if (s0 + u < splits) v[u] = __ldcg(reinterpret_cast<const float4*>(part + static_cast<long>(s0 + u) * D));
 #pragma unroll
       for (int u = 0; u < 8; ++u)
-        if (s0 + u < p.num_splits) {           // parts are added in their order, whatever the order of arrival
+        if (s0 + u < splits) {           // parts are added in their order, whatever the order of arrival
           const float f = exp2f(sm_pm[h][s0 + u] - ref);
           acc[0] += v[u].x * f;
           acc[1] += v[u].y * f;
@@ -583,6 +596,9 @@ struct FusedInputs {
   const float* k_weight = nullptr;
   float eps = 0.f;
   const float* inv_freq = nullptr;
+  const int* live_longest = nullptr;   // see DecodeParams
+  const int* parts_table = nullptr;
+  int table_shift = 0, table_len = 0;
 };
 
 static int decode_tma(const void* q, const FusedInputs& fused, const void* k_pool, const void* v_pool, void* out, const int* kv_len,
@@ -607,6 +623,11 @@ static int decode_tma(const void* q, const FusedInputs& fused, const void* k_poo
   p.k_weight = fused.k_weight;
   p.eps = fused.eps;
   p.inv_freq = fused.inv_freq;
+  if (fused.live_longest != nullptr && (fused.parts_table == nullptr || fused.table_len <= 0 || fused.table_shift < 0)) return B200_ERR_BAD_SIZE;
+  p.live_longest = fused.live_longest;
+  p.parts_table = fused.parts_table;
+  p.table_shift = fused.table_shift;
+  p.table_len = fused.table_len;
   p.k_pool = static_cast<bf16*>(const_cast<void*>(k_pool));
   p.v_pool = static_cast<bf16*>(const_cast<void*>(v_pool));
   p.out = static_cast<bf16*>(out);
@@ -648,8 +669,14 @@ static int decode_tma(const void* q, const FusedInputs& fused, const void* k_poo
 extern "C" int b200_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, void* out, const int* kv_len,
                                          const int* block_table, int table_stride, int page_size, int num_pages, int requests,
                                          int nq, int nkv, float scale, int num_splits, float* scratch, long scratch_floats,
-                                         unsigned* tickets, long ticket_count, cudaStream_t stream) {
-  return decode_tma(q, FusedInputs{}, k_pool, v_pool, out, kv_len, block_table, table_stride, page_size, num_pages, requests, nq,
+                                         unsigned* tickets, long ticket_count, const int* live_longest,
+                                         const int* parts_table, int table_shift, int table_len, cudaStream_t stream) {
+  FusedInputs plain;
+  plain.live_longest = live_longest;
+  plain.parts_table = parts_table;
+  plain.table_shift = table_shift;
+  plain.table_len = table_len;
+  return decode_tma(q, plain, k_pool, v_pool, out, kv_len, block_table, table_stride, page_size, num_pages, requests, nq,
                     nkv, scale, num_splits, scratch, scratch_floats, tickets, ticket_count, stream);
 }
 
@@ -662,9 +689,14 @@ extern "C" int b200_attention_decode_tma_fused(const void* qkv, int qkv_stride, 
                                                const int* kv_len, const int* block_table, int table_stride, int page_size,
                                                int num_pages, int requests, int nq, int nkv, float scale, int num_splits,
                                                float* scratch, long scratch_floats, unsigned* tickets, long ticket_count,
-                                               cudaStream_t stream) {
+                                               const int* live_longest, const int* parts_table, int table_shift,
+                                               int table_len, cudaStream_t stream) {
   if (qkv == nullptr) return B200_ERR_BAD_SIZE;
   FusedInputs fused;
+  fused.live_longest = live_longest;
+  fused.parts_table = parts_table;
+  fused.table_shift = table_shift;
+  fused.table_len = table_len;
   fused.qkv = qkv;
   fused.qkv_stride = qkv_stride;
   fused.q_weight = q_weight;

@@ -10,15 +10,17 @@ the sampling kernels that write the drawn token back into the records.  One grap
   its bucket with rows that point at the padding slot, which is never live (length 0,
   no pages: the cache-write and the attention kernels skip them), so a batch that
   shrinks or grows by one does not pay a new capture;
-* *length class*: kernels launched under capture size their grids from an upper bound
-  of the sequence lengths that cannot change afterwards; with one graph per class of
-  lengths (steps of a quarter of the largest power of two below, at least 512) the
-  decode attention is cut into the number of parts that suits the live lengths rather
-  than the longest sequence the engine was opened for;
 * whether some row needs the top-k / top-p pass of the sampler.
 
+Kernels launched under capture size their grids from an upper bound of the sequence
+lengths that cannot change afterwards (the longest sequence the engine was opened for).
+The decode attention still cuts a replay's sequences into the number of parts that
+suits them: the host sends the longest length of the batch along, and the kernel looks
+up, in a table of the host's own choices by length, how many of its grid's parts to use
+(``ops/attention_bf16.LiveParts``); the CTAs of the others leave at once.
+
 All per-step input lives in one persistent device buffer whose layout is fixed by the
-bucket and the table width: the slots of the batch and the block tables.  It is copied
+bucket and the table width: the slots of the batch, the longest length, the block tables.  It is copied
 only when it differs from what the device already holds, so a replay is at most one
 host-to-device copy plus one graph launch.  Graphs share one memory pool: they run one
 after the other on one stream, and what leaves a graph (the drawn ids) lies outside it.
@@ -37,35 +39,26 @@ from ..cache.manager import RequestCache
 from .step import StepContext, _round_up
 
 
-def length_class(longest: int, limit: int) -> int:
-    """The upper bound under which a sequence of ``longest`` tokens is captured."""
-
-    floor = 1
-    while floor * 2 <= longest:
-        floor *= 2
-    step = max(512, floor // 4)
-    return min(limit, -(-longest // step) * step) if limit >= longest else longest
-
-
 class DecodeGraph:
-    """One captured decode step for exactly ``batch`` rows of at most ``bound`` tokens."""
+    """One captured decode step for exactly ``batch`` rows."""
 
-    def __init__(self, owner: "DecodeGraphs", batch: int, bound: int, filtered: bool) -> None:
+    def __init__(self, owner: "DecodeGraphs", batch: int, filtered: bool) -> None:
         runner = owner.runner
-        self.runner, self.batch, self.bound, self.filtered = runner, batch, bound, filtered
+        self.runner, self.batch, self.filtered = runner, batch, filtered
         manager = runner.manager
+        self.bound = manager.max_seq_len
         # a block table wide enough for the longest sequence, per group (groups may differ in page size)
         self.table_widths = [_round_up(-(-manager.max_seq_len // pool.page_size), 4) for pool in manager.groups]
         self.groups = len(manager.layout.groups)
         b = batch
-        # what the host sends every step (slots, tables), then what never changes, then what the device fills in
-        sizes = [b] + [b * w for w in self.table_widths] + [b, b + 1, b] + [b, b, b]
+        # what the host sends every step (slots, longest length, tables), then what never changes, then what the device fills in
+        sizes = [b, 1] + [b * w for w in self.table_widths] + [b, b + 1, b] + [b, b, b]
         self.offsets, total = [], 0
         for size in sizes:
             self.offsets.append(total)
             total += _round_up(size, 4)
         self.sizes = sizes
-        self.sent = self.offsets[1 + self.groups]          # words copied per step
+        self.sent = self.offsets[2 + self.groups]          # words copied per step
         device = runner.runtime.device
         self.dev = torch.zeros(total, dtype=torch.int32, device=device)
         self.host = [torch.zeros(self.sent, dtype=torch.int32, pin_memory=True) for _ in range(2)]
@@ -78,9 +71,9 @@ class DecodeGraph:
         self.kernel_launches = 0
         ramp = torch.arange(b + 1, dtype=torch.int32, device=device)
         g = self.groups
-        self._view(1 + g).copy_(ramp[:b])                   # token -> entry
-        self._view(2 + g).copy_(ramp)                       # first token of each entry
-        self._view(3 + g).copy_(ramp[:b])                   # rows whose logits are wanted: all
+        self._view(2 + g).copy_(ramp[:b])                   # token -> entry
+        self._view(3 + g).copy_(ramp)                       # first token of each entry
+        self._view(4 + g).copy_(ramp[:b])                   # rows whose logits are wanted: all
         self.ctx = self._static_context()
 
     def _view(self, i: int) -> torch.Tensor:
@@ -90,10 +83,13 @@ class DecodeGraph:
         runner, b, g = self.runner, self.batch, self.groups
         ctx = StepContext(runner.runtime, runner.manager)
         ctx.num_tokens = ctx.num_entries = ctx.num_logit_rows = b
+        from ..ops.attention_bf16 import LiveParts
+
         ctx.slots = ctx.row_slots = self._view(0)
-        ctx.tables = [self._view(1 + i).view(b, self.table_widths[i]) for i in range(g)]
-        ctx.token_entry, ctx.q_start, ctx.logit_rows = self._view(1 + g), self._view(2 + g), self._view(3 + g)
-        ctx.token_ids, ctx.positions, ctx.kv_len = self._view(4 + g), self._view(5 + g), self._view(6 + g)
+        ctx.live_parts = LiveParts(self._view(1), self.bound)
+        ctx.tables = [self._view(2 + i).view(b, self.table_widths[i]) for i in range(g)]
+        ctx.token_entry, ctx.q_start, ctx.logit_rows = self._view(2 + g), self._view(3 + g), self._view(4 + g)
+        ctx.token_ids, ctx.positions, ctx.kv_len = self._view(5 + g), self._view(6 + g), self._view(7 + g)
         ctx.q_lens = [1] * b
         # kernels launched under capture may only size their grids from limits that never change
         ctx.kv_lens = [self.bound] * b
@@ -112,9 +108,10 @@ class DecodeGraph:
         sent = np.full(self.sent, -1, dtype=np.int32)
         sent[:b] = manager.padding_slot
         sent[: len(requests)] = [r.slot for r in requests]
-        sent[b : self.offsets[1]] = 0
+        sent[b : self.offsets[2]] = 0
+        sent[self.offsets[1]] = max(r.length for r in requests) + 1     # the longest sequence once this step has run
         for g in range(self.groups):
-            o, w = self.offsets[1 + g], self.table_widths[g]
+            o, w = self.offsets[2 + g], self.table_widths[g]
             table = sent[o : o + b * w].reshape(b, w)
             for i, r in enumerate(requests):
                 row = r.tables[g]
@@ -193,11 +190,11 @@ class DecodeGraph:
 
 
 class DecodeGraphs:
-    """Graphs by (batch-size bucket, length class, filtered), captured on first use."""
+    """Graphs by (batch-size bucket, filtered), captured on first use."""
 
     def __init__(self, runner: Any) -> None:
         self.runner = runner
-        self._graphs: dict[tuple[int, int, bool], DecodeGraph] = {}
+        self._graphs: dict[tuple[int, bool], DecodeGraph] = {}
         self._pool = None
 
     def bucket(self, batch: int) -> int:
@@ -213,7 +210,7 @@ class DecodeGraphs:
         """Some captured graph of the bucket that holds ``batch`` rows (for reports)."""
 
         size = self.bucket(batch)
-        return next((g for (b, _, _), g in self._graphs.items() if b == size), None)
+        return next((g for (b, _), g in self._graphs.items() if b == size), None)
 
     def run(self, requests: Sequence[RequestCache], sampler: Any, filtered: bool) -> tuple[torch.Tensor, torch.Tensor]:
         """Replay the step for these requests; returns (drawn ids on the device, logits).
@@ -222,8 +219,7 @@ class DecodeGraphs:
         runner = self.runner
         if self._pool is None:
             self._pool = torch.cuda.graph_pool_handle()
-        longest = max(r.length for r in requests) + 1
-        key = (self.bucket(len(requests)), length_class(longest, runner.manager.max_seq_len), bool(filtered))
+        key = (self.bucket(len(requests)), bool(filtered))
         graph = self._graphs.get(key)
         if graph is None:
             graph = self._graphs[key] = DecodeGraph(self, *key)

@@ -85,6 +85,7 @@ class StepContext:
         self.all_decode = False
         self.captured = False   # True while a CUDA graph holds this batch's launches
         self.logits_at_every_row = False         # the wanted rows are all rows, in order
+        self.live_parts: Any = None              # under a graph capture: how the decode attention finds its parts per replay
         self.row_slots: torch.Tensor = None      # [M] int32 slot of each sampled row (step_sampled / decode_sampled)
         self.staged_records: torch.Tensor = None # [M, SLOT_WORDS] int32 records the host writes for the sampled rows
 

@@ -33,9 +33,11 @@ _TMA_TABLE = {
     "b200_attention_decode_tma_scratch_floats": [c_int, c_int, c_int],
     "b200_attention_decode_tma_tickets": [c_int, c_int, c_int],
     "b200_attention_decode_tma_error": [],
-    "b200_attention_decode_tma": [c_void_p] * 6 + [c_int] * 6 + [c_float, c_int, c_void_p, c_long, c_void_p, c_long, c_void_p],
+    "b200_attention_decode_tma": [c_void_p] * 6 + [c_int] * 6 + [c_float, c_int, c_void_p, c_long, c_void_p, c_long]
+                                 + [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "b200_attention_decode_tma_fused": [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p] + [c_void_p] * 5 + [c_int] * 6
-                                       + [c_float, c_int, c_void_p, c_long, c_void_p, c_long, c_void_p],
+                                       + [c_float, c_int, c_void_p, c_long, c_void_p, c_long]
+                                       + [c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
 FUSE_DECODE = os.environ.get("LLM_RUNTIME_STUDY_B200_FUSE_DECODE", "1") != "0"
 # "tma": pages streamed by TMA, parts merged in the same launch; "mma": the cp.async kernels of attention_mma.cu
@@ -232,7 +234,7 @@ def check_tcgen05_error(head_dim: int) -> None:
 
 def decode_attention(
     q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, *, kv_len: torch.Tensor, block_table: torch.Tensor,
-    scale: float, window: int = 0, splits: int = 1, backend: str | None = None,
+    scale: float, window: int = 0, splits: int = 1, backend: str | None = None, live: "LiveParts | None" = None,
 ) -> torch.Tensor:
     """One query token per request (row ``i`` of ``q`` belongs to row ``i`` of
     ``block_table``) over its ``kv_len[i]`` cached keys, the sequence cut into
@@ -243,7 +245,7 @@ def decode_attention(
         native.require(t, name, dtype=torch.bfloat16)
     n, nq, d, nkv, page_size, _, _ = _geometry(q, keys)
     if (backend or DECODE_BACKEND) == "tma" and tma_supported(d, page_size, window) and splits <= TMA_MAX_SPLITS:
-        return _decode_attention_tma(q, keys, values, kv_len, block_table, scale, splits)
+        return _decode_attention_tma(q, keys, values, kv_len, block_table, scale, splits, live)
     lib = library_name(d)
     floats = native.query("b200_attention_decode_scratch_floats", n, nq, splits, library=lib)
     scratch = torch.empty(max(floats, 1), dtype=torch.float32, device=q.device)
@@ -279,7 +281,7 @@ def decode_slots(head_dim: int, page_size: int, window: int, ctas: int = 1) -> i
     return _CTAS_PER_SM * native.sm_count()
 
 
-def _decode_attention_tma(q, keys, values, kv_len, block_table, scale, splits) -> torch.Tensor:
+def _decode_attention_tma(q, keys, values, kv_len, block_table, scale, splits, live=None) -> torch.Tensor:
     n, nq, d, nkv, page_size, _, _ = _geometry(q, keys)
     count = native.query("b200_attention_decode_tma_tickets", n, nq, nkv, library=tma_library_name(d))
     lib = tma_library_name(d, tma_depth(count))
@@ -290,8 +292,41 @@ def _decode_attention_tma(q, keys, values, kv_len, block_table, scale, splits) -
     native.call(
         "b200_attention_decode_tma", q.data_ptr(), keys.data_ptr(), values.data_ptr(), out.data_ptr(), kv_len.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], page_size, keys.shape[0], n, nq, nkv, float(scale), splits,
-        scratch.data_ptr(), floats, tickets.data_ptr(), tickets.numel(), native.stream_ptr(), library=lib)
+        scratch.data_ptr(), floats, tickets.data_ptr(), tickets.numel(),
+        *_live_arguments(live, n, nq, nkv, d, page_size, q.device), native.stream_ptr(), library=lib)
     return out
+
+
+PARTS_TABLE_SHIFT = 7       # one entry of a parts table per 128 tokens of length
+_PARTS_TABLES: dict[tuple, torch.Tensor] = {}
+
+
+class LiveParts:
+    """For a decode attention launch that is recorded into a CUDA graph: the grid is sized for ``bound`` (the
+    longest sequence there may ever be), and every replay uses as many parts as the host would choose for the
+    longest sequence of *that* batch, which it finds in ``longest`` (a device int the host writes before each
+    replay) through a table of the host's choices by length."""
+
+    def __init__(self, longest: torch.Tensor, bound: int) -> None:
+        self.longest, self.bound = longest, bound
+
+    def table(self, requests: int, nq: int, nkv: int, d: int, page_size: int, window: int, device) -> torch.Tensor:
+        key = (device.index, requests, nq, nkv, d, page_size, window, self.bound)
+        have = _PARTS_TABLES.get(key)
+        if have is None:
+            entries = (self.bound >> PARTS_TABLE_SHIFT) + 1
+            # entry i serves the lengths i * 128 .. i * 128 + 127: what the host picks for the longest of them
+            values = [parts_for(requests, nq, nkv, d, page_size, window, min(self.bound, ((i + 1) << PARTS_TABLE_SHIFT) - 1))
+                      for i in range(entries)]
+            have = _PARTS_TABLES[key] = torch.tensor(values, dtype=torch.int32, device=device)
+        return have
+
+
+def _live_arguments(live: "LiveParts | None", n: int, nq: int, nkv: int, d: int, page_size: int, device) -> tuple:
+    if live is None:
+        return None, None, 0, 0
+    table = live.table(n, nq, nkv, d, page_size, 0, device)
+    return live.longest.data_ptr(), table.data_ptr(), PARTS_TABLE_SHIFT, table.numel()
 
 
 def fused_decode_supported(head_dim: int, page_size: int, window: int, rotary_dim: int) -> bool:
@@ -305,7 +340,7 @@ def fused_decode_supported(head_dim: int, page_size: int, window: int, rotary_di
 def decode_attention_fused(
     qkv: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, *, num_q_heads: int, q_weight: torch.Tensor | None,
     k_weight: torch.Tensor | None, eps: float, inv_freq: torch.Tensor | None, kv_len: torch.Tensor, block_table: torch.Tensor,
-    scale: float, splits: int = 1,
+    scale: float, splits: int = 1, live: "LiveParts | None" = None,
 ) -> torch.Tensor:
     """Decode attention straight from the rows of the stacked q/k/v projection (``[requests, (nq + 2 nkv) d]``, one new
     token per request): per-head RMS norm of q and k (weights optional), rotation by the token's position
@@ -335,17 +370,24 @@ def decode_attention_fused(
         "b200_attention_decode_tma_fused", qkv.data_ptr(), qkv.stride(0), native.ptr(q_weight), native.ptr(k_weight), float(eps),
         native.ptr(inv_freq), keys.data_ptr(), values.data_ptr(), out.data_ptr(), kv_len.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], page_size, keys.shape[0], n, nq, nkv, float(scale), splits, scratch.data_ptr(), floats,
-        tickets.data_ptr(), tickets.numel(), native.stream_ptr(), library=lib)
+        tickets.data_ptr(), tickets.numel(), *_live_arguments(live, n, nq, nkv, d, page_size, qkv.device),
+        native.stream_ptr(), library=lib)
     return out
 
 
-def decode_parts(ctx: Any, n: int, nq: int, nkv: int, d: int, page_size: int, window: int) -> int:
-    """The number of parts the decode kernels cut each sequence of this batch into."""
+def parts_for(n: int, nq: int, nkv: int, d: int, page_size: int, window: int, longest: int) -> int:
+    """The number of parts the decode kernels cut each of ``n`` sequences into when the longest holds ``longest`` tokens."""
 
     slices = -(-(nq // nkv) // 16)
     if DECODE_BACKEND == "tma" and tma_supported(d, page_size, window):
         slices = -(-(nq // nkv) // 8)        # that kernel takes eight query heads of a group per CTA
-    return decode_splits(n, nkv, slices, ctx.max_kv_len, decode_slots(d, page_size, window, n * nkv * slices), d)
+    return decode_splits(n, nkv, slices, longest, decode_slots(d, page_size, window, n * nkv * slices), d)
+
+
+def decode_parts(ctx: Any, n: int, nq: int, nkv: int, d: int, page_size: int, window: int) -> int:
+    """The number of parts for this batch (under a graph capture: for the longest sequence there may ever be)."""
+
+    return parts_for(n, nq, nkv, d, page_size, window, ctx.max_kv_len)
 
 
 def check_decode_tma_error(head_dim: int) -> None:
@@ -370,7 +412,8 @@ def try_paged_attention(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Tens
     _, _, _, nkv, _, gs, slices = _geometry(q, cache.keys)
     if ctx.all_decode and n == ctx.num_entries:
         return decode_attention(q, cache.keys, cache.values, kv_len=ctx.kv_len, block_table=table, scale=scale,
-                                window=window, splits=decode_parts(ctx, n, nq, nkv, d, cache.keys.shape[2], window))
+                                window=window, splits=decode_parts(ctx, n, nq, nkv, d, cache.keys.shape[2], window),
+                                live=getattr(ctx, "live_parts", None))
     maps = ctx.__dict__.setdefault("_tile_maps", {})
     page_size = cache.keys.shape[2]
     if PREFILL_BACKEND == "tcgen05" and tc_supported(d, page_size, window) and ctx.max_q_len >= TC_MIN_PORTION:

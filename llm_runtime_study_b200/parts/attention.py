@@ -122,7 +122,8 @@ class GroupedQueryAttention(Mixer):
                     q_weight=self.q_norm.weight if self.q_norm is not None else None,
                     k_weight=self.k_norm.weight if self.k_norm is not None else None,
                     eps=self.q_norm.eps if self.q_norm is not None else 1.0,
-                    inv_freq=rotary[0] if rotary else None, kv_len=ctx.kv_len, block_table=table, scale=self.scale, splits=splits)
+                    inv_freq=rotary[0] if rotary else None, kv_len=ctx.kv_len, block_table=table, scale=self.scale, splits=splits,
+                    live=getattr(ctx, "live_parts", None))
                 return self.o_proj(out.view(out.shape[0], -1), torch.float32, add_to=residual, next_norm=next_norm)
         if self.position is not None and rotary is None:
             nq, nkv, d = self.num_heads, written_kv_heads, self.head_dim

@@ -222,13 +222,8 @@ def test_graph_buckets_pad_with_empty_rows(tmp_path):
     class Runner:
         manager = Manager()
 
-    from llm_runtime_study_b200.engine.graph import length_class
-
     graphs = DecodeGraphs(Runner())
     assert [graphs.bucket(n) for n in (1, 2, 3, 5, 8, 9, 33, 48)] == [1, 2, 4, 8, 8, 16, 48, 48]
-    # lengths are captured under bounds a quarter of a power of two apart (at least 512), never above the limit
-    assert [length_class(n, 4096) for n in (1, 512, 513, 2049, 2560, 2561, 4000)] == [512, 512, 1024, 2560, 2560, 3072, 4096]
-    assert length_class(9000, 40960) == 10240 and length_class(300, 384) == 384
 
 
 def test_engine_to_and_cache_handles(tmp_path):
