@@ -84,12 +84,9 @@ struct DecodeParams {
   bf16* k_pool;            // [pages][nkv][page_size][D], written at the new position
   bf16* v_pool;
   // A launch recorded into a CUDA graph has its grid fixed for good, sized (num_splits) for the longest sequence
-  // the engine may ever hold.  How many of those parts a replay uses is looked up on the device: the host writes
-  // the longest length of the batch into *live_longest before every replay, and parts_table[length >> table_shift]
-  // is what the host would choose for that length.  CTAs of the parts beyond it leave at once.
-  const int* live_longest; // nullptr: every launch uses num_splits parts
-  const int* parts_table;
-  int table_shift, table_len;
+  // the engine may ever hold.  How many of those parts a replay uses the host says before every replay, in
+  // *live_parts (what it would choose for the batch's longest sequence); the CTAs of the parts beyond leave at once.
+  const int* live_parts;   // nullptr: every launch uses num_splits parts
 };
 
 __device__ int g_decode_error = 0;
@@ -137,11 +134,8 @@ __global__ void __launch_bounds__(128) decode_attention_tma_kernel(const __grid_
   // the newest were written by earlier steps.  Only q, the newest key and the outputs depend on the
   // kernel before this one, so the first blocks can be asked for before the dependency wait.
   const int len = p.kv_len[b];
-  int splits = p.num_splits;     // parts in use: all of the grid's, or what the table says for the batch's longest sequence
-  if (p.live_longest != nullptr) {
-    const int at = min(max(*p.live_longest, 0) >> p.table_shift, p.table_len - 1);
-    splits = max(1, min(p.parts_table[at], p.num_splits));
-  }
+  int splits = p.num_splits;     // parts in use: all of the grid's, or as many as the host says this batch needs
+  if (p.live_parts != nullptr) splits = max(1, min(*p.live_parts, p.num_splits));
   if (split >= splits) return;   // the whole CTA: nothing of it has touched a barrier or a ticket
   int chunk = (len + splits - 1) / splits;
   chunk = ((chunk + 63) / 64) * 64;
@@ -596,9 +590,7 @@ struct FusedInputs {
   const float* k_weight = nullptr;
   float eps = 0.f;
   const float* inv_freq = nullptr;
-  const int* live_longest = nullptr;   // see DecodeParams
-  const int* parts_table = nullptr;
-  int table_shift = 0, table_len = 0;
+  const int* live_parts = nullptr;     // see DecodeParams
 };
 
 static int decode_tma(const void* q, const FusedInputs& fused, const void* k_pool, const void* v_pool, void* out, const int* kv_len,
@@ -623,11 +615,7 @@ static int decode_tma(const void* q, const FusedInputs& fused, const void* k_poo
   p.k_weight = fused.k_weight;
   p.eps = fused.eps;
   p.inv_freq = fused.inv_freq;
-  if (fused.live_longest != nullptr && (fused.parts_table == nullptr || fused.table_len <= 0 || fused.table_shift < 0)) return B200_ERR_BAD_SIZE;
-  p.live_longest = fused.live_longest;
-  p.parts_table = fused.parts_table;
-  p.table_shift = fused.table_shift;
-  p.table_len = fused.table_len;
+  p.live_parts = fused.live_parts;
   p.k_pool = static_cast<bf16*>(const_cast<void*>(k_pool));
   p.v_pool = static_cast<bf16*>(const_cast<void*>(v_pool));
   p.out = static_cast<bf16*>(out);
@@ -669,13 +657,9 @@ static int decode_tma(const void* q, const FusedInputs& fused, const void* k_poo
 extern "C" int b200_attention_decode_tma(const void* q, const void* k_pool, const void* v_pool, void* out, const int* kv_len,
                                          const int* block_table, int table_stride, int page_size, int num_pages, int requests,
                                          int nq, int nkv, float scale, int num_splits, float* scratch, long scratch_floats,
-                                         unsigned* tickets, long ticket_count, const int* live_longest,
-                                         const int* parts_table, int table_shift, int table_len, cudaStream_t stream) {
+                                         unsigned* tickets, long ticket_count, const int* live_parts, cudaStream_t stream) {
   FusedInputs plain;
-  plain.live_longest = live_longest;
-  plain.parts_table = parts_table;
-  plain.table_shift = table_shift;
-  plain.table_len = table_len;
+  plain.live_parts = live_parts;
   return decode_tma(q, plain, k_pool, v_pool, out, kv_len, block_table, table_stride, page_size, num_pages, requests, nq,
                     nkv, scale, num_splits, scratch, scratch_floats, tickets, ticket_count, stream);
 }
@@ -689,14 +673,10 @@ extern "C" int b200_attention_decode_tma_fused(const void* qkv, int qkv_stride, 
                                                const int* kv_len, const int* block_table, int table_stride, int page_size,
                                                int num_pages, int requests, int nq, int nkv, float scale, int num_splits,
                                                float* scratch, long scratch_floats, unsigned* tickets, long ticket_count,
-                                               const int* live_longest, const int* parts_table, int table_shift,
-                                               int table_len, cudaStream_t stream) {
+                                               const int* live_parts, cudaStream_t stream) {
   if (qkv == nullptr) return B200_ERR_BAD_SIZE;
   FusedInputs fused;
-  fused.live_longest = live_longest;
-  fused.parts_table = parts_table;
-  fused.table_shift = table_shift;
-  fused.table_len = table_len;
+  fused.live_parts = live_parts;
   fused.qkv = qkv;
   fused.qkv_stride = qkv_stride;
   fused.q_weight = q_weight;

@@ -15,12 +15,12 @@ the sampling kernels that write the drawn token back into the records.  One grap
 Kernels launched under capture size their grids from an upper bound of the sequence
 lengths that cannot change afterwards (the longest sequence the engine was opened for).
 The decode attention still cuts a replay's sequences into the number of parts that
-suits them: the host sends the longest length of the batch along, and the kernel looks
-up, in a table of the host's own choices by length, how many of its grid's parts to use
-(``ops/attention_bf16.LiveParts``); the CTAs of the others leave at once.
+suits them: with the step's other inputs the host sends, for every kind of attention
+launch in the graph, how many of its grid's parts this batch's longest sequence needs
+(``ops/attention_bf16.LiveParts``); the CTAs of the other parts leave at once.
 
 All per-step input lives in one persistent device buffer whose layout is fixed by the
-bucket and the table width: the slots of the batch, the longest length, the block tables.  It is copied
+bucket and the table width: the slots of the batch, the numbers of parts, the block tables.  It is copied
 only when it differs from what the device already holds, so a replay is at most one
 host-to-device copy plus one graph launch.  Graphs share one memory pool: they run one
 after the other on one stream, and what leaves a graph (the drawn ids) lies outside it.
@@ -39,6 +39,9 @@ from ..cache.manager import RequestCache
 from .step import StepContext, _round_up
 
 
+LIVE_PLACES = 8      # kinds of decode attention launches (geometries) a captured step may hold
+
+
 class DecodeGraph:
     """One captured decode step for exactly ``batch`` rows."""
 
@@ -51,8 +54,8 @@ class DecodeGraph:
         self.table_widths = [_round_up(-(-manager.max_seq_len // pool.page_size), 4) for pool in manager.groups]
         self.groups = len(manager.layout.groups)
         b = batch
-        # what the host sends every step (slots, longest length, tables), then what never changes, then what the device fills in
-        sizes = [b, 1] + [b * w for w in self.table_widths] + [b, b + 1, b] + [b, b, b]
+        # what the host sends every step (slots, numbers of parts, tables), then what never changes, then what the device fills in
+        sizes = [b, LIVE_PLACES] + [b * w for w in self.table_widths] + [b, b + 1, b] + [b, b, b]
         self.offsets, total = [], 0
         for size in sizes:
             self.offsets.append(total)
@@ -109,7 +112,8 @@ class DecodeGraph:
         sent[:b] = manager.padding_slot
         sent[: len(requests)] = [r.slot for r in requests]
         sent[b : self.offsets[2]] = 0
-        sent[self.offsets[1]] = max(r.length for r in requests) + 1     # the longest sequence once this step has run
+        parts = self.ctx.live_parts.fill(max(r.length for r in requests) + 1)    # for the longest sequence once this step has run
+        sent[self.offsets[1] : self.offsets[1] + len(parts)] = parts
         for g in range(self.groups):
             o, w = self.offsets[2 + g], self.table_widths[g]
             table = sent[o : o + b * w].reshape(b, w)
@@ -184,6 +188,7 @@ class DecodeGraph:
         self._fill(requests)
         if self.graph is None:
             self.capture(sampler, ids, pool)
+            self._fill(requests)      # the attention launches have said by now what they need to be told
         self.graph.replay()
         native.add_launches(self.kernel_launches)
         return self.logits[: len(requests)]

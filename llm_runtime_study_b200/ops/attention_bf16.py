@@ -34,10 +34,10 @@ _TMA_TABLE = {
     "b200_attention_decode_tma_tickets": [c_int, c_int, c_int],
     "b200_attention_decode_tma_error": [],
     "b200_attention_decode_tma": [c_void_p] * 6 + [c_int] * 6 + [c_float, c_int, c_void_p, c_long, c_void_p, c_long]
-                                 + [c_void_p, c_void_p, c_int, c_int, c_void_p],
+                                 + [c_void_p, c_void_p],
     "b200_attention_decode_tma_fused": [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p] + [c_void_p] * 5 + [c_int] * 6
                                        + [c_float, c_int, c_void_p, c_long, c_void_p, c_long]
-                                       + [c_void_p, c_void_p, c_int, c_int, c_void_p],
+                                       + [c_void_p, c_void_p],
 }
 FUSE_DECODE = os.environ.get("LLM_RUNTIME_STUDY_B200_FUSE_DECODE", "1") != "0"
 # "tma": pages streamed by TMA, parts merged in the same launch; "mma": the cp.async kernels of attention_mma.cu
@@ -293,40 +293,46 @@ def _decode_attention_tma(q, keys, values, kv_len, block_table, scale, splits, l
         "b200_attention_decode_tma", q.data_ptr(), keys.data_ptr(), values.data_ptr(), out.data_ptr(), kv_len.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], page_size, keys.shape[0], n, nq, nkv, float(scale), splits,
         scratch.data_ptr(), floats, tickets.data_ptr(), tickets.numel(),
-        *_live_arguments(live, n, nq, nkv, d, page_size, q.device), native.stream_ptr(), library=lib)
+        _live_argument(live, n, nq, nkv, d, page_size), native.stream_ptr(), library=lib)
     return out
 
 
-PARTS_TABLE_SHIFT = 7       # one entry of a parts table per 128 tokens of length
-_PARTS_TABLES: dict[tuple, torch.Tensor] = {}
+PARTS_TABLE_SHIFT = 7       # the host's choices of parts are tabulated per 128 tokens of length
 
 
 class LiveParts:
-    """For a decode attention launch that is recorded into a CUDA graph: the grid is sized for ``bound`` (the
-    longest sequence there may ever be), and every replay uses as many parts as the host would choose for the
-    longest sequence of *that* batch, which it finds in ``longest`` (a device int the host writes before each
-    replay) through a table of the host's choices by length."""
+    """For decode attention launches that are recorded into a CUDA graph: a launch's grid is sized for ``bound``
+    (the longest sequence there may ever be), and every replay uses as many parts as the host would choose for
+    the longest sequence of *that* batch.  Each kind of launch (a geometry of heads and pages) registers once,
+    while the graph is being made, and gets a place in ``values`` (device ints that travel with the step's other
+    inputs); before every replay ``fill(longest)`` gives the numbers for all places."""
 
-    def __init__(self, longest: torch.Tensor, bound: int) -> None:
-        self.longest, self.bound = longest, bound
+    def __init__(self, values: torch.Tensor, bound: int) -> None:
+        self.values, self.bound = values, bound
+        self._places: dict[tuple, int] = {}
+        self._choices: list[list[int]] = []      # per place: parts by length >> PARTS_TABLE_SHIFT
 
-    def table(self, requests: int, nq: int, nkv: int, d: int, page_size: int, window: int, device) -> torch.Tensor:
-        key = (device.index, requests, nq, nkv, d, page_size, window, self.bound)
-        have = _PARTS_TABLES.get(key)
-        if have is None:
+    def place(self, requests: int, nq: int, nkv: int, d: int, page_size: int, window: int) -> torch.Tensor:
+        key = (requests, nq, nkv, d, page_size, window)
+        at = self._places.get(key)
+        if at is None:
+            if len(self._places) >= self.values.numel():
+                raise KernelError(f"more than {self.values.numel()} kinds of decode attention in one captured step")
+            at = self._places[key] = len(self._places)
             entries = (self.bound >> PARTS_TABLE_SHIFT) + 1
             # entry i serves the lengths i * 128 .. i * 128 + 127: what the host picks for the longest of them
-            values = [parts_for(requests, nq, nkv, d, page_size, window, min(self.bound, ((i + 1) << PARTS_TABLE_SHIFT) - 1))
-                      for i in range(entries)]
-            have = _PARTS_TABLES[key] = torch.tensor(values, dtype=torch.int32, device=device)
-        return have
+            self._choices.append([parts_for(requests, nq, nkv, d, page_size, window, min(self.bound, ((i + 1) << PARTS_TABLE_SHIFT) - 1))
+                                  for i in range(entries)])
+        return self.values[at : at + 1]
+
+    def fill(self, longest: int) -> list[int]:
+        """The numbers of parts, place by place, for a batch whose longest sequence holds ``longest`` tokens."""
+
+        return [choices[min(max(longest, 0) >> PARTS_TABLE_SHIFT, len(choices) - 1)] for choices in self._choices]
 
 
-def _live_arguments(live: "LiveParts | None", n: int, nq: int, nkv: int, d: int, page_size: int, device) -> tuple:
-    if live is None:
-        return None, None, 0, 0
-    table = live.table(n, nq, nkv, d, page_size, 0, device)
-    return live.longest.data_ptr(), table.data_ptr(), PARTS_TABLE_SHIFT, table.numel()
+def _live_argument(live: "LiveParts | None", n: int, nq: int, nkv: int, d: int, page_size: int):
+    return None if live is None else live.place(n, nq, nkv, d, page_size, 0).data_ptr()
 
 
 def fused_decode_supported(head_dim: int, page_size: int, window: int, rotary_dim: int) -> bool:
@@ -370,7 +376,7 @@ def decode_attention_fused(
         "b200_attention_decode_tma_fused", qkv.data_ptr(), qkv.stride(0), native.ptr(q_weight), native.ptr(k_weight), float(eps),
         native.ptr(inv_freq), keys.data_ptr(), values.data_ptr(), out.data_ptr(), kv_len.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], page_size, keys.shape[0], n, nq, nkv, float(scale), splits, scratch.data_ptr(), floats,
-        tickets.data_ptr(), tickets.numel(), *_live_arguments(live, n, nq, nkv, d, page_size, qkv.device),
+        tickets.data_ptr(), tickets.numel(), _live_argument(live, n, nq, nkv, d, page_size),
         native.stream_ptr(), library=lib)
     return out
 

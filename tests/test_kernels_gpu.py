@@ -421,24 +421,28 @@ def test_decode_attention_tma_finds_a_far_key(boost):
 
 def test_decode_attention_tma_uses_as_many_parts_as_the_batch_needs():
     """A launch whose grid is sized for long sequences (as under a CUDA graph) with the number of parts in use
-    looked up on the device from the longest length of the batch: whatever that length says, the result is the
-    plain one, the CTAs of unused parts leave the tickets alone, and a second launch finds them at zero."""
+    told by the host through a device int: whatever it says, the result is the plain one, the CTAs of unused
+    parts leave the tickets alone, and a second launch finds them at zero."""
 
     mma = _mma()
     nq, nkv, d, page = 8, 2, 128, 16
     lens = [1, 17, 64, 131, 700, 1024]
     q, kp, vp, pos, ent, table, want = _attention_case(torch.bfloat16, nq, nkv, d, page, [(L, 1) for L in lens])
     args = (dev(q), dev(kp), dev(vp))
-    longest = torch.zeros(1, dtype=torch.int32, device="cuda")
-    live = mma.LiveParts(longest, 32768)
-    chosen = live.table(len(lens), nq, nkv, d, page, 0, torch.device("cuda:0")).cpu()
-    assert int(chosen[0]) == 1 and int(chosen[-1]) > 4            # short batches in one part, long ones in many
+    values = torch.zeros(8, dtype=torch.int32, device="cuda")
+    live = mma.LiveParts(values, 32768)
     kw = dict(kv_len=dev(torch.tensor(lens, dtype=torch.int32)), block_table=dev(table), scale=1 / math.sqrt(d), splits=16, live=live)
-    for said in (1024, 1, 200, 5000, 32768, 10**6):              # what the host says the longest is picks the parts; never the result
-        longest.fill_(said)
+    out = mma.decode_attention(*args, **kw)                    # the first launch registers its geometry; told 0, it uses one part
+    torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
+    assert live.fill(1) == [1] and live.fill(32768)[0] > 4      # short batches in one part, long ones in many
+    for longest in (1024, 1, 200, 5000, 32768, 10**6):
+        chosen = live.fill(longest)
+        values[: len(chosen)] = torch.tensor(chosen, dtype=torch.int32)
         for _ in range(2):
             out = mma.decode_attention(*args, **kw)
             torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
+    values.fill_(99)                                            # more than the grid has: all of the grid's parts
+    torch.testing.assert_close(mma.decode_attention(*args, **kw).cpu().double(), want, **BF16_TOL)
     mma.check_decode_tma_error(d)
 
 

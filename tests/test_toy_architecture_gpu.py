@@ -219,3 +219,130 @@ def test_toy_architecture_generates_through_the_engine(tmp_path, state_mixer, ca
                 break
     engine.cache_manager.check()
     assert engine.cache_manager.active_sequences == 0
+
+
+def register_memo_toy():
+    """A second toy: a mixer that keeps one vector per token in pages of its own (its own tensor, its own page
+    size) and answers each token with the mean of what it has kept up to there."""
+
+    from llm_runtime_study_b200.config import Architecture, register_architecture
+    from llm_runtime_study_b200.models import LayerDescription, ModelDescription
+    from llm_runtime_study_b200.parts import MIXERS, Mixer, Projection
+    from llm_runtime_study_b200.parts.base import PagedTensors
+    from llm_runtime_study_b200.weights import TensorSpec
+
+    class RunningMean(Mixer):
+        def __init__(self, *, hidden_size: int, width: int, page_size: int) -> None:
+            self.hidden_size, self.width, self.page = hidden_size, width, page_size
+
+        def tensor_specs(self):
+            return {"in.weight": TensorSpec((self.width, self.hidden_size)), "out.weight": TensorSpec((self.hidden_size, self.width))}
+
+        def load(self, tensors, runtime):
+            self.runtime = runtime
+            self.inp = Projection([tensors["in.weight"]], None, runtime)
+            self.out = Projection([tensors["out.weight"]], None, runtime)
+
+        def cache_requirement(self):
+            return PagedTensors(tensors=(("memo", (self.width,)),), page_size=self.page)
+
+        def forward(self, x, ctx, cache):
+            memo = cache.tensors["memo"]                       # [pages, page, width]
+            assert cache.page_size == self.page and memo.shape[1:] == (self.page, self.width)
+            kept = self.inp(x).float()
+            table = ctx.block_table(cache.group).cpu()
+            means = torch.empty_like(kept)
+            at = 0
+            for entry, (n, after) in enumerate(zip(ctx.q_lens, ctx.kv_lens)):
+                for i in range(n):
+                    pos = after - n + i
+                    memo[table[entry, pos // self.page], pos % self.page] = kept[at + i].to(memo.dtype)
+                pages = table[entry, : -(-after // self.page)].to(x.device).long()
+                history = memo[pages].reshape(-1, self.width)[:after].float()
+                sums = history.cumsum(dim=0)[after - n:]
+                means[at : at + n] = sums / torch.arange(after - n + 1, after + 1, device=x.device)[:, None]
+                at += n
+            return self.out(means.to(x.dtype), torch.float32)
+
+    MIXERS.register("toy_running_mean", RunningMean, replace=True)
+
+    def describe(cfg):
+        norm = {"kind": "rms_norm", "dim": H, "eps": EPS}
+        attention = {"kind": "gqa_attention", "hidden_size": H, "num_heads": NQ, "num_kv_heads": NKV, "head_dim": D,
+                     "position": {"kind": "rope", "head_dim": D, "theta": THETA}}
+        ffn = {"kind": "swiglu", "hidden_size": H, "intermediate_size": I}
+        block = lambda mixer: {"kind": "pre_norm", "mixer": mixer, "feed_forward": ffn, "mixer_norm": norm, "ffn_norm": norm,
+                               "names": {"mixer": "mix"}}
+        layers = (LayerDescription(block({"kind": "toy_running_mean", "hidden_size": H, "width": 24, "page_size": 4}), "toy.layers.0"),
+                  LayerDescription(block(attention), "toy.layers.1"))
+        return ModelDescription(
+            architecture="ToyMemo", vocab_size=V, hidden_size=H, max_positions=128, eos_token_ids=(0,),
+            embedding={"prefix": "toy.embed", "vocab_size": V, "hidden_size": H}, layers=layers, order=(0, 1),
+            final_norm={"prefix": "toy.norm", **norm}, head={"prefix": "toy.head", "vocab_size": V, "hidden_size": H, "tied": True})
+
+    class Config:
+        def validate_context_length(self, n):
+            assert n <= 128
+
+    register_architecture(Architecture("ToyMemo", "toy_memo", lambda raw: Config(), describe), replace=True)
+
+
+def plain_memo_toy(w, tokens):
+    w = {n: t.double() for n, t in w.items()}
+    T = len(tokens)
+    h = w["toy.embed.weight"][torch.tensor(tokens)]
+    cos, sin = plain.rotary_tables(torch.arange(T), D, THETA, torch.float64)
+
+    def ffn(h, p):
+        return h + plain.swiglu(plain.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], EPS), w, f"{p}.mlp")
+
+    x = plain.rms_norm(h, w["toy.layers.0.input_layernorm.weight"], EPS)
+    kept = x @ w["toy.layers.0.mix.in.weight"].T
+    means = kept.cumsum(dim=0) / torch.arange(1, T + 1)[:, None]
+    h = ffn(h + means @ w["toy.layers.0.mix.out.weight"].T, "toy.layers.0")
+    p = "toy.layers.1"
+    x = plain.rms_norm(h, w[f"{p}.input_layernorm.weight"], EPS)
+    q = plain.rotate((x @ w[f"{p}.mix.q_proj.weight"].T).view(T, NQ, D), cos, sin)
+    k = plain.rotate((x @ w[f"{p}.mix.k_proj.weight"].T).view(T, NKV, D), cos, sin)
+    v = (x @ w[f"{p}.mix.v_proj.weight"].T).view(T, NKV, D)
+    o = plain.causal_attention(q, k, v, 1 / math.sqrt(D)).reshape(T, NQ * D) @ w[f"{p}.mix.o_proj.weight"].T
+    h = ffn(h + o, p)
+    return plain.rms_norm(h, w["toy.norm.weight"], EPS) @ w["toy.embed.weight"].T
+
+
+def test_a_mixer_with_pages_of_its_own_kind():
+    """Two page groups in one model: the attention layer's keys and values in pages of 8, the toy mixer's one
+    vector per token in pages of 4; replayed whole, in portions and mixed, with pages of both groups reused."""
+
+    import tempfile
+
+    from llm_runtime_study_b200.engine.replay import TraceReplayer
+    from llm_runtime_study_b200.engine.runtime import load
+    from llm_runtime_study_b200.weights import Checkpoint, write_random_model
+
+    register_memo_toy()
+    with tempfile.TemporaryDirectory() as tmp:
+        write_random_model(f"{tmp}/toy", {"model_type": "toy_memo", "architectures": ["ToyMemo"], "torch_dtype": "float32"}, seed=9)
+        weights = Checkpoint.from_model_dir(f"{tmp}/toy").get_tensors()
+        loaded = load(f"{tmp}/toy", device="cuda:0", dtype="float32")
+    layout = loaded.model.cache_layout()
+    assert len(layout.groups) == 2 and [g.requirement.page_size for g in layout.groups] == [4, None]
+    rng = random.Random(4)
+    requests = {f"m{i}": helpers.random_tokens(rng, V, n) for i, n in enumerate([3, 21, 40, 9, 17])}
+    want = {rid: plain_memo_toy(weights, toks) for rid, toks in requests.items()}
+    for steps in (helpers.trace_whole(requests), helpers.trace_chunked(requests, random.Random(1)),
+                  helpers.trace_mixed(requests, random.Random(2), live_max=3)):
+        replayer = TraceReplayer(loaded, max_tokens=helpers.pool_tokens(steps), page_size=8)
+        manager = replayer.runner.manager
+        assert [pool.page_size for pool in manager.groups] == [4, 8]
+        outputs = {}
+        for record in steps:
+            rows = replayer.run_step(record)
+            if rows is not None:
+                outputs[record["step"]] = torch.from_numpy(rows.copy())
+            manager.check()
+        got = helpers.collect_logits(steps, outputs)
+        for rid, toks in requests.items():
+            rows = torch.stack([got[rid][p] for p in range(len(toks))]).double()
+            torch.testing.assert_close(rows, want[rid], atol=3e-5, rtol=1e-4)
+        assert manager.all_free and manager.active_sequences == 0
