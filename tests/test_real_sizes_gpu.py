@@ -182,8 +182,9 @@ def test_captured_decode_step_at_real_sizes(material, dtype, lengths):
     """The decode step as generation runs it at head size 128: slot records in, drawn tokens out,
     replayed from a CUDA graph.  Three requests fill a bucket of four with one padded row; twelve go
     to a bucket of sixteen, where the large projections take the split-K kernels.  The engine is
-    opened for 4,096 tokens while the requests hold far fewer, so the captured launch (sized for a
-    class of lengths) differs from the eager one (sized for the live lengths).  Eight steps, against
+    opened for 4,096 tokens while the requests hold far fewer, so the captured launch (a grid
+    sized for 4,096 tokens, told at every replay how many of its parts to use) differs from the eager one
+    (sized for the live lengths).  Eight steps, against
     the same launches issued one by one (the same bits in 32-bit) and against the plain model."""
 
     from tests.test_generate_gpu import _decode_both_ways
