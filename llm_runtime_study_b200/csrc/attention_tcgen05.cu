@@ -341,6 +341,385 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// The same attention with two row tiles per CTA, for portions long enough to fill both.
+//
+// One CTA owns 256 rows of S: two tiles of 128 (consecutive tokens of one request times the query heads
+// of one KV head) that share one stream of K and V.  Keys are taken 128 at a time (a product over 64 keys
+// is too short for the time it takes to issue); the whole of tensor memory belongs to the CTA (S of both
+// row tiles, 128 columns each, and O of both), one CTA per SM.
+//   warps 0-3 / 4-7  softmax of row tile 0 / 1, one row per thread
+//   warp 8           TMA loads: both Q tiles once, then K and V tile by tile through the block table
+//   warp 9           tensor-core issue, in the order  P_0(j) V, S_0(j+1), P_1(j) V, S_1(j+1):  while the
+//                    threads of one row tile turn S into P, the tensor core works for the other, and both
+//                    read every K and V stage (half the shared-memory and L2 traffic of the one-tile kernel)
+//   warps 10, 11     nothing: warps 8-11 are a warpgroup that gives most of its registers to the softmax
+//                    warps (setmaxnreg), which hold a row of 128 scores each.
+// The tensor core executes one CTA's products in the order of issue, so S_t(j+1) may be issued right
+// behind P_t(j) V although it overwrites the columns that hold P_t(j).
+//
+// What shortens the chain S -> P -> P V -> next S, which is what a row tile's time is made of:
+//  * the exponentials of a tile start from the reference maximum of the tiles before it, without a pass for
+//    the tile's own maximum: a weight 2^(s - reference) may be any size that float32 holds (the final
+//    division uses the same reference), so only when a row's weights of one tile add up to more than
+//    kSpeculationLimit is the maximum found, O rescaled and the tile redone;
+//  * P is handed over in two halves of 64 keys, so the product of the first half runs while the second
+//    half is exponentiated;
+//  * one lane of each warp arrives on the barrier, not 128 threads one after the other.
+constexpr int PBN = 128;                             // keys per tile
+constexpr uint32_t PKV_SUB = PBN * 128;              // bytes of one 64-column sub-tile of a K or V stage
+constexpr uint32_t PKV_BYTES = DSUB * PKV_SUB;
+constexpr int KSTAGES_P = 3, VSTAGES_P = D == 128 ? 2 : 3;   // more than half of an SM's shared memory either way: one CTA per SM
+constexpr uint32_t PAIR_SMEM_TILES = 2 * Q_BYTES + (KSTAGES_P + VSTAGES_P) * PKV_BYTES;
+constexpr uint32_t PAIR_BARRIER_BYTES = 512;
+constexpr uint32_t PAIR_TMEM_COLS = 512;
+constexpr uint32_t PAIR_O_COL = 2 * PBN;
+constexpr int kPairThreads = 384;                    // three warpgroups: every quarter of the SM holds two softmax warps and one other
+constexpr int kPairSoftmaxRegs = 216, kPairOtherRegs = 72;   // 2 * 216 + 72 = 3 * 168, what the launch gives each quarter
+constexpr float kSpeculationLimit = 1099511627776.f;  // 2^40
+static_assert(PAIR_SMEM_TILES > 116 * 1024, "two of these CTAs on one SM would wait for each other's tensor memory");
+static_assert((1 + 2 * (KSTAGES_P + VSTAGES_P) + 2 + 4 + 2 + 2) * 8 + 4 <= PAIR_BARRIER_BYTES, "barriers");
+
+__global__ void __launch_bounds__(kPairThreads, 1)
+prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                              const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* q_smem = smem;                               // [2]
+  unsigned char* k_smem = q_smem + 2 * Q_BYTES;               // [KSTAGES_P]
+  unsigned char* v_smem = k_smem + KSTAGES_P * PKV_BYTES;     // [VSTAGES_P]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PAIR_SMEM_TILES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;                  // [KSTAGES_P]
+  uint64_t* k_empty = k_full + KSTAGES_P;
+  uint64_t* v_full = k_empty + KSTAGES_P;       // [VSTAGES_P]
+  uint64_t* v_empty = v_full + VSTAGES_P;
+  uint64_t* s_full = v_empty + VSTAGES_P;       // [2]: per row tile
+  uint64_t* p_full = s_full + 2;                // [2 row tiles][2 halves]
+  uint64_t* o_done = p_full + 4;                // [2]: all of P_t(j) V is in O
+  uint64_t* o_half = o_done + 2;                // [2]: the first half of P_t(j) V is in O
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_half + 2);
+
+  pdl_wait();
+  if ((smem_addr(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(&g_attn_error, 9);
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.y;
+  const int kvh = blockIdx.x / p.slices, slice = blockIdx.x % p.slices;
+  const int entry = p.tile_entry[tile], tok0 = p.tile_start[tile], ntok = p.tile_count[tile];
+  const int* table = p.block_table + static_cast<size_t>(entry) * p.table_stride;
+  const int tpc = BM / p.gs;                                  // tokens of one row tile
+  const int p_first = p.positions[tok0], p_last = p_first + ntok - 1;
+  const int ntok1 = ntok > tpc ? ntok - tpc : 0;              // tokens of the second row tile
+  const int nt0 = (p_first + min(ntok, tpc) - 1) / PBN + 1;   // key tiles that row tile 0 can see
+  const int nt1 = ntok1 > 0 ? p_last / PBN + 1 : 0;           // nt1 >= nt0 unless tile 1 is empty
+  const int ntiles = max(nt0, nt1);
+  const int head0 = kvh * p.group + slice * p.gs;
+  if (ntok > 2 * tpc) {                                       // the caller cut its tiles for another kernel
+    if (threadIdx.x == 0) atomicExch(&g_attn_error, 18);
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < KSTAGES_P; ++s) {
+      mbar_init(k_full + s, 1);
+      mbar_init(k_empty + s, 1);
+    }
+    for (int s = 0; s < VSTAGES_P; ++s) {
+      mbar_init(v_full + s, 1);
+      mbar_init(v_empty + s, 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(s_full + t, 1);
+      mbar_init(p_full + 2 * t, 4);             // one arrival per softmax warp
+      mbar_init(p_full + 2 * t + 1, 4);
+      mbar_init(o_done + t, 1);
+      mbar_init(o_half + t, 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 9) tmem_alloc(tmem_slot, PAIR_TMEM_COLS);
+  for (uint32_t i = threadIdx.x; i < VSTAGES_P * PKV_BYTES / 16; i += kPairThreads)   // see the one-tile kernel
+    reinterpret_cast<uint4*>(v_smem)[i] = make_uint4(0, 0, 0, 0);
+  fence_async_shared();
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // All four warps of a warpgroup execute the same setmaxnreg instruction, as it demands.
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kPairOtherRegs));
+    if (warp == 8) {
+      // ---------------------------------------------------------------- TMA producer
+      if (lane == 0) {
+        const uint32_t tile_bytes = DSUB * 128u * p.gs * tpc;
+        mbar_expect_tx(q_full, ntok1 > 0 ? 2 * tile_bytes : tile_bytes);
+        for (int t = 0; t < (ntok1 > 0 ? 2 : 1); ++t)
+          for (int sub = 0; sub < DSUB; ++sub)
+            tma_load_3d(q_smem + t * Q_BYTES + sub * Q_SUB, &map_q, q_full, sub * 64, head0, tok0 + t * tpc);
+      }
+      const int pages_per_tile = PBN / p.page_size;
+      const int boxes = pages_per_tile * DSUB;             // at most 32: pages of 8 tokens, head size 128
+      const int my_page = lane / DSUB, my_sub = lane % DSUB;
+      const bool has_box = lane < boxes;
+      auto fetch_id = [&](int j) -> int {
+        const int t0 = j * PBN + my_page * p.page_size;
+        return (has_box && t0 <= p_last) ? table[t0 >> p.page_shift] : -1;
+      };
+      auto load_boxes = [&](unsigned char* dst, const CUtensorMap* map, uint64_t* bar, int id) {
+        const unsigned valid = __ballot_sync(0xffffffffu, id >= 0);
+        if (lane == 0) mbar_expect_tx(bar, static_cast<uint32_t>(__popc(valid)) * p.page_size * 128u);
+        __syncwarp();
+        if (id >= 0)
+          tma_load_2d(dst + my_sub * PKV_SUB + my_page * p.page_size * 128, map, bar, my_sub * 64, (id * p.nkv + kvh) * p.page_size);
+      };
+      // K of tile j + 1 is asked for before V of tile j: S_t(j+1) is issued ahead of P_t(j+1) V, and the K ring
+      // is the deeper one.
+      int id_k = fetch_id(0), id_v = -1;
+      for (int j = 0; j <= ntiles; ++j) {
+        int next_id = -1;
+        if (j < ntiles) {
+          const int s = j % KSTAGES_P;
+          if (j + 1 < ntiles) next_id = fetch_id(j + 1);
+          bool free_k = mbar_wait(k_empty + s, ((j / KSTAGES_P) & 1) ^ 1);
+          if (!__all_sync(0xffffffffu, free_k)) { if (lane == 0) atomicExch(&g_attn_error, 11); break; }
+          load_boxes(k_smem + s * PKV_BYTES, &map_k, k_full + s, id_k);
+        }
+        if (j > 0) {
+          const int jv = j - 1, s = jv % VSTAGES_P;
+          bool free_v = mbar_wait(v_empty + s, ((jv / VSTAGES_P) & 1) ^ 1);
+          if (!__all_sync(0xffffffffu, free_v)) { if (lane == 0) atomicExch(&g_attn_error, 11); break; }
+          load_boxes(v_smem + s * PKV_BYTES, &map_v, v_full + s, id_v);
+        }
+        id_v = id_k;
+        id_k = next_id;
+      }
+    } else if (warp == 9) {
+      // ---------------------------------------------------------------- tensor-core issue
+      constexpr uint32_t idesc_s = umma_idesc_bf16(BM, PBN, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, D, 1);
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbar_wait(bar, parity) ? 1 : 0) != 0; };
+      const int nt[2] = {nt0, nt1};
+      bool ok = wait_all(q_full, 0);
+      if (!ok) atomicExch(&g_attn_error, 12);
+      const uint32_t q_addr = smem_addr(q_smem);
+      // S_t(j) = Q_t K_j^T; the caller has waited for K_j.  `last`: no other row tile reads K_j after this one.
+      auto issue_s = [&](int t, int j, bool last) {
+        const int s = j % KSTAGES_P;
+        const uint32_t k_addr = smem_addr(k_smem + s * PKV_BYTES);
+        if (elect_one()) {
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k)
+            umma_bf16_ss(tmem_base + t * PBN, umma_desc_sw128(q_addr + t * Q_BYTES + (k >> 2) * Q_SUB + (k & 3) * 32, 16, 1024),
+                         umma_desc_sw128(k_addr + (k >> 2) * PKV_SUB + (k & 3) * 32, 16, 1024), idesc_s, k != 0);
+          umma_commit_to(s_full + t);
+          if (last) umma_commit_to(k_empty + s);
+        }
+        __syncwarp();
+      };
+      if (ok) {
+        ok = wait_all(k_full, 0);
+        if (!ok) atomicExch(&g_attn_error, 12);
+      }
+      if (ok) {
+        tcgen05_fence_after();
+        issue_s(0, 0, nt1 == 0);
+        if (nt1 > 0) issue_s(1, 0, true);
+      }
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int s = j % VSTAGES_P;
+        bool have_v = false, have_k = false;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j >= nt[t]) continue;
+          const uint32_t v_addr = smem_addr(v_smem + s * PKV_BYTES);
+          const bool last_pv = t == 1 || j >= nt[1];
+          for (int half = 0; half < 2 && ok; ++half) {    // P_t(j) arrives in two halves of 64 keys
+            if (!wait_all(p_full + 2 * t + half, j & 1)) { atomicExch(&g_attn_error, 13); ok = false; break; }
+            if (!have_v) {
+              if (!wait_all(v_full + s, (j / VSTAGES_P) & 1)) { atomicExch(&g_attn_error, 13); ok = false; break; }
+              have_v = true;
+            }
+            tcgen05_fence_after();
+            if (elect_one()) {
+#pragma unroll
+              for (int k = 4 * half; k < 4 * half + 4; ++k)     // P_t lies where S_t was: 8 columns per 16 keys
+                umma_bf16_ts(tmem_base + PAIR_O_COL + t * D, tmem_base + t * PBN + k * 8,
+                             umma_desc_sw128(v_addr + k * 2048, PKV_SUB, 1024), idesc_pv, (j | k) != 0);
+              if (half == 0) {
+                umma_commit_to(o_half + t);
+              } else {
+                umma_commit_to(o_done + t);
+                if (last_pv) umma_commit_to(v_empty + s);
+              }
+            }
+            __syncwarp();
+          }
+          if (ok && j + 1 < nt[t]) {
+            if (!have_k) {
+              if (!wait_all(k_full + (j + 1) % KSTAGES_P, ((j + 1) / KSTAGES_P) & 1)) { atomicExch(&g_attn_error, 12); ok = false; break; }
+              have_k = true;
+              tcgen05_fence_after();
+            }
+            issue_s(t, j + 1, t == 1 || j + 1 >= nt[1]);
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax: warps 0-3 row tile 0, warps 4-7 row tile 1
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(kPairSoftmaxRegs));
+    const int t = warp >> 2;
+    const int my_tiles = t == 0 ? nt0 : nt1;
+    const int row = threadIdx.x & (BM - 1);
+    const int tl = row / p.gs, g = row - tl * p.gs;
+    const int ntok_t = t == 0 ? min(ntok, tpc) : ntok1;
+    const bool row_ok = tl < ntok_t && slice * p.gs + g < p.group;
+    const int first_pos = p_first + t * tpc;             // position of the tile's first row
+    const int row_hi = first_pos + tl;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const uint32_t s_col = lane_base + t * PBN, o_col = lane_base + PAIR_O_COL + t * D;
+    float m_used = -INFINITY, l = 0.f;       // m_used: the reference maximum, in units of log2 after scaling
+    bool ok = true;
+    for (int j = 0; j < my_tiles; ++j) {
+      if (!mbar_wait(s_full + t, j & 1)) { atomicExch(&g_attn_error, 14); ok = false; break; }
+      tcgen05_fence_after();
+      float sv[PBN];
+      {
+        uint32_t r[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld_32_nowait(s_col + c * 32, r[c]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sv[c * 32 + i] = __uint_as_float(r[c][i]);
+      }
+      const int t0 = j * PBN;
+      if (t0 + PBN - 1 > first_pos) {        // some key of the tile is hidden from some row
+#pragma unroll
+        for (int i = 0; i < PBN; ++i) sv[i] = t0 + i <= row_hi ? sv[i] : -INFINITY;
+      }
+      // weights of one half (64 keys) from the current reference, handed to the tensor core; returns their sum
+      auto half_weights = [&](int half) -> float {
+        const float neg_ref = -m_used;
+        float lsum[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t words[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float e0 = exp2_fast(fmaf(sv[half * 64 + 2 * c], p.scale_log2, neg_ref));
+          const float e1 = exp2_fast(fmaf(sv[half * 64 + 2 * c + 1], p.scale_log2, neg_ref));
+          lsum[(2 * c) & 3] += e0;
+          lsum[(2 * c + 1) & 3] += e1;
+          words[c] = pack_bf16(e0, e1);
+        }
+        tmem_st_32(s_col + half * 32, words);
+        return (lsum[0] + lsum[1]) + (lsum[2] + lsum[3]);
+      };
+      auto hand_over = [&](int half) {
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full + 2 * t + half);
+      };
+      // Every row sees key 0, so from the second tile on the reference is finite.  Speculate on it:
+      float first_half = 0.f;
+      bool redo = j == 0;
+      if (j > 0) {
+        first_half = half_weights(0);
+        redo = !(first_half < kSpeculationLimit);
+      }
+      // rescale what O and l hold by 2^(old reference - new reference); every lane takes part
+      auto move_reference = [&](float m_new) {
+        const float factor = exp2f(m_used - m_new);
+        uint32_t r[32];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          tmem_ld_32(o_col + c * 32, r);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+          tmem_st_32(o_col + c * 32, r);
+        }
+        l *= factor;
+        first_half *= factor;
+        m_used = m_new;
+      };
+      if (!__any_sync(0xffffffffu, redo)) {
+        hand_over(0);
+        float second_half = half_weights(1);
+        const bool grow = !(second_half < kSpeculationLimit);
+        if (__any_sync(0xffffffffu, grow)) {
+          // The first half is with the tensor core already.  Once its product is in O, move the reference
+          // to the maximum of the second half and redo that half.
+          if (!mbar_wait(o_half + t, j & 1)) { atomicExch(&g_attn_error, 16); ok = false; break; }
+          tcgen05_fence_after();
+          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int i = PBN / 2; i < PBN; ++i) mx[i & 3] = fmaxf(mx[i & 3], sv[i]);
+          const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+          move_reference(grow ? fmaxf(m_used, m_half) : m_used);
+          second_half = half_weights(1);
+        }
+        hand_over(1);
+        l += first_half + second_half;
+        continue;
+      }
+      // The tile's own maximum: on the first tile, and when a row's weights outgrew the reference.
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < PBN; ++i) mx[i & 3] = fmaxf(mx[i & 3], sv[i]);
+      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      const float m_new = fmaxf(m_used, m_tile * p.scale_log2);
+      if (j > 0) {
+        // O must hold every product issued so far and no later one: P_t(j-1) V has been issued and
+        // P_t(j) V waits for this warp's arrival.
+        if (!mbar_wait(o_done + t, (j - 1) & 1)) { atomicExch(&g_attn_error, 15); ok = false; break; }
+        tcgen05_fence_after();
+        move_reference(m_new);
+      }
+      m_used = m_new;
+      const float a = half_weights(0);
+      hand_over(0);
+      const float b = half_weights(1);
+      hand_over(1);
+      l += a + b;
+    }
+    if (ok && my_tiles > 0) {
+      if (!mbar_wait(o_done + t, (my_tiles - 1) & 1)) {
+        atomicExch(&g_attn_error, 17);
+      } else {
+        tcgen05_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        bf16* dst = p.out + (static_cast<size_t>(tok0 + t * tpc + tl) * p.nq + head0 + g) * D;
+        uint32_t r[32];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          tmem_ld_32(o_col + c * 32, r);
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 q;
+              q.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+              q.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+              q.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+              q.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + i) = q;
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, PAIR_TMEM_COLS);
+  }
+}
+
 // rows x cols bf16 matrix with `row_bytes` between rows; box = [box_rows, 64 columns], 128-byte swizzle
 static int make_map_2d(CUtensorMap* map, const void* base, uint64_t rows, int cols, int box_rows) {
   EncodeTiledFn fn = tensor_map_encoder();
@@ -373,12 +752,15 @@ extern "C" int b200_attention_tcgen05_tokens_per_tile(int group) {
   return BM / gs;
 }
 
+// Tokens per CTA of the two-tile kernel.
+extern "C" int b200_attention_tcgen05_tokens_per_pair(int group) { return 2 * b200_attention_tcgen05_tokens_per_tile(group); }
+
 // q, out: [tokens, nq, D]; pools: [pages, nkv, page_size, D].  page_size must be 8, 16, 32 or 64.
-extern "C" int b200_attention_prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                              const int* positions, const int* block_table, int table_stride,
-                                              int page_size, int num_pages, int tokens, int nq, int nkv, float scale,
-                                              const int* tile_entry, const int* tile_start, const int* tile_count,
-                                              int num_tiles, cudaStream_t stream) {
+// `pair` != 0: the two-tile kernel; the tiles of the list then hold up to twice as many tokens.
+static int prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool, void* out, const int* positions,
+                           const int* block_table, int table_stride, int page_size, int num_pages, int tokens, int nq,
+                           int nkv, float scale, const int* tile_entry, const int* tile_start, const int* tile_count,
+                           int num_tiles, bool pair, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || table_stride <= 0 || tokens <= 0) return B200_ERR_BAD_SIZE;
   if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return B200_ERR_BAD_SIZE;
@@ -416,11 +798,36 @@ extern "C" int b200_attention_prefill_tcgen05(const void* q, const void* k_pool,
   if (int e = make_map_2d(&map_k, k_pool, pool_rows, D, page_size)) return e;
   if (int e = make_map_2d(&map_v, v_pool, pool_rows, D, page_size)) return e;
 
-  constexpr size_t smem = SMEM_TILES + 256;
-  static DeviceOnce once;
-  if (int e = configure_once(once, prefill_attention_tcgen05_kernel, smem)) return e;
   dim3 grid(nkv * p.slices, num_tiles);
   if (grid.y > 65535) return B200_ERR_TOO_LARGE;
-  launch(prefill_attention_tcgen05_kernel, grid, dim3(kTcThreads), smem, stream, map_q, map_k, map_v, p);
+  if (pair) {
+    constexpr size_t smem = PAIR_SMEM_TILES + PAIR_BARRIER_BYTES;
+    static DeviceOnce once;
+    if (int e = configure_once(once, prefill_attention_pair_kernel, smem)) return e;
+    launch(prefill_attention_pair_kernel, grid, dim3(kPairThreads), smem, stream, map_q, map_k, map_v, p);
+  } else {
+    constexpr size_t smem = SMEM_TILES + 256;
+    static DeviceOnce once;
+    if (int e = configure_once(once, prefill_attention_tcgen05_kernel, smem)) return e;
+    launch(prefill_attention_tcgen05_kernel, grid, dim3(kTcThreads), smem, stream, map_q, map_k, map_v, p);
+  }
   return launch_status();
+}
+
+extern "C" int b200_attention_prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                              const int* positions, const int* block_table, int table_stride,
+                                              int page_size, int num_pages, int tokens, int nq, int nkv, float scale,
+                                              const int* tile_entry, const int* tile_start, const int* tile_count,
+                                              int num_tiles, cudaStream_t stream) {
+  return prefill_tcgen05(q, k_pool, v_pool, out, positions, block_table, table_stride, page_size, num_pages, tokens, nq, nkv,
+                         scale, tile_entry, tile_start, tile_count, num_tiles, false, stream);
+}
+
+extern "C" int b200_attention_prefill_tcgen05_pair(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                                   const int* positions, const int* block_table, int table_stride,
+                                                   int page_size, int num_pages, int tokens, int nq, int nkv, float scale,
+                                                   const int* tile_entry, const int* tile_start, const int* tile_count,
+                                                   int num_tiles, cudaStream_t stream) {
+  return prefill_tcgen05(q, k_pool, v_pool, out, positions, block_table, table_stride, page_size, num_pages, tokens, nq, nkv,
+                         scale, tile_entry, tile_start, tile_count, num_tiles, true, stream);
 }

@@ -54,7 +54,12 @@ _TC_TABLE = {
     "b200_attention_tcgen05_error": [],
     "b200_attention_tcgen05_tokens_per_tile": [c_int],
     "b200_attention_prefill_tcgen05": [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_int, c_int, c_float] + [c_void_p] * 3 + [c_int, c_void_p],
+    "b200_attention_prefill_tcgen05_pair": [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_int, c_int, c_float] + [c_void_p] * 3 + [c_int, c_void_p],
 }
+# Two row tiles per CTA (one CTA per SM, 128 keys a tile) for steps with a portion of at least this many tokens
+# (measured at the Qwen3-8B geometry: 5 to 11 % faster from 2,048 new tokens on, slower at 1,024 and below);
+# below it the one-tile kernel (two CTAs per SM, 64 keys a tile).  0 turns the two-tile kernel off.
+TC_PAIR_MIN_PORTION = int(os.environ.get("LLM_RUNTIME_STUDY_B200_ATTENTION_PAIR_MIN", "2048"))
 TC_HEAD_DIMS = (64, 128)
 TC_PAGE_SIZES = (8, 16, 32, 64)
 TC_MIN_PORTION = 32     # shorter portions only: the mma.sync kernel wastes fewer rows
@@ -201,10 +206,11 @@ def prefill_attention(
 
 def prefill_attention_tcgen05(
     q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, *, positions: torch.Tensor, block_table: torch.Tensor,
-    q_lens, scale: float, tiles: tuple[torch.Tensor, int] | None = None,
+    q_lens, scale: float, tiles: tuple[torch.Tensor, int] | None = None, pair: bool = False,
 ) -> torch.Tensor:
     """The same contract as ``prefill_attention`` (no window), on tcgen05 tensor cores with
-    TMEM accumulators and TMA loads of the pages."""
+    TMEM accumulators and TMA loads of the pages.  ``pair``: the kernel with two row tiles
+    per CTA; ``tiles`` must then hold tiles of ``2 * (128 // gs)`` tokens."""
 
     for t, name in ((q, "q"), (keys, "keys"), (values, "values")):
         native.require(t, name, dtype=torch.bfloat16)
@@ -213,11 +219,11 @@ def prefill_attention_tcgen05(
         raise KernelError(f"the tcgen05 attention kernel does not take head size {d} with pages of {page_size}")
     lib = tc_library_name(d)
     if tiles is None:
-        tiles = tile_map(q_lens, 128 // gs, q.device)
+        tiles = tile_map(q_lens, (2 if pair else 1) * (128 // gs), q.device)
     table, count = tiles
     out = torch.empty_like(q)
     native.call(
-        "b200_attention_prefill_tcgen05", q.data_ptr(), keys.data_ptr(), values.data_ptr(), out.data_ptr(),
+        "b200_attention_prefill_tcgen05_pair" if pair else "b200_attention_prefill_tcgen05", q.data_ptr(), keys.data_ptr(), values.data_ptr(), out.data_ptr(),
         positions.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, keys.shape[0], n, nq, nkv,
         float(scale), table[0].data_ptr(), table[1].data_ptr(), table[2].data_ptr(), count, native.stream_ptr(),
         library=lib)
@@ -423,12 +429,13 @@ def try_paged_attention(q: torch.Tensor, cache: Any, ctx: Any, table: torch.Tens
     maps = ctx.__dict__.setdefault("_tile_maps", {})
     page_size = cache.keys.shape[2]
     if PREFILL_BACKEND == "tcgen05" and tc_supported(d, page_size, window) and ctx.max_q_len >= TC_MIN_PORTION:
-        per_tile = 128 // gs
+        pair = 0 < TC_PAIR_MIN_PORTION <= ctx.max_q_len
+        per_tile = (2 if pair else 1) * (128 // gs)
         key = ("tc", per_tile)
         if key not in maps:
             maps[key] = tile_map(ctx.q_lens, per_tile, q.device, ctx.kv_lens)
         return prefill_attention_tcgen05(q, cache.keys, cache.values, positions=ctx.positions, block_table=table,
-                                         q_lens=ctx.q_lens, scale=scale, tiles=maps[key])
+                                         q_lens=ctx.q_lens, scale=scale, tiles=maps[key], pair=pair)
     per_tile = 64 // gs
     if per_tile not in maps:
         maps[per_tile] = tile_map(ctx.q_lens, per_tile, q.device, ctx.kv_lens)

@@ -203,7 +203,7 @@ def test_qk_write_without_norm_or_rotation(dtype):
     assert torch.equal(kp.cpu()[1, 0, :3].reshape(3, -1), qkv[:, nq * d : (nq + nkv) * d])
 
 
-def _attention_case(dtype, nq, nkv, d, page, lens_and_chunks, window=0, seed=6, boost=None):
+def _attention_case(dtype, nq, nkv, d, page, lens_and_chunks, window=0, seed=6, boost=None, boost_size=16.0):
     """Requests with cached length L and the last n tokens as queries."""
 
     torch.manual_seed(seed)
@@ -214,9 +214,9 @@ def _attention_case(dtype, nq, nkv, d, page, lens_and_chunks, window=0, seed=6, 
         if boost is not None:   # one far key dominates the last query's scores
             t = boost if boost >= 0 else L + boost
             k[t] = 0
-            k[t, :, 0] = 16.0
+            k[t, :, 0] = boost_size
             q[L - 1] = 0
-            q[L - 1, :, 0] = 16.0
+            q[L - 1, :, 0] = boost_size
             v[t] = 5.0
         q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
         out = plain.causal_attention(q.double(), k.double(), v.double(), 1 / math.sqrt(d), window=window or None)
@@ -678,26 +678,37 @@ def test_projections_refuse_unaligned_widths():
 # ------------------------------------------------------------- tcgen05 prefill attention
 @pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (32, 8, 128, 16), (4, 4, 64, 8), (6, 1, 64, 32), (5, 1, 128, 64),
                                            (32, 1, 64, 16), (12, 2, 128, 8)])
-def test_prefill_attention_tcgen05(nq, nkv, d, page):
+@pytest.mark.parametrize("pair", [False, True])
+def test_prefill_attention_tcgen05(nq, nkv, d, page, pair):
+    """Both kernels (one and two row tiles per CTA): portions that fill no tile, one tile, one and a bit, many;
+    with and without a cached prefix; a last key tile that only the second row tile sees (129 keys, 65 new)."""
+
     q, kp, vp, pos, ent, table, want = _attention_case(
-        torch.bfloat16, nq, nkv, d, page, [(1, 1), (33, 33), (70, 5), (131, 1), (64, 2), (200, 200), (129, 65), (513, 300)])
+        torch.bfloat16, nq, nkv, d, page, [(1, 1), (33, 33), (70, 5), (131, 1), (64, 2), (200, 200), (129, 65), (513, 300),
+                                           (260, 9), (128, 128), (1000, 64)])
     out = _mma().prefill_attention_tcgen05(dev(q), dev(kp), dev(vp), positions=dev(pos), block_table=dev(table),
-                                           q_lens=_q_lens(ent), scale=1 / math.sqrt(d))
+                                           q_lens=_q_lens(ent), scale=1 / math.sqrt(d), pair=pair)
     _mma().check_tcgen05_error(d)
     torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
 
 
-@pytest.mark.parametrize("boost", [0, 15, 16, 63, 64, -2, 300, 511, 512])
-def test_tcgen05_attention_finds_a_far_key(boost):
+@pytest.mark.parametrize("boost", [0, 15, 16, 63, 64, -2, 300, 511, 512, 127, 128, 640, 200, 350])
+@pytest.mark.parametrize("pair,new,size", [(False, 3, 16.0), (True, 3, 16.0), (True, 40, 16.0), (True, 40, 40.0), (False, 40, 40.0)])
+def test_tcgen05_attention_finds_a_far_key(boost, pair, new, size):
+    """One key outweighs all others for the last query, by 2^46 or (size 40) by 2^288, which float32 cannot hold:
+    the kernels must move their reference maximum when they meet it, in whichever half of whichever tile it lies."""
+
     nq, nkv, d, page = 8, 2, 64, 16
-    q, kp, vp, pos, ent, table, want = _attention_case(torch.bfloat16, nq, nkv, d, page, [(700, 3)], boost=boost)
+    q, kp, vp, pos, ent, table, want = _attention_case(torch.bfloat16, nq, nkv, d, page, [(700, new)], boost=boost,
+                                                       boost_size=size)
     out = _mma().prefill_attention_tcgen05(dev(q), dev(kp), dev(vp), positions=dev(pos), block_table=dev(table),
-                                           q_lens=[3], scale=1 / math.sqrt(d))
+                                           q_lens=[new], scale=1 / math.sqrt(d), pair=pair)
     _mma().check_tcgen05_error(d)
     torch.testing.assert_close(out.cpu().double(), want, atol=3e-2, rtol=2e-2)
 
 
-def test_tcgen05_attention_rescales_when_the_maximum_grows():
+@pytest.mark.parametrize("pair", [False, True])
+def test_tcgen05_attention_rescales_when_the_maximum_grows(pair):
     """Scores that keep growing along the sequence force the lazy rescaling of O in TMEM."""
 
     torch.manual_seed(11)
@@ -709,7 +720,7 @@ def test_tcgen05_attention_rescales_when_the_maximum_grows():
     want = plain.causal_attention(q.double(), k.double(), v.double(), 1 / math.sqrt(d))
     kp, vp, ids = _scatter_to_pages(k, v, page, nkv, d, torch.bfloat16, seed=3)
     out = _mma().prefill_attention_tcgen05(dev(q), dev(kp), dev(vp), positions=dev(torch.arange(L, dtype=torch.int32)),
-                                           block_table=dev(ids.view(1, -1)), q_lens=[L], scale=1 / math.sqrt(d))
+                                           block_table=dev(ids.view(1, -1)), q_lens=[L], scale=1 / math.sqrt(d), pair=pair)
     _mma().check_tcgen05_error(d)
     torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
 

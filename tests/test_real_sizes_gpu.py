@@ -139,6 +139,26 @@ def test_real_sizes_under_every_cut(material, dtype):
                     assert torch.equal(results["whole"][rid][p], other[rid][p]), (name, rid, p)
 
 
+def test_two_tile_attention_for_portions_of_every_size(material, monkeypatch):
+    """The prefill attention with two row tiles per CTA normally serves steps with a portion of 2,048 tokens
+    and more (the whole and tail drives above reach it).  Here it serves every step that the tcgen05 attention
+    takes at all: portions that fill one row tile or less, an odd number of tiles, tiles that start in the
+    middle of a key tile, beside other requests' tokens."""
+
+    from llm_runtime_study_b200.ops import attention_bf16
+
+    monkeypatch.setattr(attention_bf16, "TC_PAIR_MIN_PORTION", attention_bf16.TC_MIN_PORTION)
+    requests, rows = material["requests"], material["rows"]
+    drives = _drives(requests)
+    for name in ("portions", "mixed"):
+        got = _replay(material["loaded"], drives[name], rows)
+        for rid in requests:
+            out = torch.stack([got[rid][p] for p in rows[rid]]).double()
+            bad, err, top = helpers.first_wrong_row(out, material["plain"]["bfloat16"][rid], TOL["bfloat16"])
+            assert bad is None, (name, rid, rows[rid][bad], err, top)
+    attention_bf16.check_tcgen05_error(128)
+
+
 def test_twelve_rows_decode_through_the_split_k_projections(material):
     """Twelve requests decoded together: 9 to 16 rows send the products with large weights (gate/up, the
     output head) to the tcgen05 split-K kernel instead of the weight-streaming one; the logits still are
