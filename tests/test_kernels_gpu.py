@@ -2,6 +2,7 @@
 operation, at sizes other than the engine's tiny models."""
 
 import math
+import random
 
 import pytest
 import torch
@@ -723,6 +724,95 @@ def test_tcgen05_attention_rescales_when_the_maximum_grows(pair):
                                            block_table=dev(ids.view(1, -1)), q_lens=[L], scale=1 / math.sqrt(d), pair=pair)
     _mma().check_tcgen05_error(d)
     torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
+
+
+# ------------------------------------------------------------- long sequences
+def _long_sequence(L, nq, nkv, d, page, seed, far=None):
+    """One sequence of L tokens in shuffled pages (written without a loop over tokens); ``far``: a key that
+    outweighs all others for the last query."""
+
+    g = torch.Generator().manual_seed(seed)
+    q, k, v = (torch.randn(L, h, d, generator=g) for h in (nq, nkv, nkv))
+    if far is not None:
+        k[far] = 0
+        k[far, :, 0] = 16.0
+        q[L - 1] = 0
+        q[L - 1, :, 0] = 16.0
+        v[far] = 5.0
+    q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    pages = -(-L // page)
+    ids = torch.randperm(pages + 3, generator=g)[:pages]
+    pools = []
+    for x, poison in ((k, 1e4), (v, -1e4)):
+        padded = torch.full((pages * page, nkv, d), poison, dtype=torch.bfloat16)
+        padded[:L] = x
+        pool = torch.full((pages + 3, nkv, page, d), poison, dtype=torch.bfloat16)
+        pool[ids] = padded.view(pages, page, nkv, d).permute(0, 2, 1, 3)
+        pools.append(pool)
+    return q, k, v, pools[0], pools[1], ids.to(torch.int32)
+
+
+def _plain_attention_rows(q, k, v, rows, scale):
+    """The plain formula (softmax of q.k^T * scale over keys 0..row, times v) in float64, for some query rows."""
+
+    group = q.shape[1] // k.shape[1]
+    out = torch.empty(len(rows), q.shape[1], q.shape[2], dtype=torch.float64)
+    for i, r in enumerate(rows):
+        for head in range(q.shape[1]):
+            kv = head // group
+            weights = torch.softmax((k[: r + 1, kv].double() @ q[r, head].double()) * scale, dim=0)
+            out[i, head] = weights @ v[: r + 1, kv].double()
+    return out
+
+
+@pytest.mark.parametrize("lens", [(32768, 20000, 9001, 4097), (16385,)])
+def test_decode_attention_over_long_sequences(lens):
+    """Tens of thousands of keys per request, in as many parts as the engine would choose and in the most the
+    kernel takes; one far key stands out in each sequence."""
+
+    mma = _mma()
+    nq, nkv, d, page = 8, 2, 128, 16
+    qs, pools_k, pools_v, tables, wants, base = [], [], [], [], [], 0
+    for i, L in enumerate(lens):
+        q, k, v, kp, vp, ids = _long_sequence(L, nq, nkv, d, page, seed=40 + i, far=(L * (i + 1)) // 7)
+        qs.append(q[L - 1 :])
+        wants.append(_plain_attention_rows(q, k, v, [L - 1], 1 / math.sqrt(d)))
+        pools_k.append(kp)
+        pools_v.append(vp)
+        tables.append(ids + base)
+        base += kp.shape[0]
+    table = torch.full((len(lens), max(t.numel() for t in tables)), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        table[i, : t.numel()] = t
+    want = torch.cat(wants)
+    chosen = mma.parts_for(len(lens), nq, nkv, d, page, 0, max(lens))
+    assert chosen > 1
+    for splits in (chosen, mma.TMA_MAX_SPLITS, 1):
+        out = mma.decode_attention(dev(torch.cat(qs)), dev(torch.cat(pools_k)), dev(torch.cat(pools_v)),
+                                   kv_len=dev(torch.tensor(lens, dtype=torch.int32)), block_table=dev(table),
+                                   scale=1 / math.sqrt(d), splits=splits)
+        torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
+    mma.check_decode_tma_error(d)
+
+
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("L,new", [(8192, 8192), (8192, 2048), (12000, 333)])
+def test_prefill_attention_over_long_sequences(pair, L, new):
+    """Thousands of new tokens behind thousands of cached ones; some rows of the result (the first and last of the
+    portion, rows at the edges of key tiles, a handful in between) against the plain formula."""
+
+    mma = _mma()
+    nq, nkv, d, page = 8, 2, 128, 16
+    q, k, v, kp, vp, ids = _long_sequence(L, nq, nkv, d, page, seed=50 + new % 7, far=L // 3)
+    first = L - new
+    rows = sorted({first, first + 1, L - 1, L - 2} | {r for r in (63, 64, 127, 128, 2047, 2048, 4095, 4096, 6143) if r >= first}
+                  | set(random.Random(new).sample(range(first, L), 12)))
+    want = _plain_attention_rows(q, k, v, rows, 1 / math.sqrt(d))
+    out = mma.prefill_attention_tcgen05(dev(q[first:]), dev(kp), dev(vp), positions=dev(torch.arange(first, L, dtype=torch.int32)),
+                                        block_table=dev(ids.view(1, -1)), q_lens=[new], scale=1 / math.sqrt(d), pair=pair)
+    mma.check_tcgen05_error(d)
+    got = out.cpu().double()[[r - first for r in rows]]
+    torch.testing.assert_close(got, want, **BF16_TOL)
 
 
 # ----------------------------------------------------------- fused SwiGLU epilogues
