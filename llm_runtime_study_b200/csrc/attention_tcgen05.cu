@@ -4,7 +4,7 @@
 // One CTA owns 128 rows of S = Q K^T: up to 128 / gs consecutive query tokens of one request
 // times the gs query heads that share one KV head.  Keys are taken 64 at a time:
 //   warp 4     TMA loads: the Q tile once (3-D map over [token, head, d]), then for every key tile
-//              the request's pages of K and V (two stages each, running two tiles ahead), one box
+//              the request's pages of K and V (rings of four or eight stages, running that far ahead), one box
 //              per page and 64-column half, found through the block table, each lane issuing one;
 //   warp 5     allocates TMEM; one lane issues tcgen05.mma: S = Q K^T (M 128, N 64, K = head size)
 //              into one of two S buffers in TMEM - the product for the next tile is issued before
@@ -17,7 +17,11 @@
 //              per column), and keeps the running maximum and sum.  O stays in TMEM; it is only
 //              rescaled (tcgen05.ld / st) when a row's maximum has grown by more than 2^8, which
 //              keeps the result exact (the final division uses the same reference maximum).
-// Two CTAs fit on an SM, so one CTA's softmax overlaps the other's matrix products.
+// One CTA per SM.  (Two used to share an SM, one's softmax overlapping the other's products; their results changed
+// from launch to launch once tiles were started longest first, also with every hand-over below in place, and not
+// with an SM to each CTA.  Two more faults showed on the way and are closed: a softmax warp that ran a tile ahead
+// arrived on the barrier of the tile before - there is one P barrier per S buffer now - and S(j+1) was written
+// over P(j-1) while P(j-1) V was still reading it.)
 //
 // Formula (mini_llm/nn/attention.py:95-99, 231-248): S = q.k^T * scale, key t visible iff
 // t <= p, P = softmax(S), o = P.v; query head j reads KV head j / (nq / nkv).
@@ -41,8 +45,14 @@ constexpr int DSUB = D / 64;               // 64-column (128-byte) sub-tiles of 
 constexpr uint32_t Q_SUB = BM * 128;       // bytes of one Q sub-tile
 constexpr uint32_t KV_SUB = BN * 128;      // bytes of one K or V sub-tile
 constexpr uint32_t Q_BYTES = DSUB * Q_SUB, KV_BYTES = DSUB * KV_SUB;
-constexpr int KSTAGES = 2;
+// One CTA per SM (the ring takes more than half of an SM's shared memory on purpose): two CTAs that share an SM's
+// tensor core gave results that changed from launch to launch (see the note at the top), and a ring this deep keeps
+// the copies of several key tiles in flight, which is what the second CTA was there to hide.
+constexpr int KSTAGES = D == 128 ? 4 : 8;
 constexpr uint32_t SMEM_TILES = Q_BYTES + 2 * KSTAGES * KV_BYTES;
+static_assert(SMEM_TILES > 116 * 1024, "one CTA per SM");
+constexpr uint32_t kBarrierBytes = 512;
+static_assert((1 + 4 * KSTAGES + 2 + 2 + 1) * 8 + 4 <= kBarrierBytes, "barriers");
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t S_COL = 0, O_COL = 2 * BN;   // two S buffers of 64 columns, then O
 constexpr int kTcThreads = 192;
@@ -79,14 +89,14 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   unsigned char* v_smem = k_smem + KSTAGES * KV_BYTES;      // [KSTAGES]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_TILES);
   uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;       // [2]
-  uint64_t* k_empty = bars + 3;      // [2]
-  uint64_t* v_full = bars + 5;       // [2]
-  uint64_t* v_empty = bars + 7;      // [2]
-  uint64_t* s_full = bars + 9;       // [2]
-  uint64_t* p_full = bars + 11;      // [2]
-  uint64_t* o_done = bars + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* k_full = bars + 1;                 // [KSTAGES]
+  uint64_t* k_empty = k_full + KSTAGES;
+  uint64_t* v_full = k_empty + KSTAGES;
+  uint64_t* v_empty = v_full + KSTAGES;
+  uint64_t* s_full = v_empty + KSTAGES;        // [2]
+  uint64_t* p_full = s_full + 2;               // [2]: one per S buffer, like s_full (see the softmax loop)
+  uint64_t* o_done = p_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
 
   pdl_wait();
   if ((smem_addr(smem) & 1023u) != 0) {      // the swizzled tiles need a 1024-byte aligned base
@@ -107,11 +117,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < KSTAGES; ++s) {
       mbar_init(k_full + s, 1);
       mbar_init(k_empty + s, 1);
       mbar_init(v_full + s, 1);
       mbar_init(v_empty + s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(s_full + s, 1);
       mbar_init(p_full + s, BM);
     }
@@ -154,12 +166,12 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       if (id >= 0)
         tma_load_2d(dst + my_sub * KV_SUB + my_page * p.page_size * 128, map, bar, my_sub * 64, (id * p.nkv + kvh) * p.page_size);
     };
-    // K and V of tile j go to stage j & 1; a stage is free again when the product that read it
+    // K and V of tile j go to stage j % KSTAGES; a stage is free again when the product that read it
     // has completed (S(j-2) for K, P.V(j-2) for V): the first two tiles find their stages free.
     int id = fetch_id(0);
     for (int j = 0; j < ntiles; ++j) {
-      const int s = j & 1;
-      const uint32_t parity = ((j >> 1) & 1) ^ 1;
+      const int s = j % KSTAGES;
+      const uint32_t parity = ((j / KSTAGES) & 1) ^ 1;
       const int next_id = j + 1 < ntiles ? fetch_id(j + 1) : -1;
       bool free_k = mbar_wait(k_empty + s, parity);
       if (!__all_sync(0xffffffffu, free_k)) { if (lane == 0) atomicExch(&g_attn_error, 1); break; }
@@ -179,16 +191,16 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     if (!ok) atomicExch(&g_attn_error, 2);
     const uint32_t q_addr = smem_addr(q_smem);
     auto issue_s = [&](int j) -> bool {        // S(j) = Q K_j^T into S buffer j & 1
-      const int s = j & 1;
-      if (!wait_all(k_full + s, (j >> 1) & 1)) return false;
+      const int s = j % KSTAGES, buf = j & 1;
+      if (!wait_all(k_full + s, (j / KSTAGES) & 1)) return false;
       tcgen05_fence_after();
       const uint32_t k_addr = smem_addr(k_smem + s * KV_BYTES);
       if (elect_one()) {
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          umma_bf16_ss(tmem_base + S_COL + s * BN, umma_desc_sw128(q_addr + (k >> 2) * Q_SUB + (k & 3) * 32, 16, 1024),
+          umma_bf16_ss(tmem_base + S_COL + buf * BN, umma_desc_sw128(q_addr + (k >> 2) * Q_SUB + (k & 3) * 32, 16, 1024),
                        umma_desc_sw128(k_addr + (k >> 2) * KV_SUB + (k & 3) * 32, 16, 1024), idesc_s, k != 0);
-        umma_commit_to(s_full + s);
+        umma_commit_to(s_full + buf);
         umma_commit_to(k_empty + s);
       }
       __syncwarp();
@@ -196,18 +208,19 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     };
     if (ok && !issue_s(0)) { atomicExch(&g_attn_error, 2); ok = false; }
     for (int j = 0; j < ntiles && ok; ++j) {
-      const int s = j & 1;
-      // S of the next tile first: its buffer was read by the softmax of tile j - 1, which has
-      // arrived on p_full (waited for in the previous round); the tensor core then has work
-      // while the softmax of tile j runs.
+      const int s = j % KSTAGES, buf = j & 1;
+      // S of the next tile first, so that the tensor core has work while the softmax of tile j runs.  Its
+      // buffer holds P(j - 1): the product P(j - 1) V must have completed (not just been issued before:
+      // products into different accumulators are not ordered among themselves by their order of issue).
+      if (j >= 1 && j + 1 < ntiles && !wait_all(o_done, (j - 1) & 1)) { atomicExch(&g_attn_error, 6); break; }
       if (j + 1 < ntiles && !issue_s(j + 1)) { atomicExch(&g_attn_error, 2); break; }
-      if (!wait_all(p_full, j & 1) || !wait_all(v_full + s, (j >> 1) & 1)) { atomicExch(&g_attn_error, 3); break; }
+      if (!wait_all(p_full + buf, (j >> 1) & 1) || !wait_all(v_full + s, (j / KSTAGES) & 1)) { atomicExch(&g_attn_error, 3); break; }
       tcgen05_fence_after();
       const uint32_t v_addr = smem_addr(v_smem + s * KV_BYTES);
       if (elect_one()) {
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k)       // P of this tile lies where its S was: 8 columns per 16 keys
-          umma_bf16_ts(tmem_base + O_COL, tmem_base + S_COL + s * BN + k * 8,
+          umma_bf16_ts(tmem_base + O_COL, tmem_base + S_COL + buf * BN + k * 8,
                        umma_desc_sw128(v_addr + k * 2048, KV_SUB, 1024), idesc_pv, (j | k) != 0);
         umma_commit_to(o_done);
         umma_commit_to(v_empty + s);
@@ -303,8 +316,12 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
         tmem_st_32(lane_base + S_COL + (j & 1) * BN, words);
       }
+      // One barrier per S buffer: S(j+1) is ready before this tile's P is handed over, so a warp that is done
+      // with tile j may be through tile j + 1 and arrive for it while another warp still works on tile j;
+      // on a single barrier that arrival would be counted for tile j and let P(j) V start on a P that is not
+      // all written.  No warp gets two tiles ahead: S(j+2) is issued behind P(j) V.
       tcgen05_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(p_full + (j & 1));
     }
     if (ok) {
       if (!mbar_wait(o_done, (ntiles - 1) & 1)) {
@@ -355,8 +372,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 //                    read every K and V stage (half the shared-memory and L2 traffic of the one-tile kernel)
 //   warps 10, 11     nothing: warps 8-11 are a warpgroup that gives most of its registers to the softmax
 //                    warps (setmaxnreg), which hold a row of 128 scores each.
-// The tensor core executes one CTA's products in the order of issue, so S_t(j+1) may be issued right
-// behind P_t(j) V although it overwrites the columns that hold P_t(j).
+// S_t(j+1) overwrites the columns that hold P_t(j): it is issued when P_t(j) V has completed.
 //
 // What shortens the chain S -> P -> P V -> next S, which is what a row tile's time is made of:
 //  * the exponentials of a tile start from the reference maximum of the tiles before it, without a pass for
@@ -558,6 +574,9 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
             __syncwarp();
           }
           if (ok && j + 1 < nt[t]) {
+            // S_t(j+1) goes where P_t(j) lies: P_t(j) V must have completed, not just been issued before
+            // (products into different accumulators are not ordered among themselves by their order of issue)
+            if (!wait_all(o_done + t, j & 1)) { atomicExch(&g_attn_error, 19); ok = false; break; }
             if (!have_k) {
               if (!wait_all(k_full + (j + 1) % KSTAGES_P, ((j + 1) / KSTAGES_P) & 1)) { atomicExch(&g_attn_error, 12); ok = false; break; }
               have_k = true;
@@ -806,7 +825,7 @@ static int prefill_tcgen05(const void* q, const void* k_pool, const void* v_pool
     if (int e = configure_once(once, prefill_attention_pair_kernel, smem)) return e;
     launch(prefill_attention_pair_kernel, grid, dim3(kPairThreads), smem, stream, map_q, map_k, map_v, p);
   } else {
-    constexpr size_t smem = SMEM_TILES + 256;
+    constexpr size_t smem = SMEM_TILES + kBarrierBytes;
     static DeviceOnce once;
     if (int e = configure_once(once, prefill_attention_tcgen05_kernel, smem)) return e;
     launch(prefill_attention_tcgen05_kernel, grid, dim3(kTcThreads), smem, stream, map_q, map_k, map_v, p);

@@ -1055,7 +1055,11 @@ static int launch_splitk(const CUtensorMap& rows, const CUtensorMap& cols, GemmP
   cudaLaunchConfig_t config{};
   config.gridDim = dim3(tiles * p.splits);
   config.blockDim = dim3(kThreads);
+  // never two of these CTAs on one SM: two CTAs that shared an SM's tensor core (in the prefill attention) gave
+  // results that changed from launch to launch; more than half of the shared memory keeps an SM to one CTA
+  constexpr size_t kOnePerSm = 120 * 1024;
   config.dynamicSmemBytes = static_cast<size_t>(p.stages) * stage + kTail;
+  if (config.dynamicSmemBytes < kOnePerSm) config.dynamicSmemBytes = kOnePerSm;
   config.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;

@@ -57,9 +57,9 @@ _TC_TABLE = {
     "b200_attention_prefill_tcgen05_pair": [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_int, c_int, c_float] + [c_void_p] * 3 + [c_int, c_void_p],
 }
 # Two row tiles per CTA (one CTA per SM, 128 keys a tile) for steps with a portion of at least this many tokens
-# (measured at the Qwen3-8B geometry: 5 to 11 % faster from 2,048 new tokens on, slower at 1,024 and below);
-# below it the one-tile kernel (two CTAs per SM, 64 keys a tile).  0 turns the two-tile kernel off.
-TC_PAIR_MIN_PORTION = int(os.environ.get("LLM_RUNTIME_STUDY_B200_ATTENTION_PAIR_MIN", "2048"))
+# (measured at the Qwen3-8B geometry: half again as fast at 2,048 new tokens and beyond, 7 % slower at 1,024);
+# below it the one-tile kernel (64 keys a tile).  0 turns the two-tile kernel off.
+TC_PAIR_MIN_PORTION = int(os.environ.get("LLM_RUNTIME_STUDY_B200_ATTENTION_PAIR_MIN", "1280"))
 TC_HEAD_DIMS = (64, 128)
 TC_PAGE_SIZES = (8, 16, 32, 64)
 TC_MIN_PORTION = 32     # shorter portions only: the mma.sync kernel wastes fewer rows

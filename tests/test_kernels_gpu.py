@@ -726,6 +726,31 @@ def test_tcgen05_attention_rescales_when_the_maximum_grows(pair):
     torch.testing.assert_close(out.cpu().double(), want, **BF16_TOL)
 
 
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("nq,nkv,d,boost", [(272, 16, 64, 1.0), (32, 8, 128, 4.0), (8, 2, 64, 3.0)])
+def test_tcgen05_attention_gives_the_same_bits_every_time(pair, nq, nkv, d, boost):
+    """Many CTAs, started longest first as the engine starts them, with scores spread widely enough that rows
+    move their reference maximum often: forty launches give the same bits, and they are the plain result.  (A
+    softmax warp that ran a tile ahead of the others once let a product start on a half-written P.)"""
+
+    mma = _mma()
+    page, L = 16, 520 if nq > 64 else 1100
+    scale = 1 / math.sqrt(d)
+    q, k, v, kp, vp, ids = _long_sequence(L, nq, nkv, d, page, seed=77)
+    q = (q.float() * boost).bfloat16()
+    gs = min(nq // nkv, 16)
+    tiles = mma.tile_map([L], (2 if pair else 1) * (128 // gs), torch.device("cuda"), [L])
+    args = dict(positions=dev(torch.arange(L, dtype=torch.int32)), block_table=dev(ids.view(1, -1)), q_lens=[L], scale=scale,
+                pair=pair, tiles=tiles)
+    qd, kd, vd = dev(q), dev(kp), dev(vp)
+    first = mma.prefill_attention_tcgen05(qd, kd, vd, **args)
+    for _ in range(40):
+        assert torch.equal(mma.prefill_attention_tcgen05(qd, kd, vd, **args), first)
+    mma.check_tcgen05_error(d)
+    rows = sorted(set(random.Random(d).sample(range(L), 24)) | {0, L - 1})
+    torch.testing.assert_close(first.cpu().double()[rows], _plain_attention_rows(q, k, v, rows, scale), **BF16_TOL)
+
+
 # ------------------------------------------------------------- long sequences
 def _long_sequence(L, nq, nkv, d, page, seed, far=None):
     """One sequence of L tokens in shuffled pages (written without a loop over tokens); ``far``: a key that
