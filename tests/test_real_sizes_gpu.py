@@ -139,6 +139,21 @@ def test_real_sizes_under_every_cut(material, dtype):
                     assert torch.equal(results["whole"][rid][p], other[rid][p]), (name, rid, p)
 
 
+def test_real_sizes_give_the_same_bits_every_time(material):
+    """bfloat16 at real sizes, whole prompts (the tcgen05 projections and both prefill attention kernels) and mixed
+    steps: three replays, the same bits."""
+
+    requests, rows = material["requests"], material["rows"]
+    drives = _drives(requests)
+    for name in ("whole", "mixed"):
+        first = _replay(material["loaded"], drives[name], rows)
+        for _ in range(2):
+            again = _replay(material["loaded"], drives[name], rows)
+            for rid in requests:
+                for p in rows[rid]:
+                    assert torch.equal(first[rid][p], again[rid][p]), (name, rid, p)
+
+
 def test_two_tile_attention_for_portions_of_every_size(material, monkeypatch):
     """The prefill attention with two row tiles per CTA normally serves steps with a portion of 2,048 tokens
     and more (the whole and tail drives above reach it).  Here it serves every step that the tcgen05 attention

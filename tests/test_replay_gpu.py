@@ -122,6 +122,19 @@ def test_cutting_does_not_change_float32_bits(setup):
                 assert torch.equal(whole[rid][p], other[rid][p]), (rid, p)
 
 
+def test_a_replay_gives_the_same_bits_every_time(setup):
+    """In both types: the same steps three times over give the same bits (nothing depends on which CTA or warp
+    came first)."""
+
+    for steps in (helpers.trace_whole(setup["requests"]), helpers.trace_mixed(setup["requests"], random.Random(12))):
+        first, _ = _replay(setup, steps)
+        for _ in range(2):
+            again, _ = _replay(setup, steps)
+            for rid in first:
+                for p in first[rid]:
+                    assert torch.equal(first[rid][p], again[rid][p]), (rid, p)
+
+
 def test_long_decoding(setup):
     """One token at a time from the first token on, well past several pages."""
 
