@@ -331,6 +331,12 @@ class LiveParts:
                                   for i in range(entries)])
         return self.values[at : at + 1]
 
+    def most(self, requests: int, nq: int, nkv: int, d: int, page_size: int, window: int) -> int:
+        """The largest number of parts any length up to the bound takes: what the recorded grid is sized for."""
+
+        self.place(requests, nq, nkv, d, page_size, window)
+        return max(self._choices[self._places[(requests, nq, nkv, d, page_size, window)]])
+
     def fill(self, longest: int) -> list[int]:
         """The numbers of parts, place by place, for a batch whose longest sequence holds ``longest`` tokens."""
 
@@ -397,8 +403,13 @@ def parts_for(n: int, nq: int, nkv: int, d: int, page_size: int, window: int, lo
 
 
 def decode_parts(ctx: Any, n: int, nq: int, nkv: int, d: int, page_size: int, window: int) -> int:
-    """The number of parts for this batch (under a graph capture: for the longest sequence there may ever be)."""
+    """The number of parts for this batch.  Under a graph capture: the most that any length up to the longest there
+    may ever be would take (the choice does not grow steadily with the length), so that the recorded grid has room
+    for whatever a replay is told to use."""
 
+    live = getattr(ctx, "live_parts", None)
+    if live is not None and not window:
+        return live.most(n, nq, nkv, d, page_size, window)
     return parts_for(n, nq, nkv, d, page_size, window, ctx.max_kv_len)
 
 

@@ -139,6 +139,29 @@ def test_real_sizes_under_every_cut(material, dtype):
                     assert torch.equal(results["whole"][rid][p], other[rid][p]), (name, rid, p)
 
 
+def test_captured_decode_has_room_for_the_parts_of_every_length():
+    """An engine opened for 32,768 tokens decoding a request of 20,000: the host's choice of parts does not grow
+    steadily with the length (21 parts here, 19 at 32,768), and the recorded launch must have room for it.  The
+    captured step gives the bits of the same launches issued one by one."""
+
+    from tests.test_generate_gpu import _decode_both_ways
+    from llm_runtime_study_b200.engine.runtime import load_random
+    from llm_runtime_study_b200.ops import attention_bf16
+    from llm_runtime_study_b200.sampling import SamplingConfig
+
+    assert attention_bf16.parts_for(1, 32, 8, 128, 16, 0, 20001) > attention_bf16.parts_for(1, 32, 8, 128, 16, 0, 32768)
+    loaded = load_random(dict(QWEN3_8B_TWO_LAYERS, max_position_embeddings=40960), 7, device="cuda:0", dtype="bfloat16",
+                         on_device=True)
+    rng = random.Random(2)
+    for lengths, bound in (((20000,), 32768), ((40, 3000, 9000), 16384)):
+        prompts = [helpers.random_tokens(rng, 151936, n) for n in lengths]
+        (eager_ids, eager_logits), (graph_ids, graph_logits) = _decode_both_ways(
+            loaded, prompts, [list(range(len(prompts)))] * 4, page=16, max_seq_len=bound, sampling=SamplingConfig())
+        assert eager_ids == graph_ids
+        for a, b in zip(eager_logits, graph_logits):
+            assert torch.equal(a, b)
+
+
 def test_real_sizes_give_the_same_bits_every_time(material):
     """bfloat16 at real sizes, whole prompts (the tcgen05 projections and both prefill attention kernels) and mixed
     steps: three replays, the same bits."""
