@@ -15,7 +15,7 @@ mini_llm/model/base.py:175, 188-190: the same contract seen from outside).
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field, replace
+from dataclasses import dataclass, replace
 from typing import Any, Sequence
 
 import numpy as np
