@@ -459,6 +459,11 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
   if (warp == 9) tmem_alloc(tmem_slot, PAIR_TMEM_COLS);
   for (uint32_t i = threadIdx.x; i < VSTAGES_P * PKV_BYTES / 16; i += kPairThreads)   // see the one-tile kernel
     reinterpret_cast<uint4*>(v_smem)[i] = make_uint4(0, 0, 0, 0);
+  // rows of the Q tiles past the last (token, head) pair (a group size that does not divide 128) are copied by nobody
+  for (uint32_t i = threadIdx.x; i < 2 * DSUB * (BM - tpc * p.gs) * 8; i += kPairThreads) {
+    const uint32_t sub = i / ((BM - tpc * p.gs) * 8), rest = i % ((BM - tpc * p.gs) * 8);
+    reinterpret_cast<uint4*>(q_smem + sub * Q_SUB + (tpc * p.gs + rest / 8) * 128)[rest % 8] = make_uint4(0, 0, 0, 0);
+  }
   fence_async_shared();
   tcgen05_fence_before();
   __syncthreads();
@@ -689,7 +694,9 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
 #pragma unroll
       for (int i = 0; i < PBN; ++i) mx[i & 3] = fmaxf(mx[i & 3], sv[i]);
       const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      const float m_new = fmaxf(m_used, m_tile * p.scale_log2);
+      // Only a row that needs it moves its reference: what a row comes to must not depend on the rows that share
+      // its warp (on whose account it may be here), least of all on rows that belong to no token.
+      const float m_new = (j == 0 || redo) ? fmaxf(m_used, m_tile * p.scale_log2) : m_used;
       if (j > 0) {
         // O must hold every product issued so far and no later one: P_t(j-1) V has been issued and
         // P_t(j) V waits for this warp's arrival.

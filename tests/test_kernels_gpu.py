@@ -727,11 +727,13 @@ def test_tcgen05_attention_rescales_when_the_maximum_grows(pair):
 
 
 @pytest.mark.parametrize("pair", [False, True])
-@pytest.mark.parametrize("nq,nkv,d,boost", [(272, 16, 64, 1.0), (32, 8, 128, 4.0), (8, 2, 64, 3.0)])
+@pytest.mark.parametrize("nq,nkv,d,boost", [(272, 16, 64, 1.0), (32, 8, 128, 4.0), (8, 2, 64, 3.0), (56, 8, 128, 1.0), (40, 8, 128, 3.0)])
 def test_tcgen05_attention_gives_the_same_bits_every_time(pair, nq, nkv, d, boost):
     """Many CTAs, started longest first as the engine starts them, with scores spread widely enough that rows
     move their reference maximum often: forty launches give the same bits, and they are the plain result.  (A
-    softmax warp that ran a tile ahead of the others once let a product start on a half-written P.)"""
+    softmax warp that ran a tile ahead of the others once let a product start on a half-written P; with groups of
+    7 or 5 query heads the last rows of a tile belong to no token, and what lay in shared memory there once decided
+    which way the rows beside them were computed.)"""
 
     mma = _mma()
     page, L = 16, 520 if nq > 64 else 1100
