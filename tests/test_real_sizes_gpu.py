@@ -278,7 +278,7 @@ def test_captured_decode_step_at_real_sizes(material, dtype, lengths):
 
 
 def test_a_real_size_folder_through_the_command_line(tmp_path):
-    """A model folder of Qwen3-8B width (two layers, two shards, 3.3 GB) written by the random-weights mode, loaded
+    """A model folder of Qwen3-8B width (four layers, two shards, 4 GB) written by the random-weights mode, loaded
     by the command line in a process of its own, and the same folder replayed step by step: the same greedy tokens.
     The loader maps one tensor at a time: the host memory the load adds stays below twice the largest tensor."""
 
@@ -293,7 +293,7 @@ def test_a_real_size_folder_through_the_command_line(tmp_path):
     from llm_runtime_study_b200.weights import write_random_model
 
     folder = tmp_path / "model"
-    write_random_model(folder, QWEN3_8B_TWO_LAYERS, 3, shards=2)
+    write_random_model(folder, dict(QWEN3_8B_TWO_LAYERS, num_hidden_layers=4), 3, shards=2)
     assert (folder / "model.safetensors.index.json").is_file()
     prompt = helpers.random_tokens(random.Random(2), 151936, 40)
     root = Path(__file__).resolve().parent.parent
